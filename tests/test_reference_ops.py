@@ -1,0 +1,94 @@
+"""CPU oracles: known-answer and self-consistency tests of the PyTorch/NumPy restatements."""
+import math
+
+import numpy as np
+import torch
+
+from viola_b200.ops import reference as ref
+from viola_b200 import ops
+
+E4M3 = torch.float8_e4m3fn
+
+
+def test_philox_known_answers():
+    # Random123 kat_vectors for philox4x32-10 (first output word).
+    cases = [(0, 0, 0), (0xffffffffffffffff,) * 3, (0x85a308d3243f6a88, 0x0370734413198a2e, 0x299f31d0a4093822)]
+    answers = [int(ref.philox(np.array([e], dtype=np.uint64), s, k)[0]) for e, s, k in cases]
+    assert answers == [0x6627e8d5, 0x408f276d, 0xd16cfe09]
+
+
+def test_stochastic_rounding_adjacent_and_probability():
+    table = torch.arange(127, dtype=torch.uint8).view(E4M3).float()
+    values = torch.full((200000,), 16.54)
+    rounded = ref.stochastic_e4m3(values, np.arange(values.numel(), dtype=np.uint64), 3, 77)
+    assert set(rounded.unique().tolist()) == {16.0, 18.0}
+    assert abs((rounded == 18.0).float().mean().item() - 0.27) < 0.005
+    assert all(v in table.tolist() for v in rounded.unique().tolist())
+    again = ref.stochastic_e4m3(values, np.arange(values.numel(), dtype=np.uint64), 3, 77)
+    assert torch.equal(rounded, again)
+    other = ref.stochastic_e4m3(values, np.arange(values.numel(), dtype=np.uint64), 4, 77)
+    assert not torch.equal(rounded, other)
+    quarter = torch.full((200000,), 1.0 + 2.0 ** -9)        # a quarter bf16 ulp above 1.0
+    kept = ref.stochastic_bf16(quarter, np.arange(quarter.numel(), dtype=np.uint64), 0, 1)
+    assert abs((kept > 1.0).float().mean().item() - 0.25) < 0.005
+
+
+def test_group_quantize_roundtrip_and_shapes():
+    torch.manual_seed(0)
+    x = torch.randn(70, 200)
+    for group in ((1, 32), (32, 32), (1, 128), (128, 128)):
+        q, s = ref.group_quantize(x, E4M3, group)
+        assert s.shape == ref.scale_shape(x.shape, group)
+        back = ref.group_dequantize(q, s, group)
+        assert ((back - x).norm() / x.norm()).item() < 0.05
+        qt, st = ref.group_quantize(x, E4M3, group, transposed=True)
+        assert qt.shape == (200, 70)
+    q, s = ops.group_quantize(x, E4M3, (1, 128), kmajor=True)
+    assert s.shape == (2, 70)
+
+
+def test_momentum_tile_and_block_geometry():
+    torch.manual_seed(1)
+    for quant in (dict(granularity="tile", tile_size=64), dict(granularity="block", block_shape=(8, 32))):
+        for shape in ((17, 31), (2, 33, 67)):
+            n = math.prod(shape)
+            qn, sn = ref.state_sizes(shape, **quant)
+            q, s = torch.zeros(qn, dtype=torch.uint8), torch.ones(sn)
+            u = torch.empty(n, dtype=torch.bfloat16)
+            g = torch.randn(n)
+            ref.momentum_update(g, q, s, q, s, u, beta=0.95, matrix_shape=shape, **quant)
+            current = ref.momentum_dequantize(q, s, shape, **quant)
+            fresh = 0.05 * g
+            assert ((current - fresh).norm() / fresh.norm()).item() < 0.06
+            torch.testing.assert_close(u.float(), ((0.05 + 0.95 * 0.05) * g).bfloat16().float(), rtol=0.01, atol=1e-7)
+
+
+def test_newton_schulz_orthogonalises():
+    torch.manual_seed(2)
+    for shape in ((64, 64), (48, 160), (160, 48)):
+        x = torch.randn(shape)
+        for result in (ref.ns_standard(x, 5).float(), ref.ns_gram(x, 5).float()):
+            singular = torch.linalg.svdvals(result)
+            assert singular.max() < 1.3 and singular.min() > 0.5
+
+
+def test_wire_codec_roundtrip_and_nan():
+    torch.manual_seed(3)
+    tile, world, n = 128, 2, 1000
+    groups = math.ceil(n / (world * tile))
+    packet = torch.zeros(world, ref.packet_bytes(groups, tile), dtype=torch.uint8)
+    x = torch.randn(n)
+    ref.wire_pack(x, packet, tile, E4M3)
+    out = torch.empty(n)
+    ref.wire_unpack(packet, out, tile, E4M3)
+    assert ((out - x).norm() / x.norm()).item() < 0.05
+    x[3] = float("nan")
+    ref.wire_pack(x, packet, tile, E4M3)
+    ref.wire_unpack(packet, out, tile, E4M3)
+    assert torch.isnan(out[:tile]).all() and torch.isfinite(out[tile:]).all()
+
+
+def test_hadamard_is_orthogonal_and_self_inverse():
+    h = ref.hadamard64_matrix()
+    torch.testing.assert_close(h @ h, torch.eye(64), atol=1e-6, rtol=0)
+    torch.testing.assert_close(h, h.t())

@@ -1,0 +1,144 @@
+// C ABI of the sm_100a kernel library.  Every entry point takes raw device
+// pointers and a stream, returns a cudaError_t as int, and allocates nothing:
+// workspaces are passed in by the caller (the Python layer owns them).
+#pragma once
+#include <cstdint>
+#include <algorithm>
+#include <cuda_runtime.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- quantisation ----------------------------------------------------------
+int vb_amax_scale(const void* x, long long n, int dtype, float* history, int history_len,
+                  long long index, int delayed, float limit, float* scale_out, unsigned int* scratch,
+                  cudaStream_t stream);
+int vb_quantize(const void* x, int rows, int cols, int dtype, const float* scale, float limit, int fmt,
+                void* q, void* qt, cudaStream_t stream);
+int vb_transpose_u8(const void* x, int rows, int cols, void* out, cudaStream_t stream);
+int vb_group_encode(const void* x, int rows, int cols, int dtype, int fmt, float limit, void* q, float* s,
+                    int gr, int gc, long long s_row, long long s_col, void* qt, float* st, int tgr, int tgc,
+                    long long st_row, long long st_col, cudaStream_t stream);
+int vb_group_decode(const void* q, const float* s, int rows, int cols, int fmt, int gr, int gc,
+                    long long s_row, long long s_col, float* out, cudaStream_t stream);
+
+// ---- tcgen05 GEMM family -----------------------------------------------------
+// D[M, N] = A[M, K] . B[N, K]^T, both operands K-major (row-major with K contiguous).
+enum VbGemmKind { VB_KIND_F16 = 0, VB_KIND_F8 = 1 };
+enum VbEpilogue { VB_EPI_LINEAR = 0, VB_EPI_AXPBY = 1, VB_EPI_GATED_FWD = 2, VB_EPI_GATED_BWD = 3 };
+enum VbActivation { VB_ACT_SILU = 0, VB_ACT_GELU = 1, VB_ACT_RELU = 2 };
+
+typedef struct VbGemmDesc {
+  int kind;              // VbGemmKind
+  int a_fmt, b_fmt;      // F16 kind: 0 fp16, 1 bf16 (must match); F8 kind: 0 e4m3, 1 e5m2
+  int epilogue;          // VbEpilogue
+  int M, N, K;           // N = logical output width (gated forward: hidden width H)
+  const void* A; long long lda;   // elements
+  const void* B; long long ldb;   // elements; rows = N (2N for gated forward, E*N for experts)
+  // scaling: per-tensor (group == 0): alpha = (*sa) * (*sb), null pointer = 1.
+  // group (== 1): fp32 scale per 128.2^k_shift K elements;
+  //   sa index = row * sa_row + (kb >> k_shift) * sa_k
+  //   sb index = (brow >> sb_shift) * sb_row + (kb >> k_shift) * sb_k   (brow = row of B)
+  int group;
+  const float* sa; const float* sb;
+  long long sa_row, sa_k, sb_row, sb_k;
+  int sb_shift, k_shift;
+  // output
+  void* out; int out_dtype; long long ldo;       // 0 fp32, 1 bf16, 2 fp16
+  const void* bias; int bias_dtype;              // [N] (gated forward: [2N]) or null
+  // AXPBY: out = alpha * round(acc) + beta * R, optional transposed copy / symmetric mirror
+  float alpha, beta;
+  const void* resid; long long ldr;
+  void* out_t; long long ldot;
+  int symmetric;         // 1: M == N, only tiles with n_tile >= m_tile are computed and mirrored
+  // gated MLP
+  int activation;        // VbActivation
+  void* aux; long long ldaux;   // [M, 2N] saved (gate | up) in out dtype (fwd: written, bwd: read)
+  // expert GEMM: rows of A are grouped by expert; offsets[e]..offsets[e+1] (device, int32, E+1)
+  const int* expert_offsets; int num_experts;
+  int* tile_map;         // workspace int32[3 * (ceil(M/128) + E)] when expert_offsets != null
+  int* status;           // int32[8] device status word (zeroed by caller) or null
+  int force_bn;          // 0 = auto, else 64 / 128 / 256
+} VbGemmDesc;
+
+int vb_gemm(const VbGemmDesc* desc, cudaStream_t stream);
+
+// ---- optimizer kernels ---------------------------------------------------------
+int vb_momentum_1d(const void* grad, int grad_dtype, long long n, const uint8_t* old_q,
+                   const float* old_scale, uint8_t* new_q, float* new_scale, void* update_bf16,
+                   int tile_size, float beta, float inv_loss_scale, int nesterov, int stochastic,
+                   long long step, unsigned long long key, cudaStream_t stream);
+int vb_momentum_2d(const void* grad, int grad_dtype, int planes, int rows, int cols, const uint8_t* old_q,
+                   const float* old_scale, uint8_t* new_q, float* new_scale, void* update_bf16, int tr,
+                   int tc, float beta, float inv_loss_scale, int nesterov, int stochastic, long long step,
+                   unsigned long long key, cudaStream_t stream);
+int vb_weight_update(void* weight, int weight_dtype, const void* update, int update_dtype, long long n,
+                     float lr, float decay, float update_scale, int stochastic, long long step,
+                     unsigned long long key, long long offset, cudaStream_t stream);
+int vb_adam_update(void* weight, int weight_dtype, const void* grad, int grad_dtype, void* first,
+                   void* second, int state_dtype, long long n, float lr, float decay, float b1, float b2,
+                   float inv_c1, float inv_c2, float eps, int adamw, int maximize, int stochastic,
+                   long long step, unsigned long long key, long long offset, cudaStream_t stream);
+int vb_copy_scaled(const void* update, int dtype, void* out, int out_dtype, long long src, long long dst,
+                   long long count, float scale, cudaStream_t stream);
+int vb_momentum16(const void* grad, int grad_dtype, void* momentum, int momentum_dtype, void* update_bf16,
+                  long long n, float beta, int nesterov, cudaStream_t stream);
+// Frobenius-norm based prescale for Newton-Schulz: out = x / (||x||_F + eps) in `out_dtype`,
+// optionally also writing the transpose.  scratch: float[2] (zeroed; self-resetting).
+int vb_sumsq(const void* x, int dtype, long long n, float* accum, cudaStream_t stream);
+int vb_ns_prescale(const void* x, int dtype, int rows, int cols, const float* sumsq, float eps, void* out,
+                   void* out_t, int out_dtype, cudaStream_t stream);
+// master -> EMA lerp fused with optional dtype casts (owner-side writeback helper)
+int vb_ema_lerp(void* ema, int ema_dtype, const void* master, int master_dtype, long long n, float decay,
+                cudaStream_t stream);
+int vb_philox_kat(unsigned long long element, unsigned long long step, unsigned long long key,
+                  unsigned int* out, int count, cudaStream_t stream);
+
+// ---- gated activation (unfused baseline + post-rotation path) ------------------
+int vb_gated_forward(const void* gu, int dtype, int rows, int hidden, int activation, void* out,
+                     cudaStream_t stream);
+int vb_gated_backward(const void* gu, const void* dh, int dtype, int rows, int hidden, int activation,
+                      void* dgu, cudaStream_t stream);
+
+// ---- Hadamard-64 rotation --------------------------------------------------------
+int vb_hadamard64(const void* x, int dtype, int rows, int cols, void* out, cudaStream_t stream);
+
+// ---- FP8 wire codec ----------------------------------------------------------------
+// packet row = [groups * tile codes][groups fp32 scales], padded to 16 B
+int vb_wire_pack(const float* x, long long n, int rows, int groups, int tile, int fmt, uint8_t* packet,
+                 long long row_stride, cudaStream_t stream);
+int vb_wire_unpack(const uint8_t* packet, long long row_stride, int rows, int groups, int tile, int fmt,
+                   int reduce, float* out, long long n, int accumulate, cudaStream_t stream);
+
+// ---- fused communication (peer memory) ----------------------------------------------
+typedef struct VbPeerTable {
+  void* buffers[16];     // symmetric data buffer on every rank (index = rank)
+  int* flags[16];        // symmetric int32 flag array on every rank
+  int world, rank;
+} VbPeerTable;
+
+// Path 1: quantise the local fp32 bucket and push [codes|scales] into the owner's slot for
+// this rank; the owner then dequantises all ranks in ascending order and adds to `accum`.
+int vb_reduce_to_owner_fp8(const float* bucket, long long n, int tile, int fmt, int owner,
+                           const VbPeerTable* peers, long long slot_bytes, long long region_offset,
+                           int flag_index, int generation, float* accum, int* status,
+                           cudaStream_t stream);
+// Path 2: all-reduce with a second quantisation (reduce-scatter by push, requantise, all-gather by push).
+int vb_allreduce_requant_fp8(float* value, long long n, int tile, int fmt, const VbPeerTable* peers,
+                             long long region_offset, long long region_bytes, int flag_index,
+                             int generation, int* status, cudaStream_t stream);
+// Path 4 helper: owner pushes `bytes` to every peer (broadcast) or row shards to each peer, then flags.
+int vb_owner_push(const void* src, long long bytes, const VbPeerTable* peers, long long dst_offset,
+                  int flag_index, int generation, int sharded, long long shard_bytes, int* status,
+                  cudaStream_t stream);
+int vb_wait_flag(const VbPeerTable* peers, int flag_index, int generation, int count, int* status,
+                 cudaStream_t stream);
+// Path 3 helper: pull peers' row shards into a local full buffer, flagging each 128-row panel.
+int vb_gather_panels(void* full, const VbPeerTable* peers, long long shard_offset, long long shard_bytes,
+                     long long panel_bytes, int* panel_flags, int generation, int* status,
+                     cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,311 @@
+// torch.ops.viola_b200.* : thin tensor -> raw-pointer adapters over the C ABI in api.h.
+// No op here allocates; outputs and workspaces are arguments.  Errors raise.
+#include <torch/library.h>
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <optional>
+#include "api.h"
+
+namespace {
+
+using at::Tensor;
+using OptTensor = std::optional<Tensor>;
+
+inline cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+inline int dtype_code(const Tensor& t) {
+  switch (t.scalar_type()) {
+    case at::kFloat: return 0;
+    case at::kBFloat16: return 1;
+    case at::kHalf: return 2;
+    default: TORCH_CHECK(false, "viola_b200: unsupported dtype ", t.scalar_type());
+  }
+}
+inline int fp8_code(const Tensor& t) {
+  if (t.scalar_type() == at::kFloat8_e4m3fn) return 0;
+  if (t.scalar_type() == at::kFloat8_e5m2) return 1;
+  TORCH_CHECK(false, "viola_b200: expected an FP8 tensor, got ", t.scalar_type());
+}
+inline void check(int rc, const char* what) {
+  TORCH_CHECK(rc == 0, "viola_b200::", what, " failed: ", cudaGetErrorString((cudaError_t)rc), " (", rc, ")");
+}
+inline void* ptr(const OptTensor& t) { return t.has_value() && t->defined() && t->numel() ? t->data_ptr() : nullptr; }
+inline void cuda_contig(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous(), "viola_b200: ", name, " must be a contiguous CUDA tensor");
+}
+
+void amax_scale(const Tensor& x, const OptTensor& history, int64_t index, bool delayed, double limit,
+                Tensor scale_out, Tensor scratch) {
+  cuda_contig(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  check(vb_amax_scale(x.data_ptr(), x.numel(), dtype_code(x), (float*)ptr(history),
+                      history.has_value() ? (int)history->numel() : 0, index, delayed, (float)limit,
+                      scale_out.data_ptr<float>(), (unsigned int*)scratch.data_ptr(), stream()),
+        "amax_scale");
+}
+
+void quantize(const Tensor& x, const Tensor& scale, double limit, const OptTensor& q, const OptTensor& qt, int64_t fmt) {
+  cuda_contig(x, "x");
+  TORCH_CHECK(x.dim() == 2);
+  c10::cuda::CUDAGuard guard(x.device());
+  check(vb_quantize(x.data_ptr(), (int)x.size(0), (int)x.size(1), dtype_code(x), scale.data_ptr<float>(), (float)limit,
+                    (int)fmt, ptr(q), ptr(qt), stream()),
+        "quantize");
+}
+
+void transpose_u8(const Tensor& x, Tensor out) {
+  cuda_contig(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.element_size() == 1 && out.numel() == x.numel());
+  c10::cuda::CUDAGuard guard(x.device());
+  check(vb_transpose_u8(x.data_ptr(), (int)x.size(0), (int)x.size(1), out.data_ptr(), stream()), "transpose_u8");
+}
+
+void group_encode(const Tensor& x, int64_t fmt, double limit, const OptTensor& q, const OptTensor& s, int64_t gr,
+                  int64_t gc, int64_t s_row, int64_t s_col, const OptTensor& qt, const OptTensor& st, int64_t tgr,
+                  int64_t tgc, int64_t st_row, int64_t st_col) {
+  cuda_contig(x, "x");
+  TORCH_CHECK(x.dim() == 2 && gc >= 32 && (!qt.has_value() || tgc >= 32), "group columns must be >= 32");
+  c10::cuda::CUDAGuard guard(x.device());
+  check(vb_group_encode(x.data_ptr(), (int)x.size(0), (int)x.size(1), dtype_code(x), (int)fmt, (float)limit, ptr(q),
+                        (float*)ptr(s), (int)gr, (int)gc, s_row, s_col, ptr(qt), (float*)ptr(st), (int)tgr, (int)tgc,
+                        st_row, st_col, stream()),
+        "group_encode");
+}
+
+void group_decode(const Tensor& q, const Tensor& s, int64_t gr, int64_t gc, int64_t s_row, int64_t s_col, Tensor out) {
+  cuda_contig(q, "q");
+  c10::cuda::CUDAGuard guard(q.device());
+  check(vb_group_decode(q.data_ptr(), s.data_ptr<float>(), (int)q.size(0), (int)q.size(1), fp8_code(q), (int)gr,
+                        (int)gc, s_row, s_col, out.data_ptr<float>(), stream()),
+        "group_decode");
+}
+
+// scale_layout = [group, sa_row, sa_k, sb_row, sb_k, sb_shift, k_shift]
+void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t epilogue, int64_t n_logical, const OptTensor& sa,
+          const OptTensor& sb, at::IntArrayRef scale_layout, const OptTensor& bias, double alpha, double beta,
+          const OptTensor& resid, const OptTensor& out_t, bool symmetric, int64_t activation, const OptTensor& aux,
+          const OptTensor& expert_offsets, const OptTensor& tile_map, const OptTensor& status, int64_t force_bn) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda());
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && out.stride(-1) == 1);
+  TORCH_CHECK(a.size(1) == b.size(1), "K mismatch");
+  c10::cuda::CUDAGuard guard(a.device());
+  VbGemmDesc d{};
+  if (a.element_size() == 1) {
+    d.kind = VB_KIND_F8;
+    d.a_fmt = fp8_code(a);
+    d.b_fmt = fp8_code(b);
+  } else {
+    d.kind = VB_KIND_F16;
+    TORCH_CHECK(a.scalar_type() == b.scalar_type(), "16-bit GEMM operands must share a dtype");
+    d.a_fmt = d.b_fmt = a.scalar_type() == at::kBFloat16 ? 1 : 0;
+    TORCH_CHECK(a.scalar_type() == at::kBFloat16 || a.scalar_type() == at::kHalf);
+  }
+  d.epilogue = (int)epilogue;
+  d.M = (int)a.size(0);
+  d.N = (int)n_logical;
+  d.K = (int)a.size(1);
+  d.A = a.data_ptr();
+  d.lda = a.stride(0);
+  d.B = b.data_ptr();
+  d.ldb = b.stride(0);
+  TORCH_CHECK(scale_layout.size() == 7);
+  d.group = (int)scale_layout[0];
+  d.sa = (const float*)ptr(sa);
+  d.sb = (const float*)ptr(sb);
+  d.sa_row = scale_layout[1]; d.sa_k = scale_layout[2]; d.sb_row = scale_layout[3]; d.sb_k = scale_layout[4];
+  d.sb_shift = (int)scale_layout[5]; d.k_shift = (int)scale_layout[6];
+  TORCH_CHECK(!d.group || (d.sa && d.sb), "group-scaled GEMM needs both scale tensors");
+  d.out = out.data_ptr();
+  d.out_dtype = dtype_code(out);
+  d.ldo = out.stride(0);
+  d.bias = ptr(bias);
+  d.bias_dtype = bias.has_value() && bias->defined() ? dtype_code(*bias) : 0;
+  d.alpha = (float)alpha; d.beta = (float)beta;
+  d.resid = ptr(resid);
+  d.ldr = resid.has_value() && resid->defined() ? resid->stride(0) : 0;
+  if (d.resid) TORCH_CHECK(resid->scalar_type() == out.scalar_type(), "residual dtype must match the output");
+  d.out_t = ptr(out_t);
+  d.ldot = out_t.has_value() && out_t->defined() ? out_t->stride(0) : 0;
+  d.symmetric = symmetric;
+  d.activation = (int)activation;
+  d.aux = ptr(aux);
+  d.ldaux = aux.has_value() && aux->defined() ? aux->stride(0) : 0;
+  if (d.aux) TORCH_CHECK(aux->scalar_type() == out.scalar_type(), "aux dtype must match the output");
+  d.expert_offsets = (const int*)ptr(expert_offsets);
+  d.num_experts = d.expert_offsets ? (int)expert_offsets->numel() - 1 : 0;
+  d.tile_map = (int*)ptr(tile_map);
+  if (d.expert_offsets) {
+    TORCH_CHECK(d.tile_map && tile_map->numel() >= 3 * ((d.M + 127) / 128 + d.num_experts), "tile_map too small");
+    TORCH_CHECK(b.size(0) == (int64_t)d.N * d.num_experts);
+  }
+  d.status = (int*)ptr(status);
+  d.force_bn = (int)force_bn;
+  check(vb_gemm(&d, stream()), "gemm");
+}
+
+void momentum_1d(const Tensor& grad, const Tensor& old_q, const Tensor& old_scale, Tensor new_q, Tensor new_scale,
+                 Tensor update, int64_t tile, double beta, double inv_loss_scale, bool nesterov, bool stochastic,
+                 int64_t step, int64_t key) {
+  cuda_contig(grad, "grad");
+  c10::cuda::CUDAGuard guard(grad.device());
+  TORCH_CHECK(update.scalar_type() == at::kBFloat16 && update.numel() >= grad.numel());
+  check(vb_momentum_1d(grad.data_ptr(), dtype_code(grad), grad.numel(), (const uint8_t*)old_q.data_ptr(),
+                       old_scale.data_ptr<float>(), (uint8_t*)new_q.data_ptr(), new_scale.data_ptr<float>(),
+                       update.data_ptr(), (int)tile, (float)beta, (float)inv_loss_scale, nesterov, stochastic, step,
+                       (unsigned long long)key, stream()),
+        "momentum_1d");
+}
+
+void momentum_2d(const Tensor& grad, int64_t planes, int64_t rows, int64_t cols, const Tensor& old_q,
+                 const Tensor& old_scale, Tensor new_q, Tensor new_scale, Tensor update, int64_t tr, int64_t tc,
+                 double beta, double inv_loss_scale, bool nesterov, bool stochastic, int64_t step, int64_t key) {
+  cuda_contig(grad, "grad");
+  c10::cuda::CUDAGuard guard(grad.device());
+  check(vb_momentum_2d(grad.data_ptr(), dtype_code(grad), (int)planes, (int)rows, (int)cols,
+                       (const uint8_t*)old_q.data_ptr(), old_scale.data_ptr<float>(), (uint8_t*)new_q.data_ptr(),
+                       new_scale.data_ptr<float>(), update.data_ptr(), (int)tr, (int)tc, (float)beta,
+                       (float)inv_loss_scale, nesterov, stochastic, step, (unsigned long long)key, stream()),
+        "momentum_2d");
+}
+
+void weight_update(Tensor weight, const Tensor& update, double lr, double decay, double update_scale, bool stochastic,
+                   int64_t step, int64_t key, int64_t offset) {
+  cuda_contig(weight, "weight");
+  cuda_contig(update, "update");
+  TORCH_CHECK(weight.numel() == update.numel());
+  c10::cuda::CUDAGuard guard(weight.device());
+  check(vb_weight_update(weight.data_ptr(), dtype_code(weight), update.data_ptr(), dtype_code(update), weight.numel(),
+                         (float)lr, (float)decay, (float)update_scale, stochastic, step, (unsigned long long)key, offset,
+                         stream()),
+        "weight_update");
+}
+
+void adam_update(Tensor weight, const Tensor& grad, Tensor first, Tensor second, double lr, double decay, double b1,
+                 double b2, double inv_c1, double inv_c2, double eps, bool adamw, bool maximize, bool stochastic,
+                 int64_t step, int64_t key, int64_t offset) {
+  cuda_contig(weight, "weight");
+  cuda_contig(grad, "grad");
+  TORCH_CHECK(first.scalar_type() == second.scalar_type());
+  c10::cuda::CUDAGuard guard(weight.device());
+  check(vb_adam_update(weight.data_ptr(), dtype_code(weight), grad.data_ptr(), dtype_code(grad), first.data_ptr(),
+                       second.data_ptr(), dtype_code(first), weight.numel(), (float)lr, (float)decay, (float)b1,
+                       (float)b2, (float)inv_c1, (float)inv_c2, (float)eps, adamw, maximize, stochastic, step,
+                       (unsigned long long)key, offset, stream()),
+        "adam_update");
+}
+
+void copy_scaled(const Tensor& update, Tensor out, int64_t src, int64_t dst, int64_t count, double scale) {
+  c10::cuda::CUDAGuard guard(update.device());
+  check(vb_copy_scaled(update.data_ptr(), dtype_code(update), out.data_ptr(), dtype_code(out), src, dst, count,
+                       (float)scale, stream()),
+        "copy_scaled");
+}
+
+void momentum16(const Tensor& grad, Tensor momentum, Tensor update, double beta, bool nesterov) {
+  c10::cuda::CUDAGuard guard(grad.device());
+  check(vb_momentum16(grad.data_ptr(), dtype_code(grad), momentum.data_ptr(), dtype_code(momentum), update.data_ptr(),
+                      grad.numel(), (float)beta, nesterov, stream()),
+        "momentum16");
+}
+
+void sumsq(const Tensor& x, int64_t round_dtype, Tensor accum) {
+  cuda_contig(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  check(vb_sumsq(x.data_ptr(), dtype_code(x) | ((int)round_dtype << 8), x.numel(), accum.data_ptr<float>(), stream()),
+        "sumsq");
+}
+
+void ns_prescale(const Tensor& x, const Tensor& sumsq_t, double eps, const OptTensor& out, const OptTensor& out_t) {
+  cuda_contig(x, "x");
+  TORCH_CHECK(x.dim() == 2);
+  const Tensor& ref = out.has_value() && out->defined() ? *out : *out_t;
+  c10::cuda::CUDAGuard guard(x.device());
+  check(vb_ns_prescale(x.data_ptr(), dtype_code(x), (int)x.size(0), (int)x.size(1), sumsq_t.data_ptr<float>(),
+                       (float)eps, ptr(out), ptr(out_t), dtype_code(ref), stream()),
+        "ns_prescale");
+}
+
+void ema_lerp(Tensor ema, const Tensor& master, double decay) {
+  cuda_contig(ema, "ema");
+  cuda_contig(master, "master");
+  c10::cuda::CUDAGuard guard(ema.device());
+  check(vb_ema_lerp(ema.data_ptr(), dtype_code(ema), master.data_ptr(), dtype_code(master), ema.numel(), (float)decay,
+                    stream()),
+        "ema_lerp");
+}
+
+void philox_kat(int64_t element, int64_t step, int64_t key, Tensor out) {
+  c10::cuda::CUDAGuard guard(out.device());
+  check(vb_philox_kat((unsigned long long)element, (unsigned long long)step, (unsigned long long)key,
+                      (unsigned int*)out.data_ptr(), (int)out.numel(), stream()),
+        "philox_kat");
+}
+
+void gated_forward(const Tensor& gu, int64_t activation, Tensor out) {
+  cuda_contig(gu, "gu");
+  c10::cuda::CUDAGuard guard(gu.device());
+  check(vb_gated_forward(gu.data_ptr(), dtype_code(gu), (int)gu.size(0), (int)(gu.size(1) / 2), (int)activation,
+                         out.data_ptr(), stream()),
+        "gated_forward");
+}
+void gated_backward(const Tensor& gu, const Tensor& dh, int64_t activation, Tensor dgu) {
+  cuda_contig(gu, "gu");
+  cuda_contig(dh, "dh");
+  c10::cuda::CUDAGuard guard(gu.device());
+  check(vb_gated_backward(gu.data_ptr(), dh.data_ptr(), dtype_code(gu), (int)gu.size(0), (int)(gu.size(1) / 2),
+                          (int)activation, dgu.data_ptr(), stream()),
+        "gated_backward");
+}
+
+void hadamard64(const Tensor& x, Tensor out) {
+  cuda_contig(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  check(vb_hadamard64(x.data_ptr(), dtype_code(x), (int)(x.numel() / x.size(-1)), (int)x.size(-1), out.data_ptr(),
+                      stream()),
+        "hadamard64");
+}
+
+void wire_pack(const Tensor& x, int64_t rows, int64_t groups, int64_t tile, int64_t fmt, Tensor packet,
+               int64_t row_stride) {
+  cuda_contig(x, "x");
+  TORCH_CHECK(x.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(x.device());
+  check(vb_wire_pack(x.data_ptr<float>(), x.numel(), (int)rows, (int)groups, (int)tile, (int)fmt,
+                     (uint8_t*)packet.data_ptr(), row_stride, stream()),
+        "wire_pack");
+}
+void wire_unpack(const Tensor& packet, int64_t row_stride, int64_t rows, int64_t groups, int64_t tile, int64_t fmt,
+                 bool reduce, Tensor out, bool accumulate) {
+  TORCH_CHECK(out.scalar_type() == at::kFloat && out.is_contiguous());
+  c10::cuda::CUDAGuard guard(out.device());
+  check(vb_wire_unpack((const uint8_t*)packet.data_ptr(), row_stride, (int)rows, (int)groups, (int)tile, (int)fmt,
+                       reduce, out.data_ptr<float>(), out.numel(), accumulate, stream()),
+        "wire_unpack");
+}
+
+}  // namespace
+
+TORCH_LIBRARY(viola_b200, m) {
+  m.def("amax_scale", &amax_scale);
+  m.def("quantize", &quantize);
+  m.def("transpose_u8", &transpose_u8);
+  m.def("group_encode", &group_encode);
+  m.def("group_decode", &group_decode);
+  m.def("gemm", &gemm);
+  m.def("momentum_1d", &momentum_1d);
+  m.def("momentum_2d", &momentum_2d);
+  m.def("weight_update", &weight_update);
+  m.def("adam_update", &adam_update);
+  m.def("copy_scaled", &copy_scaled);
+  m.def("momentum16", &momentum16);
+  m.def("sumsq", &sumsq);
+  m.def("ns_prescale", &ns_prescale);
+  m.def("ema_lerp", &ema_lerp);
+  m.def("philox_kat", &philox_kat);
+  m.def("gated_forward", &gated_forward);
+  m.def("gated_backward", &gated_backward);
+  m.def("hadamard64", &hadamard64);
+  m.def("wire_pack", &wire_pack);
+  m.def("wire_unpack", &wire_unpack);
+}

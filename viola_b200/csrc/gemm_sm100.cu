@@ -1,0 +1,722 @@
+// tcgen05 / TMEM / TMA GEMM family for sm_100a.
+//
+//   D[M, N] = A[M, K] . B[N, K]^T     (both operands K-major)
+//
+// One persistent, warp-specialised kernel template covers every GEMM-shaped op in
+// the library:
+//   * FP8 Linear forward / dgrad / wgrad with per-tensor scales (any e4m3 / e5m2 mix
+//     through the instruction descriptor)             [replaces the reference's
+//     T.gemm / mma.sync kernels, viola/nn/_linear_kernels.py:124-228]
+//   * group-scaled FP8 GEMM, one fp32 scale per 128 K-elements on each operand
+//     (two-level accumulation: UMMA over one K-block into a TMEM stage, promotion
+//     with sa*sb into fp32 registers while the next K-block's MMA runs)
+//                                                     [viola/nn/_grouped_kernels.py:195-293]
+//   * fused gated-MLP forward (gate and up share the A tile, act(g)*u epilogue, aux
+//     save) and backward (dgrad + gated derivative)   [viola/nn/_mlp_kernels.py:16-231]
+//   * expert (ragged-M) GEMM through a tile -> expert map
+//   * Newton-Schulz GEMMs in bf16 / fp16 with the two polynomial epilogues, an
+//     optional transposed second output and a symmetric-output mode
+//                                                     [viola/optim/_orthogonalize_kernels.py:16-50]
+//
+// Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer (one elected lane)
+// and TMEM owner, warps 2-5 = epilogue (TMEM lane quadrant = warp % 4).
+// Pipeline: smem ring (full/empty mbarriers, TMA complete_tx / tcgen05.commit) and a
+// TMEM accumulator ring (tmem_full via tcgen05.commit, tmem_empty via epilogue arrive).
+// TMA loads are never cluster-multicast.  Every wait is bounded (common/ptx.cuh).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <mutex>
+#include "api.h"
+#include "common/ptx.cuh"
+
+namespace vb {
+
+constexpr int BM = 128;
+constexpr int BK_BYTES = 128;  // one 128-byte swizzle span along K per stage
+constexpr int kThreads = 192;
+
+struct GemmArgs {
+  int M, N, K;
+  int num_m_tiles, num_n_tiles, num_k_blocks, num_tiles;
+  uint32_t idesc;
+  int b_gate_up_offset;  // gated forward: row offset of the "up" half inside B (= N)
+  const float* sa;
+  const float* sb;
+  long long sa_row, sa_k, sb_row, sb_k;
+  int sb_shift, k_shift;
+  void* out;
+  int out_dtype;
+  long long ldo;
+  const void* bias;
+  int bias_dtype;
+  float alpha, beta;
+  const void* resid;
+  long long ldr;
+  void* out_t;
+  long long ldot;
+  int symmetric;
+  int activation;
+  void* aux;
+  long long ldaux;
+  const int* tile_map;  // expert mode: [3 * num_m_tiles] = (row0, row_end, expert), row0 < 0 = unused
+  int expert_rows;      // rows of B per expert (= N)
+  int* status;
+};
+
+// ---------------------------------------------------------------------------------------
+// small device helpers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float round_to(float v, int dt) {
+  if (dt == 1) return __bfloat162float(__float2bfloat16_rn(v));
+  if (dt == 2) return __half2float(__float2half_rn(v));
+  return v;
+}
+__device__ __forceinline__ float load_elem(const void* p, long long i, int dt) {
+  if (dt == 0) return reinterpret_cast<const float*>(p)[i];
+  if (dt == 1) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+  return __half2float(reinterpret_cast<const __half*>(p)[i]);
+}
+__device__ __forceinline__ void store_elem(void* p, long long i, int dt, float v) {
+  if (dt == 0) reinterpret_cast<float*>(p)[i] = v;
+  else if (dt == 1) reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+  else reinterpret_cast<__half*>(p)[i] = __float2half_rn(v);
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b, int dt) {
+  if (dt == 1) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&t);
+  }
+  __half2 t = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+
+// Store 32 consecutive values of one row; vectorised when the whole chunk is in range and
+// the destination is 16-byte aligned, scalar with bounds checks otherwise.
+__device__ __forceinline__ void store_row32(void* base, long long ld, int dt, long long row, int col0,
+                                            int ncols, const float (&v)[32]) {
+  const long long off = row * ld + col0;
+  if (dt == 0) {
+    float* p = reinterpret_cast<float*>(base) + off;
+    if (col0 + 32 <= ncols && ((reinterpret_cast<uintptr_t>(p) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        reinterpret_cast<float4*>(p)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < ncols) p[j] = v[j];
+    }
+  } else {
+    uint16_t* p = reinterpret_cast<uint16_t*>(base) + off;
+    if (col0 + 32 <= ncols && ((reinterpret_cast<uintptr_t>(p) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 t;
+        t.x = pack2(v[8 * j + 0], v[8 * j + 1], dt);
+        t.y = pack2(v[8 * j + 2], v[8 * j + 3], dt);
+        t.z = pack2(v[8 * j + 4], v[8 * j + 5], dt);
+        t.w = pack2(v[8 * j + 6], v[8 * j + 7], dt);
+        reinterpret_cast<uint4*>(p)[j] = t;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < ncols) store_elem(base, off + j, dt, v[j]);
+    }
+  }
+}
+// Load 32 consecutive values of one row as floats (zeros out of range).
+__device__ __forceinline__ void load_row32(const void* base, long long ld, int dt, long long row, int col0,
+                                           int ncols, float (&v)[32]) {
+  const long long off = row * ld + col0;
+  if (dt != 0) {
+    const uint16_t* p = reinterpret_cast<const uint16_t*>(base) + off;
+    if (col0 + 32 <= ncols && ((reinterpret_cast<uintptr_t>(p) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 t = reinterpret_cast<const uint4*>(p)[j];
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float2 f;
+          if (dt == 1) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e]));
+          else f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+          v[8 * j + 2 * e] = f.x;
+          v[8 * j + 2 * e + 1] = f.y;
+        }
+      }
+      return;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = (col0 + j < ncols) ? load_elem(base, off + j, dt) : 0.f;
+}
+
+__device__ __forceinline__ float act_fn(float g, int act) {
+  if (act == VB_ACT_SILU) return g / (1.f + __expf(-g));
+  if (act == VB_ACT_RELU) return fmaxf(g, 0.f);
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float t = tanhf(k0 * (g + k1 * g * g * g));
+  return 0.5f * g * (1.f + t);
+}
+__device__ __forceinline__ float act_grad(float g, int act) {
+  if (act == VB_ACT_SILU) {
+    float s = 1.f / (1.f + __expf(-g));
+    return s * (1.f + g * (1.f - s));
+  }
+  if (act == VB_ACT_RELU) return g > 0.f ? 1.f : 0.f;
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float t = tanhf(k0 * (g + k1 * g * g * g));
+  return 0.5f * (1.f + t) + 0.5f * g * (1.f - t * t) * k0 * (1.f + 3.f * k1 * g * g);
+}
+
+// tile id -> (m_tile, n_tile).  Plain: groups of 8 M-tiles sweep N (L2 reuse of B across the
+// wave, of A inside a group).  Symmetric: row-major walk over the upper triangle.
+__device__ __forceinline__ void tile_coords(const GemmArgs& a, int t, int& mt, int& nt) {
+  if (a.symmetric) {
+    int m = 0, T = a.num_m_tiles;
+    while (t >= T - m) { t -= T - m; ++m; }
+    mt = m; nt = m + t;
+    return;
+  }
+  const int group = 8 * a.num_n_tiles;
+  const int g = t / group, first_m = g * 8;
+  const int gm = min(8, a.num_m_tiles - first_m);
+  const int in = t % group;
+  mt = first_m + in % gm;
+  nt = in / gm;
+}
+
+template <int KIND, int BN, bool GROUP, int EPI>
+struct Config {
+  static constexpr bool kGatedFwd = EPI == VB_EPI_GATED_FWD;
+  static constexpr int kBBoxRows = kGatedFwd ? BN / 2 : BN;
+  static constexpr int kABytes = BM * BK_BYTES;
+  static constexpr int kBBytes = BN * BK_BYTES;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kAcc = GROUP ? (512 / BN > 4 ? 4 : 512 / BN) : 2;
+  static constexpr int kTmemCols = kAcc * BN;
+  static constexpr int kBarrierBytes = 1024;
+  static constexpr int kSbStage = GROUP ? 4 * 2 * BN * (int)sizeof(float) : 0;  // per-warp staged B scales
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kSbStage + 1024;
+  static constexpr int kElemBytes = KIND == VB_KIND_F8 ? 1 : 2;
+  static constexpr int kBK = BK_BYTES / kElemBytes;  // elements per K-block
+  static constexpr int kUmmaKBytes = 32;
+  static constexpr int kMmasPerStage = BK_BYTES / kUmmaKBytes;
+  static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512, "TMEM columns");
+  static_assert(kSmemBytes > 116 * 1024, "one CTA per SM so TMEM allocation never contends");
+};
+
+template <int KIND, int BN, bool GROUP, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const GemmArgs args) {
+  using C = Config<KIND, BN, GROUP, EPI>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_base = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* full_bar = bars;                         // [kStages]
+  uint64_t* empty_bar = bars + C::kStages;           // [kStages]
+  uint64_t* tmem_full = bars + 2 * C::kStages;       // [kAcc]
+  uint64_t* tmem_empty = tmem_full + C::kAcc;        // [kAcc]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + C::kAcc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* sb_stage = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes + C::kBarrierBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::kStages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < C::kAcc; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
+      int mt, nt;
+      tile_coords(args, t, mt, nt);
+      int a_row = mt * BM, b_row = nt * C::kBBoxRows;
+      if (args.tile_map != nullptr) {
+        const int row0 = args.tile_map[3 * mt];
+        if (row0 < 0) continue;
+        a_row = row0;
+        b_row += args.tile_map[3 * mt + 2] * args.expert_rows;
+      }
+      for (int kb = 0; kb < args.num_k_blocks; ++kb) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, args.status, kTimeoutEmpty));
+        if (!ok) break;
+        if (lane == 0) {
+          uint8_t* sa_ptr = stage_base + stage * C::kStageBytes;
+          uint8_t* sb_ptr = sa_ptr + C::kABytes;
+          mbar_expect_tx(&full_bar[stage], C::kStageBytes);
+          tma_load_2d(sa_ptr, &tmA, &full_bar[stage], kb * C::kBK, a_row);
+          tma_load_2d(sb_ptr, &tmB, &full_bar[stage], kb * C::kBK, b_row);
+          if constexpr (C::kGatedFwd)
+            tma_load_2d(sb_ptr + C::kBBoxRows * BK_BYTES, &tmB, &full_bar[stage], kb * C::kBK,
+                        b_row + args.b_gate_up_offset);
+        }
+        __syncwarp();
+        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    int stage = 0, acc = 0;
+    uint32_t phase = 0, acc_phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
+      if (args.tile_map != nullptr) {
+        int mt, nt;
+        tile_coords(args, t, mt, nt);
+        if (args.tile_map[3 * mt] < 0) continue;
+      }
+      if constexpr (!GROUP) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, args.status, kTimeoutTmemEmpty));
+        if (!ok) break;
+        tc_fence_after_sync();
+      }
+      for (int kb = 0; kb < args.num_k_blocks; ++kb) {
+        if constexpr (GROUP) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, args.status, kTimeoutTmemEmpty));
+          if (!ok) break;
+        }
+        ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase, abort_flag, args.status, kTimeoutFull));
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (lane == 0) {
+          const uint32_t a_addr = smem_u32(stage_base + stage * C::kStageBytes);
+          const uint32_t b_addr = a_addr + C::kABytes;
+          const uint64_t adesc = make_kmajor_sw128_desc(a_addr);
+          const uint64_t bdesc = make_kmajor_sw128_desc(b_addr);
+          const uint32_t d_tmem = tmem_base + acc * BN;
+#pragma unroll
+          for (int k = 0; k < C::kMmasPerStage; ++k) {
+            const uint32_t accumulate = GROUP ? (k > 0) : (kb > 0 || k > 0);
+            const uint64_t koff = (uint64_t)((k * C::kUmmaKBytes) >> 4);
+            if constexpr (KIND == VB_KIND_F8) mma_f8_ss(d_tmem, adesc + koff, bdesc + koff, args.idesc, accumulate);
+            else mma_f16_ss(d_tmem, adesc + koff, bdesc + koff, args.idesc, accumulate);
+          }
+          tc_commit(&empty_bar[stage]);
+          if constexpr (GROUP) tc_commit(&tmem_full[acc]);
+        }
+        __syncwarp();
+        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        if constexpr (GROUP) {
+          if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1; }
+        }
+      }
+      if (!ok) break;
+      if constexpr (!GROUP) {
+        if (lane == 0) tc_commit(&tmem_full[acc]);
+        __syncwarp();
+        if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int quad = warp & 3;            // TMEM lane quadrant this warp may read
+    const int row_in_tile = quad * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    constexpr int NCHUNK = BN / 32;
+    constexpr int NOUT = C::kGatedFwd ? NCHUNK / 2 : NCHUNK;  // output chunks per tile
+    for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
+      int mt, nt;
+      tile_coords(args, t, mt, nt);
+      long long grow = (long long)mt * BM + row_in_tile;
+      long long row_end = args.M;
+      int expert = 0;
+      if (args.tile_map != nullptr) {
+        const int row0 = args.tile_map[3 * mt];
+        if (row0 < 0) continue;
+        grow = (long long)row0 + row_in_tile;
+        row_end = args.tile_map[3 * mt + 1];
+        expert = args.tile_map[3 * mt + 2];
+      }
+      const bool row_ok = grow < row_end;
+      const int n0 = nt * (C::kGatedFwd ? BN / 2 : BN);  // first logical output column
+      const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+
+      float accr[GROUP ? BN : 1];
+      if constexpr (GROUP) {
+#pragma unroll
+        for (int j = 0; j < BN; ++j) accr[j] = 0.f;
+        for (int kb = 0; kb < args.num_k_blocks; ++kb) {
+          const int ks = kb >> args.k_shift;
+          // B scales for this K-block: scalar per 32-column chunk when a scale block spans
+          // >= 32 B rows, otherwise one value per column staged through shared memory.
+          const bool per_col = args.sb_shift < 5;
+          float* sbs = sb_stage + ((warp - 2) * 2 + (kb & 1)) * BN;  // private to this warp: no CTA barrier
+          if (per_col) {
+            for (int j = lane; j < BN; j += 32) {
+              int brow = C::kGatedFwd ? (j < BN / 2 ? n0 + j : args.b_gate_up_offset + n0 + (j - BN / 2)) : n0 + j;
+              const bool in = C::kGatedFwd ? (brow - (j < BN / 2 ? 0 : args.b_gate_up_offset) < args.N) : (brow < args.N);
+              brow += expert * args.expert_rows;
+              sbs[j] = in ? args.sb[(long long)(brow >> args.sb_shift) * args.sb_row + (long long)ks * args.sb_k] : 0.f;
+            }
+            __syncwarp();
+          }
+          const float sa_v = row_ok ? args.sa[grow * args.sa_row + (long long)ks * args.sa_k] : 0.f;
+          ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full[acc], acc_phase, abort_flag, args.status, kTimeoutTmemFull));
+          if (!ok) break;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int c = 0; c < NCHUNK; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + lane_addr + acc * BN + c * 32, r);
+            tmem_ld_wait();
+            if (per_col) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) accr[c * 32 + j] = fmaf(__uint_as_float(r[j]), sa_v * sbs[c * 32 + j], accr[c * 32 + j]);
+            } else {
+              int brow = C::kGatedFwd ? (c < NCHUNK / 2 ? n0 + c * 32 : args.b_gate_up_offset + n0 + (c - NCHUNK / 2) * 32)
+                                      : n0 + c * 32;
+              const int limit_rows = C::kGatedFwd ? 2 * args.N : args.N;
+              brow = min(brow, limit_rows - 1) + expert * args.expert_rows;
+              const float s = sa_v * args.sb[(long long)(brow >> args.sb_shift) * args.sb_row + (long long)ks * args.sb_k];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) accr[c * 32 + j] = fmaf(__uint_as_float(r[j]), s, accr[c * 32 + j]);
+            }
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+          if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1; }
+        }
+        if (!ok) break;
+      } else {
+        ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full[acc], acc_phase, abort_flag, args.status, kTimeoutTmemFull));
+        if (!ok) break;
+        tc_fence_after_sync();
+      }
+
+      const float alpha_pt = GROUP ? 1.f
+                                   : (args.sa != nullptr ? args.sa[0] : 1.f) * (args.sb != nullptr ? args.sb[0] : 1.f);
+#pragma unroll
+      for (int c = 0; c < NOUT; ++c) {
+        float v[32];
+        float v2[C::kGatedFwd ? 32 : 1];
+        if constexpr (GROUP) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = accr[c * 32 + j];
+          if constexpr (C::kGatedFwd) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v2[j] = accr[BN / 2 + c * 32 + j];
+          }
+        } else {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + lane_addr + acc * BN + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha_pt;
+          if constexpr (C::kGatedFwd) {
+            tmem_ld_32x32(tmem_base + lane_addr + acc * BN + BN / 2 + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v2[j] = __uint_as_float(r[j]) * alpha_pt;
+          }
+        }
+        const int col0 = n0 + c * 32;
+        if (col0 >= args.N) continue;  // warp-uniform
+        if constexpr (EPI == VB_EPI_LINEAR) {
+          if (args.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < args.N) v[j] += load_elem(args.bias, col0 + j, args.bias_dtype);
+          }
+          if (row_ok) store_row32(args.out, args.ldo, args.out_dtype, grow, col0, args.N, v);
+        } else if constexpr (EPI == VB_EPI_AXPBY) {
+          float res[32];
+          if (args.resid != nullptr && row_ok) load_row32(args.resid, args.ldr, args.out_dtype, grow, col0, args.N, res);
+          else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) res[j] = 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            v[j] = round_to(args.alpha * round_to(v[j], args.out_dtype) + args.beta * res[j], args.out_dtype);
+          if (row_ok) store_row32(args.out, args.ldo, args.out_dtype, grow, col0, args.N, v);
+          void* tbase = args.out_t;
+          long long tld = args.ldot;
+          if (args.symmetric && mt != nt) { tbase = args.out; tld = args.ldo; }
+          if (tbase != nullptr && row_ok) {
+            // transposed copy: lanes hold consecutive rows -> consecutive addresses per column
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < args.N) store_elem(tbase, (long long)(col0 + j) * tld + grow, args.out_dtype, v[j]);
+          }
+        } else if constexpr (EPI == VB_EPI_GATED_FWD) {
+          if (args.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < args.N) {
+                v[j] += load_elem(args.bias, col0 + j, args.bias_dtype);
+                v2[j] += load_elem(args.bias, args.N + col0 + j, args.bias_dtype);
+              }
+          }
+          float h[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = round_to(v[j], args.out_dtype);
+            v2[j] = round_to(v2[j], args.out_dtype);
+            h[j] = act_fn(v[j], args.activation) * v2[j];
+          }
+          if (row_ok) {
+            store_row32(args.out, args.ldo, args.out_dtype, grow, col0, args.N, h);
+            if (args.aux != nullptr) {
+              store_row32(args.aux, args.ldaux, args.out_dtype, grow, col0, args.N, v);
+              // "up" half lives at column offset N; bound by 2N but chunk validity is the same
+              float* dummy = nullptr; (void)dummy;
+              const long long off_cols = args.N;
+              // shift base pointer by N columns
+              void* up_base = (args.out_dtype == 0)
+                                  ? (void*)(reinterpret_cast<float*>(args.aux) + off_cols)
+                                  : (void*)(reinterpret_cast<uint16_t*>(args.aux) + off_cols);
+              store_row32(up_base, args.ldaux, args.out_dtype, grow, col0, args.N, v2);
+            }
+          }
+        } else {  // VB_EPI_GATED_BWD: v = d; aux = [g | u]; out = [dG | dU]
+          if (row_ok) {
+            float g[32], u[32], dg[32], du[32];
+            const void* up_base = (args.out_dtype == 0)
+                                      ? (const void*)(reinterpret_cast<const float*>(args.aux) + args.N)
+                                      : (const void*)(reinterpret_cast<const uint16_t*>(args.aux) + args.N);
+            load_row32(args.aux, args.ldaux, args.out_dtype, grow, col0, args.N, g);
+            load_row32(up_base, args.ldaux, args.out_dtype, grow, col0, args.N, u);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float d = round_to(v[j], args.out_dtype);
+              dg[j] = d * u[j] * act_grad(g[j], args.activation);
+              du[j] = d * act_fn(g[j], args.activation);
+            }
+            void* out_up = (args.out_dtype == 0) ? (void*)(reinterpret_cast<float*>(args.out) + args.N)
+                                                 : (void*)(reinterpret_cast<uint16_t*>(args.out) + args.N);
+            store_row32(args.out, args.ldo, args.out_dtype, grow, col0, args.N, dg);
+            store_row32(out_up, args.ldo, args.out_dtype, grow, col0, args.N, du);
+          }
+        }
+      }
+      if constexpr (!GROUP) {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  // On the error path TMA copies may still be in flight towards this CTA's shared memory:
+  // give them a bounded grace period before the CTA (and its smem) goes away.
+  if (*abort_flag) {
+    const long long start = clock64();
+    while (clock64() - start < 2000000LL) { __nanosleep(256); }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// Builds the tile -> (row0, row_end, expert) map for the expert GEMM from device offsets.
+__global__ void expert_tile_map_kernel(const int* __restrict__ offsets, int num_experts, int max_tiles,
+                                       int* __restrict__ tile_map) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int t = 0;
+  for (int e = 0; e < num_experts; ++e) {
+    const int begin = offsets[e], end = offsets[e + 1];
+    for (int r = begin; r < end && t < max_tiles; r += BM) {
+      tile_map[3 * t] = r;
+      tile_map[3 * t + 1] = end;
+      tile_map[3 * t + 2] = e;
+      ++t;
+    }
+  }
+  for (; t < max_tiles; ++t) {
+    tile_map[3 * t] = -1;
+    tile_map[3 * t + 1] = 0;
+    tile_map[3 * t + 2] = 0;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// 2-D K-major tensor map: inner dim = K (contiguous), outer = rows; box = (128 bytes of K) x box_rows.
+static int make_map(CUtensorMap* map, const void* base, int kind, int fmt, long long rows, long long k,
+                    long long ld_elems, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return (int)cudaErrorNotSupported;
+  const int elem = kind == VB_KIND_F8 ? 1 : 2;
+  CUtensorMapDataType dt = kind == VB_KIND_F8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                              : (fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)(ld_elems * elem)};
+  cuuint32_t box[2] = {(cuuint32_t)(BK_BYTES / elem), (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (strides[0] & 15) != 0) return (int)cudaErrorMisalignedAddress;
+  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+static int sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+    if (count <= 0) count = 148;
+  }
+  return count;
+}
+
+template <int KIND, int BN, bool GROUP, int EPI>
+static int launch(const VbGemmDesc& d, cudaStream_t stream) {
+  using C = Config<KIND, BN, GROUP, EPI>;
+  GemmArgs a{};
+  a.M = d.M; a.N = d.N; a.K = d.K;
+  const bool expert = d.expert_offsets != nullptr;
+  a.num_m_tiles = expert ? (d.M + BM - 1) / BM + d.num_experts : (d.M + BM - 1) / BM;
+  constexpr int n_per_tile = C::kGatedFwd ? BN / 2 : BN;
+  a.num_n_tiles = (d.N + n_per_tile - 1) / n_per_tile;
+  a.num_k_blocks = (d.K + C::kBK - 1) / C::kBK;
+  if (d.symmetric) {
+    if (d.M != d.N || BN != BM || expert) return (int)cudaErrorInvalidValue;
+    a.num_tiles = a.num_m_tiles * (a.num_m_tiles + 1) / 2;
+  } else {
+    a.num_tiles = a.num_m_tiles * a.num_n_tiles;
+  }
+  a.idesc = make_idesc(d.a_fmt, d.b_fmt, BM, BN);
+  a.b_gate_up_offset = d.N;
+  a.sa = d.sa; a.sb = d.sb;
+  a.sa_row = d.sa_row; a.sa_k = d.sa_k; a.sb_row = d.sb_row; a.sb_k = d.sb_k;
+  a.sb_shift = d.sb_shift; a.k_shift = d.k_shift;
+  a.out = d.out; a.out_dtype = d.out_dtype; a.ldo = d.ldo;
+  a.bias = d.bias; a.bias_dtype = d.bias_dtype;
+  a.alpha = d.alpha; a.beta = d.beta; a.resid = d.resid; a.ldr = d.ldr;
+  a.out_t = d.out_t; a.ldot = d.ldot; a.symmetric = d.symmetric;
+  a.activation = d.activation; a.aux = d.aux; a.ldaux = d.ldaux;
+  a.tile_map = expert ? d.tile_map : nullptr;
+  a.expert_rows = d.N;
+  a.status = d.status;
+  if (a.num_tiles <= 0 || a.num_k_blocks <= 0) return 0;
+
+  const long long b_rows = (long long)(C::kGatedFwd ? 2 : 1) * d.N * (expert ? d.num_experts : 1);
+  CUtensorMap tmA, tmB;
+  int rc = make_map(&tmA, d.A, KIND, d.a_fmt, d.M, d.K, d.lda, BM);
+  if (rc) return rc;
+  rc = make_map(&tmB, d.B, KIND, d.b_fmt, b_rows, d.K, d.ldb, C::kBBoxRows);
+  if (rc) return rc;
+  if (expert) {
+    expert_tile_map_kernel<<<1, 32, 0, stream>>>(d.expert_offsets, d.num_experts, a.num_m_tiles, d.tile_map);
+  }
+  auto kernel = gemm_kernel<KIND, BN, GROUP, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int grid = std::min(a.num_tiles, sm_count());
+  kernel<<<grid, kThreads, C::kSmemBytes, stream>>>(tmA, tmB, a);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace vb
+
+using namespace vb;
+
+extern "C" int vb_gemm(const VbGemmDesc* desc, cudaStream_t stream) {
+  const VbGemmDesc& d = *desc;
+  if (d.M <= 0 || d.N <= 0 || d.K <= 0) return 0;
+  const int elem = d.kind == VB_KIND_F8 ? 1 : 2;
+  if ((d.K * elem) % 16 != 0) return (int)cudaErrorInvalidValue;
+  const int sms = sm_count();
+  int bn = d.force_bn;
+  const bool group = d.group != 0;
+  if (bn == 0) {
+    if (group || d.symmetric) bn = 128;
+    else {
+      const long long tiles256 = (long long)((d.M + 127) / 128) * ((d.N + 255) / 256);
+      bn = (d.N > 128 && tiles256 >= sms / 2) ? 256 : 128;
+      if (d.epilogue == VB_EPI_GATED_FWD) bn = 256;
+    }
+  }
+#define VB_LAUNCH(KIND, BNV, GROUPV, EPIV) return launch<KIND, BNV, GROUPV, EPIV>(d, stream)
+  if (d.kind == VB_KIND_F8) {
+    switch (d.epilogue) {
+      case VB_EPI_LINEAR:
+        if (group) { VB_LAUNCH(VB_KIND_F8, 128, true, VB_EPI_LINEAR); }
+        if (bn == 256) { VB_LAUNCH(VB_KIND_F8, 256, false, VB_EPI_LINEAR); }
+        VB_LAUNCH(VB_KIND_F8, 128, false, VB_EPI_LINEAR);
+      case VB_EPI_GATED_FWD:
+        if (group) { VB_LAUNCH(VB_KIND_F8, 128, true, VB_EPI_GATED_FWD); }
+        VB_LAUNCH(VB_KIND_F8, 256, false, VB_EPI_GATED_FWD);
+      case VB_EPI_GATED_BWD:
+        if (group) { VB_LAUNCH(VB_KIND_F8, 128, true, VB_EPI_GATED_BWD); }
+        VB_LAUNCH(VB_KIND_F8, 128, false, VB_EPI_GATED_BWD);
+      default:
+        return (int)cudaErrorInvalidValue;
+    }
+  } else {
+    if (group) return (int)cudaErrorInvalidValue;
+    switch (d.epilogue) {
+      case VB_EPI_LINEAR:
+        if (bn == 256) { VB_LAUNCH(VB_KIND_F16, 256, false, VB_EPI_LINEAR); }
+        VB_LAUNCH(VB_KIND_F16, 128, false, VB_EPI_LINEAR);
+      case VB_EPI_AXPBY:
+        if (bn == 256 && !d.symmetric) { VB_LAUNCH(VB_KIND_F16, 256, false, VB_EPI_AXPBY); }
+        VB_LAUNCH(VB_KIND_F16, 128, false, VB_EPI_AXPBY);
+      default:
+        return (int)cudaErrorInvalidValue;
+    }
+  }
+#undef VB_LAUNCH
+}

@@ -1,0 +1,523 @@
+"""Operator layer: CUDA tensors run the hand-written sm_100a kernels in ``viola_b200/_C.so``
+(``torch.ops.viola_b200.*``); CPU tensors run the PyTorch restatements in ``reference.py``.
+
+There is no silent fallback on a GPU: if a CUDA tensor reaches an op and the extension cannot be
+loaded, the call raises.  Function names and argument conventions mirror the reference's kernel
+wrappers (viola/nn/_linear_kernels.py:231-291, viola/nn/_grouped_kernels.py:127-171,310-328,
+viola/optim/_kernels.py:61-83,296-337, viola/distributed/_fp8_kernels.py:84-93) so the module layer
+reads the same.
+"""
+
+from __future__ import annotations
+
+import math
+import os
+import threading
+from pathlib import Path
+
+import torch
+
+from . import reference
+from .reference import packet_bytes, packet_views, scale_shape, state_sizes  # noqa: F401
+
+_LIB_PATH = Path(__file__).resolve().parent.parent / "_C.so"
+_lock = threading.Lock()
+_loaded = False
+_load_error = None
+
+FP8_DTYPES = (torch.float8_e4m3fn, torch.float8_e5m2)
+_FMT = {torch.float8_e4m3fn: 0, torch.float8_e5m2: 1}
+_ACT = {"silu": 0, "gelu": 1, "relu": 2}
+EPI_LINEAR, EPI_AXPBY, EPI_GATED_FWD, EPI_GATED_BWD = 0, 1, 2, 3
+_NO_GROUP = (0, 0, 0, 0, 0, 0, 0)
+
+launch_count = 0  # number of library kernels launched through this layer (bench bookkeeping)
+
+
+def load(build_if_missing: bool = True):
+    """Load ``_C.so`` (building it in-tree when absent).  Raises if that is impossible."""
+    global _loaded, _load_error
+    if _loaded:
+        return True
+    with _lock:
+        if _loaded:
+            return True
+        try:
+            if not _LIB_PATH.exists() and build_if_missing:
+                from ..build import build
+                build()
+            torch.ops.load_library(str(_LIB_PATH))
+            _loaded = True
+        except Exception as error:  # pragma: no cover - exercised only on broken installs
+            _load_error = error
+            raise RuntimeError(f"viola_b200: cannot load the sm_100a kernel library {_LIB_PATH}: {error}") from error
+    return True
+
+
+def _ops():
+    load()
+    return torch.ops.viola_b200
+
+
+def _count(n=1):
+    global launch_count
+    launch_count += n
+
+
+# ------------------------------------------------------------------------------ workspaces
+_scratch = {}
+_status = {}
+
+
+def _amax_scratch(device):
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    buffer = _scratch.get(key)
+    if buffer is None:
+        buffer = _scratch[key] = torch.zeros(2, device=device, dtype=torch.int32)
+    return buffer
+
+
+def status_word(device):
+    """Per-device int32[8] error word written by bounded waits inside the kernels."""
+    device = torch.device(device)
+    word = _status.get(device)
+    if word is None:
+        word = _status[device] = torch.zeros(8, device=device, dtype=torch.int32)
+    return word
+
+
+_STATUS_NAMES = {1: "wait for TMA data timed out", 2: "wait for a free smem stage timed out",
+                 3: "wait for the MMA commit timed out", 4: "wait for TMEM drain timed out",
+                 5: "wait on a peer flag timed out", 6: "wait on a gathered panel timed out", 7: "bad argument"}
+
+
+def check_status(device=None):
+    """Synchronising check of the kernel status words; raises with the recorded location."""
+    for dev, word in list(_status.items()):
+        if device is not None and torch.device(device) != dev:
+            continue
+        values = word.tolist()
+        if values[0]:
+            word.zero_()
+            raise RuntimeError(f"viola_b200 kernel reported: {_STATUS_NAMES.get(values[0], values[0])} "
+                               f"(block {values[1]}, warp {values[2]}, detail {values[3]}) on {dev}")
+
+
+def _limit(dtype, limit):
+    return reference.fp8_limit(dtype, limit)
+
+
+# ------------------------------------------------------------------------------ per-tensor scaling
+def tensor_scale(x, *, history=None, index=0, delayed=False, fp8_dtype=torch.float8_e4m3fn, quantization_limit=None):
+    if not x.is_cuda:
+        return reference.tensor_scale(x, history=history, index=index, delayed=delayed, fp8_dtype=fp8_dtype,
+                                      quantization_limit=quantization_limit)
+    scale = torch.empty(1, device=x.device, dtype=torch.float32)
+    _ops().amax_scale(x.detach().contiguous().view(-1), history, int(index), bool(delayed),
+                      _limit(fp8_dtype, quantization_limit), scale, _amax_scratch(x.device))
+    _count()
+    return scale
+
+
+def quantize(x, scale, *, rowwise=True, transpose=False, fp8_dtype=torch.float8_e4m3fn, out=None, out_t=None,
+             quantization_limit=None):
+    if not x.is_cuda:
+        return reference.quantize(x, scale, rowwise=rowwise, transpose=transpose, fp8_dtype=fp8_dtype, out=out,
+                                  out_t=out_t, quantization_limit=quantization_limit)
+    x = x.detach().contiguous()
+    empty = None
+    q = out if out is not None else (torch.empty(x.shape, device=x.device, dtype=fp8_dtype) if rowwise else None)
+    qt = out_t if out_t is not None else (
+        torch.empty(x.shape[::-1], device=x.device, dtype=fp8_dtype) if transpose else None)
+    if q is not None or qt is not None:
+        _ops().quantize(x, scale, _limit(fp8_dtype, quantization_limit), q, qt, _FMT[fp8_dtype])
+        _count()
+    if q is None or qt is None:
+        empty = torch.empty((0, 0), device=x.device, dtype=fp8_dtype)
+    return (q if q is not None else empty), (qt if qt is not None else empty)
+
+
+def transpose(q, out=None):
+    if not q.is_cuda:
+        return reference.transpose(q, out)
+    if out is None:
+        out = torch.empty(q.shape[::-1], device=q.device, dtype=q.dtype)
+    _ops().transpose_u8(q.contiguous(), out)
+    _count()
+    return out
+
+
+def _pad_k(t, multiple):
+    k = t.shape[1]
+    if k % multiple == 0 and t.stride(1) == 1 and (t.stride(0) * t.element_size()) % 16 == 0 \
+            and t.data_ptr() % 16 == 0:
+        return t
+    padded = torch.zeros((t.shape[0], (k + multiple - 1) // multiple * multiple), device=t.device, dtype=torch.uint8
+                         if t.element_size() == 1 else t.dtype)
+    if t.element_size() == 1:
+        padded[:, :k] = t.view(torch.uint8)
+        return padded.view(t.dtype)
+    padded[:, :k] = t
+    return padded
+
+
+def _gemm(a, b, out, epilogue, n_logical, *, sa=None, sb=None, layout=_NO_GROUP, bias=None, alpha=1.0, beta=0.0,
+          resid=None, out_t=None, symmetric=False, activation=0, aux=None, expert_offsets=None, tile_map=None,
+          force_bn=0):
+    multiple = 16 if a.element_size() == 1 else 8
+    a, b = _pad_k(a, multiple), _pad_k(b, multiple)
+    _ops().gemm(a, b, out, epilogue, n_logical, sa, sb, list(layout), bias, float(alpha), float(beta), resid, out_t,
+                bool(symmetric), int(activation), aux, expert_offsets, tile_map, status_word(a.device), int(force_bn))
+    _count(2 if expert_offsets is not None else 1)
+    return out
+
+
+def gemm(a, b, sa, sb, *, out_dtype, bias=None, out=None, force_bn=0):
+    """(a * sa) @ (b * sb).T (+ bias): FP8 or 16-bit operands with per-tensor fp32 scales."""
+    if not a.is_cuda:
+        result = reference.gemm(a, b, sa, sb, out_dtype=out_dtype, bias=bias)
+        return result if out is None else out.copy_(result)
+    if out is None:
+        out = torch.empty((a.shape[0], b.shape[0]), device=a.device, dtype=out_dtype)
+    return _gemm(a, b, out, EPI_LINEAR, b.shape[0], sa=sa, sb=sb, bias=bias, force_bn=force_bn)
+
+
+# ------------------------------------------------------------------------------ group scaling
+def _log2(v):
+    assert v > 0 and v & (v - 1) == 0, f"{v} is not a power of two"
+    return v.bit_length() - 1
+
+
+def group_quantize(x, dtype, group, *, limit=None, transposed=False, out=None, scale_out=None, kmajor=False):
+    """Encode ``x`` (or ``x.T`` when ``transposed``) with one fp32 scale per ``group`` block.
+
+    Scales come back as ``[ceil(R/gr), ceil(C/gc)]`` or, with ``kmajor``, as its transpose
+    (one contiguous row of scales per K-block: the layout the GEMM promotion loop reads).
+    """
+    if not x.is_cuda:
+        q, s = reference.group_quantize(x, dtype, group, limit=limit, transposed=transposed, out=out)
+        if kmajor:
+            s = s.t().contiguous()
+        if scale_out is not None:
+            s = scale_out.copy_(s)
+        return q, s
+    x = x.detach().contiguous()
+    shape = tuple(x.shape[::-1]) if transposed else tuple(x.shape)
+    nr, nc = scale_shape(shape, group)
+    q = out if out is not None else torch.empty(shape, device=x.device, dtype=dtype)
+    s = scale_out if scale_out is not None else torch.empty((nc, nr) if kmajor else (nr, nc), device=x.device,
+                                                            dtype=torch.float32)
+    s_row, s_col = (1, nr) if kmajor else (nc, 1)
+    gr, gc = group
+    if transposed:
+        _ops().group_encode(x, _FMT[dtype], _limit(dtype, limit), None, None, 1, 32, 0, 0, q, s, gr, gc, s_row, s_col)
+    else:
+        _ops().group_encode(x, _FMT[dtype], _limit(dtype, limit), q, s, gr, gc, s_row, s_col, None, None, 1, 32, 0, 0)
+    _count()
+    return q, s
+
+
+def group_quantize_pair(x, dtype, group, group_t, *, limit=None, kmajor=False):
+    """Rowwise and transposed encodings from one read of ``x``: returns (q, s, qt, st)."""
+    if not x.is_cuda or max(*group, *group_t) > 128:
+        q, s = group_quantize(x, dtype, group, limit=limit, kmajor=kmajor)
+        qt, st = group_quantize(x, dtype, group_t, limit=limit, transposed=True, kmajor=kmajor)
+        return q, s, qt, st
+    x = x.detach().contiguous()
+    rows, cols = x.shape
+    nr, nc = scale_shape((rows, cols), group)
+    tnr, tnc = scale_shape((cols, rows), group_t)
+    q = torch.empty((rows, cols), device=x.device, dtype=dtype)
+    qt = torch.empty((cols, rows), device=x.device, dtype=dtype)
+    s = torch.empty((nc, nr) if kmajor else (nr, nc), device=x.device, dtype=torch.float32)
+    st = torch.empty((tnc, tnr) if kmajor else (tnr, tnc), device=x.device, dtype=torch.float32)
+    s_row, s_col = (1, nr) if kmajor else (nc, 1)
+    st_row, st_col = (1, tnr) if kmajor else (tnc, 1)
+    # the 1x128 fast path only exists for the single-output call; the pair always uses the tile kernel
+    _ops().group_encode(x, _FMT[dtype], _limit(dtype, limit), q, s, group[0], group[1], s_row, s_col, qt, st,
+                        group_t[0], group_t[1], st_row, st_col)
+    _count()
+    return q, s, qt, st
+
+
+def group_dequantize(q, scale, group, *, kmajor=False):
+    if not q.is_cuda:
+        return reference.group_dequantize(q, scale.t() if kmajor else scale, group)
+    out = torch.empty(q.shape, device=q.device, dtype=torch.float32)
+    nr, nc = scale_shape(tuple(q.shape), group)
+    s_row, s_col = (1, nr) if kmajor else (nc, 1)
+    _ops().group_decode(q.contiguous(), scale.contiguous(), group[0], group[1], s_row, s_col, out)
+    _count()
+    return out
+
+
+def _group_layout(a, b_rows, k, ga, gb, sa_kmajor, sb_kmajor):
+    """scale_layout for the kernel, or None when the group shapes need the dequantise fallback."""
+    if ga[0] != 1 or ga[1] != gb[1] or ga[1] < 128:
+        return None
+    gk = ga[1]
+    nk = (k + gk - 1) // gk
+    m = a.shape[0]
+    nb = (b_rows + gb[0] - 1) // gb[0]
+    sa_row, sa_k = (1, m) if sa_kmajor else (nk, 1)
+    sb_row, sb_k = (1, nb) if sb_kmajor else (nk, 1)
+    return (1, sa_row, sa_k, sb_row, sb_k, _log2(gb[0]), _log2(gk // 128))
+
+
+def group_gemm(a, b, sa, sb, ga, gb, *, out_dtype, bias=None, sa_kmajor=False, sb_kmajor=False, out=None):
+    """Group-scaled FP8 GEMM: sum over K-groups of (A_g . B_g^T) * sa[row, g] * sb[col-block, g]."""
+    if not a.is_cuda:
+        result = reference.group_gemm(a, b, sa.t() if sa_kmajor else sa, sb.t() if sb_kmajor else sb, ga, gb,
+                                      out_dtype=out_dtype, bias=bias)
+        return result if out is None else out.copy_(result)
+    if out is None:
+        out = torch.empty((a.shape[0], b.shape[0]), device=a.device, dtype=out_dtype)
+    layout = _group_layout(a, b.shape[0], a.shape[1], ga, gb, sa_kmajor, sb_kmajor)
+    if layout is None:
+        # Group shapes the tcgen05 promotion loop does not cover (K-groups below 128 or multi-row
+        # activation groups): decode to bf16 and run the 16-bit tensor-core GEMM.
+        da = group_dequantize(a, sa, ga, kmajor=sa_kmajor).to(torch.bfloat16)
+        db = group_dequantize(b, sb, gb, kmajor=sb_kmajor).to(torch.bfloat16)
+        return _gemm(da, db, out, EPI_LINEAR, b.shape[0], bias=bias)
+    return _gemm(a, b, out, EPI_LINEAR, b.shape[0], sa=sa, sb=sb, layout=layout, bias=bias)
+
+
+# ------------------------------------------------------------------------------ fused gated MLP GEMMs
+def gated_gemm_forward(a, w, sa, sw, *, activation, out_dtype, bias=None, save=True, group=None, sa_kmajor=False,
+                       sw_kmajor=False):
+    """h = act(A.Wg^T) * (A.Wu^T) with W = [Wg; Wu] ([2H, K]); returns (h, aux=[g|u] or None)."""
+    hidden = w.shape[0] // 2
+    if not a.is_cuda:
+        if group is None:
+            z = reference.gemm(a, w, sa, sw, out_dtype=out_dtype, bias=bias)
+        else:
+            z = reference.group_gemm(a, w, sa.t() if sa_kmajor else sa, sw.t() if sw_kmajor else sw, group[0],
+                                     group[1], out_dtype=out_dtype, bias=bias)
+        return reference.gated_forward(z, activation), (z if save else None)
+    h = torch.empty((a.shape[0], hidden), device=a.device, dtype=out_dtype)
+    aux = torch.empty((a.shape[0], 2 * hidden), device=a.device, dtype=out_dtype) if save else None
+    layout = _NO_GROUP
+    if group is not None:
+        layout = _group_layout(a, w.shape[0], a.shape[1], group[0], group[1], sa_kmajor, sw_kmajor)
+        if layout is None or (layout[5] > 0 and hidden % (1 << layout[5])):
+            z = group_gemm(a, w, sa, sw, group[0], group[1], out_dtype=out_dtype, bias=bias, sa_kmajor=sa_kmajor,
+                           sb_kmajor=sw_kmajor)
+            return gated_forward(z, activation), (z if save else None)
+    _gemm(a, w, h, EPI_GATED_FWD, hidden, sa=sa, sb=sw, layout=layout, bias=bias, activation=_ACT[activation], aux=aux)
+    return h, aux
+
+
+def gated_gemm_backward(dy, wt, sg, st, aux, *, activation, out_dtype, group=None, sg_kmajor=False, st_kmajor=False):
+    """[dG | dU] from d = dY.Wdown (wt = Wdown^T, [H, out]) and the saved aux = [g | u]."""
+    hidden = wt.shape[0]
+    if not dy.is_cuda:
+        if group is None:
+            d = reference.gemm(dy, wt, sg, st, out_dtype=out_dtype)
+        else:
+            d = reference.group_gemm(dy, wt, sg.t() if sg_kmajor else sg, st.t() if st_kmajor else st, group[0],
+                                     group[1], out_dtype=out_dtype)
+        return reference.gated_backward(aux, d, activation)
+    out = torch.empty((dy.shape[0], 2 * hidden), device=dy.device, dtype=out_dtype)
+    layout = _NO_GROUP
+    if group is not None:
+        layout = _group_layout(dy, hidden, dy.shape[1], group[0], group[1], sg_kmajor, st_kmajor)
+        if layout is None:
+            d = group_gemm(dy, wt, sg, st, group[0], group[1], out_dtype=out_dtype, sa_kmajor=sg_kmajor,
+                           sb_kmajor=st_kmajor)
+            return gated_backward(aux, d, activation)
+    _gemm(dy, wt, out, EPI_GATED_BWD, hidden, sa=sg, sb=st, layout=layout, activation=_ACT[activation], aux=aux)
+    return out
+
+
+def gated_forward(gu, activation):
+    if not gu.is_cuda:
+        return reference.gated_forward(gu, activation)
+    gu = gu.contiguous()
+    out = torch.empty((*gu.shape[:-1], gu.shape[-1] // 2), device=gu.device, dtype=gu.dtype)
+    _ops().gated_forward(gu.view(-1, gu.shape[-1]), _ACT[activation], out)
+    _count()
+    return out
+
+
+def gated_backward(gu, dh, activation):
+    if not gu.is_cuda:
+        return reference.gated_backward(gu, dh, activation)
+    gu, dh = gu.contiguous(), dh.contiguous()
+    out = torch.empty_like(gu)
+    _ops().gated_backward(gu.view(-1, gu.shape[-1]), dh.view(-1, dh.shape[-1]), _ACT[activation], out)
+    _count()
+    return out
+
+
+# ------------------------------------------------------------------------------ expert (ragged-M) GEMM
+def expert_gemm(a, w, offsets, sa, sw, *, out_dtype, group=None, sa_kmajor=False, sw_kmajor=False, out=None):
+    """out[rows of expert e] = A[rows of e] . W[e]^T.  ``w`` is [E, N, K]; ``offsets`` int32 [E+1] on device."""
+    experts, n, k = w.shape
+    if not a.is_cuda:
+        result = torch.empty((a.shape[0], n), dtype=out_dtype)
+        bounds = offsets.tolist()
+        for e in range(experts):
+            lo, hi = bounds[e], bounds[e + 1]
+            if group is None:
+                result[lo:hi] = reference.gemm(a[lo:hi], w[e], sa, sw[e] if sw is not None and sw.numel() > 1 else sw,
+                                               out_dtype=out_dtype)
+            else:
+                sa_e = (sa.t() if sa_kmajor else sa)[lo:hi]
+                result[lo:hi] = reference.group_gemm(a[lo:hi], w[e], sa_e, sw[e], group[0], group[1],
+                                                     out_dtype=out_dtype)
+        return result if out is None else out.copy_(result)
+    if out is None:
+        out = torch.empty((a.shape[0], n), device=a.device, dtype=out_dtype)
+    tile_map = torch.empty(3 * ((a.shape[0] + 127) // 128 + experts), device=a.device, dtype=torch.int32)
+    w2 = w.reshape(experts * n, k)
+    layout = _NO_GROUP
+    if group is not None:
+        layout = _group_layout(a, experts * n, k, group[0], group[1], sa_kmajor, sw_kmajor)
+        assert layout is not None and n % group[1][0] == 0, "expert GEMM needs 1xK activation groups and N % block == 0"
+        sw = sw.reshape(-1, sw.shape[-1]) if not sw_kmajor else sw
+    return _gemm(a, w2, out, EPI_LINEAR, n, sa=sa, sb=sw, layout=layout, expert_offsets=offsets, tile_map=tile_map)
+
+
+# ------------------------------------------------------------------------------ Newton-Schulz GEMM
+def ns_gemm(a, b, *, out=None, alpha=1.0, beta=0.0, resid=None, out_t=None, symmetric=False, force_bn=0):
+    """out = alpha * round(a @ b.T) + beta * resid in the operands' 16-bit dtype."""
+    if not a.is_cuda:
+        acc = (a.float() @ b.float().t()).to(a.dtype).float()
+        result = (alpha * acc + (beta * resid.float() if resid is not None else 0.0)).to(a.dtype)
+        if out_t is not None:
+            out_t.copy_(result.t())
+        return result if out is None else out.copy_(result)
+    if out is None:
+        out = torch.empty((a.shape[0], b.shape[0]), device=a.device, dtype=a.dtype)
+    return _gemm(a, b, out, EPI_AXPBY, b.shape[0], alpha=alpha, beta=beta, resid=resid, out_t=out_t,
+                 symmetric=symmetric, force_bn=force_bn)
+
+
+def sumsq(x, round_dtype, accum):
+    code = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}[round_dtype]
+    _ops().sumsq(x.contiguous().view(-1), code, accum)
+    _count()
+
+
+def ns_prescale(x, sumsq_t, *, out=None, out_t=None, eps=1e-7):
+    _ops().ns_prescale(x.contiguous(), sumsq_t, eps, out, out_t)
+    _count()
+
+
+# ------------------------------------------------------------------------------ optimizer kernels
+def momentum_dequantize(q, scales, shape, **quant):
+    return reference.momentum_dequantize(q, scales, shape, **quant)
+
+
+def momentum_update(grad, q, scales, next_q, next_scales, out, *, beta, tile_size=256, nesterov=True, loss_scale=1.0,
+                    granularity="tile", block_shape=(16, 16), matrix_shape=None, rounding="nearest", rounding_step=0,
+                    rounding_key=0):
+    if not grad.is_cuda:
+        return reference.momentum_update(grad, q, scales, next_q, next_scales, out, beta=beta, tile_size=tile_size,
+                                         nesterov=nesterov, loss_scale=loss_scale, granularity=granularity,
+                                         block_shape=block_shape, matrix_shape=matrix_shape, rounding=rounding,
+                                         rounding_step=rounding_step, rounding_key=rounding_key)
+    flat = grad.detach().reshape(-1)
+    if not flat.is_contiguous():
+        flat = flat.contiguous()
+    key = int(rounding_key) & ((1 << 63) - 1)
+    if granularity == "tile":
+        _ops().momentum_1d(flat, q, scales, next_q, next_scales, out, int(tile_size), float(beta),
+                           1.0 / float(loss_scale), bool(nesterov), rounding == "stochastic", int(rounding_step), key)
+    else:
+        rows, cols = matrix_shape[-2:]
+        _ops().momentum_2d(flat, math.prod(matrix_shape[:-2]), rows, cols, q, scales, next_q, next_scales, out,
+                           int(block_shape[0]), int(block_shape[1]), float(beta), 1.0 / float(loss_scale),
+                           bool(nesterov), rounding == "stochastic", int(rounding_step), key)
+    _count()
+
+
+def weight_update(weight, update, lr, weight_decay, *, update_scale=1.0, rounding="nearest", step=0, key=0, offset=0):
+    if not weight.is_cuda:
+        return reference.weight_update(weight, update, lr, weight_decay, update_scale=update_scale, rounding=rounding,
+                                       step=step, key=key, offset=offset)
+    _ops().weight_update(weight.detach().view(-1), update.detach().reshape(-1).contiguous(), float(lr),
+                         float(weight_decay), float(update_scale), rounding == "stochastic", int(step),
+                         int(key) & ((1 << 63) - 1), int(offset))
+    _count()
+
+
+def adam_update(weight, grad, first, second, *, lr, weight_decay, betas, eps, step, rounding="nearest", key=0,
+                offset=0, adamw=True, maximize=False, bias_correction=True):
+    if not weight.is_cuda:
+        return reference.adam_update(weight, grad, first, second, lr=lr, weight_decay=weight_decay, betas=betas,
+                                     eps=eps, step=step, rounding=rounding, key=key, offset=offset, adamw=adamw,
+                                     maximize=maximize, bias_correction=bias_correction)
+    b1, b2 = betas
+    inv_c1 = 1.0 / (1.0 - b1 ** step) if bias_correction else 1.0
+    inv_c2 = 1.0 / (1.0 - b2 ** step) if bias_correction else 1.0
+    _ops().adam_update(weight.detach().view(-1), grad.detach().reshape(-1).contiguous(), first.view(-1),
+                       second.view(-1), float(lr), float(weight_decay), float(b1), float(b2), inv_c1, inv_c2,
+                       float(eps), bool(adamw), bool(maximize), rounding == "stochastic", int(step - 1),
+                       int(key) & ((1 << 63) - 1), int(offset))
+    _count()
+
+
+def copy_scaled(update, partition, src, dst, count, scale):
+    if not update.is_cuda:
+        return reference.copy_scaled(update, partition, src, dst, count, scale)
+    _ops().copy_scaled(update.contiguous().view(-1), partition.view(-1), int(src), int(dst), int(count), float(scale))
+    _count()
+
+
+def momentum16(grad, momentum, out, beta, nesterov=True):
+    if not grad.is_cuda:
+        return reference.momentum16(grad, momentum, out, beta, nesterov)
+    _ops().momentum16(grad.detach().reshape(-1).contiguous(), momentum.view(-1), out, float(beta), bool(nesterov))
+    _count()
+
+
+def ema_lerp(ema, master, decay):
+    if not ema.is_cuda:
+        return reference.ema_lerp(ema, master, decay)
+    _ops().ema_lerp(ema.view(-1), master.detach().reshape(-1).contiguous(), float(decay))
+    _count()
+
+
+def philox(element, step, key, count=1, device=None):
+    """``count`` consecutive Philox words starting at ``element`` (device kernel on CUDA, NumPy on CPU)."""
+    if device is None or torch.device(device).type != "cuda":
+        import numpy as np
+        return torch.from_numpy(reference.philox(np.arange(element, element + count, dtype=np.uint64), step, key)
+                                .astype("int64"))
+    out = torch.empty(count, device=device, dtype=torch.int32)
+    _ops().philox_kat(int(element), int(step), int(key), out)
+    _count()
+    return out.to(torch.int64) & 0xFFFFFFFF
+
+
+def hadamard64(x, out=None):
+    if not x.is_cuda:
+        result = reference.hadamard64(x)
+        return result if out is None else out.copy_(result)
+    x = x.contiguous()
+    out = torch.empty_like(x) if out is None else out
+    _ops().hadamard64(x, out)
+    _count()
+    return out
+
+
+# ------------------------------------------------------------------------------ wire codec
+def wire_pack(source, packet, tile_size, fp8_dtype):
+    if not source.is_cuda:
+        return reference.wire_pack(source, packet, tile_size, fp8_dtype)
+    rows = packet.shape[0]
+    groups = packet.shape[1] // (tile_size + 4)
+    _ops().wire_pack(source.contiguous().view(-1), rows, groups, int(tile_size), _FMT[fp8_dtype], packet,
+                     packet.stride(0))
+    _count()
+
+
+def wire_unpack(packet, out, tile_size, fp8_dtype, *, reduce=False, accumulate=False):
+    if not out.is_cuda:
+        return reference.wire_unpack(packet, out, tile_size, fp8_dtype, reduce=reduce, accumulate=accumulate)
+    rows = packet.shape[0]
+    groups = packet.shape[1] // (tile_size + 4)
+    _ops().wire_unpack(packet, packet.stride(0), rows, groups, int(tile_size), _FMT[fp8_dtype], bool(reduce),
+                       out.view(-1), bool(accumulate))
+    _count()

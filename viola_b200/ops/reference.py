@@ -1,0 +1,436 @@
+"""Plain PyTorch / NumPy restatements of every device kernel.
+
+These serve three purposes: (1) the oracle the GPU numerics tests compare against, (2) the CPU
+execution path of the library (module construction, Gloo plumbing tests, checkpoints), and (3)
+documentation of the arithmetic contract.  Nothing here is performance-sensitive.
+
+Arithmetic follows the reference implementation: scale = max(amax, 1e-30) / limit and
+codes = clamp(x / scale, +-limit) with NaN preserved (viola/nn/_linear_kernels.py:49-104),
+group encode (viola/nn/_grouped_kernels.py:135-151), momentum / weight / Adam updates
+(viola/optim/_kernels.py:88-293), Philox4x32-10 and the stochastic-rounding grids
+(viola/optim/_kernels.py:12-58), the wire codec (viola/distributed/_fp8_kernels.py:18-69), the
+gated activations (viola/nn/_gated_kernels.py:16-67), Hadamard-64 (viola/nn/_rotation_kernels.py:11-25,
+126-130) and the two Newton-Schulz recurrences (viola/optim/_orthogonalize.py:10-54).
+"""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+FP8_MAX = {torch.float8_e4m3fn: 448.0, torch.float8_e5m2: 57344.0}
+
+
+def fp8_limit(dtype, limit=None):
+    return FP8_MAX[dtype] if limit is None else float(limit)
+
+
+# --------------------------------------------------------------------------- per-tensor scaling
+def tensor_scale(x, *, history=None, index=0, delayed=False, fp8_dtype=torch.float8_e4m3fn,
+                 quantization_limit=None):
+    limit = fp8_limit(fp8_dtype, quantization_limit)
+    amax = x.detach().float().abs().max() if x.numel() else x.new_zeros((), dtype=torch.float32)
+    chosen = amax
+    if history is not None:
+        if delayed and index != 0:
+            chosen = history.max()
+        history[index % history.numel()] = amax
+    return (chosen.clamp_min(1e-30) / limit).reshape(1).to(torch.float32)
+
+
+def _encode(value, scale, limit, dtype):
+    q = value / scale
+    q = torch.where(torch.isnan(q), q, q.clamp(-limit, limit))
+    return q.to(dtype)
+
+
+def quantize(x, scale, *, rowwise=True, transpose=False, fp8_dtype=torch.float8_e4m3fn, out=None, out_t=None,
+             quantization_limit=None):
+    limit = fp8_limit(fp8_dtype, quantization_limit)
+    codes = _encode(x.detach().float(), scale.float(), limit, fp8_dtype)
+    q = qt = None
+    if rowwise:
+        q = codes if out is None else out.copy_(codes)
+    if transpose:
+        qt = codes.t().contiguous() if out_t is None else out_t.copy_(codes.t())
+    empty = x.new_empty((0, 0), dtype=fp8_dtype)
+    return (q if q is not None else empty), (qt if qt is not None else empty)
+
+
+def transpose(q, out=None):
+    result = q.t().contiguous()
+    return result if out is None else out.copy_(result)
+
+
+def gemm(a, b, sa, sb, *, out_dtype, bias=None):
+    """(a * sa) @ (b * sb).T + bias, accumulated in fp32."""
+    acc = a.float() @ b.float().t()
+    alpha = (sa.float() if sa is not None else 1.0) * (sb.float() if sb is not None else 1.0)
+    acc = acc * alpha
+    if bias is not None:
+        acc = acc + bias.float()
+    return acc.to(out_dtype)
+
+
+# --------------------------------------------------------------------------- group scaling
+def scale_shape(shape, group):
+    return tuple((n + g - 1) // g for n, g in zip(shape, group))
+
+
+def group_quantize(x, dtype, group, *, limit=None, transposed=False, out=None, scale_out=None):
+    limit = fp8_limit(dtype, limit)
+    value = x.detach().float()
+    value = value.t() if transposed else value
+    shape = tuple(value.shape)
+    gr, gc = group
+    nr, nc = scale_shape(shape, group)
+    blocks = F.pad(value, (0, nc * gc - shape[1], 0, nr * gr - shape[0])).reshape(nr, gr, nc, gc)
+    magnitude = torch.where(torch.isnan(blocks), torch.full_like(blocks, float("inf")), blocks.abs())
+    scales = magnitude.amax((1, 3)).clamp_min(1e-30) / limit
+    codes = blocks / scales[:, None, :, None]
+    codes = torch.where(torch.isnan(codes), codes, codes.clamp(-limit, limit))
+    codes = codes.reshape(nr * gr, nc * gc)[:shape[0], :shape[1]].to(dtype)
+    q = codes.contiguous() if out is None else out.copy_(codes)
+    s = scales.contiguous() if scale_out is None else scale_out.copy_(scales)
+    return q, s
+
+
+def group_dequantize(q, scale, group):
+    expanded = scale.float().repeat_interleave(group[0], 0).repeat_interleave(group[1], 1)
+    return q.float() * expanded[:q.shape[0], :q.shape[1]]
+
+
+def group_gemm(a, b, sa, sb, ga, gb, *, out_dtype, bias=None):
+    acc = group_dequantize(a, sa, ga) @ group_dequantize(b, sb, gb).t()
+    if bias is not None:
+        acc = acc + bias.float()
+    return acc.to(out_dtype)
+
+
+# --------------------------------------------------------------------------- gated activations
+def activation(g, name):
+    if name == "silu":
+        return g / (1.0 + torch.exp(-g))
+    if name == "relu":
+        return g.clamp_min(0.0)
+    return 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g * g * g)))
+
+
+def activation_grad(g, name):
+    if name == "silu":
+        s = 1.0 / (1.0 + torch.exp(-g))
+        return s * (1.0 + g * (1.0 - s))
+    if name == "relu":
+        return (g > 0).to(g.dtype)
+    k0, k1 = 0.7978845608028654, 0.044715
+    t = torch.tanh(k0 * (g + k1 * g * g * g))
+    return 0.5 * (1.0 + t) + 0.5 * g * (1.0 - t * t) * k0 * (1.0 + 3.0 * k1 * g * g)
+
+
+def gated_forward(gu, name):
+    hidden = gu.shape[-1] // 2
+    g, u = gu[..., :hidden].float(), gu[..., hidden:].float()
+    return (activation(g, name) * u).to(gu.dtype)
+
+
+def gated_backward(gu, dh, name):
+    hidden = gu.shape[-1] // 2
+    g, u, d = gu[..., :hidden].float(), gu[..., hidden:].float(), dh.float()
+    return torch.cat((d * u * activation_grad(g, name), d * activation(g, name)), dim=-1).to(gu.dtype)
+
+
+# --------------------------------------------------------------------------- Hadamard-64
+def _h4():
+    return (torch.ones(4, 4) - 2 * torch.flip(torch.eye(4), dims=(1,))) / 2
+
+
+def hadamard64_matrix(dtype=torch.float32):
+    h4 = _h4()
+    return torch.kron(torch.kron(h4, h4), h4).to(dtype)
+
+
+def hadamard64(x):
+    """Rotate every 64-wide group of the last dimension by the regular (symmetric, self-inverse) H64."""
+    shape = x.shape
+    value = x.detach().float().reshape(-1, shape[-1] // 64, 64)
+    return (value @ hadamard64_matrix().to(value.device)).reshape(shape).to(x.dtype)
+
+
+# --------------------------------------------------------------------------- Philox / stochastic rounding
+_M0, _M1 = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57)
+_MASK32 = np.uint64(0xFFFFFFFF)
+
+
+def philox(element, step, key):
+    """Philox4x32-10 first output word; ``element`` may be an array (uint64)."""
+    element = np.asarray(element, dtype=np.uint64)
+    step = np.uint64(int(step) & 0xFFFFFFFFFFFFFFFF)
+    key = np.uint64(int(key) & 0xFFFFFFFFFFFFFFFF)
+    a = element & _MASK32
+    b = element >> np.uint64(32)
+    c = np.full_like(a, step & _MASK32)
+    d = np.full_like(a, step >> np.uint64(32))
+    k0 = np.uint64(key & _MASK32)
+    k1 = np.uint64(key >> np.uint64(32))
+    for _ in range(10):
+        p0 = _M0 * a
+        p1 = _M1 * c
+        lo0, hi0 = p0 & _MASK32, p0 >> np.uint64(32)
+        lo1, hi1 = p1 & _MASK32, p1 >> np.uint64(32)
+        a, b, c, d = hi1 ^ b ^ k0, lo1, hi0 ^ d ^ k1, lo0
+        k0 = (k0 + np.uint64(0x9E3779B9)) & _MASK32
+        k1 = (k1 + np.uint64(0xBB67AE85)) & _MASK32
+    return a.astype(np.uint32)
+
+
+def _uniform(elements, step, key):
+    return (philox(elements, step, key) >> np.uint32(8)).astype(np.float32) * np.float32(2.0 ** -24)
+
+
+def _stochastic_grid(x, elements, step, key, mantissa, min_exponent):
+    value = x.detach().float().cpu().numpy().astype(np.float32)
+    flat = value.reshape(-1)
+    a = np.abs(flat)
+    exponent = ((a.view(np.uint32) >> np.uint32(23)) & np.uint32(255)).astype(np.int32) - 127
+    spacing = np.exp2(np.maximum(exponent - mantissa, min_exponent).astype(np.float32)).astype(np.float32)
+    with np.errstate(invalid="ignore", divide="ignore"):
+        lower = (np.floor(a / spacing) * spacing).astype(np.float32)
+        probability = ((a - lower) / spacing).astype(np.float32)
+    uniform = _uniform(elements, step, key)
+    rounded = np.copysign(lower + np.where(uniform < probability, spacing, np.float32(0)), flat).astype(np.float32)
+    rounded = np.where(np.isfinite(flat), rounded, flat)
+    return torch.from_numpy(rounded.reshape(value.shape)).to(x.device)
+
+
+def stochastic_e4m3(x, elements, step, key):
+    return _stochastic_grid(x, elements, step, key, 3, -9)
+
+
+def stochastic_fp16(x, elements, step, key):
+    rounded = _stochastic_grid(x, elements, step, key, 10, -24)
+    return torch.where(x.float().abs() > 65504.0, x.float(), rounded)
+
+
+def stochastic_bf16(x, elements, step, key):
+    value = x.detach().float().cpu().numpy().astype(np.float32).reshape(-1)
+    bits = value.view(np.uint32).astype(np.uint64)
+    noise = (philox(elements, step, key) >> np.uint32(16)).astype(np.uint64)
+    rounded = ((bits + noise) & np.uint64(0xFFFF0000)).astype(np.uint32).view(np.float32)
+    rounded = np.where(np.isfinite(value), rounded, value)
+    return torch.from_numpy(rounded.reshape(x.shape).copy()).to(x.device)
+
+
+def _round_store(value, dtype, rounding, elements, step, key):
+    if rounding == "stochastic" and dtype == torch.bfloat16:
+        return stochastic_bf16(value, elements, step, key).to(dtype)
+    if rounding == "stochastic" and dtype == torch.float16:
+        return stochastic_fp16(value, elements, step, key).to(dtype)
+    return value.to(dtype)
+
+
+# --------------------------------------------------------------------------- optimizer kernels
+def state_sizes(shape, *, granularity="tile", tile_size=256, block_shape=(16, 16)):
+    n = math.prod(shape)
+    if granularity == "tile":
+        blocks = (n + tile_size - 1) // tile_size
+        return blocks * tile_size, blocks
+    rows, cols = shape[-2:]
+    tr, tc = block_shape
+    tiles = (rows + tr - 1) // tr * ((cols + tc - 1) // tc)
+    return n, math.prod(shape[:-2]) * tiles
+
+
+def momentum_dequantize(q, scales, shape, *, granularity="tile", tile_size=256, block_shape=(16, 16)):
+    n = math.prod(shape)
+    codes = q.view(torch.float8_e4m3fn).float()
+    if granularity == "tile":
+        return (codes.view(-1, tile_size) * scales[:, None]).flatten()[:n]
+    rows, cols = shape[-2:]
+    tr, tc = block_shape
+    expanded = scales.view(-1, (rows + tr - 1) // tr, (cols + tc - 1) // tc)
+    expanded = expanded.repeat_interleave(tr, 1).repeat_interleave(tc, 2)[:, :rows, :cols]
+    return (codes.view(-1, rows, cols) * expanded).flatten()
+
+
+def momentum_update(grad, q, scales, next_q, next_scales, out, *, beta, tile_size=256, nesterov=True, loss_scale=1.0,
+                    granularity="tile", block_shape=(16, 16), matrix_shape=None, rounding="nearest", rounding_step=0,
+                    rounding_key=0):
+    """In-place on ``next_q`` / ``next_scales`` / ``out`` (bf16 Newton-Schulz input)."""
+    n = grad.numel()
+    beta = np.float32(beta)
+    g = grad.detach().reshape(-1).float() * np.float32(1.0 / float(loss_scale))
+    shape = (n,) if matrix_shape is None else tuple(matrix_shape)
+    old = momentum_dequantize(q, scales, shape, granularity=granularity, tile_size=tile_size, block_shape=block_shape)
+    m = float(beta) * old + float(np.float32(1.0) - beta) * g
+    update = float(np.float32(1.0) - beta) * g + float(beta) * m if nesterov else m
+    out.reshape(-1)[:n].copy_(update.to(torch.bfloat16))
+    if granularity == "tile":
+        blocks = (n + tile_size - 1) // tile_size
+        padded = F.pad(m, (0, blocks * tile_size - n)).view(blocks, tile_size)
+        scale = padded.abs().amax(1).clamp_min(1e-30) / 448.0
+        codes = padded / scale[:, None]
+        codes = torch.where(torch.isnan(codes), codes, codes.clamp(-448.0, 448.0)).flatten()
+        if rounding == "stochastic":
+            codes = stochastic_e4m3(codes, np.arange(codes.numel(), dtype=np.uint64), rounding_step, rounding_key)
+        next_q.view(torch.float8_e4m3fn).copy_(codes.to(torch.float8_e4m3fn))
+        next_scales.copy_(scale)
+        return
+    rows, cols = shape[-2:]
+    planes = n // (rows * cols)
+    tr, tc = block_shape
+    nr, nc = (rows + tr - 1) // tr, (cols + tc - 1) // tc
+    value = F.pad(m.view(planes, rows, cols), (0, nc * tc - cols, 0, nr * tr - rows)).view(planes, nr, tr, nc, tc)
+    scale = value.abs().amax((2, 4)).clamp_min(1e-30) / 448.0
+    codes = value / scale[:, :, None, :, None]
+    codes = torch.where(torch.isnan(codes), codes, codes.clamp(-448.0, 448.0))
+    codes = codes.reshape(planes, nr * tr, nc * tc)[:, :rows, :cols].reshape(-1)
+    if rounding == "stochastic":
+        codes = stochastic_e4m3(codes, np.arange(n, dtype=np.uint64), rounding_step, rounding_key)
+    next_q.view(torch.float8_e4m3fn).copy_(codes.to(torch.float8_e4m3fn))
+    next_scales.copy_(scale.reshape(-1))
+
+
+def weight_update(weight, update, lr, weight_decay, *, update_scale=1.0, rounding="nearest", step=0, key=0, offset=0):
+    lr32, wd32, us32 = np.float32(lr), np.float32(weight_decay), np.float32(update_scale)
+    keep = float(np.float32(1.0) - lr32 * wd32)
+    rate = float(lr32 * us32)
+    value = weight.detach().float() * keep - rate * update.detach().reshape(weight.shape).float()
+    elements = np.arange(weight.numel(), dtype=np.uint64) + np.uint64(offset)
+    weight.copy_(_round_store(value, weight.dtype, rounding, elements, step, key))
+
+
+def adam_update(weight, grad, first, second, *, lr, weight_decay, betas, eps, step, rounding="nearest", key=0,
+                offset=0, adamw=True, maximize=False, bias_correction=True):
+    b1, b2 = (float(np.float32(b)) for b in betas)
+    lr, decay, eps = float(np.float32(lr)), float(np.float32(weight_decay)), float(np.float32(eps))
+    inv_c1 = float(np.float32(1.0 / (1.0 - betas[0] ** step))) if bias_correction else 1.0
+    inv_c2 = float(np.float32(1.0 / (1.0 - betas[1] ** step))) if bias_correction else 1.0
+    w = weight.detach().float()
+    g = grad.detach().reshape(weight.shape).float()
+    if maximize:
+        g = -g
+    if not adamw:
+        g = g + decay * w
+    m = b1 * first.float() + float(np.float32(1.0) - np.float32(b1)) * g
+    v = b2 * second.float() + float(np.float32(1.0) - np.float32(b2)) * g * g
+    first.copy_(m.to(first.dtype))
+    second.copy_(v.to(second.dtype))
+    if adamw:
+        w = w * float(np.float32(1.0) - np.float32(lr) * np.float32(decay))
+    value = w - lr * (m * inv_c1) / (torch.sqrt(v * inv_c2) + eps)
+    elements = np.arange(weight.numel(), dtype=np.uint64) + np.uint64(offset)
+    weight.copy_(_round_store(value, weight.dtype, rounding, elements, step - 1, key))
+
+
+def copy_scaled(update, partition, src, dst, count, scale):
+    flat = update.contiguous().view(-1)
+    partition.view(-1)[dst:dst + count].copy_((flat[src:src + count].float() * scale).to(partition.dtype))
+
+
+def momentum16(grad, momentum, out, beta, nesterov=True):
+    g = grad.detach().reshape(-1).float()
+    fresh = beta * momentum.reshape(-1).float() + (1.0 - beta) * g
+    out.reshape(-1)[:g.numel()].copy_(((1.0 - beta) * g + beta * fresh if nesterov else fresh).to(out.dtype))
+    momentum.reshape(-1).copy_(fresh.to(momentum.dtype))
+
+
+def ema_lerp(ema, master, decay):
+    ema.mul_(decay).add_(master.to(ema.dtype), alpha=1 - decay)
+
+
+# --------------------------------------------------------------------------- Newton-Schulz
+def ns_standard(matrix, steps=5, dtype=torch.bfloat16):
+    transposed = matrix.shape[-2] > matrix.shape[-1]
+    x = matrix.to(dtype)
+    if transposed:
+        x = x.mT
+    x = (x.float() / (x.float().norm(dim=(-2, -1), keepdim=True) + 1e-7)).to(dtype)
+    for _ in range(steps):
+        gram = (x.float() @ x.float().mT).to(dtype)
+        polynomial = (-4.7750 * gram.float() + 2.0315 * (gram.float() @ gram.float()).to(dtype).float()).to(dtype)
+        x = (3.4445 * x.float() + (polynomial.float() @ x.float()).to(dtype).float()).to(dtype)
+    return x.mT if transposed else x
+
+
+def ns_gram(matrix, steps=5):
+    dtype = torch.float16
+    transposed = matrix.shape[-2] > matrix.shape[-1]
+    x = matrix.to(dtype)
+    if transposed:
+        x = x.mT
+    x = (x.float() / (x.float().norm(dim=(-2, -1), keepdim=True) + 1e-7)).to(dtype)
+
+    def mm(a, b):
+        return (a.float() @ b.float()).to(dtype)
+
+    if x.shape[-2] == x.shape[-1]:
+        for _ in range(steps):
+            r = mm(x, x.mT)
+            x = (3.4445 * x.float() + mm((-4.7750 * r.float() + 2.0315 * mm(r, r).float()).to(dtype), x).float()).to(dtype)
+    else:
+        for length in (min(steps, 2), max(steps - 2, 0)):
+            if not length:
+                continue
+            r = mm(x, x.mT)
+            q = None
+            for i in range(length):
+                z = (-4.7750 * r.float() + 2.0315 * mm(r, r).float()).to(dtype)
+                if i == 0:
+                    q = z.clone()
+                    q.diagonal(dim1=-2, dim2=-1).add_(3.4445)
+                else:
+                    q = (3.4445 * q.float() + mm(z, q).float()).to(dtype)
+                if i + 1 < length:
+                    rz = (3.4445 * r.float() + mm(z, r).float()).to(dtype)
+                    r = (3.4445 * rz.float() + mm(z, rz).float()).to(dtype)
+            x = mm(q, x)
+    return x.mT if transposed else x
+
+
+# --------------------------------------------------------------------------- wire codec
+def packet_bytes(groups, tile_size):
+    return (groups * (tile_size + 4) + 15) // 16 * 16
+
+
+def packet_views(packet, tile_size, fp8_dtype):
+    groups = packet.shape[1] // (tile_size + 4)
+    width = groups * tile_size
+    codes = packet[:, :width].view(fp8_dtype)
+    scales = packet[:, width:width + groups * 4].view(torch.float32)
+    return codes, scales
+
+
+def wire_pack(source, packet, tile_size, fp8_dtype):
+    codes, scales = packet_views(packet, tile_size, fp8_dtype)
+    rows, groups = scales.shape
+    width = groups * tile_size
+    value = F.pad(source.detach().reshape(-1).float(), (0, max(0, rows * width - source.numel())))[:rows * width]
+    value = value.view(rows, groups, tile_size)
+    magnitude = torch.where(torch.isnan(value), torch.full_like(value, float("inf")), value.abs())
+    scale = magnitude.amax(-1).clamp_min(1e-30) / FP8_MAX[fp8_dtype]
+    limit = FP8_MAX[fp8_dtype]
+    q = value / scale[..., None]
+    q = torch.where(torch.isnan(q), q, q.clamp(-limit, limit))
+    codes.copy_(q.view(rows, width).to(fp8_dtype))
+    scales.copy_(scale)
+
+
+def wire_unpack(packet, out, tile_size, fp8_dtype, *, reduce=False, accumulate=False):
+    codes, scales = packet_views(packet, tile_size, fp8_dtype)
+    rows, groups = scales.shape
+    value = codes.float().view(rows, groups, tile_size) * scales[..., None]
+    if reduce:
+        total = torch.zeros(groups * tile_size, dtype=torch.float32, device=packet.device)
+        for rank in range(rows):
+            total = total + value[rank].reshape(-1)
+        flat = total
+    else:
+        flat = value.reshape(-1)
+    flat = flat[:out.numel()]
+    if accumulate:
+        out.view(-1).add_(flat)
+    else:
+        out.view(-1).copy_(flat)

@@ -1,0 +1,576 @@
+"""FP8 Linear layer: FP8 / BF16 / FP16 weight storage, FP8 tensor-core forward, dgrad and wgrad.
+
+Public surface and semantics follow the reference layer (viola/nn/linear.py:150-412, grouped
+recipe viola/nn/_grouped_linear.py:10-102): constructor options, parameter / buffer names
+(``weight``, ``bias``, ``weight_scale``, the three quantizers' ``history`` + extra state), the
+``refresh_weight`` / ``dequantize_weight`` / ``from_float`` / ``rebuild_weight_cache`` methods and
+the memory / fast modes.  The implementation is different: one functional core
+(:func:`linear_forward` / :func:`linear_backward`) drives the sm_100a kernels in
+:mod:`viola_b200.ops` (tcgen05 GEMMs with TMEM accumulators, fused amax->scale, one-read
+rowwise+transposed quantisers) and is shared with the fused gated MLP.
+
+Scaling recipes: ``current`` / ``delayed`` = one fp32 scale per tensor; ``grouped`` = one fp32 scale
+per (rows x cols) group, K-groups of 128 and wider run the two-level-accumulation tcgen05 kernel,
+other shapes decode to bf16 first; ``mxfp8`` = power-of-two (UE8M0-representable) group scales.
+The accumulator is always fp32 in tensor memory; ``accum_dtype='fp16'`` only keeps its documented
+effect on the quantisation range (``_quantization_limit``).
+"""
+
+from __future__ import annotations
+
+import math
+from types import SimpleNamespace
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..precision import settings
+
+_FORMATS = {"e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
+_STORAGE = {"bf16": torch.bfloat16, "fp16": torch.float16}
+_SAVED = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
+
+
+class _Quantizer(nn.Module):
+    """Amax history ring for delayed scaling plus the running call index (checkpointed)."""
+
+    def __init__(self, scaling, history_len, device):
+        super().__init__()
+        self.scaling = scaling
+        self.index = 0
+        self.register_buffer("history", torch.zeros(history_len, device=device, dtype=torch.float32))
+
+    def scale(self, x, fp8_dtype=torch.float8_e4m3fn, quantization_limit=None):
+        result = ops.tensor_scale(x, history=self.history, index=self.index, delayed=self.scaling == "delayed",
+                                  fp8_dtype=fp8_dtype, quantization_limit=quantization_limit)
+        self.index += 1
+        return result
+
+    def get_extra_state(self):
+        return {"index": self.index, "scaling": self.scaling}
+
+    def set_extra_state(self, state):
+        self.index, self.scaling = state["index"], state["scaling"]
+
+
+def transpose_group(group):
+    """Group shape seen from the transposed matrix: 2-D blocks flip, 1-D row groups stay 1-D."""
+    return tuple(group[::-1]) if group[0] >= 32 else tuple(group)
+
+
+def _pow2_scales(scale):
+    return torch.exp2(torch.ceil(torch.log2(scale)))
+
+
+# ------------------------------------------------------------------------------------------------
+# quantisation helpers (activation side)
+# ------------------------------------------------------------------------------------------------
+def _quantize_activation(layer, x, fmt, group, quantizer, limit, *, row, transposed, scale=None):
+    """Returns SimpleNamespace(q, s, qt, st).  Per-tensor recipes share one scale for both layouts."""
+    result = SimpleNamespace(q=None, s=None, qt=None, st=None)
+    if layer._grouped_scaling:
+        if row and transposed:
+            result.q, result.s, result.qt, result.st = ops.group_quantize_pair(x, fmt, group, group, limit=limit,
+                                                                               kmajor=True)
+        elif row:
+            result.q, result.s = ops.group_quantize(x, fmt, group, limit=limit, kmajor=True)
+        elif transposed:
+            result.qt, result.st = ops.group_quantize(x, fmt, group, limit=limit, transposed=True, kmajor=True)
+        if layer._native_scaling:
+            _requantize_pow2(layer, x, fmt, group, limit, result)
+        return result
+    if layer.rotation_size:
+        x = ops.hadamard64(x)
+    if scale is None:
+        scale = quantizer.scale(x, fmt, limit)
+    q, qt = ops.quantize(x, scale, rowwise=row, transpose=transposed, fp8_dtype=fmt, quantization_limit=limit)
+    result.q = q if row else None
+    result.qt = qt if transposed else None
+    result.s = result.st = scale
+    return result
+
+
+def _requantize_pow2(layer, x, fmt, group, limit, result):
+    """MXFP8 recipe: round every group scale up to a power of two and re-encode with it."""
+    limit_value = ops.reference.fp8_limit(fmt, limit)
+    value = x.detach().float()
+    for transposed, q_name, s_name in ((False, "q", "s"), (True, "qt", "st")):
+        scale = getattr(result, s_name)
+        if scale is None:
+            continue
+        source = value.t() if transposed else value
+        pow2 = _pow2_scales(scale.t())            # scales are K-block-major: back to [rows/gr, cols/gc]
+        expanded = pow2.repeat_interleave(group[0], 0).repeat_interleave(group[1], 1)[:source.shape[0], :source.shape[1]]
+        codes = source / expanded
+        codes = torch.where(torch.isnan(codes), codes, codes.clamp(-limit_value, limit_value)).to(fmt)
+        setattr(result, q_name, codes.contiguous())
+        setattr(result, s_name, pow2.t().contiguous())
+
+
+def _weight_operands(layer, weight, *, need_transpose):
+    """FP8 codes + scales of W (and W^T when asked) for this call, from whatever storage W uses."""
+    fmt = layer.fp8_dtype
+    out = SimpleNamespace(q=None, s=None, qt=None, st=None)
+    if layer._grouped_scaling:
+        gw = layer.weight_group_shape
+        limit = layer._group_limit(gw, fmt, weight=True)
+        if layer.weight_dtype == "fp8":
+            out.q, out.s = weight, layer._scale_float()
+            if need_transpose and layer.weight_transpose.numel():
+                out.qt, out.st = layer.weight_transpose, layer.weight_transpose_scale
+        else:
+            out.q, out.s = layer._encode_weight(weight, gw, limit)
+            if need_transpose:
+                out.qt, out.st = layer._encode_weight(weight, transpose_group(gw), limit, transposed=True)
+        return out
+    limit = layer._quantization_limit(max(weight.shape), fmt)
+    if layer.weight_dtype == "fp8":
+        out.q, out.s = weight, layer.weight_scale
+        if need_transpose and layer.weight_transpose.numel():
+            out.qt = layer.weight_transpose
+    else:
+        source = ops.hadamard64(weight) if layer.rotation_size else weight
+        out.s = layer.weight_quantizer.scale(source, fmt, limit)
+        out.q, qt = ops.quantize(source, out.s, transpose=need_transpose, fp8_dtype=fmt, quantization_limit=limit)
+        out.qt = qt if need_transpose else None
+    out.st = out.s
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# functional core, shared by Linear and the fused MLP
+# ------------------------------------------------------------------------------------------------
+def linear_forward(layer, x, weight, bias, *, need_input_grad, need_weight_grad, gated=None, encoded=None):
+    """y = x W^T + b on 2-D ``x``.  Returns (y, saved, aux) where ``saved`` feeds :func:`linear_backward`.
+
+    ``gated`` = activation name turns the GEMM into the fused gate/up epilogue (``aux`` = [g | u]);
+    ``encoded`` = already quantised input (q, s, qt, st) produced by a fused producer.
+    """
+    fmt = layer.fp8_dtype
+    need_backward = need_input_grad or need_weight_grad
+    save_fp8 = need_weight_grad and layer.saved_input_dtype == "fp8"
+    gx, gw = layer.input_group_shape, layer.weight_group_shape
+    if layer._grouped_scaling:
+        limit = layer._group_limit(gx, fmt)
+    else:
+        limit = layer._quantization_limit(max(x.shape), fmt)
+    qx = encoded if encoded is not None else _quantize_activation(
+        layer, x, fmt, gx, layer.input_quantizer, limit, row=True, transposed=save_fp8)
+    w = _weight_operands(layer, weight, need_transpose=need_input_grad and layer.cache_weight_transpose)
+    aux = None
+    if gated is not None:
+        group = (gx, gw) if layer._grouped_scaling else None
+        y, aux = ops.gated_gemm_forward(qx.q, w.q, qx.s, w.s, activation=gated, out_dtype=x.dtype, bias=bias,
+                                        save=need_backward, group=group, sa_kmajor=True)
+    elif layer._grouped_scaling:
+        y = ops.group_gemm(qx.q, w.q, qx.s, w.s, gx, gw, out_dtype=x.dtype, bias=bias, sa_kmajor=True)
+    else:
+        y = ops.gemm(qx.q, w.q, qx.s, w.s, out_dtype=x.dtype, bias=bias)
+    saved = None
+    if need_backward:
+        saved = SimpleNamespace(x=None, x_scale=None, x_is_fp8=save_fp8, input_scale=qx.s, weight=weight,
+                                weight_scale=w.s, wt=w.qt, wt_scale=w.st, limit=limit, x_dtype=x.dtype,
+                                weight_grad_dtype=getattr(weight, "grad_dtype", None) or torch.float32,
+                                bias_grad_dtype=(getattr(bias, "grad_dtype", None) or bias.dtype) if bias is not None else None)
+        if save_fp8:
+            saved.x, saved.x_scale = qx.qt, qx.st
+        elif need_weight_grad:
+            saved.x = x.to(_SAVED[layer.saved_input_dtype])
+    return y, saved, aux
+
+
+def linear_backward(layer, saved, dy, *, need_input_grad, need_weight_grad, need_bias_grad, gated=None, aux=None):
+    """Returns (dx, dw, db).  ``gated``: dx becomes [dG | dU] through the fused derivative epilogue."""
+    fmt, bfmt = layer.fp8_dtype, layer.backward_fp8_dtype
+    gg, gx, gw = layer.grad_group_shape, layer.input_group_shape, layer.weight_group_shape
+    grouped = layer._grouped_scaling
+    if grouped:
+        limit = layer._group_limit(gg, bfmt)
+    else:
+        limit = layer._quantization_limit(max(dy.shape), bfmt)
+    dx = dw = db = None
+    # memory mode keeps one FP8 copy of dY alive at a time; fast mode encodes both layouts in one read
+    both = need_input_grad and need_weight_grad and layer.mode == "fast"
+    qg = _quantize_activation(layer_no_rotation(layer), dy, bfmt, gg, layer.grad_quantizer, limit,
+                              row=need_input_grad, transposed=both or (need_weight_grad and not need_input_grad))
+    if need_input_grad:
+        wt, wt_scale = saved.wt, saved.wt_scale
+        if wt is None or not wt.numel():
+            wt, wt_scale = layer._transposed_weight(saved.weight, saved.weight_scale)
+        if gated is not None and not layer.rotation_size:
+            group = (gg, transpose_group(gw)) if grouped else None
+            dx = ops.gated_gemm_backward(qg.q, wt, qg.s, wt_scale, aux, activation=gated, out_dtype=saved.x_dtype,
+                                         group=group, sg_kmajor=True)
+        else:
+            if grouped:
+                dx = ops.group_gemm(qg.q, wt, qg.s, wt_scale, gg, transpose_group(gw), out_dtype=saved.x_dtype,
+                                    sa_kmajor=True)
+            else:
+                dx = ops.gemm(qg.q, wt, qg.s, wt_scale, out_dtype=saved.x_dtype)
+            if layer.rotation_size:
+                ops.hadamard64(dx, out=dx)
+            if gated is not None:
+                dx = ops.gated_backward(aux, dx, gated)
+        del wt
+    if need_weight_grad:
+        if qg.qt is None:
+            qg.q = None
+            late = _quantize_activation(layer_no_rotation(layer), dy, bfmt, gg, layer.grad_quantizer, limit, row=False,
+                                        transposed=True, scale=None if grouped else qg.s)
+            qg.qt, qg.st = late.qt, late.st
+        if saved.x_is_fp8:
+            xt, xt_scale = saved.x, saved.x_scale
+        else:
+            enc = _quantize_activation(layer, saved.x, fmt, gx, layer.input_quantizer, saved.limit, row=False,
+                                       transposed=True, scale=None if grouped else saved.input_scale)
+            xt, xt_scale = enc.qt, enc.st
+        if grouped:
+            dw = ops.group_gemm(qg.qt, xt, qg.st, xt_scale, gg, gx, out_dtype=saved.weight_grad_dtype, sa_kmajor=True,
+                                sb_kmajor=True)
+        else:
+            dw = ops.gemm(qg.qt, xt, qg.st, xt_scale, out_dtype=saved.weight_grad_dtype)
+        if layer.rotation_size:
+            ops.hadamard64(dw, out=dw)
+    if need_bias_grad:
+        db = dy.sum(dim=0, dtype=saved.bias_grad_dtype)
+    return dx, dw, db
+
+
+class _NoRotation:
+    """View of a layer whose rotation is disabled (output gradients are never rotated)."""
+
+    def __init__(self, layer):
+        self._layer = layer
+
+    rotation_size = 0
+
+    def __getattr__(self, name):
+        return getattr(self._layer, name)
+
+
+def layer_no_rotation(layer):
+    return _NoRotation(layer) if layer.rotation_size else layer
+
+
+class _LinearFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, layer, need_backward):
+        shape = x.shape
+        x2 = x.reshape(-1, layer.in_features).contiguous()
+        need_x = need_backward and ctx.needs_input_grad[0]
+        need_w = need_backward and ctx.needs_input_grad[1]
+        y, saved, _ = linear_forward(layer, x2, weight, bias, need_input_grad=need_x, need_weight_grad=need_w)
+        if need_backward:
+            ctx.layer, ctx.saved, ctx.shape = layer, saved, shape
+            if saved is None:
+                ctx.saved = SimpleNamespace(bias_grad_dtype=(getattr(bias, "grad_dtype", None) or bias.dtype)
+                                            if bias is not None else None)
+        return y.reshape(*shape[:-1], layer.out_features)
+
+    @staticmethod
+    def backward(ctx, dy):
+        layer = ctx.layer
+        dy2 = dy.reshape(-1, layer.out_features).contiguous()
+        need_x, need_w, need_b = ctx.needs_input_grad[:3]
+        if not (need_x or need_w):
+            db = dy2.sum(dim=0, dtype=ctx.saved.bias_grad_dtype) if need_b else None
+            return None, None, db, None, None
+        dx, dw, db = linear_backward(layer, ctx.saved, dy2, need_input_grad=need_x, need_weight_grad=need_w,
+                                     need_bias_grad=need_b)
+        if dx is not None:
+            dx = dx.reshape(*ctx.shape[:-1], layer.in_features)
+        return dx, dw, db, None, None
+
+
+class Linear(nn.Module):
+    """FP8-compute linear layer with selectable weight storage.
+
+    Build and move the model first, then construct the optimizer and call
+    ``viola_b200.optim.bind_optimizer(model, optimizer)`` (or hand both to ``violaEngine``).  Inputs and
+    outputs are ordinary 16/32-bit tensors.
+    """
+
+    def __init__(self, in_features, out_features, bias=True, *, mode="memory", weight_dtype="fp8",
+                 forward_dtype="e4m3", backward_dtype="e5m2", cache_weight_transpose=None, saved_input_dtype="fp8",
+                 scaling="current", history_len=16, autotune=False, accum_dtype="fp32", accum_block_size=0,
+                 accum_reduce_dtype="fp32", quantization_limit=None, rotation_size=0, weight_group_shape=(32, 32),
+                 input_group_shape=(1, 32), grad_group_shape=(1, 32), device=None, dtype=None):
+        super().__init__()
+        if mode not in ("memory", "fast"):
+            raise ValueError("mode must be 'memory' or 'fast'")
+        if weight_dtype not in ("fp8", "bf16", "fp16"):
+            raise ValueError("weight_dtype must be fp8, bf16 or fp16")
+        if saved_input_dtype not in ("fp8", "bf16", "fp16", "fp32"):
+            raise ValueError("saved_input_dtype must be fp8, bf16, fp16 or fp32")
+        if scaling not in ("current", "delayed", "grouped", "mxfp8") or history_len <= 0:
+            raise ValueError("scaling must be current, delayed, grouped or mxfp8 and history_len positive")
+        if accum_dtype not in ("fp32", "fp16") or accum_reduce_dtype not in ("fp32", "bf16"):
+            raise ValueError("unsupported accumulation dtype")
+        if accum_block_size < 0 or accum_block_size % 32:
+            raise ValueError("accum_block_size must be a non-negative multiple of 32")
+        if rotation_size not in (0, 64) or (rotation_size and in_features % rotation_size):
+            raise ValueError("rotation_size must be 0 or 64 and divide in_features")
+        self.in_features, self.out_features = in_features, out_features
+        self.mode, self.weight_dtype, self.saved_input_dtype = mode, weight_dtype, saved_input_dtype
+        self.forward_dtype, self.backward_dtype = forward_dtype, backward_dtype
+        self.fp8_dtype, self.backward_fp8_dtype = _FORMATS[forward_dtype], _FORMATS[backward_dtype]
+        self._grouped_scaling = scaling in ("grouped", "mxfp8")
+        self._native_scaling = scaling == "mxfp8"
+        self.weight_group_shape = tuple(weight_group_shape)
+        self.input_group_shape = tuple(input_group_shape)
+        self.grad_group_shape = tuple(grad_group_shape)
+        if self._grouped_scaling:
+            if rotation_size:
+                raise ValueError("grouped scaling does not combine with rotation_size")
+            for gr, gc in (self.weight_group_shape, self.input_group_shape, self.grad_group_shape):
+                if gr <= 0 or gr & (gr - 1) or gc < 32 or gc & (gc - 1):
+                    raise ValueError("group shapes must be powers of two with at least 32 columns")
+            if self._native_scaling and (accum_dtype != "fp32" or accum_block_size or accum_reduce_dtype != "fp32"):
+                raise ValueError("mxfp8 accumulates in fp32")
+        self.autotune = autotune
+        self.accum_dtype, self.accum_block_size, self.accum_reduce_dtype = accum_dtype, accum_block_size, accum_reduce_dtype
+        self.quantization_limit = quantization_limit
+        self.rotation_size = rotation_size
+        self.cache_weight_transpose = (mode == "fast") if cache_weight_transpose is None else cache_weight_transpose
+        policy = settings()
+        master_dtype = policy["master_weight_dtype"] or torch.float32
+        gradient_dtype = policy["gradient_dtype"] or torch.float32
+        dtype = dtype or torch.get_default_dtype()
+        fp8_storage = weight_dtype == "fp8"
+        # With FP8 storage the initial real-valued weight is kept aside and handed to the optimizer
+        # as its master copy; 16-bit storage is initialised in place.
+        self._initial_weight = (torch.empty((out_features, in_features), device=device, dtype=master_dtype)
+                                if fp8_storage else None)
+        self._master_ref = None
+        storage = self.fp8_dtype if fp8_storage else _STORAGE[weight_dtype]
+        self.weight = nn.Parameter(torch.empty((out_features, in_features), device=device, dtype=storage))
+        self.weight.grad_dtype = gradient_dtype
+        self.bias = nn.Parameter(torch.empty(out_features, device=device, dtype=dtype)) if bias else None
+        if self.bias is not None:
+            self.bias.grad_dtype = gradient_dtype
+        if self._grouped_scaling:
+            shape = ops.scale_shape((out_features, in_features), self.weight_group_shape) if fp8_storage else (0, 0)
+        else:
+            shape = (1,) if fp8_storage else (0,)
+        scale_dtype = torch.uint8 if self._native_scaling else torch.float32
+        self.register_buffer("weight_scale", torch.full(shape, 127 if self._native_scaling else 1, device=device,
+                                                        dtype=scale_dtype), persistent=fp8_storage)
+        self.register_buffer("weight_transpose", torch.empty(0, 0, device=device, dtype=self.fp8_dtype),
+                             persistent=False)
+        if self._grouped_scaling:
+            self.register_buffer("weight_transpose_scale", torch.empty(0, 0, device=device, dtype=torch.float32),
+                                 persistent=False)
+        self.weight_quantizer = _Quantizer(scaling, history_len, device)
+        self.input_quantizer = _Quantizer(scaling, history_len, device)
+        self.grad_quantizer = _Quantizer(scaling, history_len, device)
+        self.reset_parameters()
+
+    # ------------------------------------------------------------------ quantisation range policy
+    def _quantization_limit(self, reduction, fp8_dtype):
+        maximum = torch.finfo(fp8_dtype).max
+        if self.quantization_limit is not None:
+            return min(self.quantization_limit, maximum)
+        if self.accum_dtype == "fp32":
+            return None
+        if self.accum_block_size:
+            reduction = self.accum_block_size
+        return min(2.0 ** math.floor(math.log2(math.sqrt(32768.0 / reduction))), maximum)
+
+    def _group_limit(self, shape, dtype, weight=False):
+        maximum = torch.finfo(dtype).max
+        if self.quantization_limit is not None:
+            return min(self.quantization_limit, maximum)
+        if self.accum_dtype == "fp32":
+            return None
+        reduction = max(shape) if weight else shape[1]
+        if self.accum_block_size:
+            reduction = math.gcd(reduction, self.accum_block_size)
+        return min(2.0 ** math.floor(math.log2(math.sqrt(32768.0 / reduction))), maximum)
+
+    # ------------------------------------------------------------------ weight (re)quantisation
+    def _scale_float(self, scale=None):
+        scale = self.weight_scale if scale is None else scale
+        return torch.exp2(scale.float() - 127) if scale.dtype == torch.uint8 else scale
+
+    def _encode_weight(self, master, group, limit, *, transposed=False):
+        q, s = ops.group_quantize(master, self.fp8_dtype, group, limit=limit, transposed=transposed)
+        if self._native_scaling:
+            s = _pow2_scales(s)
+            value = master.detach().float().t() if transposed else master.detach().float()
+            expanded = s.repeat_interleave(group[0], 0).repeat_interleave(group[1], 1)[:value.shape[0], :value.shape[1]]
+            limit_value = ops.reference.fp8_limit(self.fp8_dtype, limit)
+            q = (value / expanded).clamp(-limit_value, limit_value).to(self.fp8_dtype)
+        return q, s
+
+    def _transposed_weight(self, weight, scale):
+        """W^T codes and scales for dgrad, built from the stored weight without touching its scale state."""
+        if self._grouped_scaling:
+            gw = self.weight_group_shape
+            limit = self._group_limit(gw, self.fp8_dtype, weight=True)
+            if self.weight_dtype != "fp8":
+                return self._encode_weight(weight, transpose_group(gw), limit, transposed=True)
+            scale = self._scale_float(scale)
+            if gw[0] >= 32:
+                return ops.transpose(weight), scale.t().contiguous()
+            decoded = ops.group_dequantize(weight, scale, gw)
+            return self._encode_weight(decoded, gw, limit, transposed=True)
+        if self.weight_dtype != "fp8":
+            source = ops.hadamard64(weight) if self.rotation_size else weight
+            _, wt = ops.quantize(source, scale, rowwise=False, transpose=True, fp8_dtype=self.fp8_dtype,
+                                 quantization_limit=self._quantization_limit(max(weight.shape), self.fp8_dtype))
+            return wt, scale
+        return ops.transpose(weight), scale
+
+    @torch.no_grad()
+    def reset_parameters(self):
+        if self._master_ref is not None and self._master_ref() is not None:
+            master = self._master_ref()
+        else:
+            master = self.weight if self.weight_dtype != "fp8" else self._initial_weight
+        nn.init.kaiming_uniform_(master, a=math.sqrt(5))
+        if self.bias is not None:
+            bound = 1 / math.sqrt(self.in_features)
+            nn.init.uniform_(self.bias, -bound, bound)
+        self.refresh_weight(master)
+
+    @torch.no_grad()
+    def quantize_master(self, master, *, out=None, out_t=None):
+        """FP8 codes of ``master`` under this layer's recipe; updates ``weight_scale`` and quantizer state.
+
+        ``out`` / ``out_t`` receive the codes and (per-tensor recipes only) their transpose; with
+        ``out=None`` a new tensor is returned and ``self.weight`` is left untouched, which is what an
+        owner rank uses before shipping codes to the other ranks.
+        """
+        if self._grouped_scaling:
+            gw = self.weight_group_shape
+            limit = self._group_limit(gw, self.fp8_dtype, weight=True)
+            q, s = self._encode_weight(master, gw, limit)
+            self.weight_scale.copy_(torch.log2(s) + 127 if self._native_scaling else s)
+            return q if out is None else out.copy_(q)
+        limit = self._quantization_limit(max(self.in_features, self.out_features), self.fp8_dtype)
+        source = ops.hadamard64(master) if self.rotation_size else master
+        scale = self.weight_quantizer.scale(source, self.fp8_dtype, limit)
+        self.weight_scale.copy_(scale)
+        q, _ = ops.quantize(source, scale, transpose=out_t is not None, fp8_dtype=self.fp8_dtype, out=out, out_t=out_t,
+                            quantization_limit=limit)
+        return q
+
+    @torch.no_grad()
+    def refresh_weight(self, master):
+        """Re-derive the compute weight from an updated master (called after every optimizer step)."""
+        if self.weight_dtype != "fp8":
+            if master is not self.weight:
+                self.weight.copy_(master)
+            return
+        if self._grouped_scaling:
+            self.quantize_master(master, out=self.weight.data)
+            if self.cache_weight_transpose:
+                self.weight_transpose, self.weight_transpose_scale = self._transposed_weight(self.weight,
+                                                                                             self.weight_scale)
+            return
+        if self.cache_weight_transpose and self.weight_transpose.numel() == 0:
+            self.weight_transpose = torch.empty((self.in_features, self.out_features), device=master.device,
+                                                dtype=self.fp8_dtype)
+        self.quantize_master(master, out=self.weight.data,
+                             out_t=self.weight_transpose if self.cache_weight_transpose else None)
+
+    def dequantize_weight(self):
+        """The real-valued weight in the original (unrotated) coordinates, as fp32."""
+        if self.weight_dtype != "fp8":
+            return self.weight.float()
+        if self._grouped_scaling:
+            return ops.group_dequantize(self.weight, self._scale_float(), self.weight_group_shape)
+        weight = self.weight.float() * self.weight_scale
+        return ops.hadamard64(weight) if self.rotation_size else weight
+
+    @classmethod
+    @torch.no_grad()
+    def from_float(cls, linear, **kwargs):
+        layer = cls(linear.in_features, linear.out_features, linear.bias is not None, device=linear.weight.device,
+                    dtype=linear.weight.dtype, **kwargs)
+        master = layer.weight if layer.weight_dtype != "fp8" else layer._initial_weight
+        master.copy_(linear.weight)
+        layer.weight_quantizer.history.zero_()      # the throw-away initialiser must not leak its amax
+        layer.weight_quantizer.index = 0
+        layer.refresh_weight(master)
+        if linear.bias is not None:
+            layer.bias.copy_(linear.bias)
+            layer.bias.requires_grad_(linear.bias.requires_grad)
+        layer.weight.requires_grad_(linear.weight.requires_grad)
+        return layer
+
+    @torch.no_grad()
+    def rebuild_weight_cache(self):
+        """Recompute the cached W^T from the current codes / scales; W itself is left alone."""
+        if self.cache_weight_transpose and self.weight_dtype == "fp8":
+            if self._grouped_scaling:
+                self.weight_transpose, self.weight_transpose_scale = self._transposed_weight(self.weight,
+                                                                                             self.weight_scale)
+            else:
+                self.weight_transpose = ops.transpose(self.weight)
+
+    def clear_weight_cache(self):
+        self.weight_transpose = self.weight_transpose.new_empty((0, 0))
+        if hasattr(self, "weight_transpose_scale"):
+            self.weight_transpose_scale = self.weight_transpose_scale.new_empty((0, 0))
+
+    # ------------------------------------------------------------------ forward
+    def _needs_backward(self, x):
+        return torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad
+                                            or (self.bias is not None and self.bias.requires_grad))
+
+    def forward(self, x):
+        if x.is_cuda and torch.is_autocast_enabled("cuda"):
+            x = x.to(torch.get_autocast_dtype("cuda"))
+        elif not x.is_cuda and torch.is_autocast_enabled("cpu"):
+            x = x.to(torch.get_autocast_dtype("cpu"))
+        return _LinearFunction.apply(x, self.weight, self.bias, self, self._needs_backward(x))
+
+    # ------------------------------------------------------------------ device moves / checkpoints
+    def _apply(self, fn, recurse=True):
+        # Only the device of the FP8 codes, scales and histories may change; dtype casts such as
+        # .half() must leave them alone.
+        weight = self._parameters["weight"]
+        self._parameters["weight"] = None
+        grad_dtype = getattr(weight, "grad_dtype", None)
+        names = ["weight_scale", "weight_transpose"] + (["weight_transpose_scale"] if self._grouped_scaling else [])
+        held = [(self, name, self._buffers.pop(name)) for name in names]
+        for quantizer in (self.weight_quantizer, self.input_quantizer, self.grad_quantizer):
+            held.append((quantizer, "history", quantizer._buffers.pop("history")))
+        super()._apply(fn, recurse)
+
+        def move(tensor):
+            return tensor.to(device=fn(torch.empty(0, device=tensor.device, dtype=torch.float32)).device)
+
+        weight.data = move(weight.data)
+        if weight.grad is not None:
+            weight.grad = move(weight.grad)
+        if grad_dtype is not None:
+            weight.grad_dtype = grad_dtype
+            if self.bias is not None:
+                self.bias.grad_dtype = grad_dtype
+        self._parameters["weight"] = weight
+        for module, name, tensor in held:
+            module._buffers[name] = move(tensor)
+        if self._initial_weight is not None:
+            self._initial_weight = move(self._initial_weight)
+        return self
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        expected = self.fp8_dtype if self.weight_dtype == "fp8" else _STORAGE[self.weight_dtype]
+        key = prefix + "weight"
+        if key in state_dict and state_dict[key].dtype != expected:
+            raise RuntimeError("checkpoint weight storage / FP8 format differs from this layer's configuration")
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+        self._initial_weight = None
+        self.rebuild_weight_cache()
+
+    def extra_repr(self):
+        groups = (f", weight_group_shape={self.weight_group_shape}, input_group_shape={self.input_group_shape}, "
+                  f"grad_group_shape={self.grad_group_shape}") if self._grouped_scaling else ""
+        return (f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, "
+                f"mode={self.mode!r}, weight_dtype={self.weight_dtype!r}, forward_dtype={self.forward_dtype!r}, "
+                f"backward_dtype={self.backward_dtype!r}, cache_weight_transpose={self.cache_weight_transpose}, "
+                f"saved_input_dtype={self.saved_input_dtype!r}, scaling={self.weight_quantizer.scaling!r}, "
+                f"accum_dtype={self.accum_dtype!r}, rotation_size={self.rotation_size}{groups}")

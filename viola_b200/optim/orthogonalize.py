@@ -1,0 +1,115 @@
+"""Quintic Newton-Schulz orthogonalisation on the tcgen05 GEMM kernel.
+
+Two recurrences with the reference's coefficients and rounding points
+(viola/optim/_orthogonalize.py:10-54; kernel epilogues viola/optim/_orthogonalize_kernels.py:16-50):
+
+* ``standard`` (bf16): ``X <- 3.4445 X + (-4.775 G + 2.0315 G G) X`` with ``G = X X^T``;
+* ``gram`` (fp16): the polynomial is composed on the small Gram matrix and applied to ``X`` once per
+  segment (two iterations, then the rest), falling back to the standard recurrence for square inputs.
+
+Every product is one launch of the warp-specialised tcgen05 kernel with the polynomial fused into
+its epilogue (``alpha * round(acc) + beta * R``).  Gram-side products are symmetric, so only the
+upper-triangular tiles are computed and mirrored.  The kernel consumes K-major operands only, so
+the iterate is carried in both orientations: the third GEMM of a step writes ``X`` row-wise and
+``X^T`` through a coalesced transposed store, which removes every explicit transpose.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+
+_A, _B, _C = 3.4445, -4.7750, 2.0315
+
+
+def _prescale(matrix, dtype):
+    """(X, X^T) = matrix / (||matrix||_F + 1e-7) rounded to ``dtype``; X is the wide orientation."""
+    rows, cols = matrix.shape
+    accum = torch.zeros(1, device=matrix.device, dtype=torch.float32)
+    source = matrix.contiguous()
+    ops.sumsq(source, dtype, accum)
+    straight = torch.empty((rows, cols), device=matrix.device, dtype=dtype)
+    flipped = torch.empty((cols, rows), device=matrix.device, dtype=dtype)
+    ops.ns_prescale(source, accum, out=straight, out_t=flipped)
+    return (flipped, straight, True) if rows > cols else (straight, flipped, False)
+
+
+def _poly(r):
+    """-4.775 R + 2.0315 R R for a symmetric R."""
+    return ops.ns_gemm(r, r, alpha=_C, beta=_B, resid=r, symmetric=True)
+
+
+def _standard_2d(matrix, steps, dtype):
+    x, xt, transposed = _prescale(matrix, dtype)
+    for step in range(steps):
+        gram = ops.ns_gemm(x, x, symmetric=True)
+        poly = _poly(gram)
+        last = step == steps - 1
+        if last and transposed:
+            return ops.ns_gemm(xt, poly, alpha=1.0, beta=_A, resid=xt)        # X^T P = (P X)^T
+        if last:
+            return ops.ns_gemm(poly, xt, alpha=1.0, beta=_A, resid=x)
+        new_t = torch.empty_like(xt)
+        x = ops.ns_gemm(poly, xt, alpha=1.0, beta=_A, resid=x, out_t=new_t)
+        xt = new_t
+    return xt if transposed else x
+
+
+def _gram_2d(matrix, steps):
+    dtype = torch.float16
+    if matrix.shape[0] == matrix.shape[1]:
+        return _standard_2d(matrix, steps, dtype)
+    x, xt, transposed = _prescale(matrix, dtype)
+    segments = [length for length in (min(steps, 2), max(steps - 2, 0)) if length]
+    for index, length in enumerate(segments):
+        r = ops.ns_gemm(x, x, symmetric=True)
+        q = None
+        for i in range(length):
+            z = _poly(r)
+            if i == 0:
+                q = z.clone()
+                q.diagonal().add_(_A)
+            else:
+                q = ops.ns_gemm(z, q, alpha=1.0, beta=_A, resid=q, symmetric=True)
+            if i + 1 < length:
+                rz = ops.ns_gemm(z, r, alpha=1.0, beta=_A, resid=r, symmetric=True)
+                r = ops.ns_gemm(z, rz, alpha=1.0, beta=_A, resid=rz, symmetric=True)
+        last = index == len(segments) - 1
+        if last and transposed:
+            return ops.ns_gemm(xt, q)                                            # X^T Q = (Q X)^T
+        if last:
+            return ops.ns_gemm(q, xt)
+        new_t = torch.empty_like(xt)
+        x = ops.ns_gemm(q, xt, out_t=new_t)
+        xt = new_t
+    return xt if transposed else x
+
+
+def _batched(fn, matrix, *args):
+    if matrix.ndim == 2:
+        return fn(matrix, *args)
+    flat = matrix.reshape(-1, *matrix.shape[-2:])
+    return torch.stack([fn(item, *args) for item in flat]).reshape(*matrix.shape[:-2], *matrix.shape[-2:])
+
+
+def standard(matrix, steps=5):
+    """bf16 Newton-Schulz; returns the orthogonalised matrix in bf16 with the input's shape."""
+    if not matrix.is_cuda:
+        return ops.reference.ns_standard(matrix, steps)
+    return _batched(_standard_2d, matrix, steps, torch.bfloat16)
+
+
+def gram(matrix, steps=5):
+    """fp16 Gram-matrix Newton-Schulz; returns fp16."""
+    if not matrix.is_cuda:
+        return ops.reference.ns_gram(matrix, steps)
+    return _batched(_gram_2d, matrix, steps)
+
+
+def orthogonalize(matrix, *, method="standard", steps=5, autotune=True):
+    """Entry point with the keyword surface of the reference's kernel-backed path."""
+    return METHODS[method](matrix, steps=steps)
+
+
+METHODS = {"standard": standard, "gram": gram}

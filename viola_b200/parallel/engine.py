@@ -1,0 +1,210 @@
+"""``violaEngine``: the training interface with four independent state-sharding switches.
+
+Public surface and step semantics of the reference engine (viola/distributed/engine.py:19-156):
+
+* ``violaEngine(config)`` — config from a YAML path, a dict or ``$VIOLA_CONFIG``; one process per GPU
+  (``LOCAL_RANK``), NCCL on CUDA and Gloo on CPU, a 1-D data-parallel mesh;
+* ``prepare_model`` / ``prepare_optimizer`` (factory or unused instance) / ``prepare_dataloader``;
+* ``accumulate()`` / ``autocast()`` / ``backward(loss, weight=None)`` / ``step(optimizer=None, scheduler=None,
+  force=False)`` / ``reduce(value, reduction="mean")``;
+* ``ema_scope()``, ``save_checkpoint`` / ``load_checkpoint``, ``close()``.
+
+Loss normalisation: unweighted losses are divided by the accumulation steps and the update by
+``world * pending / accumulation`` (so a forced partial flush is still a mean); weighted losses are
+multiplied by their weight and the update divided by the all-reduced weight sum.
+"""
+
+from __future__ import annotations
+
+import os
+from contextlib import contextmanager, nullcontext
+
+import torch
+import torch.distributed as dist
+
+from ..precision import set_gradient_dtype, set_master_weight_dtype
+from . import checkpoint
+from .config import dtype as to_dtype, read_config
+from .data import prepare_dataloader
+from .parameters import synchronize_model
+from .sharder import shard_parameters
+from .state import DistributedState
+
+
+class violaEngine:  # noqa: N801 - public name kept identical to the reference
+    def __init__(self, config=None):
+        self.config = read_config(config)
+        device_type = self.config.get("device", "cuda" if torch.cuda.is_available() else "cpu")
+        if device_type == "cuda":
+            self.device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+            torch.cuda.set_device(self.device)
+        else:
+            self.device = torch.device(device_type)
+        if not dist.is_initialized():
+            if "RANK" not in os.environ:       # single process without a launcher
+                os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+                os.environ.setdefault("MASTER_PORT", "29533")
+                os.environ.setdefault("RANK", "0")
+                os.environ.setdefault("WORLD_SIZE", "1")
+            dist.init_process_group("nccl" if self.device.type == "cuda" else "gloo")
+        self.rank, self.world_size = dist.get_rank(), dist.get_world_size()
+        self.is_main_process = self.rank == 0
+        from torch.distributed.device_mesh import init_device_mesh
+        self.mesh = init_device_mesh(self.device.type, (self.world_size,), mesh_dim_names=("dp",))
+        self.group = self.mesh.get_group()
+        self.global_ranks = [int(r) for r in self.mesh.mesh.tolist()]
+        policy = self.config["precision"]
+        set_master_weight_dtype(to_dtype(policy["master_weight_dtype"]), rounding=policy["master_rounding"],
+                                seed=policy["master_rounding_seed"])
+        set_gradient_dtype(to_dtype(policy["gradient_dtype"]))
+        self.accumulation_steps = self.config["gradient_accumulation_steps"]
+        self.global_step = self.micro_step = self._pending_microbatches = 0
+        self.sync_gradients = True
+        self._in_accumulate = self._in_ema = False
+        self._weighted = None
+        self._loss_weight = 0.0
+        self.model = self.state = self.optimizer = self.ema = None
+        self.sharder = None
+        self.transport = None
+
+    # ------------------------------------------------------------------ preparation
+    def prepare_model(self, model):
+        """Move to the device, make all ranks identical to rank 0, shard parameters if configured."""
+        self.model = model.to(self.device)
+        if self.world_size > 1:
+            synchronize_model(self.model, self.group, self.global_ranks[0], self.rank == 0, initial=True)
+        if self.config["sharding"]["parameters"]:
+            self.sharder = shard_parameters(self.model, self.group, self.rank, self.world_size,
+                                            blocks=self.config["sharding"]["blocks"])
+        return self.model
+
+    def prepare_optimizer(self, factory):
+        optimizer = factory(self.model.parameters()) if callable(factory) else factory
+        self.transport = self._make_transport()
+        self.state = DistributedState(self.model, optimizer, self, self.sharder, self.transport)
+        self.optimizer, self.ema = optimizer, self.state.ema
+        return optimizer
+
+    def _make_transport(self):
+        communication = self.config["communication"]
+        backend = communication.get("backend", "auto")
+        if self.world_size == 1 or self.device.type != "cuda" or backend == "nccl":
+            return None
+        try:
+            from .symm import PeerTransport
+            return PeerTransport(self, fp8_format=communication["fp8_format"], tile_size=communication["fp8_tile_size"],
+                                 fp8=communication["dtype"] == "fp8", overlap=communication.get("overlap", True))
+        except Exception:
+            if backend == "p2p":
+                raise
+            return None
+
+    def prepare_dataloader(self, loader):
+        return prepare_dataloader(loader, rank=self.rank, world_size=self.world_size)
+
+    # ------------------------------------------------------------------ training step
+    def autocast(self):
+        precision = self.config["mixed_precision"]
+        if precision == "no":
+            return nullcontext()
+        return torch.autocast(self.device.type, dtype=to_dtype(precision))
+
+    def _start_microbatch(self):
+        self.micro_step += 1
+        self._pending_microbatches += 1
+        self.sync_gradients = self._pending_microbatches >= self.accumulation_steps
+
+    @contextmanager
+    def accumulate(self, model=None):
+        if self._in_accumulate:
+            raise RuntimeError("accumulate() does not nest")
+        self._in_accumulate = True
+        self._start_microbatch()
+        try:
+            yield
+        finally:
+            self._in_accumulate = False
+
+    def backward(self, loss, *, weight=None):
+        """Backpropagate a local mean loss; ``weight`` may be its number of valid tokens / samples."""
+        if not self._in_accumulate:
+            self._start_microbatch()
+        weighted = weight is not None
+        if self._weighted is not None and self._weighted != weighted:
+            raise RuntimeError("weighted and unweighted losses cannot be mixed inside one accumulation window")
+        self._weighted = weighted
+        if weighted:
+            weight = float(weight)
+            self._loss_weight += weight
+            loss = loss * weight
+        else:
+            loss = loss / self.accumulation_steps
+        self.state.backward(loss)
+
+    def step(self, optimizer=None, *, scheduler=None, force=False):
+        """Returns True only after a real optimizer update that every rank performed."""
+        if self._in_ema:
+            raise RuntimeError("step() inside ema_scope()")
+        if optimizer is not None and optimizer is not self.optimizer:
+            raise ValueError("step() received an optimizer the engine did not prepare")
+        if not self._pending_microbatches or (not self.sync_gradients and not force):
+            return False
+        if self._weighted:
+            divisor = torch.tensor(self._loss_weight, device=self.device, dtype=torch.float64)
+            if self.world_size > 1:
+                dist.all_reduce(divisor, group=self.group)
+        else:
+            divisor = self.world_size * self._pending_microbatches / self.accumulation_steps
+        updated = self.state.step(divisor)
+        self._pending_microbatches = 0
+        self._weighted, self._loss_weight = None, 0.0
+        self.sync_gradients = True
+        if updated:
+            self.global_step += 1
+            if scheduler is not None:
+                scheduler.step()
+        return updated
+
+    @torch.no_grad()
+    def reduce(self, value, *, reduction="mean"):
+        value = torch.as_tensor(value, device=self.device).detach().clone()
+        if self.world_size > 1:
+            dist.all_reduce(value, group=self.group)
+        return value / self.world_size if reduction == "mean" else value
+
+    # ------------------------------------------------------------------ evaluation with EMA weights
+    @contextmanager
+    def ema_scope(self):
+        """Evaluate with the EMA weights, then restore compute weights, buffers and modes exactly."""
+        if self._pending_microbatches or self._in_ema:
+            raise RuntimeError("ema_scope() needs an update boundary and does not nest")
+        self._in_ema = True
+        modes = [(module, module.training) for module in self.model.modules()]
+        buffers = checkpoint.capture_buffers(self.model, clone=True)
+        saved = self.state.parameters.snapshot() if self.ema.decay else {}
+        try:
+            if self.ema.decay:
+                self.ema.apply()
+            self.model.eval()
+            with torch.no_grad():
+                yield self.model
+        finally:
+            with torch.no_grad():
+                if self.ema.decay:
+                    self.state.parameters.restore(saved)
+                checkpoint.restore_buffers(self.model, buffers, sharded=self.sharder is not None)
+            for module, training in modes:
+                module.training = training
+            self._in_ema = False
+
+    def save_checkpoint(self, path, *, scheduler=None, extra=None):
+        return checkpoint.save(self, path, scheduler=scheduler, extra=extra)
+
+    def load_checkpoint(self, path, *, scheduler=None):
+        return checkpoint.load(self, path, scheduler=scheduler)
+
+    def close(self):
+        if self.state is not None:
+            self.state.close()
+        if self.transport is not None:
+            self.transport.close()

@@ -1,0 +1,186 @@
+"""Gradient accumulation with replicated or whole-parameter-owned placement.
+
+Structure and rules of the reference's ``GradientState`` (viola/distributed/gradients.py:21-156):
+a flat accumulator (all parameters, or only the owned ones when gradients are sharded); buckets
+that walk the parameters in reverse order, break at every owner change and at ``bucket_mb``; a
+post-accumulate hook that steals ``param.grad``; reduce-to-owner per microbatch for sharded
+gradients; one all-reduce at the step for replicated gradients; unused parameters contribute
+zeros; usage flags agreed with a MAX reduction.
+
+What differs: buckets are drained as soon as their gradients exist even when parameters are
+sharded (this package's sharder issues no collectives of its own during backward when the
+peer-memory transport is active, so there is no collective-order hazard), the transport is
+pluggable (collectives here, fused peer-memory kernels in :mod:`viola_b200.parallel.symm`), and with
+a single rank every communication step is skipped.
+"""
+
+from __future__ import annotations
+
+from functools import partial
+
+import torch
+import torch.distributed as dist
+
+from .config import dtype as to_dtype
+from .fp8 import FP8Communication
+
+
+class GradientState:
+    def __init__(self, store, *, gradient_dtype, communication_dtype=None, bucket_mb=25, fp8_format="e4m3",
+                 fp8_tile_size=256, shard=False, defer_reduction=False, transport=None):
+        self.store = store
+        self.records = store.records
+        self.rank, self.world, self.group = store.rank, store.world, store.group
+        self.shard = shard and self.world > 1
+        self.requested_shard = shard
+        self.defer_reduction = defer_reduction
+        self.gradient_dtype = gradient_dtype
+        self.fp8_requested = communication_dtype == "fp8"
+        self.dtype = torch.float32 if self.fp8_requested else (to_dtype(communication_dtype) or gradient_dtype)
+        device = self.records[0].parameter.device
+        if self.fp8_requested and device.type != "cuda" and self.world > 1:
+            raise RuntimeError("FP8 gradient communication needs CUDA")
+        element = torch.empty((), dtype=self.dtype).element_size()
+        total = sum(r.numel for r in self.records)
+        capacity = min(max(1, int(bucket_mb * 1024 * 1024) // element), total)
+        owned = [r for r in self.records if not self.shard or r.owner == self.rank]
+        self.accumulator = torch.zeros(sum(r.numel for r in owned), device=device, dtype=gradient_dtype)
+        self.local, offset = {}, 0
+        for index, record in enumerate(self.records):
+            if not self.shard or record.owner == self.rank:
+                self.local[index] = self.accumulator[offset:offset + record.numel]
+                offset += record.numel
+        # buckets: (owner, [(record index, offset in parameter, offset in bucket, length)], filled)
+        self.buckets, self.piece_counts = [], [0] * len(self.records)
+        pieces, filled, owner = [], 0, None
+        for index in reversed(range(len(self.records))):
+            record = self.records[index]
+            if pieces and record.owner != owner:
+                self.buckets.append((owner, pieces, filled))
+                pieces, filled = [], 0
+            owner, position = record.owner, 0
+            while position < record.numel:
+                length = min(record.numel - position, capacity - filled)
+                pieces.append((index, position, filled, length))
+                self.piece_counts[index] += 1
+                position += length
+                filled += length
+                if filled == capacity:
+                    self.buckets.append((owner, pieces, filled))
+                    pieces, filled = [], 0
+        if pieces:
+            self.buckets.append((owner, pieces, filled))
+        self.bucket_capacity = max(length for _, _, length in self.buckets)
+        self.buffer = (torch.empty(self.bucket_capacity, device=device, dtype=self.dtype) if self.world > 1 else None)
+        self.transport = transport
+        self.fp8 = None
+        if self.fp8_requested and self.world > 1 and transport is None:
+            self.fp8 = FP8Communication(self.bucket_capacity, self.group, self.rank, self.world, store.global_ranks,
+                                        device, mode="reduce" if self.shard else "all_reduce", fp8_format=fp8_format,
+                                        tile_size=fp8_tile_size)
+        self.used = [False] * len(self.records)
+        self.pending = [None] * len(self.records)
+        self.in_backward = False
+        self.hooks = []
+        self._bound = set()
+
+    # ------------------------------------------------------------------ hooks
+    def bind(self, index, parameter):
+        if id(parameter) in self._bound:
+            return
+        self._bound.add(id(parameter))
+        self.hooks.append(parameter.register_post_accumulate_grad_hook(partial(self._ready, index)))
+
+    def begin_backward(self):
+        self.in_backward = True
+        self.seen = [False] * len(self.records)
+        self.remaining = self.piece_counts.copy()
+        self.next_bucket = 0
+        if self.store.sharder is not None:
+            self.store.sharder.begin_backward()
+
+    @torch.no_grad()
+    def _ready(self, index, parameter):
+        self.seen[index] = self.used[index] = True
+        gradient = parameter.grad.contiguous().view(-1)
+        parameter.grad = None
+        if self.shard:
+            self.pending[index] = gradient
+            if not self.defer_reduction:
+                self._drain()
+        else:
+            self.local[index].add_(gradient)
+        if self.store.sharder is not None:
+            self.store.sharder.gradient_arrived(parameter)
+
+    @torch.no_grad()
+    def _drain(self, *, final=False):
+        while self.next_bucket < len(self.buckets):
+            owner, pieces, length = self.buckets[self.next_bucket]
+            if not final and any(not self.seen[i] for i, _, _, _ in pieces):
+                break
+            buffer = self.buffer[:length]
+            for index, source, target, size in pieces:
+                slot = buffer[target:target + size]
+                gradient = self.pending[index]
+                if gradient is None:
+                    slot.zero_()
+                else:
+                    slot.copy_(gradient[source:source + size])
+                self.remaining[index] -= 1
+                if not self.remaining[index]:
+                    self.pending[index] = None
+            if self.transport is not None:
+                self.transport.reduce_to_owner(buffer, owner, self._owner_slices(pieces) if self.rank == owner else None)
+            else:
+                if self.fp8 is not None:
+                    self.fp8.reduce(buffer, owner)
+                else:
+                    dist.reduce(buffer, dst=self.store.global_ranks[owner], group=self.group)
+                if self.rank == owner:
+                    for index, target, source, size in pieces:
+                        self.local[index][target:target + size].add_(buffer[source:source + size])
+            self.next_bucket += 1
+
+    def _owner_slices(self, pieces):
+        return [(self.local[index][target:target + size], source, size) for index, target, source, size in pieces]
+
+    def finish_backward(self):
+        if self.shard:
+            self._drain(final=True)
+        if self.store.sharder is not None:
+            self.store.sharder.finish_backward()
+        self.in_backward = False
+
+    # ------------------------------------------------------------------ step-time reduction
+    @torch.no_grad()
+    def reduce(self, divisor):
+        """Agree on which parameters were used anywhere, finish replicated reductions, normalise."""
+        if self.world > 1:
+            used = torch.tensor(self.used, device=self.accumulator.device, dtype=torch.int32)
+            dist.all_reduce(used, op=dist.ReduceOp.MAX, group=self.group)
+            active = used.bool().tolist()
+            if not self.shard:
+                for _, pieces, length in self.buckets:
+                    buffer = self.buffer[:length]
+                    for index, source, target, size in pieces:
+                        buffer[target:target + size].copy_(self.local[index][source:source + size])
+                    if self.transport is not None and self.fp8_requested:
+                        self.transport.all_reduce(buffer)
+                    elif self.fp8 is not None:
+                        self.fp8.all_reduce(buffer)
+                    else:
+                        dist.all_reduce(buffer, group=self.group)
+                    for index, target, source, size in pieces:
+                        self.local[index][target:target + size].copy_(buffer[source:source + size])
+        else:
+            active = list(self.used)
+        if self.transport is not None:
+            self.transport.synchronize()
+        self.accumulator.div_(divisor)
+        return active
+
+    @torch.no_grad()
+    def zero_grad(self):
+        self.accumulator.zero_()
+        self.used = [False] * len(self.records)

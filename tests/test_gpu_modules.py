@@ -1,0 +1,193 @@
+"""GPU modules against their own CPU (plain PyTorch) execution path, which restates every kernel.
+
+Bounds follow the reference checks: Linear fwd/dX/dW < 0.3 % relative L2 with bf16 outputs
+(checks/linear.py:38), fused MLP < 2.5 % (checks/mlp.py:44), Newton-Schulz against the PyTorch
+recurrence, FP8Muon one step against the CPU kernels, and a short training run that must reduce the
+loss (checks/linear.py trains 100 steps to < 15 % loss; here a smaller problem, fewer steps).
+"""
+import copy
+
+import pytest
+import torch
+
+import viola_b200 as viola
+from conftest import rel_l2
+from viola_b200 import ops
+from viola_b200.nn import GroupedLinear, Linear, MLP
+from viola_b200.optim import FP8Muon, bind_optimizer
+from viola_b200.optim import orthogonalize
+
+pytestmark = pytest.mark.gpu
+GROUPED = dict(scaling="grouped", weight_group_shape=(128, 128), input_group_shape=(1, 128), grad_group_shape=(1, 128))
+
+
+@pytest.fixture(autouse=True)
+def _status():
+    yield
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+        ops.check_status()
+
+
+def run_both(module_cpu, x_cpu, dtype=torch.bfloat16):
+    """Forward + backward of the same module on CPU and on the GPU; returns the six tensors."""
+    module_gpu = copy.deepcopy(module_cpu).cuda()
+    results = []
+    for module, x in ((module_cpu, x_cpu), (module_gpu, x_cpu.cuda())):
+        x = x.to(dtype).requires_grad_(True)
+        y = module(x)
+        torch.manual_seed(1)
+        dy = torch.randn(y.shape, dtype=y.dtype).to(y.device)
+        y.backward(dy)
+        grads = [p.grad for p in module.parameters() if p.ndim >= 2]
+        results.append((y.detach(), x.grad, grads))
+        module.zero_grad()
+    return results
+
+
+@pytest.mark.parametrize("options", [dict(), dict(mode="fast"), dict(forward_dtype="e5m2", backward_dtype="e4m3"),
+                                     dict(weight_dtype="bf16"), dict(scaling="delayed"), dict(saved_input_dtype="bf16"),
+                                     GROUPED, dict(GROUPED, mode="fast"), dict(GROUPED, weight_group_shape=(1, 128)),
+                                     dict(scaling="grouped"), dict(scaling="mxfp8"), dict(rotation_size=64)])
+def test_linear_matches_cpu_path(options):
+    torch.manual_seed(0)
+    layer = Linear(384, 640, **options)
+    (y0, dx0, dw0), (y1, dx1, dw1) = run_both(layer, torch.randn(4, 100, 384))
+    assert rel_l2(y1.cpu(), y0) < 3e-3
+    assert rel_l2(dx1.cpu(), dx0) < 3e-3
+    assert rel_l2(dw1[0].cpu(), dw0[0]) < 3e-3
+    assert dw1[0].dtype == torch.float32
+
+
+@pytest.mark.parametrize("options", [dict(), GROUPED, dict(mode="fast"), dict(weight_dtype="bf16")])
+@pytest.mark.parametrize("activation", ["silu", "gelu"])
+def test_mlp_matches_cpu_path(options, activation):
+    torch.manual_seed(0)
+    mlp = MLP(256, 512, activation=activation, **options)
+    (y0, dx0, dw0), (y1, dx1, dw1) = run_both(mlp, torch.randn(300, 256))
+    assert rel_l2(y1.cpu(), y0) < 2.5e-2
+    assert rel_l2(dx1.cpu(), dx0) < 2.5e-2
+    for a, b in zip(dw1, dw0):
+        assert rel_l2(a.cpu(), b) < 2.5e-2
+
+
+def test_frozen_weight_and_no_grad_paths():
+    layer = Linear(128, 256).cuda()
+    layer.weight.requires_grad_(False)
+    x = torch.randn(64, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    layer(x).sum().backward()
+    assert x.grad is not None and layer.weight.grad is None and layer.bias.grad is not None
+    with torch.no_grad():
+        assert layer(x).shape == (64, 256)
+
+
+def test_expert_linear():
+    torch.manual_seed(0)
+    for scaling in ("current", "grouped"):
+        layer = GroupedLinear(4, 256, 384, scaling=scaling).cuda()
+        counts = [130, 0, 77, 300]
+        offsets = torch.tensor([0, 130, 130, 207, 507], device="cuda", dtype=torch.int32)
+        x = torch.randn(sum(counts), 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        y = layer(x, offsets)
+        y.float().square().mean().backward()
+        expected = torch.cat([x[offsets[e]:offsets[e + 1]].float() @ layer.weight[e].float().t() for e in range(4)])
+        assert rel_l2(y, expected) < 5e-2
+        xr = x.detach().float().requires_grad_(True)
+        wr = layer.weight.detach().float().requires_grad_(True)
+        ref = torch.cat([xr[offsets[e]:offsets[e + 1]] @ wr[e].t() for e in range(4)])
+        ref.square().mean().backward()
+        assert rel_l2(x.grad, xr.grad) < 8e-2
+        assert rel_l2(layer.weight.grad, wr.grad) < 8e-2
+
+
+@pytest.mark.parametrize("shape", [(256, 256), (128, 512), (1152, 384), (2, 96, 160)])
+@pytest.mark.parametrize("method", ["standard", "gram"])
+def test_newton_schulz(shape, method):
+    torch.manual_seed(0)
+    x = torch.randn(shape, device="cuda").bfloat16()
+    result = orthogonalize.METHODS[method](x, steps=5)
+    expected = orthogonalize.METHODS[method](x.cpu(), steps=5)
+    assert result.shape == x.shape and result.dtype == expected.dtype
+    assert rel_l2(result.cpu(), expected) < 6e-2
+    singular = torch.linalg.svdvals(result.float().reshape(-1, *shape[-2:])[0])
+    assert singular.max() < 1.3 and singular.min() > 0.4
+
+
+@pytest.mark.parametrize("options", [dict(), dict(rounding="stochastic", rounding_seed=3), dict(granularity="block"),
+                                     dict(ns_method="gram"), dict(mode="stable", adjust_lr_fn="original")])
+def test_fp8_muon_step_matches_cpu(options):
+    torch.manual_seed(0)
+    params_cpu = [torch.nn.Parameter(torch.randn(256, 512) * 0.02), torch.nn.Parameter(torch.randn(512)),
+                  torch.nn.Parameter(torch.randn(384, 256) * 0.02)]
+    params_gpu = [torch.nn.Parameter(p.detach().cuda()) for p in params_cpu]
+    grads = [torch.randn_like(p) * 1e-3 for p in params_cpu]
+    optimizers = [FP8Muon(params, lr=1e-2, weight_decay=0.01, **options) for params in (params_cpu, params_gpu)]
+    for _ in range(2):
+        for params, optimizer in zip((params_cpu, params_gpu), optimizers):
+            for p, g in zip(params, grads):
+                p.grad = g.to(p.device)
+            optimizer.step()
+    for a, b in zip(params_cpu, params_gpu):
+        delta_a, delta_b = a.detach(), b.detach().cpu()
+        assert rel_l2(delta_b, delta_a) < 2e-3
+    state = optimizers[1].state[params_gpu[0]]
+    assert state["momentum_q"].dtype == torch.uint8 and state["momentum_scale"].dtype == torch.float32
+
+
+def test_training_reduces_loss_and_resumes_exactly():
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(Linear(128, 256), torch.nn.GELU(), Linear(256, 128)).cuda()
+    optimizer = bind_optimizer(model, FP8Muon(model.parameters(), lr=2e-2))
+    x, target = torch.randn(512, 128, device="cuda"), torch.randn(512, 128, device="cuda")
+    losses = []
+    for step in range(60):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = (model(x).float() - target).square().mean()
+        loss.backward()
+        optimizer.step()
+        optimizer.zero_grad()
+        losses.append(loss.item())
+        if step == 29:
+            saved = copy.deepcopy((model.state_dict(), optimizer.state_dict()))
+    assert losses[-1] < 0.85 * losses[0], losses[::10]
+    clone = torch.nn.Sequential(Linear(128, 256), torch.nn.GELU(), Linear(256, 128)).cuda()
+    clone_optimizer = bind_optimizer(clone, FP8Muon(clone.parameters(), lr=2e-2))
+    clone.load_state_dict(saved[0])
+    clone_optimizer.load_state_dict(saved[1])
+    replay = []
+    for step in range(30, 60):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = (clone(x).float() - target).square().mean()
+        loss.backward()
+        clone_optimizer.step()
+        clone_optimizer.zero_grad()
+        replay.append(loss.item())
+    assert replay == losses[30:]
+
+
+def test_engine_single_gpu_dit_step():
+    from viola_b200.models import DiT, NoiseSchedule, diffusion_loss, muon_parameter_groups
+    config = dict(mixed_precision="bf16", gradient_accumulation_steps=2,
+                  sharding=dict(parameters=True, gradients=True, optimizer=True, ema=True),
+                  communication=dict(dtype="fp8"), ema=dict(decay=0.999))
+    engine = viola.violaEngine(config)
+    torch.manual_seed(0)
+    model = engine.prepare_model(DiT(width=256, depth=2, heads=4, patch=2))
+    engine.prepare_optimizer(lambda params: FP8Muon(muon_parameter_groups(model, lr=1e-3)))
+    schedule = NoiseSchedule(device=engine.device)
+    losses = []
+    for step in range(4):
+        for micro in range(2):
+            latents = torch.randn(8, 4, 32, 32, device=engine.device)
+            labels = torch.randint(0, 1000, (8,), device=engine.device)
+            timesteps = torch.randint(0, 1000, (8,), device=engine.device)
+            with engine.accumulate():
+                with engine.autocast():
+                    loss = diffusion_loss(model, schedule, latents, labels, timesteps, torch.randn_like(latents))
+                engine.backward(loss)
+        assert engine.step()
+        losses.append(loss.item())
+    assert all(v == v for v in losses) and engine.global_step == 4
+    with engine.ema_scope() as averaged:
+        assert not averaged.training
+    engine.close()

@@ -310,13 +310,13 @@ def test_wire_codec(tile, fmt):
     ops.wire_unpack(packet, out, tile, fmt)
     rout = torch.empty(n)
     ref.wire_unpack(packet.cpu(), rout, tile, fmt)
-    assert rel_l2(out, rout) < 2e-6
+    assert rel_l2(out.cpu(), rout) < 2e-6
     width = groups * tile
     partial = torch.empty(width, device=dev())
     ops.wire_unpack(packet, partial, tile, fmt, reduce=True)
     rpartial = torch.empty(width)
     ref.wire_unpack(packet.cpu(), rpartial, tile, fmt, reduce=True)
-    assert rel_l2(partial, rpartial) < 2e-6
+    assert rel_l2(partial.cpu(), rpartial) < 2e-6
     x[5] = float("nan")
     ops.wire_pack(x, packet, tile, fmt)
     ops.wire_unpack(packet, out, tile, fmt)

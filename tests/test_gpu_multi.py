@@ -1,0 +1,187 @@
+"""Fused peer-memory communication paths on 2+ GPUs, against the collective-library path and the
+fake-quant oracle (bounds of checks/fp8_communication.py:75: reduce-to-owner < 2e-6, all-reduce with
+two quantisations < 3e-3 relative L2), plus the bounded-wait failure path on one GPU.
+"""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+GPUS = torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def free_port():
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        return sock.getsockname()[1]
+
+
+def launch(target, world, *args):
+    context = mp.get_context("spawn")
+    results = context.Queue()
+    port = free_port()
+    processes = [context.Process(target=target, args=(rank, world, port, *args, results)) for rank in range(world)]
+    for process in processes:
+        process.start()
+    for process in processes:
+        process.join(timeout=600)
+    codes = [process.exitcode for process in processes]
+    assert all(code == 0 for code in codes), codes
+    return [results.get(timeout=5) for _ in processes]
+
+
+def setup(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+
+
+def fake_quant(x, tile, fmt):
+    limit = 448.0 if fmt == torch.float8_e4m3fn else 57344.0
+    padded = torch.nn.functional.pad(x, (0, (-x.numel()) % tile)).view(-1, tile)
+    scale = padded.abs().amax(1, keepdim=True).clamp_min(1e-30) / limit
+    return ((padded / scale).to(fmt).float() * scale).flatten()[:x.numel()]
+
+
+def collectives_worker(rank, world, port, results):
+    setup(rank, world, port)
+    import viola_b200 as viola
+    from viola_b200 import ops
+    from viola_b200.parallel.symm import PeerTransport
+    engine = viola.violaEngine(dict(communication=dict(dtype="fp8", backend="p2p")))
+    device = engine.device
+    tile, fmt = 256, torch.float8_e4m3fn
+    for n in (1000, 70_001, 3_000_000):
+        torch.manual_seed(n + rank)
+        local = torch.randn(n, device=device) * 1e-3
+        local[::997] *= 100
+        gathered = [torch.empty_like(local) for _ in range(world)]
+        dist.all_gather(gathered, local)
+        # ---- path 1: reduce to owner (two generations to exercise the ack flow) ----
+        transport = PeerTransport(engine, tile_size=tile)
+        owner = 1 % world
+        accum = torch.zeros(n, device=device) if rank == owner else None
+        transport.attach_gradients([(owner, [], n)], [accum], n)
+        transport.finalize()
+        transport.finalize_gradients()
+        expected = torch.zeros(n, device=device)
+        for generation in range(2):
+            index, staging = transport.next_staging()
+            staging[:n].copy_(local * (generation + 1))
+            transport.reduce_to_owner(0, index, n)
+            for source in gathered:
+                expected += fake_quant(source * (generation + 1), tile, fmt)
+        transport.synchronize()
+        torch.cuda.synchronize()
+        ops.check_status()
+        if rank == owner:
+            assert rel_l2(accum, expected) < 2e-6, (n, rel_l2(accum, expected))
+        dist.barrier()
+        # ---- path 2: all-reduce with requantisation ----
+        transport = PeerTransport(engine, tile_size=tile)
+        transport.attach_all_reduce(n)
+        transport.finalize()
+        transport.finalize_all_reduce()
+        value = local.clone()
+        transport.all_reduce(value)
+        again = local.clone()
+        transport.all_reduce(again)
+        torch.cuda.synchronize()
+        ops.check_status()
+        exact = torch.stack(gathered).sum(0)
+        assert rel_l2(value, exact) < 5e-2
+        assert torch.equal(value, again)
+        # identical on every rank, and equal to the collective-library implementation
+        from viola_b200.parallel.fp8 import FP8Communication
+        library = FP8Communication(n, engine.group, rank, world, engine.global_ranks, device, mode="all_reduce",
+                                   tile_size=tile)
+        reference = local.clone()
+        library.all_reduce(reference)
+        assert rel_l2(value, reference) < 3e-3
+        everyone = [torch.empty_like(value) for _ in range(world)]
+        dist.all_gather(everyone, value)
+        assert all(torch.equal(everyone[0], other) for other in everyone)
+        dist.barrier()
+    dist.destroy_process_group()
+    results.put(rank)
+
+
+def training_worker(rank, world, port, backend, results):
+    setup(rank, world, port)
+    import viola_b200 as viola
+    from viola_b200 import ops
+    from viola_b200.models import DiT, NoiseSchedule, diffusion_loss, muon_parameter_groups
+    config = dict(mixed_precision="bf16", gradient_accumulation_steps=2,
+                  sharding=dict(parameters=True, gradients=True, optimizer=True, ema=True),
+                  communication=dict(dtype="fp8", backend=backend, bucket_mb=1), ema=dict(decay=0.999))
+    engine = viola.violaEngine(config)
+    torch.manual_seed(0)
+    model = engine.prepare_model(DiT(width=256, depth=3, heads=4, patch=2))
+    engine.prepare_optimizer(lambda params: viola.optim.FP8Muon(muon_parameter_groups(model, lr=1e-3)))
+    assert (engine.transport is not None) == (backend == "p2p")
+    schedule = NoiseSchedule(device=engine.device)
+    losses = []
+    for step in range(3):
+        for micro in range(2):
+            generator = torch.Generator(device=engine.device).manual_seed(100 * step + 10 * micro + rank)
+            latents = torch.randn(4, 4, 32, 32, device=engine.device, generator=generator)
+            labels = torch.randint(0, 1000, (4,), device=engine.device, generator=generator)
+            timesteps = torch.randint(0, 1000, (4,), device=engine.device, generator=generator)
+            noise = torch.randn(4, 4, 32, 32, device=engine.device, generator=generator)
+            with engine.accumulate():
+                with engine.autocast():
+                    loss = diffusion_loss(model, schedule, latents, labels, timesteps, noise)
+                engine.backward(loss)
+        assert engine.step()
+        losses.append(loss.item())
+    torch.cuda.synchronize()
+    ops.check_status()
+    weights = engine.state.parameters.model_state_dict()
+    engine.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    if rank == 0:
+        results.put((losses, {k: v.float() for k, v in weights.items() if isinstance(v, torch.Tensor)}))
+    else:
+        results.put(None)
+
+
+@pytest.mark.skipif(GPUS < 2, reason="needs 2 GPUs")
+def test_fused_collectives_match_oracle():
+    launch(collectives_worker, min(GPUS, 4))
+
+
+@pytest.mark.skipif(GPUS < 2, reason="needs 2 GPUs")
+def test_engine_peer_backend_matches_collective_backend():
+    outputs = {}
+    for backend in ("nccl", "p2p"):
+        outputs[backend] = next(item for item in launch(training_worker, 2, backend) if item is not None)
+    losses_a, weights_a = outputs["nccl"]
+    losses_b, weights_b = outputs["p2p"]
+    assert losses_a == pytest.approx(losses_b, rel=2e-2)
+    for name in weights_a:
+        assert rel_l2(weights_b[name], weights_a[name]) < 2e-2, name
+
+
+def test_bounded_wait_reports_and_returns():
+    """A wait on a flag nobody sets runs out of its budget, records a status and leaves the GPU usable."""
+    from viola_b200 import ops
+    ops.load()
+    device = torch.device("cuda", 0)
+    flags = torch.zeros(4, device=device, dtype=torch.int32)
+    status = ops.status_word(device)
+    torch.ops.viola_b200.wait_flags(flags.data_ptr(), 4, -1, 1, 2_000_000, status)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="peer flag"):
+        ops.check_status(device)
+    flags.fill_(1)
+    torch.ops.viola_b200.wait_flags(flags.data_ptr(), 4, -1, 1, 2_000_000, status)
+    torch.cuda.synchronize()
+    ops.check_status(device)
+    assert torch.ones(8, device=device).sum().item() == 8

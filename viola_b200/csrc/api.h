@@ -111,33 +111,48 @@ int vb_wire_pack(const float* x, long long n, int rows, int groups, int tile, in
 int vb_wire_unpack(const uint8_t* packet, long long row_stride, int rows, int groups, int tile, int fmt,
                    int reduce, float* out, long long n, int accumulate, cudaStream_t stream);
 
-// ---- fused communication (peer memory) ----------------------------------------------
+// ---- fused communication over peer memory (comm.cu) ---------------------------------
+// Every rank maps every rank's symmetric heap; buffers[r] is rank r's heap base in this
+// process's address space and offsets are identical on all ranks.
 typedef struct VbPeerTable {
-  void* buffers[16];     // symmetric data buffer on every rank (index = rank)
-  int* flags[16];        // symmetric int32 flag array on every rank
+  void* buffers[16];
   int world, rank;
 } VbPeerTable;
 
-// Path 1: quantise the local fp32 bucket and push [codes|scales] into the owner's slot for
-// this rank; the owner then dequantises all ranks in ascending order and adds to `accum`.
-int vb_reduce_to_owner_fp8(const float* bucket, long long n, int tile, int fmt, int owner,
-                           const VbPeerTable* peers, long long slot_bytes, long long region_offset,
-                           int flag_index, int generation, float* accum, int* status,
-                           cudaStream_t stream);
-// Path 2: all-reduce with a second quantisation (reduce-scatter by push, requantise, all-gather by push).
+// Path 1 (non-owner): quantise the local fp32 bucket tile by tile and store codes + scales straight
+// into the owner's receive slot, then raise the owner's flag for this source rank.
+int vb_reduce_push_fp8(const float* bucket, long long n, int tile, int fmt, void* dst_codes, float* dst_scales,
+                       int* dst_flag, const int* ack_flag, int generation, unsigned int* counter,
+                       long long wait_clocks, int max_blocks, int* status, cudaStream_t stream);
+// Path 1 (owner): wait for every peer's flag, then accum += sum over ranks (ascending, fp32) of the
+// dequantised contributions; the owner's own bucket goes through the same quantise-dequantise.
+int vb_reduce_accumulate_fp8(const float* bucket, long long n, int tile, int fmt, const void* recv,
+                             long long slot_stride, long long scales_offset, const int* flags,
+                             const VbPeerTable* peers, long long ack_offset, int generation, float* accum,
+                             unsigned int* counter, long long wait_clocks, int max_blocks, int* status,
+                             cudaStream_t stream);
+// Path 2: in-place FP8 all-reduce with a second quantisation of the partial sums.
 int vb_allreduce_requant_fp8(float* value, long long n, int tile, int fmt, const VbPeerTable* peers,
-                             long long region_offset, long long region_bytes, int flag_index,
-                             int generation, int* status, cudaStream_t stream);
-// Path 4 helper: owner pushes `bytes` to every peer (broadcast) or row shards to each peer, then flags.
-int vb_owner_push(const void* src, long long bytes, const VbPeerTable* peers, long long dst_offset,
-                  int flag_index, int generation, int sharded, long long shard_bytes, int* status,
+                             long long a2a_offset, long long gather_offset, long long slot,
+                             long long a2a_flag_offset, long long gather_flag_offset, int generation,
+                             unsigned int* counters, long long wait_clocks, int max_blocks, int* status,
+                             cudaStream_t stream);
+// Path 4: master -> (EMA) -> FP8 codes stored into every rank (shard_rows == 0) or per-row-slab owner.
+int vb_quantize_push(const void* master, int master_dtype, long long rows, long long cols, const float* scale,
+                     float limit, int fmt, void* ema, int ema_dtype, float decay, const VbPeerTable* peers,
+                     long long dst_offset, long long shard_rows, int max_blocks, cudaStream_t stream);
+int vb_byte_push(const void* src, long long bytes, const VbPeerTable* peers, long long dst_offset,
+                 long long shard_bytes, int max_blocks, cudaStream_t stream);
+// flags[rank] = value on every peer (and optionally on this rank); bounded wait on local flags
+int vb_signal(const VbPeerTable* peers, long long flag_offset, int value, int include_self, cudaStream_t stream);
+int vb_wait_flags(const int* flags, int count, int skip, int expected, long long wait_clocks, int* status,
                   cudaStream_t stream);
-int vb_wait_flag(const VbPeerTable* peers, int flag_index, int generation, int count, int* status,
-                 cudaStream_t stream);
-// Path 3 helper: pull peers' row shards into a local full buffer, flagging each 128-row panel.
-int vb_gather_panels(void* full, const VbPeerTable* peers, long long shard_offset, long long shard_bytes,
-                     long long panel_bytes, int* panel_flags, int generation, int* status,
-                     cudaStream_t stream);
+// Path 3: pull every peer's row slab of every parameter of a unit into the local full buffer.
+// entries: device array of {shard_offset, shard_bytes, full_offset} (3 x int64 each);
+// piece_prefix: device int64[num_entries * world + 1] prefix sums of 64 KiB pieces per (entry, visit slot).
+int vb_gather_pull(const void* entries, int num_entries, const VbPeerTable* peers, long long shard_region_offset,
+                   void* full, const long long* piece_prefix, unsigned int* piece_counts, int* panel_flags,
+                   int generation, long long total_pieces, int max_blocks, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -284,6 +284,102 @@ void wire_unpack(const Tensor& packet, int64_t row_stride, int64_t rows, int64_t
         "wire_unpack");
 }
 
+// ---- peer-memory kernels -----------------------------------------------------------------------
+VbPeerTable peer_table(at::IntArrayRef heaps, int64_t rank) {
+  VbPeerTable table{};
+  TORCH_CHECK(heaps.size() <= 16, "at most 16 ranks per node");
+  table.world = (int)heaps.size();
+  table.rank = (int)rank;
+  for (size_t i = 0; i < heaps.size(); ++i) table.buffers[i] = reinterpret_cast<void*>(heaps[i]);
+  return table;
+}
+
+void reduce_push_fp8(const Tensor& bucket, int64_t tile, int64_t fmt, int64_t dst_codes, int64_t dst_scales,
+                     int64_t dst_flag, int64_t ack_flag, int64_t generation, Tensor counter, int64_t wait_clocks,
+                     int64_t max_blocks, Tensor status) {
+  cuda_contig(bucket, "bucket");
+  c10::cuda::CUDAGuard guard(bucket.device());
+  check(vb_reduce_push_fp8(bucket.data_ptr<float>(), bucket.numel(), (int)tile, (int)fmt, reinterpret_cast<void*>(dst_codes),
+                           reinterpret_cast<float*>(dst_scales), reinterpret_cast<int*>(dst_flag),
+                           reinterpret_cast<const int*>(ack_flag), (int)generation, (unsigned int*)counter.data_ptr(),
+                           wait_clocks, (int)max_blocks, (int*)status.data_ptr(), stream()),
+        "reduce_push_fp8");
+}
+
+void reduce_accumulate_fp8(const Tensor& bucket, int64_t tile, int64_t fmt, int64_t recv, int64_t slot_stride,
+                           int64_t scales_offset, int64_t flags, at::IntArrayRef heaps, int64_t rank, int64_t ack_offset,
+                           int64_t generation, Tensor accum, Tensor counter, int64_t wait_clocks, int64_t max_blocks,
+                           Tensor status) {
+  cuda_contig(bucket, "bucket");
+  TORCH_CHECK(accum.scalar_type() == at::kFloat && accum.numel() >= bucket.numel());
+  c10::cuda::CUDAGuard guard(bucket.device());
+  VbPeerTable table = peer_table(heaps, rank);
+  check(vb_reduce_accumulate_fp8(bucket.data_ptr<float>(), bucket.numel(), (int)tile, (int)fmt,
+                                 reinterpret_cast<const void*>(recv), slot_stride, scales_offset,
+                                 reinterpret_cast<const int*>(flags), &table, ack_offset, (int)generation,
+                                 accum.data_ptr<float>(), (unsigned int*)counter.data_ptr(), wait_clocks, (int)max_blocks,
+                                 (int*)status.data_ptr(), stream()),
+        "reduce_accumulate_fp8");
+}
+
+void allreduce_requant_fp8(Tensor value, int64_t tile, int64_t fmt, at::IntArrayRef heaps, int64_t rank, int64_t a2a_offset,
+                           int64_t gather_offset, int64_t slot, int64_t a2a_flag_offset, int64_t gather_flag_offset,
+                           int64_t generation, Tensor counters, int64_t wait_clocks, int64_t max_blocks, Tensor status) {
+  cuda_contig(value, "value");
+  c10::cuda::CUDAGuard guard(value.device());
+  VbPeerTable table = peer_table(heaps, rank);
+  check(vb_allreduce_requant_fp8(value.data_ptr<float>(), value.numel(), (int)tile, (int)fmt, &table, a2a_offset,
+                                 gather_offset, slot, a2a_flag_offset, gather_flag_offset, (int)generation,
+                                 (unsigned int*)counters.data_ptr(), wait_clocks, (int)max_blocks, (int*)status.data_ptr(),
+                                 stream()),
+        "allreduce_requant_fp8");
+}
+
+void quantize_push(const Tensor& master, const Tensor& scale, double limit, int64_t fmt, const OptTensor& ema, double decay,
+                   at::IntArrayRef heaps, int64_t rank, int64_t dst_offset, int64_t shard_rows, int64_t max_blocks) {
+  cuda_contig(master, "master");
+  TORCH_CHECK(master.dim() == 2);
+  c10::cuda::CUDAGuard guard(master.device());
+  VbPeerTable table = peer_table(heaps, rank);
+  check(vb_quantize_push(master.data_ptr(), dtype_code(master), master.size(0), master.size(1), scale.data_ptr<float>(),
+                         (float)limit, (int)fmt, ptr(ema), ema.has_value() && ema->defined() ? dtype_code(*ema) : 0,
+                         (float)decay, &table, dst_offset, shard_rows, (int)max_blocks, stream()),
+        "quantize_push");
+}
+
+void byte_push(const Tensor& src, at::IntArrayRef heaps, int64_t rank, int64_t dst_offset, int64_t shard_bytes,
+               int64_t max_blocks) {
+  cuda_contig(src, "src");
+  c10::cuda::CUDAGuard guard(src.device());
+  VbPeerTable table = peer_table(heaps, rank);
+  check(vb_byte_push(src.data_ptr(), (long long)src.numel() * src.element_size(), &table, dst_offset, shard_bytes,
+                     (int)max_blocks, stream()),
+        "byte_push");
+}
+
+void signal(at::IntArrayRef heaps, int64_t rank, int64_t flag_offset, int64_t value, bool include_self) {
+  VbPeerTable table = peer_table(heaps, rank);
+  check(vb_signal(&table, flag_offset, (int)value, include_self, stream()), "signal");
+}
+
+void wait_flags(int64_t flags, int64_t count, int64_t skip, int64_t expected, int64_t wait_clocks, Tensor status) {
+  c10::cuda::CUDAGuard guard(status.device());
+  check(vb_wait_flags(reinterpret_cast<const int*>(flags), (int)count, (int)skip, (int)expected, wait_clocks,
+                      (int*)status.data_ptr(), stream()),
+        "wait_flags");
+}
+
+void gather_pull(const Tensor& entries, at::IntArrayRef heaps, int64_t rank, int64_t shard_region_offset, Tensor full,
+                 const Tensor& piece_prefix, Tensor piece_counts, Tensor panel_flags, int64_t generation,
+                 int64_t total_pieces, int64_t max_blocks) {
+  c10::cuda::CUDAGuard guard(full.device());
+  VbPeerTable table = peer_table(heaps, rank);
+  check(vb_gather_pull(entries.data_ptr(), (int)(entries.numel() / 3), &table, shard_region_offset, full.data_ptr(),
+                       (const long long*)piece_prefix.data_ptr(), (unsigned int*)piece_counts.data_ptr(),
+                       (int*)panel_flags.data_ptr(), (int)generation, total_pieces, (int)max_blocks, stream()),
+        "gather_pull");
+}
+
 }  // namespace
 
 TORCH_LIBRARY(viola_b200, m) {
@@ -308,4 +404,12 @@ TORCH_LIBRARY(viola_b200, m) {
   m.def("hadamard64", &hadamard64);
   m.def("wire_pack", &wire_pack);
   m.def("wire_unpack", &wire_unpack);
+  m.def("reduce_push_fp8", &reduce_push_fp8);
+  m.def("reduce_accumulate_fp8", &reduce_accumulate_fp8);
+  m.def("allreduce_requant_fp8", &allreduce_requant_fp8);
+  m.def("quantize_push", &quantize_push);
+  m.def("byte_push", &byte_push);
+  m.def("signal", &signal);
+  m.def("wait_flags", &wait_flags);
+  m.def("gather_pull", &gather_pull);
 }

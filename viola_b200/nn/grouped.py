@@ -40,6 +40,7 @@ class _ExpertLinearFunction(torch.autograd.Function):
             y = ops.expert_gemm(qx, qw.view(experts, n, k), offsets, sx, sw, out_dtype=x.dtype)
         ctx.save_for_backward(x2, weight, offsets)
         ctx.layer = layer
+        ctx.weight_grad_dtype = layer.weight.grad_dtype or torch.float32
         return y
 
     @staticmethod
@@ -65,7 +66,7 @@ class _ExpertLinearFunction(torch.autograd.Function):
                 dx = ops.expert_gemm(qg, qwt.view(experts, k, n), offsets, sg, swt, out_dtype=x.dtype)
         if ctx.needs_input_grad[1]:
             # dW[e] = dY[rows e]^T @ X[rows e]: K = the expert's token count, one GEMM per expert
-            dw = torch.zeros(weight.shape, device=weight.device, dtype=getattr(weight, "grad_dtype", None) or torch.float32)
+            dw = torch.zeros(weight.shape, device=weight.device, dtype=ctx.weight_grad_dtype)
             bounds = offsets.tolist()
             for e in range(experts):
                 lo, hi = bounds[e], bounds[e + 1]

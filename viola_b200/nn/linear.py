@@ -528,6 +528,20 @@ class Linear(nn.Module):
         return _LinearFunction.apply(x, self.weight, self.bias, self, self._needs_backward(x))
 
     # ------------------------------------------------------------------ device moves / checkpoints
+    def __deepcopy__(self, memo):
+        # Parameter.grad_dtype is not carried by copy.deepcopy; an FP8 parameter would then ask
+        # autograd for FP8 gradients.
+        import copy
+        clone = self.__class__.__new__(self.__class__)
+        memo[id(self)] = clone
+        for key, value in self.__dict__.items():
+            clone.__dict__[key] = copy.deepcopy(value, memo)
+        for name in ("weight", "bias"):
+            source, target = self._parameters.get(name), clone._parameters.get(name)
+            if source is not None and target is not None:
+                target.grad_dtype = source.grad_dtype
+        return clone
+
     def _apply(self, fn, recurse=True):
         # Only the device of the FP8 codes, scales and histories may change; dtype casts such as
         # .half() must leave them alone.

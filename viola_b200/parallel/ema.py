@@ -67,8 +67,10 @@ class EMAState:
     @torch.no_grad()
     def apply(self):
         """Write the averages into the compute weights (through the owners, like an optimizer step)."""
+        self.store.begin_writes()
         for record in self.store.records:
             self.store.write(record, self.weights.get(record.name), record.owner)
+        self.store.end_writes()
 
 
 class ShardedEMA:

@@ -43,13 +43,6 @@ class GradientState:
         element = torch.empty((), dtype=self.dtype).element_size()
         total = sum(r.numel for r in self.records)
         capacity = min(max(1, int(bucket_mb * 1024 * 1024) // element), total)
-        owned = [r for r in self.records if not self.shard or r.owner == self.rank]
-        self.accumulator = torch.zeros(sum(r.numel for r in owned), device=device, dtype=gradient_dtype)
-        self.local, offset = {}, 0
-        for index, record in enumerate(self.records):
-            if not self.shard or record.owner == self.rank:
-                self.local[index] = self.accumulator[offset:offset + record.numel]
-                offset += record.numel
         # buckets: (owner, [(record index, offset in parameter, offset in bucket, length)], filled)
         self.buckets, self.piece_counts = [], [0] * len(self.records)
         pieces, filled, owner = [], 0, None
@@ -70,9 +63,31 @@ class GradientState:
                     pieces, filled = [], 0
         if pieces:
             self.buckets.append((owner, pieces, filled))
+        # The accumulator is laid out in bucket order, so every bucket is one contiguous slice of it
+        # (a parameter that spans buckets ends one bucket and starts the next, hence stays contiguous).
+        kept = [not self.shard or bucket_owner == self.rank for bucket_owner, _, _ in self.buckets]
+        self.accumulator = torch.zeros(sum(length for (_, _, length), keep in zip(self.buckets, kept) if keep),
+                                       device=device, dtype=gradient_dtype)
+        self.local, self.bucket_slices, offset = {}, [], 0
+        for (bucket_owner, bucket_pieces, length), keep in zip(self.buckets, kept):
+            if not keep:
+                self.bucket_slices.append(None)
+                continue
+            self.bucket_slices.append(self.accumulator[offset:offset + length])
+            for index, position, target, size in bucket_pieces:
+                if position == 0:
+                    self.local[index] = self.accumulator[offset + target:offset + target + self.records[index].numel]
+            offset += length
         self.bucket_capacity = max(length for _, _, length in self.buckets)
         self.buffer = (torch.empty(self.bucket_capacity, device=device, dtype=self.dtype) if self.world > 1 else None)
-        self.transport = transport
+        self.transport = transport if (transport is not None and self.fp8_requested and self.world > 1
+                                       and gradient_dtype == torch.float32) else None
+        if self.transport is not None:
+            if self.shard:
+                self.transport.attach_gradients(self.buckets, self.bucket_slices, self.bucket_capacity)
+            else:
+                self.transport.attach_all_reduce(self.bucket_capacity)
+        transport = self.transport
         self.fp8 = None
         if self.fp8_requested and self.world > 1 and transport is None:
             self.fp8 = FP8Communication(self.bucket_capacity, self.group, self.rank, self.world, store.global_ranks,
@@ -119,7 +134,11 @@ class GradientState:
             owner, pieces, length = self.buckets[self.next_bucket]
             if not final and any(not self.seen[i] for i, _, _, _ in pieces):
                 break
-            buffer = self.buffer[:length]
+            if self.transport is not None:
+                staging_index, staging = self.transport.next_staging()
+                buffer = staging[:length]
+            else:
+                buffer = self.buffer[:length]
             for index, source, target, size in pieces:
                 slot = buffer[target:target + size]
                 gradient = self.pending[index]
@@ -131,7 +150,7 @@ class GradientState:
                 if not self.remaining[index]:
                     self.pending[index] = None
             if self.transport is not None:
-                self.transport.reduce_to_owner(buffer, owner, self._owner_slices(pieces) if self.rank == owner else None)
+                self.transport.reduce_to_owner(self.next_bucket, staging_index, length)
             else:
                 if self.fp8 is not None:
                     self.fp8.reduce(buffer, owner)
@@ -141,9 +160,6 @@ class GradientState:
                     for index, target, source, size in pieces:
                         self.local[index][target:target + size].add_(buffer[source:source + size])
             self.next_bucket += 1
-
-    def _owner_slices(self, pieces):
-        return [(self.local[index][target:target + size], source, size) for index, target, source, size in pieces]
 
     def finish_backward(self):
         if self.shard:
@@ -161,18 +177,21 @@ class GradientState:
             dist.all_reduce(used, op=dist.ReduceOp.MAX, group=self.group)
             active = used.bool().tolist()
             if not self.shard:
-                for _, pieces, length in self.buckets:
-                    buffer = self.buffer[:length]
-                    for index, source, target, size in pieces:
-                        buffer[target:target + size].copy_(self.local[index][source:source + size])
-                    if self.transport is not None and self.fp8_requested:
-                        self.transport.all_reduce(buffer)
+                for bucket in self.bucket_slices:      # bucket-ordered accumulator: reduce in place, no staging
+                    if self.transport is not None:
+                        self.transport.all_reduce(bucket)
+                    elif self.fp8 is not None and bucket.dtype == torch.float32:
+                        self.fp8.all_reduce(bucket)
                     elif self.fp8 is not None:
+                        buffer = self.buffer[:bucket.numel()].copy_(bucket)
                         self.fp8.all_reduce(buffer)
+                        bucket.copy_(buffer)
+                    elif bucket.dtype == self.dtype:
+                        dist.all_reduce(bucket, group=self.group)
                     else:
+                        buffer = self.buffer[:bucket.numel()].copy_(bucket)
                         dist.all_reduce(buffer, group=self.group)
-                    for index, target, source, size in pieces:
-                        self.local[index][target:target + size].copy_(buffer[source:source + size])
+                        bucket.copy_(buffer)
         else:
             active = list(self.used)
         if self.transport is not None:

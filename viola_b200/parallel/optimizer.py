@@ -106,10 +106,12 @@ class OptimizerState:
 
     @torch.no_grad()
     def writeback(self, active):
+        self.store.begin_writes()
         for record, used in zip(self.store.records, active):
             if used:
                 # always one source, even with replicated state: stochastic / FP8 results stay identical
                 self.store.write(record, self.parameters.get(record.index), record.owner)
+        self.store.end_writes()
 
     @torch.no_grad()
     def full_value(self, record):

@@ -86,8 +86,10 @@ class ParameterRecord:
 
 
 class ParameterStore:
-    def __init__(self, model, optimizer, group, rank, world, global_ranks, gradient_dtype, sharder=None):
+    def __init__(self, model, optimizer, group, rank, world, global_ranks, gradient_dtype, sharder=None,
+                 transport=None):
         self.model, self.group, self.rank, self.world = model, group, rank, world
+        self.transport = transport if sharder is not None else None
         self.global_ranks = list(global_ranks)          # mesh rank -> global rank
         self.sharder = sharder
         self.gradient_dtype = gradient_dtype
@@ -106,6 +108,8 @@ class ParameterStore:
         self.by_parameter = {r.parameter: r for r in self.records}
         self.local = [r for r in self.records if r.owner == rank]
         self.hooks = []
+        if self.transport is not None:
+            self.transport.attach_parameters(sharder, self.records)
 
     def metadata(self):
         return [dict(name=r.name, index=r.index, shape=r.shape, dtype=r.dtype, owner=r.owner, placement=r.placement)
@@ -164,10 +168,63 @@ class ParameterStore:
                     unit.full_view(entry).copy_(local[:entry.rows].view(entry.shape))
         torch.autograd.graph.increment_version(record.parameter)
 
+    # ------------------------------------------------------------------ peer-memory write path
+    def begin_writes(self):
+        """Cross-rank barrier before owners overwrite storage that peers may still be reading."""
+        if self.transport is not None and self.world > 1:
+            token = torch.zeros(1, device=self.records[0].parameter.device)
+            dist.all_reduce(token, group=self.group)
+
+    def end_writes(self):
+        """Publish this rank's stores and wait (bounded, on the stream) for every owner's."""
+        if self.transport is not None and self.world > 1:
+            self.transport.publish_step()
+
+    @torch.no_grad()
+    def _write_peer(self, record, value, source):
+        """Sharded storage in the symmetric heap: the owner stores into every rank's slab directly."""
+        layer, transport = record.layer, self.transport
+        fp8_layer = layer is not None and layer.weight_dtype == "fp8"
+        if fp8_layer and record.index in transport.header_offset:
+            if self.rank == source:
+                limit = layer._quantization_limit(max(layer.in_features, layer.out_features), layer.fp8_dtype)
+                master = value
+                if layer.rotation_size:
+                    from .. import ops
+                    master = ops.hadamard64(value)
+                scale = layer.weight_quantizer.scale(master, layer.fp8_dtype, limit)
+                layer.weight_scale.copy_(scale)
+                from ..ops.reference import fp8_limit
+                transport.write_fp8_weight(record, master.contiguous(), layer.weight_scale, fp8_limit(layer.fp8_dtype, limit))
+            else:
+                layer.weight_quantizer.index += 1
+            layer.clear_weight_cache()
+            torch.autograd.graph.increment_version(record.parameter)
+            return True
+        entry = record.entry
+        if entry.shard_bytes % 16 or (record.unit.heap_offset + entry.shard_offset) % 16:
+            return False
+        if fp8_layer:                       # group-scaled FP8: codes by peer stores, scales by a small broadcast
+            payload = layer.quantize_master(value) if self.rank == source else None
+        else:
+            payload = value.to(record.dtype) if self.rank == source else None
+        if self.rank == source:
+            transport.write_bytes(record, payload)
+        if fp8_layer:
+            header = layer.weight_scale.reshape(-1).float().contiguous()
+            dist.broadcast(header, src=self.global_ranks[source], group=self.group)
+            layer.weight_scale.copy_(header.view(layer.weight_scale.shape).to(layer.weight_scale.dtype))
+            layer.clear_weight_cache()
+        torch.autograd.graph.increment_version(record.parameter)
+        return True
+
     @torch.no_grad()
     def write(self, record, value, source):
         """Owner ``source`` holds the new real-valued ``value``; update the compute storage everywhere."""
         layer = record.layer
+        if self.transport is not None and record.unit is not None and self.world > 1 and not record.unit.unsharded:
+            if self._write_peer(record, value, source):
+                return
         if layer is not None and layer.weight_dtype == "fp8":
             codes = None
             if self.rank == source:

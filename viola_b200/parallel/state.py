@@ -27,7 +27,7 @@ class DistributedState:
         self.sharding = {key: config["sharding"][key] for key in ("parameters", "gradients", "optimizer", "ema")}
         gradient_dtype = to_dtype(config["precision"]["gradient_dtype"])
         self.parameters = ParameterStore(model, optimizer, self.group, self.rank, self.world, self.mesh_ranks,
-                                         gradient_dtype, sharder)
+                                         gradient_dtype, sharder, transport)
         self.optimizer = OptimizerState(self.parameters, optimizer, config)
         communication = config["communication"]
         self.gradients = GradientState(self.parameters, gradient_dtype=gradient_dtype,
@@ -38,6 +38,15 @@ class DistributedState:
                                        transport=transport)
         for position, record in enumerate(self.parameters.records):
             self.gradients.bind(position, record.parameter)
+        if transport is not None:
+            transport.finalize()
+            if self.gradients.transport is not None:
+                if self.gradients.shard:
+                    transport.finalize_gradients()
+                else:
+                    transport.finalize_all_reduce()
+            if self.parameters.transport is not None:
+                transport.finalize_parameters()
         self.ema = EMAState(self.parameters, self.optimizer, decay=config["ema"]["decay"],
                             dtype=to_dtype(config["ema"]["dtype"]), shard=self.sharding["ema"])
 

@@ -9,6 +9,7 @@ import itertools
 import os
 import socket
 import tempfile
+import time
 
 import pytest
 import torch
@@ -162,8 +163,17 @@ def run_world(target, world, *args):
     processes = [context.Process(target=target, args=(rank, world, port, *args, results)) for rank in range(world)]
     for process in processes:
         process.start()
+    deadline = time.time() + 600
+    while any(process.exitcode is None for process in processes) and time.time() < deadline:
+        if any(process.exitcode not in (None, 0) for process in processes):
+            break
+        time.sleep(0.2)
     for process in processes:
-        process.join(timeout=600)
+        if process.exitcode is None:
+            process.join(timeout=5)
+        if process.exitcode is None:
+            process.kill()
+            process.join()
     assert all(process.exitcode == 0 for process in processes), [process.exitcode for process in processes]
     return [results.get(timeout=5) for _ in processes]
 

@@ -129,7 +129,7 @@ def test_fp8_muon_step_matches_cpu(options):
             optimizer.step()
     for a, b in zip(params_cpu, params_gpu):
         delta_a, delta_b = a.detach(), b.detach().cpu()
-        assert rel_l2(delta_b, delta_a) < 5e-3
+        assert rel_l2(delta_b, delta_a) < (1e-2 if options.get("ns_method") == "gram" else 5e-3)
     state = optimizers[1].state[params_gpu[0]]
     assert state["momentum_q"].dtype == torch.uint8 and state["momentum_scale"].dtype == torch.float32
 

@@ -4,6 +4,7 @@ two quantisations < 3e-3 relative L2), plus the bounded-wait failure path on one
 """
 import os
 import socket
+import time
 
 import pytest
 import torch
@@ -29,8 +30,18 @@ def launch(target, world, *args):
     processes = [context.Process(target=target, args=(rank, world, port, *args, results)) for rank in range(world)]
     for process in processes:
         process.start()
+    # fail fast: a rank that dies must not leave its peers waiting in a collective
+    deadline = time.time() + 300
+    while any(process.exitcode is None for process in processes) and time.time() < deadline:
+        if any(process.exitcode not in (None, 0) for process in processes):
+            break
+        time.sleep(0.2)
     for process in processes:
-        process.join(timeout=600)
+        if process.exitcode is None:
+            process.join(timeout=5)
+        if process.exitcode is None:
+            process.kill()
+            process.join()
     codes = [process.exitcode for process in processes]
     assert all(code == 0 for code in codes), codes
     return [results.get(timeout=5) for _ in processes]
@@ -45,7 +56,8 @@ def setup(rank, world, port):
 def fake_quant(x, tile, fmt):
     limit = 448.0 if fmt == torch.float8_e4m3fn else 57344.0
     padded = torch.nn.functional.pad(x, (0, (-x.numel()) % tile)).view(-1, tile)
-    scale = padded.abs().amax(1, keepdim=True).clamp_min(1e-30) / limit
+    amax = padded.abs().amax(1, keepdim=True).clamp_min(1e-30)
+    scale = amax / torch.full_like(amax, limit)      # tensor / tensor is a true division (scalar divisors are not)
     return ((padded / scale).to(fmt).float() * scale).flatten()[:x.numel()]
 
 

@@ -60,6 +60,9 @@ typedef struct VbGemmDesc {
   int* tile_map;         // workspace int32[3 * (ceil(M/128) + E)] when expert_offsets != null
   int* status;           // int32[8] device status word (zeroed by caller) or null
   int force_bn;          // 0 = auto, else 64 / 128 / 256
+  // batched problems (LINEAR / AXPBY): A is [batch * M, K], B is [batch * N, K]; strides in elements
+  int batch;
+  long long out_batch_stride, resid_batch_stride, out_t_batch_stride;
 } VbGemmDesc;
 
 int vb_gemm(const VbGemmDesc* desc, cudaStream_t stream);
@@ -86,9 +89,9 @@ int vb_momentum16(const void* grad, int grad_dtype, void* momentum, int momentum
                   long long n, float beta, int nesterov, cudaStream_t stream);
 // Frobenius-norm based prescale for Newton-Schulz: out = x / (||x||_F + eps) in `out_dtype`,
 // optionally also writing the transpose.  scratch: float[2] (zeroed; self-resetting).
-int vb_sumsq(const void* x, int dtype, long long n, float* accum, cudaStream_t stream);
+int vb_sumsq(const void* x, int dtype, long long n, float* accum, int batch, cudaStream_t stream);
 int vb_ns_prescale(const void* x, int dtype, int rows, int cols, const float* sumsq, float eps, void* out,
-                   void* out_t, int out_dtype, cudaStream_t stream);
+                   void* out_t, int out_dtype, int batch, cudaStream_t stream);
 // master -> EMA lerp fused with optional dtype casts (owner-side writeback helper)
 int vb_ema_lerp(void* ema, int ema_dtype, const void* master, int master_dtype, long long n, float decay,
                 cudaStream_t stream);

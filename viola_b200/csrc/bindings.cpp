@@ -85,9 +85,11 @@ void group_decode(const Tensor& q, const Tensor& s, int64_t gr, int64_t gc, int6
 void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t epilogue, int64_t n_logical, const OptTensor& sa,
           const OptTensor& sb, at::IntArrayRef scale_layout, const OptTensor& bias, double alpha, double beta,
           const OptTensor& resid, const OptTensor& out_t, bool symmetric, int64_t activation, const OptTensor& aux,
-          const OptTensor& expert_offsets, const OptTensor& tile_map, const OptTensor& status, int64_t force_bn) {
+          const OptTensor& expert_offsets, const OptTensor& tile_map, const OptTensor& status, int64_t force_bn,
+          int64_t batch) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda());
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && out.stride(-1) == 1);
+  TORCH_CHECK(batch >= 1 && a.size(0) % batch == 0 && b.size(0) % batch == 0);
   TORCH_CHECK(a.size(1) == b.size(1), "K mismatch");
   c10::cuda::CUDAGuard guard(a.device());
   VbGemmDesc d{};
@@ -102,7 +104,8 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t epilogue, int64_
     TORCH_CHECK(a.scalar_type() == at::kBFloat16 || a.scalar_type() == at::kHalf);
   }
   d.epilogue = (int)epilogue;
-  d.M = (int)a.size(0);
+  d.batch = (int)batch;
+  d.M = (int)(a.size(0) / batch);
   d.N = (int)n_logical;
   d.K = (int)a.size(1);
   d.A = a.data_ptr();
@@ -118,15 +121,18 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t epilogue, int64_
   TORCH_CHECK(!d.group || (d.sa && d.sb), "group-scaled GEMM needs both scale tensors");
   d.out = out.data_ptr();
   d.out_dtype = dtype_code(out);
-  d.ldo = out.stride(0);
+  d.ldo = out.stride(-2);
+  d.out_batch_stride = batch > 1 ? out.stride(0) : 0;
   d.bias = ptr(bias);
   d.bias_dtype = bias.has_value() && bias->defined() ? dtype_code(*bias) : 0;
   d.alpha = (float)alpha; d.beta = (float)beta;
   d.resid = ptr(resid);
-  d.ldr = resid.has_value() && resid->defined() ? resid->stride(0) : 0;
+  d.ldr = resid.has_value() && resid->defined() ? resid->stride(-2) : 0;
+  d.resid_batch_stride = batch > 1 && d.resid ? resid->stride(0) : 0;
   if (d.resid) TORCH_CHECK(resid->scalar_type() == out.scalar_type(), "residual dtype must match the output");
   d.out_t = ptr(out_t);
-  d.ldot = out_t.has_value() && out_t->defined() ? out_t->stride(0) : 0;
+  d.ldot = out_t.has_value() && out_t->defined() ? out_t->stride(-2) : 0;
+  d.out_t_batch_stride = batch > 1 && d.out_t ? out_t->stride(0) : 0;
   d.symmetric = symmetric;
   d.activation = (int)activation;
   d.aux = ptr(aux);
@@ -210,19 +216,23 @@ void momentum16(const Tensor& grad, Tensor momentum, Tensor update, double beta,
 }
 
 void sumsq(const Tensor& x, int64_t round_dtype, Tensor accum) {
+  // x: [batch, n] (or [n]); accum: float[batch], pre-zeroed
   cuda_contig(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
-  check(vb_sumsq(x.data_ptr(), dtype_code(x) | ((int)round_dtype << 8), x.numel(), accum.data_ptr<float>(), stream()),
+  const int64_t batch = accum.numel();
+  check(vb_sumsq(x.data_ptr(), dtype_code(x) | ((int)round_dtype << 8), x.numel() / batch, accum.data_ptr<float>(),
+                 (int)batch, stream()),
         "sumsq");
 }
 
 void ns_prescale(const Tensor& x, const Tensor& sumsq_t, double eps, const OptTensor& out, const OptTensor& out_t) {
   cuda_contig(x, "x");
-  TORCH_CHECK(x.dim() == 2);
+  TORCH_CHECK(x.dim() == 2 || x.dim() == 3);
   const Tensor& ref = out.has_value() && out->defined() ? *out : *out_t;
   c10::cuda::CUDAGuard guard(x.device());
-  check(vb_ns_prescale(x.data_ptr(), dtype_code(x), (int)x.size(0), (int)x.size(1), sumsq_t.data_ptr<float>(),
-                       (float)eps, ptr(out), ptr(out_t), dtype_code(ref), stream()),
+  const int batch = x.dim() == 3 ? (int)x.size(0) : 1;
+  check(vb_ns_prescale(x.data_ptr(), dtype_code(x), (int)x.size(-2), (int)x.size(-1), sumsq_t.data_ptr<float>(),
+                       (float)eps, ptr(out), ptr(out_t), dtype_code(ref), batch, stream()),
         "ns_prescale");
 }
 

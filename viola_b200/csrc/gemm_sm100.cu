@@ -61,8 +61,18 @@ struct GemmArgs {
   long long ldaux;
   const int* tile_map;  // expert mode: [3 * num_m_tiles] = (row0, row_end, expert), row0 < 0 = unused
   int expert_rows;      // rows of B per expert (= N)
+  // batched mode: `batch` independent problems stacked along the rows of A, B and the outputs
+  int batch, tiles_per_batch;
+  long long b_rows_per_batch, out_bs, resid_bs, out_t_bs;
   int* status;
 };
+
+__device__ __forceinline__ void* advance(void* p, long long elems, int dt) {
+  return p == nullptr ? nullptr : (void*)(reinterpret_cast<char*>(p) + elems * (dt == 0 ? 4 : 2));
+}
+__device__ __forceinline__ const void* advance(const void* p, long long elems, int dt) {
+  return p == nullptr ? nullptr : (const void*)(reinterpret_cast<const char*>(p) + elems * (dt == 0 ? 4 : 2));
+}
 
 // ---------------------------------------------------------------------------------------
 // small device helpers
@@ -259,8 +269,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     bool ok = true;
     for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
       int mt, nt;
-      tile_coords(args, t, mt, nt);
-      int a_row = mt * BM, b_row = nt * C::kBBoxRows;
+      const int bi = t / args.tiles_per_batch;
+      tile_coords(args, t - bi * args.tiles_per_batch, mt, nt);
+      int a_row = bi * args.M + mt * BM, b_row = (int)(bi * args.b_rows_per_batch) + nt * C::kBBoxRows;
       if (args.tile_map != nullptr) {
         const int row0 = args.tile_map[3 * mt];
         if (row0 < 0) continue;
@@ -348,9 +359,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     constexpr int NOUT = C::kGatedFwd ? NCHUNK / 2 : NCHUNK;  // output chunks per tile
     for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
       int mt, nt;
-      tile_coords(args, t, mt, nt);
+      const int bi = t / args.tiles_per_batch;
+      tile_coords(args, t - bi * args.tiles_per_batch, mt, nt);
       long long grow = (long long)mt * BM + row_in_tile;
       long long row_end = args.M;
+      void* const out_base = advance(args.out, bi * args.out_bs, args.out_dtype);
+      const void* const resid_base = advance(args.resid, bi * args.resid_bs, args.out_dtype);
+      void* const out_t_base = advance(args.out_t, bi * args.out_t_bs, args.out_dtype);
       int expert = 0;
       if (args.tile_map != nullptr) {
         const int row0 = args.tile_map[3 * mt];
@@ -450,10 +465,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int j = 0; j < 32; ++j)
               if (col0 + j < args.N) v[j] += load_elem(args.bias, col0 + j, args.bias_dtype);
           }
-          if (row_ok) store_row32(args.out, args.ldo, args.out_dtype, grow, col0, args.N, v);
+          if (row_ok) store_row32(out_base, args.ldo, args.out_dtype, grow, col0, args.N, v);
         } else if constexpr (EPI == VB_EPI_AXPBY) {
           float res[32];
-          if (args.resid != nullptr && row_ok) load_row32(args.resid, args.ldr, args.out_dtype, grow, col0, args.N, res);
+          if (resid_base != nullptr && row_ok) load_row32(resid_base, args.ldr, args.out_dtype, grow, col0, args.N, res);
           else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) res[j] = 0.f;
@@ -461,10 +476,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             v[j] = round_to(args.alpha * round_to(v[j], args.out_dtype) + args.beta * res[j], args.out_dtype);
-          if (row_ok) store_row32(args.out, args.ldo, args.out_dtype, grow, col0, args.N, v);
-          void* tbase = args.out_t;
+          if (row_ok) store_row32(out_base, args.ldo, args.out_dtype, grow, col0, args.N, v);
+          void* tbase = out_t_base;
           long long tld = args.ldot;
-          if (args.symmetric && mt != nt) { tbase = args.out; tld = args.ldo; }
+          if (args.symmetric && mt != nt) { tbase = out_base; tld = args.ldo; }
           if (tbase != nullptr && row_ok) {
             // transposed copy: lanes hold consecutive rows -> consecutive addresses per column
 #pragma unroll
@@ -629,10 +644,15 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream) {
   a.num_k_blocks = (d.K + C::kBK - 1) / C::kBK;
   if (d.symmetric) {
     if (d.M != d.N || BN != BM || expert) return (int)cudaErrorInvalidValue;
-    a.num_tiles = a.num_m_tiles * (a.num_m_tiles + 1) / 2;
+    a.tiles_per_batch = a.num_m_tiles * (a.num_m_tiles + 1) / 2;
   } else {
-    a.num_tiles = a.num_m_tiles * a.num_n_tiles;
+    a.tiles_per_batch = a.num_m_tiles * a.num_n_tiles;
   }
+  a.batch = d.batch > 1 ? d.batch : 1;
+  if (a.batch > 1 && (expert || EPI == VB_EPI_GATED_FWD || EPI == VB_EPI_GATED_BWD)) return (int)cudaErrorInvalidValue;
+  a.num_tiles = a.batch * a.tiles_per_batch;
+  a.b_rows_per_batch = d.N;
+  a.out_bs = d.out_batch_stride; a.resid_bs = d.resid_batch_stride; a.out_t_bs = d.out_t_batch_stride;
   a.idesc = make_idesc(d.a_fmt, d.b_fmt, BM, BN);
   a.b_gate_up_offset = d.N;
   a.sa = d.sa; a.sb = d.sb;
@@ -648,9 +668,9 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream) {
   a.status = d.status;
   if (a.num_tiles <= 0 || a.num_k_blocks <= 0) return 0;
 
-  const long long b_rows = (long long)(C::kGatedFwd ? 2 : 1) * d.N * (expert ? d.num_experts : 1);
+  const long long b_rows = (long long)(C::kGatedFwd ? 2 : 1) * d.N * (expert ? d.num_experts : 1) * a.batch;
   CUtensorMap tmA, tmB;
-  int rc = make_map(&tmA, d.A, KIND, d.a_fmt, d.M, d.K, d.lda, BM);
+  int rc = make_map(&tmA, d.A, KIND, d.a_fmt, (long long)d.M * a.batch, d.K, d.lda, BM);
   if (rc) return rc;
   rc = make_map(&tmB, d.B, KIND, d.b_fmt, b_rows, d.K, d.ldb, C::kBBoxRows);
   if (rc) return rc;

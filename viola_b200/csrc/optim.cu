@@ -211,9 +211,12 @@ momentum16_kernel(const void* __restrict__ grad, int gdt, void* __restrict__ mom
 // sum of squares of x rounded to `round_dt` first (Newton-Schulz normalises the bf16/fp16 copy)
 __global__ void __launch_bounds__(256)
 sumsq_kernel(const void* __restrict__ x, int dt, int round_dt, long long n, float* __restrict__ accum) {
+  // blockIdx.y selects one of gridDim.y stacked tensors of n elements each
+  accum += blockIdx.y;
+  const long long base = (long long)blockIdx.y * n;
   float s = 0.f;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    float v = load_as_float(x, i, dt);
+    float v = load_as_float(x, base + i, dt);
     if (round_dt == kBF16) v = __bfloat162float(__float2bfloat16_rn(v));
     else if (round_dt == kF16) v = __half2float(__float2half_rn(v));
     s += v * v;
@@ -235,7 +238,13 @@ __global__ void __launch_bounds__(256)
 ns_prescale_kernel(const void* __restrict__ x, int dt, int rows, int cols, const float* __restrict__ sumsq,
                    float eps, void* __restrict__ out, void* __restrict__ out_t, int odt) {
   __shared__ float tile[64][65];
-  const float inv = 1.f / (sqrtf(sumsq[0]) + eps);
+  // blockIdx.z selects one of the stacked matrices
+  const float inv = 1.f / (sqrtf(sumsq[blockIdx.z]) + eps);
+  const long long plane = (long long)blockIdx.z * rows * cols;
+  const int esize = dt == kF32 ? 4 : 2, osize = odt == kF32 ? 4 : 2;
+  x = reinterpret_cast<const char*>(x) + plane * esize;
+  if (out != nullptr) out = reinterpret_cast<char*>(out) + plane * osize;
+  if (out_t != nullptr) out_t = reinterpret_cast<char*>(out_t) + plane * osize;
   const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
   for (int i = threadIdx.x; i < 64 * 64; i += blockDim.x) {
     const int tr = i >> 6, tc = i & 63;
@@ -444,16 +453,17 @@ extern "C" int vb_momentum16(const void* grad, int grad_dtype, void* momentum, i
   return (int)cudaGetLastError();
 }
 
-extern "C" int vb_sumsq(const void* x, int dtype, long long n, float* accum, cudaStream_t stream) {
+extern "C" int vb_sumsq(const void* x, int dtype, long long n, float* accum, int batch, cudaStream_t stream) {
   // `dtype` packs the storage dtype in the low byte and the rounding dtype in the next byte.
-  if (n <= 0) return 0;
-  sumsq_kernel<<<grid_for(n, 1024), 256, 0, stream>>>(x, dtype & 0xff, (dtype >> 8) & 0xff, n, accum);
+  if (n <= 0 || batch <= 0) return 0;
+  dim3 grid(std::min(grid_for(n, 1024), 256), batch);
+  sumsq_kernel<<<grid, 256, 0, stream>>>(x, dtype & 0xff, (dtype >> 8) & 0xff, n, accum);
   return (int)cudaGetLastError();
 }
 
 extern "C" int vb_ns_prescale(const void* x, int dtype, int rows, int cols, const float* sumsq, float eps, void* out,
-                              void* out_t, int out_dtype, cudaStream_t stream) {
-  dim3 grid((cols + 63) / 64, (rows + 63) / 64);
+                              void* out_t, int out_dtype, int batch, cudaStream_t stream) {
+  dim3 grid((cols + 63) / 64, (rows + 63) / 64, batch);
   ns_prescale_kernel<<<grid, 256, 0, stream>>>(x, dtype, rows, cols, sumsq, eps, out, out_t, out_dtype);
   return (int)cudaGetLastError();
 }

@@ -28,7 +28,13 @@ def position_embedding(size, width):
 
 
 def modulate(x, shift, scale):
-    return x * (1 + scale[:, None]) + shift[:, None]
+    """x * (1 + scale) + shift with per-sample vectors, as one fused multiply-add."""
+    return torch.addcmul(shift[:, None], x, (1 + scale)[:, None])
+
+
+def gated_residual(x, gate, y):
+    """x + gate * y with a per-sample gate vector, as one fused multiply-add."""
+    return torch.addcmul(x, gate[:, None], y)
 
 
 class Block(nn.Module):
@@ -50,9 +56,9 @@ class Block(nn.Module):
         b, n, d = h.shape
         q, k, v = self.qkv(h).view(b, n, 3, self.heads, d // self.heads).permute(2, 0, 3, 1, 4).unbind(0)
         h = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(b, n, d)
-        x = x + g1[:, None] * self.proj(h)
+        x = gated_residual(x, g1, self.proj(h))
         h = modulate(self.norm2(x), s2, a2)
-        return x + g2[:, None] * self.fc2(F.gelu(self.fc1(h), approximate="tanh"))
+        return gated_residual(x, g2, self.fc2(F.gelu(self.fc1(h), approximate="tanh")))
 
 
 class DiT(nn.Module):

@@ -163,11 +163,12 @@ def _pad_k(t, multiple):
 
 def _gemm(a, b, out, epilogue, n_logical, *, sa=None, sb=None, layout=_NO_GROUP, bias=None, alpha=1.0, beta=0.0,
           resid=None, out_t=None, symmetric=False, activation=0, aux=None, expert_offsets=None, tile_map=None,
-          force_bn=0):
+          force_bn=0, batch=1):
     multiple = 16 if a.element_size() == 1 else 8
     a, b = _pad_k(a, multiple), _pad_k(b, multiple)
     _ops().gemm(a, b, out, epilogue, n_logical, sa, sb, list(layout), bias, float(alpha), float(beta), resid, out_t,
-                bool(symmetric), int(activation), aux, expert_offsets, tile_map, status_word(a.device), int(force_bn))
+                bool(symmetric), int(activation), aux, expert_offsets, tile_map, status_word(a.device), int(force_bn),
+                int(batch))
     _count(2 if expert_offsets is not None else 1)
     return out
 
@@ -380,22 +381,32 @@ def expert_gemm(a, w, offsets, sa, sw, *, out_dtype, group=None, sa_kmajor=False
 
 # ------------------------------------------------------------------------------ Newton-Schulz GEMM
 def ns_gemm(a, b, *, out=None, alpha=1.0, beta=0.0, resid=None, out_t=None, symmetric=False, force_bn=0):
-    """out = alpha * round(a @ b.T) + beta * resid in the operands' 16-bit dtype."""
+    """out = alpha * round(a @ b^T) + beta * resid in the operands' 16-bit dtype.
+
+    ``a`` [.., m, k] and ``b`` [.., n, k] may carry one leading batch dimension (contiguous stacks):
+    the whole stack is one persistent-kernel launch.
+    """
     if not a.is_cuda:
-        acc = (a.float() @ b.float().t()).to(a.dtype).float()
+        acc = (a.float() @ b.float().mT).to(a.dtype).float()
         result = (alpha * acc + (beta * resid.float() if resid is not None else 0.0)).to(a.dtype)
         if out_t is not None:
-            out_t.copy_(result.t())
+            out_t.copy_(result.mT)
         return result if out is None else out.copy_(result)
+    batch = a.shape[0] if a.ndim == 3 else 1
+    m, n = a.shape[-2], b.shape[-2]
     if out is None:
-        out = torch.empty((a.shape[0], b.shape[0]), device=a.device, dtype=a.dtype)
-    return _gemm(a, b, out, EPI_AXPBY, b.shape[0], alpha=alpha, beta=beta, resid=resid, out_t=out_t,
-                 symmetric=symmetric, force_bn=force_bn)
+        out = torch.empty((*a.shape[:-2], m, n), device=a.device, dtype=a.dtype)
+    a2 = a.reshape(batch * m, a.shape[-1]) if a.ndim == 3 else a
+    b2 = b.reshape(batch * n, b.shape[-1]) if b.ndim == 3 else b
+    _gemm(a2, b2, out, EPI_AXPBY, n, alpha=alpha, beta=beta, resid=resid, out_t=out_t, symmetric=symmetric,
+          force_bn=force_bn, batch=batch)
+    return out
 
 
 def sumsq(x, round_dtype, accum):
+    """accum[b] += sum of squares of x[b] (rounded to ``round_dtype`` first); accum has one entry per matrix."""
     code = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}[round_dtype]
-    _ops().sumsq(x.contiguous().view(-1), code, accum)
+    _ops().sumsq(x.contiguous(), code, accum)
     _count()
 
 

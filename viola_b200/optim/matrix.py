@@ -77,6 +77,7 @@ class MatrixOptimizer(torch.optim.Optimizer):
             self.step_was_skipped = True
             return loss
         distributed, running = {}, 0
+        self._begin_local()
         for group in self.param_groups:
             indices = group.get("viola_parameter_indices")
             for position, param in enumerate(group["params"]):
@@ -88,14 +89,17 @@ class MatrixOptimizer(torch.optim.Optimizer):
                     distributed[param] = (group, index)
                 else:
                     self._step_local(param, param.grad, self.state[param], group, index)
+        self._finish_local()
         if distributed:
             for batch in self.partition.batches:
                 self._step_batch(batch, distributed)
-        self._finish_step()
         return loss
 
-    def _finish_step(self):
-        """Hook for subclasses that batch work across parameters (default: nothing)."""
+    def _begin_local(self):
+        """Called before the plain-tensor parameters are visited (subclasses may start batching)."""
+
+    def _finish_local(self):
+        """Called after the plain-tensor parameters were visited, before DTensor owner rounds."""
 
     def _step_batch(self, batch, contexts):
         from ..parallel.communication import gather_to_owner, replicate_tensor, write_from_owner

@@ -57,6 +57,8 @@ class FP8Muon(MatrixOptimizer):
                         master_rounding_seed=policy["master_rounding_seed"])
         self.observer = None
         self._workspace = {}
+        self._deferred = None
+        self.ns_batch = 32          # matrices of one shape orthogonalised per batched launch
         super().__init__(params, defaults, shard_state=shard_state, skip_nonfinite=skip_nonfinite)
 
     def add_param_group(self, group):
@@ -100,18 +102,21 @@ class FP8Muon(MatrixOptimizer):
                           f"(e.g. {unaligned[:3]}); shapes are kept and edge groups cover the valid elements only.",
                           stacklevel=3)
 
-    def _momentum(self, param, grad, state, group, key):
+    def _momentum(self, param, grad, state, group, key, out=None):
         shape = _matrix_shape(param, group)
         quant = {name: group[name] for name in ("granularity", "tile_size", "block_shape")}
         if "momentum_q" not in state:
             codes, scales = ops.state_sizes(shape, **quant)
             state["momentum_q"] = torch.zeros(codes, device=param.device, dtype=torch.uint8)
             state["momentum_scale"] = torch.ones(scales, device=param.device, dtype=torch.float32)
-        work = self._workspace.get(param.device)
-        if work is None or work.numel() < param.numel():
-            work = self._workspace[param.device] = torch.empty(param.numel(), device=param.device,
-                                                               dtype=torch.bfloat16)
-        matrix = work[:param.numel()].view(shape)
+        if out is not None:
+            matrix = out
+        else:
+            work = self._workspace.get(param.device)
+            if work is None or work.numel() < param.numel():
+                work = self._workspace[param.device] = torch.empty(param.numel(), device=param.device,
+                                                                   dtype=torch.bfloat16)
+            matrix = work[:param.numel()].view(shape)
         q, scale = state["momentum_q"], state["momentum_scale"]
         before = (q.clone(), scale.clone()) if self.observer is not None else (None, None)
         ops.momentum_update(grad, q, scale, q, scale, matrix.view(-1), beta=group["momentum"],
@@ -129,6 +134,13 @@ class FP8Muon(MatrixOptimizer):
         if param.dtype not in (torch.float32, torch.bfloat16, torch.float16):
             raise RuntimeError("bind FP8 modules with viola_b200.optim.bind_optimizer before stepping")
         state.setdefault("step", 0)
+        if (_use_muon(param, group) and self._deferred is not None and param.is_cuda
+                and len(_matrix_shape(param, group)) == 2):
+            # same-shape matrices are orthogonalised together after the parameter loop
+            shape = _matrix_shape(param, group)
+            self._deferred.setdefault((shape, group["ns_method"], group["ns_steps"], param.device), []).append(
+                (param, grad, state, group, key, master_key))
+            return
         if _use_muon(param, group):
             matrix = self._momentum(param, grad, state, group, key)
             method = METHODS[group["ns_method"]]
@@ -150,3 +162,33 @@ class FP8Muon(MatrixOptimizer):
                             weight_decay=group["weight_decay"], betas=group["betas"], eps=group["eps"],
                             step=state["step"] + 1, rounding=group["master_rounding"], key=master_key)
         state["step"] += 1
+
+    # ------------------------------------------------------------------ batched Newton-Schulz
+    def _begin_local(self):
+        self._deferred = {} if self.observer is None else None
+
+    def _finish_local(self):
+        deferred, self._deferred = self._deferred, None
+        if not deferred:
+            return
+        for (shape, method, steps, device), items in deferred.items():
+            for start in range(0, len(items), self.ns_batch):
+                chunk = items[start:start + self.ns_batch]
+                key = ("stack", shape, device)
+                stack = self._workspace.get(key)
+                if stack is None or stack.shape[0] < len(chunk):
+                    stack = self._workspace[key] = torch.empty((len(chunk), *shape), device=device,
+                                                               dtype=torch.bfloat16)
+                stack = stack[:len(chunk)]
+                for slot, (param, grad, state, group, rounding_key, _) in enumerate(chunk):
+                    self._momentum(param, grad, state, group, rounding_key, out=stack[slot])
+                updates = METHODS[method](stack, steps=steps)
+                rows, cols = shape
+                for slot, (param, _, state, group, _, master_key) in enumerate(chunk):
+                    if group["adjust_lr_fn"] == "match_rms_adamw":
+                        scale = 0.2 * max(rows, cols) ** 0.5
+                    else:
+                        scale = max(1.0, rows / cols) ** 0.5
+                    ops.weight_update(param, updates[slot], group["lr"], group["weight_decay"], update_scale=scale,
+                                      rounding=group["master_rounding"], step=state["step"], key=master_key)
+                    state["step"] += 1

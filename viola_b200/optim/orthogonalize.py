@@ -25,12 +25,13 @@ _A, _B, _C = 3.4445, -4.7750, 2.0315
 
 def _prescale(matrix, dtype):
     """(X, X^T) = matrix / (||matrix||_F + 1e-7) rounded to ``dtype``; X is the wide orientation."""
-    rows, cols = matrix.shape
-    accum = torch.zeros(1, device=matrix.device, dtype=torch.float32)
+    rows, cols = matrix.shape[-2:]
+    lead = tuple(matrix.shape[:-2])
+    accum = torch.zeros(max(1, matrix.numel() // (rows * cols)), device=matrix.device, dtype=torch.float32)
     source = matrix.contiguous()
     ops.sumsq(source, dtype, accum)
-    straight = torch.empty((rows, cols), device=matrix.device, dtype=dtype)
-    flipped = torch.empty((cols, rows), device=matrix.device, dtype=dtype)
+    straight = torch.empty((*lead, rows, cols), device=matrix.device, dtype=dtype)
+    flipped = torch.empty((*lead, cols, rows), device=matrix.device, dtype=dtype)
     ops.ns_prescale(source, accum, out=straight, out_t=flipped)
     return (flipped, straight, True) if rows > cols else (straight, flipped, False)
 
@@ -58,7 +59,7 @@ def _standard_2d(matrix, steps, dtype):
 
 def _gram_2d(matrix, steps):
     dtype = torch.float16
-    if matrix.shape[0] == matrix.shape[1]:
+    if matrix.shape[-2] == matrix.shape[-1]:
         return _standard_2d(matrix, steps, dtype)
     x, xt, transposed = _prescale(matrix, dtype)
     segments = [length for length in (min(steps, 2), max(steps - 2, 0)) if length]
@@ -69,7 +70,7 @@ def _gram_2d(matrix, steps):
             z = _poly(r)
             if i == 0:
                 q = z.clone()
-                q.diagonal().add_(_A)
+                q.diagonal(dim1=-2, dim2=-1).add_(_A)
             else:
                 q = ops.ns_gemm(z, q, alpha=1.0, beta=_A, resid=q, symmetric=True)
             if i + 1 < length:
@@ -87,10 +88,11 @@ def _gram_2d(matrix, steps):
 
 
 def _batched(fn, matrix, *args):
+    """2-D inputs run as is; stacks of matrices run as ONE batched launch per GEMM of the recurrence."""
     if matrix.ndim == 2:
         return fn(matrix, *args)
     flat = matrix.reshape(-1, *matrix.shape[-2:])
-    return torch.stack([fn(item, *args) for item in flat]).reshape(*matrix.shape[:-2], *matrix.shape[-2:])
+    return fn(flat, *args).reshape(matrix.shape)
 
 
 def standard(matrix, steps=5):

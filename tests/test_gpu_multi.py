@@ -4,6 +4,7 @@ two quantisations < 3e-3 relative L2), plus the bounded-wait failure path on one
 """
 import os
 import socket
+import tempfile
 import time
 
 import pytest
@@ -84,6 +85,7 @@ def collectives_worker(rank, world, port, results):
         transport.finalize_gradients()
         expected = torch.zeros(n, device=device)
         for generation in range(2):
+            transport.begin_microbatch()
             index, staging = transport.next_staging()
             staging[:n].copy_(local * (generation + 1))
             transport.reduce_to_owner(0, index, n)
@@ -124,7 +126,7 @@ def collectives_worker(rank, world, port, results):
     results.put(rank)
 
 
-def training_worker(rank, world, port, backend, results):
+def training_worker(rank, world, port, backend, directory, results):
     setup(rank, world, port)
     import viola_b200 as viola
     from viola_b200 import ops
@@ -159,9 +161,9 @@ def training_worker(rank, world, port, backend, results):
     dist.barrier()
     dist.destroy_process_group()
     if rank == 0:
-        results.put((losses, {k: v.float() for k, v in weights.items() if isinstance(v, torch.Tensor)}))
-    else:
-        results.put(None)
+        torch.save((losses, {k: v.float() for k, v in weights.items() if isinstance(v, torch.Tensor)}),
+                   os.path.join(directory, f"{backend}.pt"))
+    results.put(rank)
 
 
 @pytest.mark.skipif(GPUS < 2, reason="needs 2 GPUs")
@@ -172,8 +174,10 @@ def test_fused_collectives_match_oracle():
 @pytest.mark.skipif(GPUS < 2, reason="needs 2 GPUs")
 def test_engine_peer_backend_matches_collective_backend():
     outputs = {}
-    for backend in ("nccl", "p2p"):
-        outputs[backend] = next(item for item in launch(training_worker, 2, backend) if item is not None)
+    with tempfile.TemporaryDirectory() as directory:
+        for backend in ("nccl", "p2p"):
+            launch(training_worker, 2, backend, directory)
+            outputs[backend] = torch.load(os.path.join(directory, f"{backend}.pt"), weights_only=False)
     losses_a, weights_a = outputs["nccl"]
     losses_b, weights_b = outputs["p2p"]
     assert losses_a == pytest.approx(losses_b, rel=2e-2)

@@ -125,13 +125,13 @@ typedef struct VbPeerTable {
 // Path 1 (non-owner): quantise the local fp32 bucket tile by tile and store codes + scales straight
 // into the owner's receive slot, then raise the owner's flag for this source rank.
 int vb_reduce_push_fp8(const float* bucket, long long n, int tile, int fmt, void* dst_codes, float* dst_scales,
-                       int* dst_flag, const int* ack_flag, int generation, unsigned int* counter,
+                       int* dst_flag, const int* ack_flag, const int* generation, unsigned int* counter,
                        long long wait_clocks, int max_blocks, int* status, cudaStream_t stream);
 // Path 1 (owner): wait for every peer's flag, then accum += sum over ranks (ascending, fp32) of the
 // dequantised contributions; the owner's own bucket goes through the same quantise-dequantise.
 int vb_reduce_accumulate_fp8(const float* bucket, long long n, int tile, int fmt, const void* recv,
                              long long slot_stride, long long scales_offset, const int* flags,
-                             const VbPeerTable* peers, long long ack_offset, int generation, float* accum,
+                             const VbPeerTable* peers, long long ack_offset, const int* generation, float* accum,
                              unsigned int* counter, long long wait_clocks, int max_blocks, int* status,
                              cudaStream_t stream);
 // Path 2: in-place FP8 all-reduce with a second quantisation of the partial sums.

@@ -305,20 +305,21 @@ VbPeerTable peer_table(at::IntArrayRef heaps, int64_t rank) {
 }
 
 void reduce_push_fp8(const Tensor& bucket, int64_t tile, int64_t fmt, int64_t dst_codes, int64_t dst_scales,
-                     int64_t dst_flag, int64_t ack_flag, int64_t generation, Tensor counter, int64_t wait_clocks,
+                     int64_t dst_flag, int64_t ack_flag, const Tensor& generation, Tensor counter, int64_t wait_clocks,
                      int64_t max_blocks, Tensor status) {
   cuda_contig(bucket, "bucket");
   c10::cuda::CUDAGuard guard(bucket.device());
   check(vb_reduce_push_fp8(bucket.data_ptr<float>(), bucket.numel(), (int)tile, (int)fmt, reinterpret_cast<void*>(dst_codes),
                            reinterpret_cast<float*>(dst_scales), reinterpret_cast<int*>(dst_flag),
-                           reinterpret_cast<const int*>(ack_flag), (int)generation, (unsigned int*)counter.data_ptr(),
+                           reinterpret_cast<const int*>(ack_flag), (const int*)generation.data_ptr(),
+                           (unsigned int*)counter.data_ptr(),
                            wait_clocks, (int)max_blocks, (int*)status.data_ptr(), stream()),
         "reduce_push_fp8");
 }
 
 void reduce_accumulate_fp8(const Tensor& bucket, int64_t tile, int64_t fmt, int64_t recv, int64_t slot_stride,
                            int64_t scales_offset, int64_t flags, at::IntArrayRef heaps, int64_t rank, int64_t ack_offset,
-                           int64_t generation, Tensor accum, Tensor counter, int64_t wait_clocks, int64_t max_blocks,
+                           const Tensor& generation, Tensor accum, Tensor counter, int64_t wait_clocks, int64_t max_blocks,
                            Tensor status) {
   cuda_contig(bucket, "bucket");
   TORCH_CHECK(accum.scalar_type() == at::kFloat && accum.numel() >= bucket.numel());
@@ -326,8 +327,8 @@ void reduce_accumulate_fp8(const Tensor& bucket, int64_t tile, int64_t fmt, int6
   VbPeerTable table = peer_table(heaps, rank);
   check(vb_reduce_accumulate_fp8(bucket.data_ptr<float>(), bucket.numel(), (int)tile, (int)fmt,
                                  reinterpret_cast<const void*>(recv), slot_stride, scales_offset,
-                                 reinterpret_cast<const int*>(flags), &table, ack_offset, (int)generation,
-                                 accum.data_ptr<float>(), (unsigned int*)counter.data_ptr(), wait_clocks, (int)max_blocks,
+                                 reinterpret_cast<const int*>(flags), &table, ack_offset,
+                                 (const int*)generation.data_ptr(), accum.data_ptr<float>(), (unsigned int*)counter.data_ptr(), wait_clocks, (int)max_blocks,
                                  (int*)status.data_ptr(), stream()),
         "reduce_accumulate_fp8");
 }

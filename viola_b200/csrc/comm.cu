@@ -87,8 +87,11 @@ __device__ __forceinline__ bool last_block_done(unsigned int* counter) {
 template <int TILE>
 __global__ void __launch_bounds__(256)
 reduce_push_kernel(const float* __restrict__ bucket, long long n, int fmt, uint8_t* dst_codes, float* dst_scales,
-                   int* dst_flag, const int* ack_flag, int generation, unsigned int* counter, long long budget,
+                   int* dst_flag, const int* ack_flag, const int* generation_ptr, unsigned int* counter, long long budget,
                    int* status) {
+  // The generation (= microbatch counter) lives in device memory so that a captured CUDA graph
+  // signals a fresh value on every replay.
+  const int generation = *generation_ptr;
   // The owner must have consumed the previous generation of this slot before it is overwritten.
   if (generation > 1 && !block_wait_flags(ack_flag, 1, -1, generation - 1, budget, status)) return;
   const long long tiles = (n + TILE - 1) / TILE;
@@ -113,8 +116,10 @@ __device__ __forceinline__ void fake_quantize_tile(float (&v)[TILE / 32], int fm
 template <int TILE>
 __global__ void __launch_bounds__(256)
 reduce_accumulate_kernel(const float* __restrict__ bucket, long long n, int fmt, const uint8_t* recv, long long slot_stride,
-                         long long scales_offset, const int* flags, Peers peers, long long ack_offset, int generation,
-                         float* __restrict__ accum, unsigned int* counter, long long budget, int* status) {
+                         long long scales_offset, const int* flags, Peers peers, long long ack_offset,
+                         const int* generation_ptr, float* __restrict__ accum, unsigned int* counter, long long budget,
+                         int* status) {
+  const int generation = *generation_ptr;
   if (!block_wait_flags(flags, peers.world, peers.rank, generation, budget, status)) return;
   const long long tiles = (n + TILE - 1) / TILE;
   const int lane = threadIdx.x & 31;
@@ -339,9 +344,19 @@ gather_pull_kernel(const GatherEntry* __restrict__ entries, int num_entries, Pee
     const uint8_t* src = peers.heap[rank] + shard_region_offset + e.shard_offset + first;
     uint8_t* dst = full + e.full_offset + (long long)rank * e.shard_bytes + first;
     const long long vectors = bytes / 16;
-    for (long long i = threadIdx.x; i < vectors; i += blockDim.x)
-      reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
-    for (long long i = vectors * 16 + threadIdx.x; i < bytes; i += blockDim.x) dst[i] = src[i];
+    long long i = threadIdx.x;
+    for (; i + 3 * (long long)blockDim.x < vectors; i += 4 * (long long)blockDim.x) {   // four peer loads in flight per thread
+      const uint4 v0 = reinterpret_cast<const uint4*>(src)[i];
+      const uint4 v1 = reinterpret_cast<const uint4*>(src)[i + blockDim.x];
+      const uint4 v2 = reinterpret_cast<const uint4*>(src)[i + 2 * blockDim.x];
+      const uint4 v3 = reinterpret_cast<const uint4*>(src)[i + 3 * blockDim.x];
+      reinterpret_cast<uint4*>(dst)[i] = v0;
+      reinterpret_cast<uint4*>(dst)[i + blockDim.x] = v1;
+      reinterpret_cast<uint4*>(dst)[i + 2 * blockDim.x] = v2;
+      reinterpret_cast<uint4*>(dst)[i + 3 * blockDim.x] = v3;
+    }
+    for (; i < vectors; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    for (long long j = vectors * 16 + threadIdx.x; j < bytes; j += blockDim.x) dst[j] = src[j];
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -387,7 +402,7 @@ static int blocks_for(long long warps_needed, int max_blocks) {
 }
 
 extern "C" int vb_reduce_push_fp8(const float* bucket, long long n, int tile, int fmt, void* dst_codes, float* dst_scales,
-                                  int* dst_flag, const int* ack_flag, int generation, unsigned int* counter,
+                                  int* dst_flag, const int* ack_flag, const int* generation, unsigned int* counter,
                                   long long wait_clocks, int max_blocks, int* status, cudaStream_t stream) {
   const long long tiles = (n + tile - 1) / tile;
   const int grid = blocks_for(tiles, max_blocks);
@@ -398,7 +413,7 @@ extern "C" int vb_reduce_push_fp8(const float* bucket, long long n, int tile, in
 
 extern "C" int vb_reduce_accumulate_fp8(const float* bucket, long long n, int tile, int fmt, const void* recv,
                                         long long slot_stride, long long scales_offset, const int* flags,
-                                        const VbPeerTable* peers, long long ack_offset, int generation, float* accum,
+                                        const VbPeerTable* peers, long long ack_offset, const int* generation, float* accum,
                                         unsigned int* counter, long long wait_clocks, int max_blocks, int* status,
                                         cudaStream_t stream) {
   const long long tiles = (n + tile - 1) / tile;

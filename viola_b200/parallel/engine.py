@@ -141,6 +141,18 @@ class violaEngine:  # noqa: N801 - public name kept identical to the reference
             loss = loss / self.accumulation_steps
         self.state.backward(loss)
 
+    def graph_microbatch(self, loss_fn, *example_inputs, eager_calls=1):
+        """Wrap one microbatch (autocast forward of ``loss_fn`` + engine backward) into a replayed CUDA graph.
+
+        Returns a callable ``run(*inputs) -> loss`` that replaces the ``accumulate()`` / ``autocast()`` /
+        ``backward()`` block for unweighted losses whose input shapes never change: inputs are copied into
+        static device buffers (host tensors in pinned memory copy asynchronously), the first
+        ``eager_calls`` invocations run eagerly, the next one is captured, and every later one replays the
+        graph, which removes the per-kernel launch cost of the several thousand launches of a microbatch
+        (parameter gathers and gradient pushes included).  ``engine.step()`` stays outside the graph.
+        """
+        return _GraphedMicrobatch(self, loss_fn, example_inputs, eager_calls)
+
     def step(self, optimizer=None, *, scheduler=None, force=False):
         """Returns True only after a real optimizer update that every rank performed."""
         if self._in_ema:
@@ -208,3 +220,54 @@ class violaEngine:  # noqa: N801 - public name kept identical to the reference
             self.state.close()
         if self.transport is not None:
             self.transport.close()
+
+
+class _GraphedMicrobatch:
+    def __init__(self, engine, loss_fn, example_inputs, eager_calls):
+        if engine.device.type != "cuda":
+            raise RuntimeError("CUDA graphs need a CUDA device")
+        from ..nn import Linear
+        if any(isinstance(m, Linear) and m.weight_quantizer.scaling == "delayed" for m in engine.model.modules()):
+            # delayed scaling reads an amax-history slot chosen by a host-side call counter,
+            # which a replayed graph cannot advance
+            raise RuntimeError("graph_microbatch does not support scaling='delayed'")
+        self.engine, self.loss_fn, self.eager_calls = engine, loss_fn, eager_calls
+        self.static_inputs = [torch.empty(t.shape, dtype=t.dtype, device=engine.device) for t in example_inputs]
+        self.graph = self.static_loss = self.marks = None
+        self.calls = 0
+
+    def _run(self):
+        engine = self.engine
+        with engine.autocast():
+            loss = self.loss_fn(*self.static_inputs)
+        engine.state.backward(loss / engine.accumulation_steps)
+        return loss.detach()
+
+    def _capture(self):
+        engine = self.engine
+        torch.cuda.synchronize(engine.device)
+        if engine.transport is not None:
+            engine.transport.forget_events()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.static_loss = self._run()
+        if engine.transport is not None:
+            engine.transport.forget_events()
+        self.marks = engine.state.gradients.capture_marks()
+
+    def __call__(self, *inputs):
+        engine = self.engine
+        if engine._in_accumulate or engine._weighted:
+            raise RuntimeError("a graphed microbatch replaces accumulate()/backward(); weighted losses are not supported")
+        for static, value in zip(self.static_inputs, inputs):
+            static.copy_(value, non_blocking=True)
+        engine._start_microbatch()
+        engine._weighted = False
+        self.calls += 1
+        if self.graph is None and self.calls <= self.eager_calls:
+            return self._run()
+        if self.graph is None:
+            self._capture()          # capturing records the work without running it: replay right away
+        engine.state.gradients.replay_marks(self.marks)
+        self.graph.replay()
+        return self.static_loss

@@ -111,6 +111,8 @@ class GradientState:
         self.seen = [False] * len(self.records)
         self.remaining = self.piece_counts.copy()
         self.next_bucket = 0
+        if self.transport is not None and self.shard:
+            self.transport.begin_microbatch()
         if self.store.sharder is not None:
             self.store.sharder.begin_backward()
 
@@ -166,6 +168,8 @@ class GradientState:
             self._drain(final=True)
         if self.store.sharder is not None:
             self.store.sharder.finish_backward()
+        if self.transport is not None:
+            self.transport.synchronize()        # side-stream work joins the compute stream every microbatch
         self.in_backward = False
 
     # ------------------------------------------------------------------ step-time reduction
@@ -198,6 +202,16 @@ class GradientState:
             self.transport.synchronize()
         self.accumulator.div_(divisor)
         return active
+
+    # ------------------------------------------------------------------ CUDA-graph replays
+    def capture_marks(self):
+        """Which parameters produced a gradient in the microbatch that was just captured."""
+        return [index for index, seen in enumerate(self.seen) if seen]
+
+    def replay_marks(self, marks):
+        """A replayed graph runs no Python hooks: restore the bookkeeping those hooks would have done."""
+        for index in marks:
+            self.used[index] = True
 
     @torch.no_grad()
     def zero_grad(self):

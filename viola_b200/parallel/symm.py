@@ -73,6 +73,8 @@ class PeerTransport:
         self.stream = torch.cuda.Stream(device=self.device) if overlap else None
         self.status = ops.status_word(self.device)
         self.counters = torch.zeros(64, device=self.device, dtype=torch.int32)
+        # microbatch counter in device memory: the generation every bucket of a microbatch signals with
+        self.micro_counter = torch.zeros(1, device=self.device, dtype=torch.int32)
         self.heap = None
         self._requests = []                      # (name, nbytes)
         self.offsets = {}
@@ -149,7 +151,6 @@ class PeerTransport:
         self.staging = [torch.empty(capacity, device=self.device, dtype=torch.float32) for _ in range(4)]
         self.staging_events = [None] * 4
         self.staging_cursor = 0
-        self.bucket_generation = [0] * len(buckets)
 
     def finalize_gradients(self):
         self.reduce_flag_offset = self.flags("reduce", max(1, self._max_owned) * self.world)
@@ -164,10 +165,17 @@ class PeerTransport:
             torch.cuda.current_stream(self.device).wait_event(event)
         return index, self.staging[index]
 
+    def begin_microbatch(self):
+        """Advance the generation all of this microbatch's buckets signal with (captured in CUDA graphs)."""
+        self.micro_counter.add_(1)
+
+    def forget_events(self):
+        """Drop cross-stream events recorded outside a CUDA-graph capture (call after a full device sync)."""
+        self.staging_events = [None] * len(self.staging_events)
+
     def reduce_to_owner(self, bucket_index, staging_index, length):
         owner = self.buckets[bucket_index][0]
-        self.bucket_generation[bucket_index] += 1
-        generation = self.bucket_generation[bucket_index]
+        generation = self.micro_counter
         buffer = self.staging[staging_index][:length]
         stream = self._enter()
         region = self.offsets["grad_receive"] + self.bucket_region[bucket_index]

@@ -148,7 +148,9 @@ def run_ours(args):
     linear_options = dict(scaling=args.scaling)
     if args.scaling == "grouped":
         linear_options.update(weight_group_shape=(128, 128), input_group_shape=(1, 128), grad_group_shape=(1, 128))
-    model = engine.prepare_model(DiT(**options, linear_options=linear_options))
+    with torch.device(device):          # build (and quantise) the weights on the GPU, not on the host
+        model = DiT(**options, linear_options=linear_options)
+    model = engine.prepare_model(model)
     engine.prepare_optimizer(lambda params: viola.optim.FP8Muon(muon_parameter_groups(model), mode="balanced",
                                                                 ns_method="standard"))
     schedule = NoiseSchedule(device=device)

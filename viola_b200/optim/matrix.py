@@ -148,5 +148,5 @@ class MatrixOptimizer(torch.optim.Optimizer):
         for old, group in zip(self._loading_groups, self.param_groups):
             for pid, param in zip(old["params"], group["params"]):
                 for name, value in self._loading.get(pid, {}).items():
-                    self.state[param][name] = value.to(device=param.device)
+                    self.state[param][name] = value.to(device=param.device, copy=True)
         del self._loading, self._loading_groups

@@ -1,0 +1,78 @@
+"""Small, self-terminating workloads for Nsight Compute captures of single kernels.
+
+Each case allocates a few hundred MB (more than the 126 MB L2, far less than a few GB), launches
+the kernel of interest a handful of times and exits.  Meant to be run as
+
+    python benchmarks/profile_case.py --case gemm_fp8 &&
+    ncu --set full --clock-control none -k regex:gemm_kernel -s 2 -c 1 -o out python benchmarks/profile_case.py --case gemm_fp8
+"""
+
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from viola_b200 import ops  # noqa: E402
+
+E4M3 = torch.float8_e4m3fn
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--case", required=True,
+                        choices=("gemm_fp8", "gemm_group", "gemm_ns", "quantize", "group_quantize", "momentum", "gated"))
+    parser.add_argument("--launches", type=int, default=4)
+    args = parser.parse_args()
+    device = torch.device("cuda")
+    torch.manual_seed(0)
+    m, n, k = 32768, 3456, 1152
+    if args.case in ("gemm_fp8", "gemm_group", "gated"):
+        x = torch.randn(m, k, device=device, dtype=torch.bfloat16)
+        w = torch.randn(n, k, device=device, dtype=torch.bfloat16) * 0.03
+        if args.case == "gemm_fp8":
+            sx, sw = ops.tensor_scale(x), ops.tensor_scale(w)
+            qx, _ = ops.quantize(x, sx)
+            qw, _ = ops.quantize(w, sw)
+            out = torch.empty(m, n, device=device, dtype=torch.bfloat16)
+            run = lambda: ops.gemm(qx, qw, sx, sw, out_dtype=torch.bfloat16, out=out)
+        elif args.case == "gemm_group":
+            qx, sx = ops.group_quantize(x, E4M3, (1, 128), kmajor=True)
+            qw, sw = ops.group_quantize(w, E4M3, (128, 128))
+            out = torch.empty(m, n, device=device, dtype=torch.bfloat16)
+            run = lambda: ops.group_gemm(qx, qw, sx, sw, (1, 128), (128, 128), out_dtype=torch.bfloat16, sa_kmajor=True,
+                                         out=out)
+        else:
+            sx, sw = ops.tensor_scale(x), ops.tensor_scale(w)
+            qx, _ = ops.quantize(x, sx)
+            qw, _ = ops.quantize(w, sw)
+            run = lambda: ops.gated_gemm_forward(qx, qw, sx, sw, activation="silu", out_dtype=torch.bfloat16)
+    elif args.case == "gemm_ns":
+        x = (torch.randn(28, 1152, 4608, device=device) / 68).bfloat16()
+        run = lambda: ops.ns_gemm(x, x, symmetric=True)
+    elif args.case == "quantize":
+        x = torch.randn(m, 4608, device=device, dtype=torch.bfloat16)
+        scale = ops.tensor_scale(x)
+        run = lambda: ops.quantize(x, scale, transpose=True)
+    elif args.case == "group_quantize":
+        x = torch.randn(m, 4608, device=device, dtype=torch.bfloat16)
+        run = lambda: ops.group_quantize_pair(x, E4M3, (1, 128), (1, 128), kmajor=True)
+    else:
+        count = 4096 * 11008
+        grad = torch.randn(count, device=device)
+        q = torch.zeros(count, device=device, dtype=torch.uint8)
+        scale = torch.ones(count // 256, device=device)
+        update = torch.empty(count, device=device, dtype=torch.bfloat16)
+        run = lambda: ops.momentum_update(grad, q, scale, q, scale, update, beta=0.95)
+    for _ in range(args.launches):
+        run()
+    torch.cuda.synchronize()
+    ops.check_status()
+    print("ok", args.case)
+
+
+if __name__ == "__main__":
+    main()

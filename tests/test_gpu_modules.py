@@ -238,3 +238,39 @@ def test_graphed_microbatch_matches_eager():
         if name.endswith(".history"):
             continue       # the amax-history slot index is a host counter: informational under "current" scaling
         assert rel_l2(weights_b[name], weights_a[name]) < 1e-3, name
+
+
+def test_producer_fused_linears_match_unfused():
+    from viola_b200.nn import activation_linear, norm_modulate_linear
+    from torch.nn import functional as F
+    torch.manual_seed(0)
+    batch, tokens, width = 6, 96, 384
+    layer = Linear(width, 512).cuda()
+    x = torch.randn(batch, tokens, width, device="cuda", dtype=torch.bfloat16)
+    shift = (torch.randn(batch, width, device="cuda") * 0.3).bfloat16()
+    scale = (torch.randn(batch, width, device="cuda") * 0.3).bfloat16()
+    dy = torch.randn(batch, tokens, 512, device="cuda", dtype=torch.bfloat16)
+    results = []
+    for fused in (True, False):
+        xs, sh, sc = (t.clone().requires_grad_(True) for t in (x, shift, scale))
+        layer.zero_grad()
+        if fused:
+            y = norm_modulate_linear(xs, sh, sc, layer)
+        else:
+            y = layer(torch.addcmul(sh[:, None], F.layer_norm(xs.float(), (width,), eps=1e-6), (1 + sc)[:, None]).bfloat16())
+        y.backward(dy)
+        results.append((y.detach(), xs.grad, sh.grad, sc.grad, layer.weight.grad.clone(), layer.bias.grad.clone()))
+    for name, a, b in zip(("y", "dx", "dshift", "dscale", "dw", "db"), *results):
+        assert rel_l2(a, b) < 2e-2, (name, rel_l2(a, b))
+    layer2 = Linear(512, width).cuda()
+    z = torch.randn(batch * tokens, 512, device="cuda", dtype=torch.bfloat16)
+    dy2 = torch.randn(batch * tokens, width, device="cuda", dtype=torch.bfloat16)
+    results = []
+    for fused in (True, False):
+        zs = z.clone().requires_grad_(True)
+        layer2.zero_grad()
+        y = activation_linear(zs, layer2, "gelu") if fused else layer2(F.gelu(zs, approximate="tanh"))
+        y.backward(dy2)
+        results.append((y.detach(), zs.grad, layer2.weight.grad.clone()))
+    for name, a, b in zip(("y", "dz", "dw"), *results):
+        assert rel_l2(a, b) < 2e-2, (name, rel_l2(a, b))

@@ -391,6 +391,58 @@ void gather_pull(const Tensor& entries, at::IntArrayRef heaps, int64_t rank, int
         "gather_pull");
 }
 
+// ---- producer-fused quantisers -------------------------------------------------------------------
+void ln_stats_amax(const Tensor& x, double eps, const Tensor& shift, const Tensor& scale, int64_t tokens, Tensor mean,
+                   Tensor rstd, const OptTensor& history, int64_t index, bool delayed, double limit, Tensor scale_out,
+                   Tensor scratch) {
+  cuda_contig(x, "x");
+  cuda_contig(shift, "shift");
+  cuda_contig(scale, "scale");
+  TORCH_CHECK(x.dim() == 2 && x.scalar_type() == at::kBFloat16 && shift.scalar_type() == at::kBFloat16 &&
+              scale.scalar_type() == at::kBFloat16);
+  c10::cuda::CUDAGuard guard(x.device());
+  check(vb_ln_stats_amax(x.data_ptr(), (int)x.size(0), (int)x.size(1), (float)eps, shift.data_ptr(), scale.data_ptr(),
+                         (int)tokens, mean.data_ptr<float>(), rstd.data_ptr<float>(), (float*)ptr(history),
+                         history.has_value() ? (int)history->numel() : 0, index, delayed, (float)limit,
+                         scale_out.data_ptr<float>(), (unsigned int*)scratch.data_ptr(), stream()),
+        "ln_stats_amax");
+}
+
+void act_amax(const Tensor& z, int64_t mode, const OptTensor& history, int64_t index, bool delayed, double limit,
+              Tensor scale_out, Tensor scratch) {
+  cuda_contig(z, "z");
+  TORCH_CHECK(z.scalar_type() == at::kBFloat16);
+  c10::cuda::CUDAGuard guard(z.device());
+  check(vb_act_amax(z.data_ptr(), z.numel(), (int)mode, (float*)ptr(history), history.has_value() ? (int)history->numel() : 0,
+                    index, delayed, (float)limit, scale_out.data_ptr<float>(), (unsigned int*)scratch.data_ptr(), stream()),
+        "act_amax");
+}
+
+void fused_quantize(const Tensor& x, int64_t mode, const OptTensor& mean, const OptTensor& rstd, const OptTensor& shift,
+                    const OptTensor& scale, int64_t tokens, const Tensor& qscale, double limit, int64_t fmt,
+                    const OptTensor& q, const OptTensor& qt) {
+  cuda_contig(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.scalar_type() == at::kBFloat16);
+  c10::cuda::CUDAGuard guard(x.device());
+  check(vb_fused_quantize(x.data_ptr(), (int)x.size(0), (int)x.size(1), (int)mode, (const float*)ptr(mean),
+                          (const float*)ptr(rstd), ptr(shift), ptr(scale), (int)tokens, qscale.data_ptr<float>(),
+                          (float)limit, (int)fmt, ptr(q), ptr(qt), stream()),
+        "fused_quantize");
+}
+
+void ln_modulate_backward(const Tensor& dh, const Tensor& x, const Tensor& mean, const Tensor& rstd, const Tensor& scale,
+                          int64_t tokens, Tensor dx, Tensor dshift, Tensor dscale) {
+  cuda_contig(dh, "dh");
+  cuda_contig(x, "x");
+  TORCH_CHECK(dh.scalar_type() == at::kBFloat16 && x.scalar_type() == at::kBFloat16 && dx.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(dshift.scalar_type() == at::kFloat && dscale.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(x.device());
+  check(vb_ln_modulate_backward(dh.data_ptr(), x.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                                scale.data_ptr(), (int)x.size(0), (int)x.size(1), (int)tokens, dx.data_ptr(),
+                                dshift.data_ptr<float>(), dscale.data_ptr<float>(), stream()),
+        "ln_modulate_backward");
+}
+
 }  // namespace
 
 TORCH_LIBRARY(viola_b200, m) {
@@ -423,4 +475,8 @@ TORCH_LIBRARY(viola_b200, m) {
   m.def("signal", &signal);
   m.def("wait_flags", &wait_flags);
   m.def("gather_pull", &gather_pull);
+  m.def("ln_stats_amax", &ln_stats_amax);
+  m.def("act_amax", &act_amax);
+  m.def("fused_quantize", &fused_quantize);
+  m.def("ln_modulate_backward", &ln_modulate_backward);
 }

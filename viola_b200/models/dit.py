@@ -17,7 +17,7 @@ import torch
 from torch import nn
 from torch.nn import functional as F
 
-from ..nn import Linear
+from ..nn import Linear, activation_linear, norm_modulate_linear
 
 
 def position_embedding(size, width):
@@ -52,13 +52,14 @@ class Block(nn.Module):
 
     def forward(self, x, c):
         s1, a1, g1, s2, a2, g2 = self.ada(F.silu(c)).chunk(6, dim=-1)
-        h = modulate(self.norm1(x), s1, a1)
-        b, n, d = h.shape
-        q, k, v = self.qkv(h).view(b, n, 3, self.heads, d // self.heads).permute(2, 0, 3, 1, 4).unbind(0)
+        b, n, d = x.shape
+        # LayerNorm + modulate are folded into the FP8 quantiser of qkv / fc1, GELU into that of fc2
+        qkv = norm_modulate_linear(x, s1, a1, self.qkv, eps=self.norm1.eps)
+        q, k, v = qkv.view(b, n, 3, self.heads, d // self.heads).permute(2, 0, 3, 1, 4).unbind(0)
         h = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(b, n, d)
         x = gated_residual(x, g1, self.proj(h))
-        h = modulate(self.norm2(x), s2, a2)
-        return gated_residual(x, g2, self.fc2(F.gelu(self.fc1(h), approximate="tanh")))
+        h = norm_modulate_linear(x, s2, a2, self.fc1, eps=self.norm2.eps)
+        return gated_residual(x, g2, activation_linear(h, self.fc2, "gelu"))
 
 
 class DiT(nn.Module):

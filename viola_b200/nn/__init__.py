@@ -3,5 +3,6 @@
 from .linear import Linear
 from .mlp import MLP
 from .grouped import GroupedLinear
+from .fused import activation_linear, norm_modulate_linear
 
-__all__ = ["Linear", "MLP", "GroupedLinear"]
+__all__ = ["Linear", "MLP", "GroupedLinear", "norm_modulate_linear", "activation_linear"]

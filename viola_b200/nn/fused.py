@@ -1,0 +1,118 @@
+"""Producer-fused FP8 linears for transformer blocks.
+
+``norm_modulate_linear(x, shift, scale, layer)`` computes ``layer(LN(x) * (1 + scale) + shift)`` and
+``activation_linear(z, layer, activation)`` computes ``layer(act(z))`` without ever writing the
+normalised / activated tensor: the FP8 quantiser of the linear recomputes it from ``x`` / ``z`` in
+the two passes a per-tensor scale needs anyway (row statistics + amax, then encode row-wise and
+transposed), and LayerNorm + modulate have a single fused backward kernel.  The reference runs
+these as separate PyTorch kernels in front of ``viola.nn.Linear`` (experiments/dit.py:33-39).
+
+Both fall back to the unfused composition when the fast path does not apply (CPU tensors, non-bf16
+activations, group-scaled or rotated layers, non-FP8 saved inputs, very wide rows).
+"""
+
+from __future__ import annotations
+
+from types import SimpleNamespace
+
+import torch
+from torch.nn import functional as F
+
+from .. import ops
+from .linear import Linear, linear_backward, linear_forward
+
+
+def _eligible(layer, x, max_width=None):
+    return (isinstance(layer, Linear) and x.is_cuda and x.dtype == torch.bfloat16 and not layer._grouped_scaling
+            and not layer.rotation_size and layer.saved_input_dtype == "fp8" and x.shape[-1] % 16 == 0
+            and (max_width is None or x.shape[-1] <= max_width))
+
+
+def _needs(ctx, positions):
+    return [ctx.needs_input_grad[p] for p in positions]
+
+
+class _NormModulateLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, shift, scale, weight, bias, layer, eps):
+        batch, tokens, width = x.shape
+        x2 = x.reshape(-1, width).contiguous()
+        shift, scale = shift.contiguous(), scale.contiguous()
+        need_w, need_b = ctx.needs_input_grad[3], bias is not None and ctx.needs_input_grad[4]
+        quantizer = layer.input_quantizer
+        limit = layer._quantization_limit(max(x2.shape), layer.fp8_dtype)
+        q, qt, qscale, mean, rstd = ops.ln_modulate_quantize(
+            x2, shift, scale, tokens, eps=eps, history=quantizer.history, index=quantizer.index,
+            delayed=quantizer.scaling == "delayed", fp8_dtype=layer.fp8_dtype, quantization_limit=limit,
+            transpose=need_w)
+        quantizer.index += 1
+        encoded = SimpleNamespace(q=q, s=qscale, qt=qt, st=qscale)
+        y, saved, _ = linear_forward(layer, x2, weight, bias, need_input_grad=True, need_weight_grad=need_w,
+                                     encoded=encoded)
+        ctx.save_for_backward(x2, scale, mean, rstd)
+        ctx.layer, ctx.saved, ctx.shape, ctx.need_b = layer, saved, x.shape, need_b
+        ctx.mod_dtypes = (shift.dtype, scale.dtype)
+        return y.reshape(batch, tokens, -1)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, scale, mean, rstd = ctx.saved_tensors
+        layer = ctx.layer
+        dy2 = dy.reshape(-1, layer.out_features).contiguous()
+        dh, dw, db = linear_backward(layer, ctx.saved, dy2, need_input_grad=True, need_weight_grad=ctx.needs_input_grad[3],
+                                     need_bias_grad=ctx.need_b)
+        dx, dshift, dscale = ops.ln_modulate_backward(dh, x2, mean, rstd, scale, ctx.shape[1])
+        return (dx.view(ctx.shape), dshift.to(ctx.mod_dtypes[0]), dscale.to(ctx.mod_dtypes[1]), dw, db, None, None)
+
+
+class _ActivationLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, z, weight, bias, layer, activation):
+        shape = z.shape
+        z2 = z.reshape(-1, shape[-1]).contiguous()
+        need_w, need_b = ctx.needs_input_grad[1], bias is not None and ctx.needs_input_grad[2]
+        quantizer = layer.input_quantizer
+        limit = layer._quantization_limit(max(z2.shape), layer.fp8_dtype)
+        q, qt, qscale = ops.activation_quantize(z2, activation, history=quantizer.history, index=quantizer.index,
+                                                delayed=quantizer.scaling == "delayed", fp8_dtype=layer.fp8_dtype,
+                                                quantization_limit=limit, transpose=need_w)
+        quantizer.index += 1
+        encoded = SimpleNamespace(q=q, s=qscale, qt=qt, st=qscale)
+        y, saved, _ = linear_forward(layer, z2, weight, bias, need_input_grad=True, need_weight_grad=need_w,
+                                     encoded=encoded)
+        ctx.save_for_backward(z2)
+        ctx.layer, ctx.saved, ctx.shape, ctx.need_b, ctx.activation = layer, saved, shape, need_b, activation
+        return y.reshape(*shape[:-1], layer.out_features)
+
+    @staticmethod
+    def backward(ctx, dy):
+        z2, = ctx.saved_tensors
+        layer = ctx.layer
+        dy2 = dy.reshape(-1, layer.out_features).contiguous()
+        da, dw, db = linear_backward(layer, ctx.saved, dy2, need_input_grad=True, need_weight_grad=ctx.needs_input_grad[1],
+                                     need_bias_grad=ctx.need_b)
+        if ctx.activation == "gelu":
+            dz = torch.ops.aten.gelu_backward(da, z2, approximate="tanh")
+        else:
+            dz = torch.ops.aten.silu_backward(da, z2)
+        return dz.view(ctx.shape), dw, db, None, None
+
+
+def norm_modulate_linear(x, shift, scale, layer, *, eps=1e-6):
+    """``layer(LayerNorm(x) * (1 + scale[:, None]) + shift[:, None])`` for ``x`` [batch, tokens, width]."""
+    if x.is_cuda and torch.is_autocast_enabled("cuda"):
+        dtype = torch.get_autocast_dtype("cuda")
+        x, shift, scale = x.to(dtype), shift.to(dtype), scale.to(dtype)
+    if _eligible(layer, x, 2048) and x.dim() == 3 and torch.is_grad_enabled() and x.requires_grad:
+        return _NormModulateLinear.apply(x, shift, scale, layer.weight, layer.bias, layer, eps)
+    normed = F.layer_norm(x, (x.shape[-1],), eps=eps)
+    return layer(torch.addcmul(shift[:, None], normed, (1 + scale)[:, None]))
+
+
+def activation_linear(z, layer, activation="gelu"):
+    """``layer(act(z))`` with ``act`` = tanh-GELU or SiLU."""
+    if z.is_cuda and torch.is_autocast_enabled("cuda"):
+        z = z.to(torch.get_autocast_dtype("cuda"))
+    if _eligible(layer, z) and torch.is_grad_enabled() and z.requires_grad and z.shape[-1] % 16 == 0:
+        return _ActivationLinear.apply(z, layer.weight, layer.bias, layer, activation)
+    return layer(F.gelu(z, approximate="tanh") if activation == "gelu" else F.silu(z))

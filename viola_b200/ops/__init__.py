@@ -532,3 +532,53 @@ def wire_unpack(packet, out, tile_size, fp8_dtype, *, reduce=False, accumulate=F
     _ops().wire_unpack(packet, packet.stride(0), rows, groups, int(tile_size), _FMT[fp8_dtype], bool(reduce),
                        out.view(-1), bool(accumulate))
     _count()
+
+
+# ------------------------------------------------------------------------------ producer-fused quantisers
+_MODES = {"ln_modulate": 1, "gelu": 2, "silu": 3}
+
+
+def ln_modulate_quantize(x, shift, scale, tokens, *, eps=1e-6, history=None, index=0, delayed=False,
+                         fp8_dtype=torch.float8_e4m3fn, quantization_limit=None, transpose=False):
+    """FP8 codes of ``LN(x) * (1 + scale[b]) + shift[b]`` without materialising it (bf16 CUDA input).
+
+    ``x`` [rows, cols], ``shift`` / ``scale`` [rows // tokens, cols].  Returns (q, qt or None, qscale, mean, rstd).
+    """
+    rows, cols = x.shape
+    limit = _limit(fp8_dtype, quantization_limit)
+    mean = torch.empty(rows, device=x.device, dtype=torch.float32)
+    rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
+    qscale = torch.empty(1, device=x.device, dtype=torch.float32)
+    _ops().ln_stats_amax(x, float(eps), shift, scale, int(tokens), mean, rstd, history, int(index), bool(delayed), limit,
+                         qscale, _amax_scratch(x.device))
+    q = torch.empty((rows, cols), device=x.device, dtype=fp8_dtype)
+    qt = torch.empty((cols, rows), device=x.device, dtype=fp8_dtype) if transpose else None
+    _ops().fused_quantize(x, 1, mean, rstd, shift, scale, int(tokens), qscale, limit, _FMT[fp8_dtype], q, qt)
+    _count(2)
+    return q, qt, qscale, mean, rstd
+
+
+def activation_quantize(z, activation, *, history=None, index=0, delayed=False, fp8_dtype=torch.float8_e4m3fn,
+                        quantization_limit=None, transpose=False):
+    """FP8 codes of ``act(z)`` (gelu / silu) without materialising it.  Returns (q, qt or None, qscale)."""
+    rows, cols = z.shape
+    limit = _limit(fp8_dtype, quantization_limit)
+    qscale = torch.empty(1, device=z.device, dtype=torch.float32)
+    mode = _MODES[activation]
+    _ops().act_amax(z, mode, history, int(index), bool(delayed), limit, qscale, _amax_scratch(z.device))
+    q = torch.empty((rows, cols), device=z.device, dtype=fp8_dtype)
+    qt = torch.empty((cols, rows), device=z.device, dtype=fp8_dtype) if transpose else None
+    _ops().fused_quantize(z, mode, None, None, None, None, 1, qscale, limit, _FMT[fp8_dtype], q, qt)
+    _count(2)
+    return q, qt, qscale
+
+
+def ln_modulate_backward(dh, x, mean, rstd, scale, tokens):
+    """Gradients of LN + modulate: returns (dx [rows, cols] bf16, dshift, dscale [samples, cols] fp32)."""
+    rows, cols = x.shape
+    dx = torch.empty_like(x)
+    dshift = torch.zeros((rows // tokens, cols), device=x.device, dtype=torch.float32)
+    dscale = torch.zeros_like(dshift)
+    _ops().ln_modulate_backward(dh, x, mean, rstd, scale, int(tokens), dx, dshift, dscale)
+    _count()
+    return dx, dshift, dscale

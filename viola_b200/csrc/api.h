@@ -63,6 +63,7 @@ typedef struct VbGemmDesc {
   // batched problems (LINEAR / AXPBY): A is [batch * M, K], B is [batch * N, K]; strides in elements
   int batch;
   long long out_batch_stride, resid_batch_stride, out_t_batch_stride;
+  int no_tma_store;      // 1: LINEAR epilogue writes with per-thread stores instead of the TMA-store path
 } VbGemmDesc;
 
 int vb_gemm(const VbGemmDesc* desc, cudaStream_t stream);

@@ -64,6 +64,7 @@ struct GemmArgs {
   // batched mode: `batch` independent problems stacked along the rows of A, B and the outputs
   int batch, tiles_per_batch;
   long long b_rows_per_batch, out_bs, resid_bs, out_t_bs;
+  int tma_store;        // LINEAR epilogue: stage in shared memory and write with TMA
   int* status;
 };
 
@@ -205,12 +206,15 @@ struct Config {
   static constexpr int kABytes = BM * BK_BYTES;
   static constexpr int kBBytes = BN * BK_BYTES;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr bool kTmaStore = EPI == VB_EPI_LINEAR;   // epilogue staged in smem and written by TMA
+  static constexpr int kStoreBytes = kTmaStore ? 4 * 2 * 4096 : 0;   // 4 warps x 2 buffers x (32 rows x 128 B)
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? ((GROUP && kTmaStore) ? 5 : 6) : 8);
   static constexpr int kAcc = GROUP ? (512 / BN > 4 ? 4 : 512 / BN) : 2;
   static constexpr int kTmemCols = kAcc * BN;
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kSbStage = GROUP ? 4 * 2 * BN * (int)sizeof(float) : 0;  // per-warp staged B scales
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kSbStage + 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kSbStage + kStoreBytes + 1024;
+  static_assert(kSmemBytes <= 232448, "dynamic shared memory limit of sm_100");
   static constexpr int kElemBytes = KIND == VB_KIND_F8 ? 1 : 2;
   static constexpr int kBK = BK_BYTES / kElemBytes;  // elements per K-block
   static constexpr int kUmmaKBytes = 32;
@@ -222,7 +226,7 @@ struct Config {
 template <int KIND, int BN, bool GROUP, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const GemmArgs args) {
+            const __grid_constant__ CUtensorMap tmC, const GemmArgs args) {
   using C = Config<KIND, BN, GROUP, EPI>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -235,6 +239,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + C::kAcc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* sb_stage = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes + C::kBarrierBytes);
+  // epilogue staging for TMA stores: the stage ring is a multiple of 1024 bytes and the barrier and
+  // scale areas are 1024 / 4096 bytes, so this region keeps the 1024-byte alignment the swizzle needs
+  uint8_t* store_stage = smem + C::kStages * C::kStageBytes + C::kBarrierBytes + C::kSbStage;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -458,14 +465,58 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
         }
         const int col0 = n0 + c * 32;
-        if (col0 >= args.N) continue;  // warp-uniform
+        const bool staged = C::kTmaStore && args.tma_store != 0;
+        if (col0 >= args.N && !staged) continue;  // warp-uniform
         if constexpr (EPI == VB_EPI_LINEAR) {
           if (args.bias != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               if (col0 + j < args.N) v[j] += load_elem(args.bias, col0 + j, args.bias_dtype);
           }
-          if (row_ok) store_row32(out_base, args.ldo, args.out_dtype, grow, col0, args.N, v);
+          if (!staged) {
+            if (row_ok) store_row32(out_base, args.ldo, args.out_dtype, grow, col0, args.N, v);
+          } else {
+            // Each warp owns 32 rows x 128 bytes per slab, double buffered.  A lane writes its row's
+            // 16-byte pieces at the 128B-swizzled position; one lane then issues the TMA store, which
+            // clips rows >= M and columns >= N by itself.
+            const int elem = args.out_dtype == 0 ? 4 : 2;
+            const int chunks_per_slab = 128 / (32 * elem);          // 1 (fp32) or 2 (16-bit)
+            const int in_slab = c % chunks_per_slab;
+            const int slab = c / chunks_per_slab;
+            uint8_t* buffer = store_stage + ((warp - 2) * 2 + (slab & 1)) * 4096;
+            if (in_slab == 0) {
+              if (lane == 0) tma_store_wait_read<1>();               // the store that last used this buffer
+              __syncwarp();
+            }
+            uint8_t* row_ptr = buffer + lane * 128;
+            const int piece0 = in_slab * (32 * elem / 16);
+            if (elem == 4) {
+#pragma unroll
+              for (int p = 0; p < 8; ++p)
+                *reinterpret_cast<float4*>(row_ptr + (((piece0 + p) ^ (lane & 7)) << 4)) =
+                    make_float4(v[4 * p], v[4 * p + 1], v[4 * p + 2], v[4 * p + 3]);
+            } else {
+#pragma unroll
+              for (int p = 0; p < 4; ++p) {
+                uint4 t;
+                t.x = pack2(v[8 * p + 0], v[8 * p + 1], args.out_dtype);
+                t.y = pack2(v[8 * p + 2], v[8 * p + 3], args.out_dtype);
+                t.z = pack2(v[8 * p + 4], v[8 * p + 5], args.out_dtype);
+                t.w = pack2(v[8 * p + 6], v[8 * p + 7], args.out_dtype);
+                *reinterpret_cast<uint4*>(row_ptr + (((piece0 + p) ^ (lane & 7)) << 4)) = t;
+              }
+            }
+            if (in_slab == chunks_per_slab - 1 || c == NOUT - 1) {
+              fence_proxy_async_smem();
+              __syncwarp();
+              const int slab_col = n0 + slab * chunks_per_slab * 32;
+              const int warp_row = mt * BM + quad * 32;
+              if (lane == 0 && slab_col < args.N && warp_row < args.M) {
+                tma_store_2d(&tmC, buffer, slab_col, warp_row);
+              }
+              if (lane == 0) tma_store_commit();
+            }
+          }
         } else if constexpr (EPI == VB_EPI_AXPBY) {
           float res[32];
           if (resid_base != nullptr && row_ok) load_row32(resid_base, args.ldr, args.out_dtype, grow, col0, args.N, res);
@@ -546,6 +597,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
   }
 
+  if constexpr (C::kTmaStore) {
+    if (warp >= 2 && lane == 0) tma_store_wait_all();   // stores read this CTA's shared memory until they finish
+  }
   // ------------------------------ teardown ------------------------------------
   // On the error path TMA copies may still be in flight towards this CTA's shared memory:
   // give them a bounded grace period before the CTA (and its smem) goes away.
@@ -621,6 +675,22 @@ static int make_map(CUtensorMap* map, const void* base, int kind, int fmt, long 
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+// Output tensor map for the TMA-store epilogue: box = 128 bytes of columns x 32 rows, 128B swizzle.
+static int make_out_map(CUtensorMap* map, void* base, int out_dtype, long long rows, long long cols, long long ld_elems) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return (int)cudaErrorNotSupported;
+  const int elem = out_dtype == 0 ? 4 : 2;
+  CUtensorMapDataType dt = out_dtype == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                          : (out_dtype == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)(ld_elems * elem)};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / elem), 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
 static int sm_count() {
   static int count = 0;
   if (count == 0) {
@@ -674,6 +744,14 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream) {
   if (rc) return rc;
   rc = make_map(&tmB, d.B, KIND, d.b_fmt, b_rows, d.K, d.ldb, C::kBBoxRows);
   if (rc) return rc;
+  CUtensorMap tmC = tmA;
+  a.tma_store = 0;
+  if (C::kTmaStore && !expert && a.batch == 1 && !d.no_tma_store) {
+    const int elem = d.out_dtype == 0 ? 4 : 2;
+    if ((reinterpret_cast<uintptr_t>(d.out) & 15) == 0 && (d.ldo * elem) % 16 == 0 &&
+        make_out_map(&tmC, d.out, d.out_dtype, d.M, d.N, d.ldo) == 0)
+      a.tma_store = 1;
+  }
   if (expert) {
     expert_tile_map_kernel<<<1, 32, 0, stream>>>(d.expert_offsets, d.num_experts, a.num_m_tiles, d.tile_map);
   }
@@ -685,7 +763,7 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream) {
     configured = true;
   }
   const int grid = std::min(a.num_tiles, sm_count());
-  kernel<<<grid, kThreads, C::kSmemBytes, stream>>>(tmA, tmB, a);
+  kernel<<<grid, kThreads, C::kSmemBytes, stream>>>(tmA, tmB, tmC, a);
   return (int)cudaGetLastError();
 }
 

@@ -18,6 +18,7 @@ from torch import nn
 from torch.nn import functional as F
 
 from ..nn import Linear, activation_linear, norm_modulate_linear
+from ..nn.attention import packed_attention
 
 
 def position_embedding(size, width):
@@ -55,8 +56,7 @@ class Block(nn.Module):
         b, n, d = x.shape
         # LayerNorm + modulate are folded into the FP8 quantiser of qkv / fc1, GELU into that of fc2
         qkv = norm_modulate_linear(x, s1, a1, self.qkv, eps=self.norm1.eps)
-        q, k, v = qkv.view(b, n, 3, self.heads, d // self.heads).permute(2, 0, 3, 1, 4).unbind(0)
-        h = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(b, n, d)
+        h = packed_attention(qkv.view(b, n, 3, self.heads, d // self.heads))
         x = gated_residual(x, g1, self.proj(h))
         h = norm_modulate_linear(x, s2, a2, self.fc1, eps=self.norm2.eps)
         return gated_residual(x, g2, activation_linear(h, self.fc2, "gelu"))

@@ -136,6 +136,45 @@ def test_ns_gemm(dtype, m, k):
     assert torch.equal(new_t, new.t())
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (640, 384, 1152), (1008, 528, 2000), (1152, 4608, 4096)])
+def test_gemm_mn_major_operands(a_mn, b_mn, m, n, k):
+    """Operands handed over transposed ([K, M] / [K, N]) are read MN-major in place and give the K-major result."""
+    torch.manual_seed(11)
+    a8 = torch.randn(m, k, device=dev()).to(E4M3)
+    b8 = torch.randn(n, k, device=dev()).to(E5M2 if not (a_mn and b_mn) else E4M3)
+    sa, sb = torch.tensor([0.5], device=dev()), torch.tensor([1.25], device=dev())
+    base = ops.gemm(a8, b8, sa, sb, out_dtype=torch.float32)
+    assert rel_l2(base, (a8.float() @ b8.float().t()) * 0.625) < 2e-5
+    a_arg = a8.view(torch.uint8).t().contiguous().view(a8.dtype) if a_mn else a8
+    b_arg = b8.view(torch.uint8).t().contiguous().view(b8.dtype) if b_mn else b8
+    for bn in (0, 128, 256):
+        out = ops.gemm(a_arg, b_arg, sa, sb, out_dtype=torch.float32, a_mn=a_mn, b_mn=b_mn, force_bn=bn)
+        assert torch.equal(out, base), (bn, rel_l2(out, base))
+    for dtype in (torch.bfloat16, torch.float16):
+        a16 = (torch.randn(m, k, device=dev()) / math.sqrt(k)).to(dtype)
+        b16 = torch.randn(n, k, device=dev()).to(dtype)
+        resid = torch.randn(m, n, device=dev()).to(dtype)
+        base16 = ops.ns_gemm(a16, b16, alpha=0.75, beta=-1.5, resid=resid)
+        out16 = ops.ns_gemm(a16.t().contiguous() if a_mn else a16, b16.t().contiguous() if b_mn else b16, alpha=0.75,
+                            beta=-1.5, resid=resid, a_mn=a_mn, b_mn=b_mn)
+        assert torch.equal(out16, base16), rel_l2(out16, base16)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(True, False), (False, True), (True, True)])
+def test_batched_ns_gemm_mn_major(a_mn, b_mn):
+    torch.manual_seed(12)
+    batch, m, n, k = 5, 384, 640, 1152
+    a = (torch.randn(batch, m, k, device=dev()) / math.sqrt(k)).bfloat16()
+    b = torch.randn(batch, n, k, device=dev()).bfloat16()
+    base = ops.ns_gemm(a, b)
+    assert rel_l2(base, a.float() @ b.float().mT) < 4e-3
+    out = ops.ns_gemm(a.mT.contiguous() if a_mn else a, b.mT.contiguous() if b_mn else b, a_mn=a_mn, b_mn=b_mn)
+    assert torch.equal(out, base)
+    ops.check_status()
+
+
 @pytest.mark.parametrize("activation", ["silu", "gelu", "relu"])
 @pytest.mark.parametrize("grouped", [False, True])
 def test_gated_gemm(activation, grouped):

@@ -63,6 +63,9 @@ typedef struct VbGemmDesc {
   // batched problems (LINEAR / AXPBY): A is [batch * M, K], B is [batch * N, K]; strides in elements
   int batch;
   long long out_batch_stride, resid_batch_stride, out_t_batch_stride;
+  // operand layouts: 0 = K-major (A is [M, K], B is [N, K]); 1 = MN-major (A stored as [K, M], B as [K, N]);
+  // lda / ldb are always the row pitch of the stored matrix
+  int a_mn_major, b_mn_major;
   int no_tma_store;      // 1: LINEAR epilogue writes with per-thread stores instead of the TMA-store path
 } VbGemmDesc;
 
@@ -98,6 +101,18 @@ int vb_ema_lerp(void* ema, int ema_dtype, const void* master, int master_dtype, 
                 cudaStream_t stream);
 int vb_philox_kat(unsigned long long element, unsigned long long step, unsigned long long key,
                   unsigned int* out, int count, cudaStream_t stream);
+
+// ---- multi-tensor optimizer kernels (multi.cu) --------------------------------------------
+// table: device array of 64-byte descriptors {p0, p1, p2, p3, n, i0, (f0, f1), (d0, d1)};
+// prefix: device int32[tensors + 1] prefix sums of 4096-element chunks; blocks = prefix[tensors].
+int vb_multi_ema(const void* table, const int* prefix, int tensors, int blocks, float decay, cudaStream_t stream);
+int vb_multi_adam(const void* table, const int* prefix, int tensors, int blocks, float lr, float decay, float b1,
+                  float b2, float inv_c1, float inv_c2, float eps, int adamw, int maximize, int stochastic,
+                  long long step, cudaStream_t stream);
+int vb_multi_weight_update(const void* table, const int* prefix, int tensors, int blocks, float lr, float decay,
+                           int stochastic, long long step, cudaStream_t stream);
+int vb_multi_momentum(const void* table, const int* prefix, int tensors, int blocks, int tile, float beta,
+                      float inv_loss_scale, int nesterov, int stochastic, long long step, cudaStream_t stream);
 
 // ---- gated activation (unfused baseline + post-rotation path) ------------------
 int vb_gated_forward(const void* gu, int dtype, int rows, int hidden, int activation, void* out,

@@ -86,13 +86,19 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t epilogue, int64_
           const OptTensor& sb, at::IntArrayRef scale_layout, const OptTensor& bias, double alpha, double beta,
           const OptTensor& resid, const OptTensor& out_t, bool symmetric, int64_t activation, const OptTensor& aux,
           const OptTensor& expert_offsets, const OptTensor& tile_map, const OptTensor& status, int64_t force_bn,
-          int64_t batch) {
+          int64_t batch, bool a_mn, bool b_mn) {
+  // a_mn: ``a`` holds A transposed, i.e. [batch * K, M]; b_mn: ``b`` holds B transposed, [batch * K, N]
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda());
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && out.stride(-1) == 1);
   TORCH_CHECK(batch >= 1 && a.size(0) % batch == 0 && b.size(0) % batch == 0);
-  TORCH_CHECK(a.size(1) == b.size(1), "K mismatch");
+  const int64_t k_a = a_mn ? a.size(0) / batch : a.size(1);
+  const int64_t k_b = b_mn ? b.size(0) / batch : b.size(1);
+  TORCH_CHECK(k_a == k_b, "K mismatch");
+  TORCH_CHECK(!b_mn || b.size(1) >= n_logical, "MN-major B must hold at least N columns");
   c10::cuda::CUDAGuard guard(a.device());
   VbGemmDesc d{};
+  d.a_mn_major = a_mn;
+  d.b_mn_major = b_mn;
   if (a.element_size() == 1) {
     d.kind = VB_KIND_F8;
     d.a_fmt = fp8_code(a);
@@ -105,9 +111,9 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t epilogue, int64_
   }
   d.epilogue = (int)epilogue;
   d.batch = (int)batch;
-  d.M = (int)(a.size(0) / batch);
+  d.M = (int)(a_mn ? a.size(1) : a.size(0) / batch);
   d.N = (int)n_logical;
-  d.K = (int)a.size(1);
+  d.K = (int)k_a;
   d.A = a.data_ptr();
   d.lda = a.stride(0);
   d.B = b.data_ptr();
@@ -443,6 +449,35 @@ void ln_modulate_backward(const Tensor& dh, const Tensor& x, const Tensor& mean,
         "ln_modulate_backward");
 }
 
+// ---- multi-tensor optimizer kernels ---------------------------------------------------------------
+void multi_ema(const Tensor& table, const Tensor& prefix, int64_t blocks, double decay) {
+  c10::cuda::CUDAGuard guard(table.device());
+  check(vb_multi_ema(table.data_ptr(), (const int*)prefix.data_ptr(), (int)table.size(0), (int)blocks, (float)decay, stream()),
+        "multi_ema");
+}
+void multi_adam(const Tensor& table, const Tensor& prefix, int64_t blocks, double lr, double decay, double b1, double b2,
+                double inv_c1, double inv_c2, double eps, bool adamw, bool maximize, bool stochastic, int64_t step) {
+  c10::cuda::CUDAGuard guard(table.device());
+  check(vb_multi_adam(table.data_ptr(), (const int*)prefix.data_ptr(), (int)table.size(0), (int)blocks, (float)lr,
+                      (float)decay, (float)b1, (float)b2, (float)inv_c1, (float)inv_c2, (float)eps, adamw, maximize,
+                      stochastic, step, stream()),
+        "multi_adam");
+}
+void multi_weight_update(const Tensor& table, const Tensor& prefix, int64_t blocks, double lr, double decay, bool stochastic,
+                         int64_t step) {
+  c10::cuda::CUDAGuard guard(table.device());
+  check(vb_multi_weight_update(table.data_ptr(), (const int*)prefix.data_ptr(), (int)table.size(0), (int)blocks, (float)lr,
+                               (float)decay, stochastic, step, stream()),
+        "multi_weight_update");
+}
+void multi_momentum(const Tensor& table, const Tensor& prefix, int64_t blocks, int64_t tile, double beta,
+                    double inv_loss_scale, bool nesterov, bool stochastic, int64_t step) {
+  c10::cuda::CUDAGuard guard(table.device());
+  check(vb_multi_momentum(table.data_ptr(), (const int*)prefix.data_ptr(), (int)table.size(0), (int)blocks, (int)tile,
+                          (float)beta, (float)inv_loss_scale, nesterov, stochastic, step, stream()),
+        "multi_momentum");
+}
+
 }  // namespace
 
 TORCH_LIBRARY(viola_b200, m) {
@@ -475,6 +510,10 @@ TORCH_LIBRARY(viola_b200, m) {
   m.def("signal", &signal);
   m.def("wait_flags", &wait_flags);
   m.def("gather_pull", &gather_pull);
+  m.def("multi_ema", &multi_ema);
+  m.def("multi_adam", &multi_adam);
+  m.def("multi_weight_update", &multi_weight_update);
+  m.def("multi_momentum", &multi_momentum);
   m.def("ln_stats_amax", &ln_stats_amax);
   m.def("act_amax", &act_amax);
   m.def("fused_quantize", &fused_quantize);

@@ -236,6 +236,20 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
   return d;
 }
 
+// Descriptor for an MN-major operand tile (the MN dimension is contiguous in memory): the tile is a
+// sequence of blocks of 128 bytes of MN x (K rows), each loaded by one TMA box with SWIZZLE_128B
+// (K-row pitch 128 B, 8-row swizzle groups 1024 B apart = SBO); LBO is the distance between
+// consecutive MN blocks.  One MMA K-step advances the start address by (K rows per MMA) x 128 B.
+__device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr, uint32_t block_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((block_bytes >> 4) & 0x3FFFu) << 16;   // leading byte offset: next 128-byte MN block
+  d |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset: next group of 8 K rows
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
 // Instruction descriptor for kind::f16 / kind::f8f6f4 with an fp32 accumulator.
 // a_fmt/b_fmt: f16 kind -> 0 = fp16, 1 = bf16;  f8f6f4 kind -> 0 = e4m3, 1 = e5m2.
 __host__ __device__ constexpr uint32_t make_idesc(int a_fmt, int b_fmt, int m, int n,

@@ -65,6 +65,7 @@ struct GemmArgs {
   int batch, tiles_per_batch;
   long long b_rows_per_batch, out_bs, resid_bs, out_t_bs;
   int tma_store;        // LINEAR epilogue: stage in shared memory and write with TMA
+  int a_mn, b_mn;       // operand stored MN-major: A as [K, M] / B as [K, N] (row-major, MN contiguous)
   int* status;
 };
 
@@ -292,8 +293,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           uint8_t* sa_ptr = stage_base + stage * C::kStageBytes;
           uint8_t* sb_ptr = sa_ptr + C::kABytes;
           mbar_expect_tx(&full_bar[stage], C::kStageBytes);
-          tma_load_2d(sa_ptr, &tmA, &full_bar[stage], kb * C::kBK, a_row);
-          tma_load_2d(sb_ptr, &tmB, &full_bar[stage], kb * C::kBK, b_row);
+          constexpr int kBlockElems = 128 / C::kElemBytes;      // MN elements per 128-byte block
+          constexpr int kBlockBytes = C::kBK * 128;             // one MN block: kBK K-rows x 128 bytes
+          if (!args.a_mn) {
+            tma_load_2d(sa_ptr, &tmA, &full_bar[stage], kb * C::kBK, a_row);
+          } else {
+#pragma unroll
+            for (int blk = 0; blk < BM / kBlockElems; ++blk)
+              tma_load_2d(sa_ptr + blk * kBlockBytes, &tmA, &full_bar[stage], mt * BM + blk * kBlockElems,
+                          bi * args.K + kb * C::kBK);
+          }
+          if (!args.b_mn) {
+            tma_load_2d(sb_ptr, &tmB, &full_bar[stage], kb * C::kBK, b_row);
+          } else {
+#pragma unroll
+            for (int blk = 0; blk < BN / kBlockElems; ++blk)
+              tma_load_2d(sb_ptr + blk * kBlockBytes, &tmB, &full_bar[stage], nt * BN + blk * kBlockElems,
+                          bi * args.K + kb * C::kBK);
+          }
           if constexpr (C::kGatedFwd)
             tma_load_2d(sb_ptr + C::kBBoxRows * BK_BYTES, &tmB, &full_bar[stage], kb * C::kBK,
                         b_row + args.b_gate_up_offset);
@@ -329,15 +346,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (lane == 0) {
           const uint32_t a_addr = smem_u32(stage_base + stage * C::kStageBytes);
           const uint32_t b_addr = a_addr + C::kABytes;
-          const uint64_t adesc = make_kmajor_sw128_desc(a_addr);
-          const uint64_t bdesc = make_kmajor_sw128_desc(b_addr);
+          constexpr uint32_t kBlockBytes = C::kBK * 128;
+          constexpr uint32_t kMnStep = (32 / C::kElemBytes) * 128;   // K rows of one MMA x 128-byte row pitch
+          const uint64_t adesc = args.a_mn ? make_mnmajor_sw128_desc(a_addr, kBlockBytes) : make_kmajor_sw128_desc(a_addr);
+          const uint64_t bdesc = args.b_mn ? make_mnmajor_sw128_desc(b_addr, kBlockBytes) : make_kmajor_sw128_desc(b_addr);
           const uint32_t d_tmem = tmem_base + acc * BN;
 #pragma unroll
           for (int k = 0; k < C::kMmasPerStage; ++k) {
             const uint32_t accumulate = GROUP ? (k > 0) : (kb > 0 || k > 0);
-            const uint64_t koff = (uint64_t)((k * C::kUmmaKBytes) >> 4);
-            if constexpr (KIND == VB_KIND_F8) mma_f8_ss(d_tmem, adesc + koff, bdesc + koff, args.idesc, accumulate);
-            else mma_f16_ss(d_tmem, adesc + koff, bdesc + koff, args.idesc, accumulate);
+            const uint64_t koff_a = (uint64_t)((k * (args.a_mn ? kMnStep : (uint32_t)C::kUmmaKBytes)) >> 4);
+            const uint64_t koff_b = (uint64_t)((k * (args.b_mn ? kMnStep : (uint32_t)C::kUmmaKBytes)) >> 4);
+            if constexpr (KIND == VB_KIND_F8) mma_f8_ss(d_tmem, adesc + koff_a, bdesc + koff_b, args.idesc, accumulate);
+            else mma_f16_ss(d_tmem, adesc + koff_a, bdesc + koff_b, args.idesc, accumulate);
           }
           tc_commit(&empty_bar[stage]);
           if constexpr (GROUP) tc_commit(&tmem_full[acc]);
@@ -675,6 +695,24 @@ static int make_map(CUtensorMap* map, const void* base, int kind, int fmt, long 
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+// Tensor map for an MN-major operand stored as [k_rows, mn] row-major: box = 128 bytes of MN x box_k rows.
+static int make_map_mn(CUtensorMap* map, const void* base, int kind, int fmt, long long k_rows, long long mn,
+                       long long ld_elems, int box_k) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return (int)cudaErrorNotSupported;
+  const int elem = kind == VB_KIND_F8 ? 1 : 2;
+  CUtensorMapDataType dt = kind == VB_KIND_F8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                              : (fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  cuuint64_t dims[2] = {(cuuint64_t)mn, (cuuint64_t)k_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)(ld_elems * elem)};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / elem), (cuuint32_t)box_k};
+  cuuint32_t estr[2] = {1, 1};
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (strides[0] & 15) != 0) return (int)cudaErrorMisalignedAddress;
+  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
 // Output tensor map for the TMA-store epilogue: box = 128 bytes of columns x 32 rows, 128B swizzle.
 static int make_out_map(CUtensorMap* map, void* base, int out_dtype, long long rows, long long cols, long long ld_elems) {
   EncodeTiledFn fn = get_encode_fn();
@@ -723,7 +761,11 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream) {
   a.num_tiles = a.batch * a.tiles_per_batch;
   a.b_rows_per_batch = d.N;
   a.out_bs = d.out_batch_stride; a.resid_bs = d.resid_batch_stride; a.out_t_bs = d.out_t_batch_stride;
-  a.idesc = make_idesc(d.a_fmt, d.b_fmt, BM, BN);
+  a.a_mn = d.a_mn_major ? 1 : 0;
+  a.b_mn = d.b_mn_major ? 1 : 0;
+  if ((a.a_mn || a.b_mn) && (expert || C::kGatedFwd)) return (int)cudaErrorInvalidValue;
+  if ((a.a_mn || a.b_mn) && d.batch > 1 && d.K % C::kBK != 0) return (int)cudaErrorInvalidValue;
+  a.idesc = make_idesc(d.a_fmt, d.b_fmt, BM, BN, a.a_mn, a.b_mn);
   a.b_gate_up_offset = d.N;
   a.sa = d.sa; a.sb = d.sb;
   a.sa_row = d.sa_row; a.sa_k = d.sa_k; a.sb_row = d.sb_row; a.sb_k = d.sb_k;
@@ -740,9 +782,11 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream) {
 
   const long long b_rows = (long long)(C::kGatedFwd ? 2 : 1) * d.N * (expert ? d.num_experts : 1) * a.batch;
   CUtensorMap tmA, tmB;
-  int rc = make_map(&tmA, d.A, KIND, d.a_fmt, (long long)d.M * a.batch, d.K, d.lda, BM);
+  int rc = a.a_mn ? make_map_mn(&tmA, d.A, KIND, d.a_fmt, (long long)d.K * a.batch, d.M, d.lda, C::kBK)
+                  : make_map(&tmA, d.A, KIND, d.a_fmt, (long long)d.M * a.batch, d.K, d.lda, BM);
   if (rc) return rc;
-  rc = make_map(&tmB, d.B, KIND, d.b_fmt, b_rows, d.K, d.ldb, C::kBBoxRows);
+  rc = a.b_mn ? make_map_mn(&tmB, d.B, KIND, d.b_fmt, (long long)d.K * a.batch, d.N, d.ldb, C::kBK)
+              : make_map(&tmB, d.B, KIND, d.b_fmt, b_rows, d.K, d.ldb, C::kBBoxRows);
   if (rc) return rc;
   CUtensorMap tmC = tmA;
   a.tma_store = 0;

@@ -41,9 +41,9 @@ class _Quantizer(nn.Module):
         self.index = 0
         self.register_buffer("history", torch.zeros(history_len, device=device, dtype=torch.float32))
 
-    def scale(self, x, fp8_dtype=torch.float8_e4m3fn, quantization_limit=None):
+    def scale(self, x, fp8_dtype=torch.float8_e4m3fn, quantization_limit=None, out=None):
         result = ops.tensor_scale(x, history=self.history, index=self.index, delayed=self.scaling == "delayed",
-                                  fp8_dtype=fp8_dtype, quantization_limit=quantization_limit)
+                                  fp8_dtype=fp8_dtype, quantization_limit=quantization_limit, out=out)
         self.index += 1
         return result
 
@@ -450,8 +450,7 @@ class Linear(nn.Module):
             return q if out is None else out.copy_(q)
         limit = self._quantization_limit(max(self.in_features, self.out_features), self.fp8_dtype)
         source = ops.hadamard64(master) if self.rotation_size else master
-        scale = self.weight_quantizer.scale(source, self.fp8_dtype, limit)
-        self.weight_scale.copy_(scale)
+        scale = self.weight_quantizer.scale(source, self.fp8_dtype, limit, out=self.weight_scale)
         q, _ = ops.quantize(source, scale, transpose=out_t is not None, fp8_dtype=self.fp8_dtype, out=out, out_t=out_t,
                             quantization_limit=limit)
         return q

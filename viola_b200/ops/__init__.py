@@ -108,11 +108,14 @@ def _limit(dtype, limit):
 
 
 # ------------------------------------------------------------------------------ per-tensor scaling
-def tensor_scale(x, *, history=None, index=0, delayed=False, fp8_dtype=torch.float8_e4m3fn, quantization_limit=None):
+def tensor_scale(x, *, history=None, index=0, delayed=False, fp8_dtype=torch.float8_e4m3fn, quantization_limit=None,
+                 out=None):
+    """scale = max(amax, 1e-30) / limit as an fp32[1] tensor (written into ``out`` when given)."""
     if not x.is_cuda:
-        return reference.tensor_scale(x, history=history, index=index, delayed=delayed, fp8_dtype=fp8_dtype,
-                                      quantization_limit=quantization_limit)
-    scale = torch.empty(1, device=x.device, dtype=torch.float32)
+        result = reference.tensor_scale(x, history=history, index=index, delayed=delayed, fp8_dtype=fp8_dtype,
+                                        quantization_limit=quantization_limit)
+        return result if out is None else out.copy_(result)
+    scale = out if out is not None else torch.empty(1, device=x.device, dtype=torch.float32)
     _ops().amax_scale(x.detach().contiguous().view(-1), history, int(index), bool(delayed),
                       _limit(fp8_dtype, quantization_limit), scale, _amax_scratch(x.device))
     _count()
@@ -161,26 +164,40 @@ def _pad_k(t, multiple):
     return padded
 
 
+def _check_mn(t):
+    # an MN-major operand ([K, MN], MN contiguous) is read in place: TMA needs 16-byte aligned rows
+    if t.stride(1) != 1 or (t.stride(0) * t.element_size()) % 16 or t.data_ptr() % 16:
+        raise ValueError("an MN-major GEMM operand needs unit column stride and 16-byte aligned rows")
+    return t
+
+
 def _gemm(a, b, out, epilogue, n_logical, *, sa=None, sb=None, layout=_NO_GROUP, bias=None, alpha=1.0, beta=0.0,
           resid=None, out_t=None, symmetric=False, activation=0, aux=None, expert_offsets=None, tile_map=None,
-          force_bn=0, batch=1):
+          force_bn=0, batch=1, a_mn=False, b_mn=False):
     multiple = 16 if a.element_size() == 1 else 8
-    a, b = _pad_k(a, multiple), _pad_k(b, multiple)
+    a = _check_mn(a) if a_mn else _pad_k(a, multiple)
+    b = _check_mn(b) if b_mn else _pad_k(b, multiple)
     _ops().gemm(a, b, out, epilogue, n_logical, sa, sb, list(layout), bias, float(alpha), float(beta), resid, out_t,
                 bool(symmetric), int(activation), aux, expert_offsets, tile_map, status_word(a.device), int(force_bn),
-                int(batch))
+                int(batch), bool(a_mn), bool(b_mn))
     _count(2 if expert_offsets is not None else 1)
     return out
 
 
-def gemm(a, b, sa, sb, *, out_dtype, bias=None, out=None, force_bn=0):
-    """(a * sa) @ (b * sb).T (+ bias): FP8 or 16-bit operands with per-tensor fp32 scales."""
+def gemm(a, b, sa, sb, *, out_dtype, bias=None, out=None, force_bn=0, a_mn=False, b_mn=False):
+    """(a * sa) @ (b * sb).T (+ bias): FP8 or 16-bit operands with per-tensor fp32 scales.
+
+    ``a_mn`` / ``b_mn``: the tensor passed holds the operand transposed (``a`` is [K, M] / ``b`` is [K, N]);
+    the tensor core reads it MN-major in place, so no transposed copy is needed.
+    """
     if not a.is_cuda:
-        result = reference.gemm(a, b, sa, sb, out_dtype=out_dtype, bias=bias)
+        result = reference.gemm(a.t() if a_mn else a, b.t() if b_mn else b, sa, sb, out_dtype=out_dtype, bias=bias)
         return result if out is None else out.copy_(result)
+    m = a.shape[1] if a_mn else a.shape[0]
+    n = b.shape[1] if b_mn else b.shape[0]
     if out is None:
-        out = torch.empty((a.shape[0], b.shape[0]), device=a.device, dtype=out_dtype)
-    return _gemm(a, b, out, EPI_LINEAR, b.shape[0], sa=sa, sb=sb, bias=bias, force_bn=force_bn)
+        out = torch.empty((m, n), device=a.device, dtype=out_dtype)
+    return _gemm(a, b, out, EPI_LINEAR, n, sa=sa, sb=sb, bias=bias, force_bn=force_bn, a_mn=a_mn, b_mn=b_mn)
 
 
 # ------------------------------------------------------------------------------ group scaling
@@ -380,26 +397,28 @@ def expert_gemm(a, w, offsets, sa, sw, *, out_dtype, group=None, sa_kmajor=False
 
 
 # ------------------------------------------------------------------------------ Newton-Schulz GEMM
-def ns_gemm(a, b, *, out=None, alpha=1.0, beta=0.0, resid=None, out_t=None, symmetric=False, force_bn=0):
+def ns_gemm(a, b, *, out=None, alpha=1.0, beta=0.0, resid=None, out_t=None, symmetric=False, force_bn=0,
+            a_mn=False, b_mn=False):
     """out = alpha * round(a @ b^T) + beta * resid in the operands' 16-bit dtype.
 
     ``a`` [.., m, k] and ``b`` [.., n, k] may carry one leading batch dimension (contiguous stacks):
-    the whole stack is one persistent-kernel launch.
+    the whole stack is one persistent-kernel launch.  With ``a_mn`` / ``b_mn`` the tensor holds the operand
+    transposed ([.., k, m] / [.., k, n]) and is read MN-major in place.
     """
     if not a.is_cuda:
-        acc = (a.float() @ b.float().mT).to(a.dtype).float()
+        acc = ((a.mT if a_mn else a).float() @ (b if b_mn else b.mT).float()).to(a.dtype).float()
         result = (alpha * acc + (beta * resid.float() if resid is not None else 0.0)).to(a.dtype)
         if out_t is not None:
             out_t.copy_(result.mT)
         return result if out is None else out.copy_(result)
     batch = a.shape[0] if a.ndim == 3 else 1
-    m, n = a.shape[-2], b.shape[-2]
+    m, n = a.shape[-1 if a_mn else -2], b.shape[-1 if b_mn else -2]
     if out is None:
         out = torch.empty((*a.shape[:-2], m, n), device=a.device, dtype=a.dtype)
-    a2 = a.reshape(batch * m, a.shape[-1]) if a.ndim == 3 else a
-    b2 = b.reshape(batch * n, b.shape[-1]) if b.ndim == 3 else b
+    a2 = a.reshape(batch * a.shape[-2], a.shape[-1]) if a.ndim == 3 else a
+    b2 = b.reshape(batch * b.shape[-2], b.shape[-1]) if b.ndim == 3 else b
     _gemm(a2, b2, out, EPI_AXPBY, n, alpha=alpha, beta=beta, resid=resid, out_t=out_t, symmetric=symmetric,
-          force_bn=force_bn, batch=batch)
+          force_bn=force_bn, batch=batch, a_mn=a_mn, b_mn=b_mn)
     return out
 
 
@@ -582,3 +601,71 @@ def ln_modulate_backward(dh, x, mean, rstd, scale, tokens):
     _ops().ln_modulate_backward(dh, x, mean, rstd, scale, int(tokens), dx, dshift, dscale)
     _count()
     return dx, dshift, dscale
+
+
+# ------------------------------------------------------------------------------ multi-tensor optimizer ops
+_DT = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+_CHUNK = 4096
+
+
+class TensorTable:
+    """Device-resident descriptor table for the multi-tensor kernels (built once per parameter set).
+
+    ``rows``: one tuple per tensor ``(p0, p1, p2, p3, n, i0, f0, f1, d0, d1)`` with tensors (or None / ints)
+    in the pointer slots.  Keeps the referenced tensors alive.
+    """
+
+    def __init__(self, rows, device):
+        import struct
+        self.keep = [t for row in rows for t in row[:4] if isinstance(t, torch.Tensor)]
+        packed, prefix = [], [0]
+        for p0, p1, p2, p3, n, i0, f0, f1, d0, d1 in rows:
+            pointers = [t.data_ptr() if isinstance(t, torch.Tensor) else int(t or 0) for t in (p0, p1, p2, p3)]
+            floats = struct.unpack("<q", struct.pack("<ff", float(f0), float(f1)))[0]
+            codes = struct.unpack("<q", struct.pack("<ii", int(d0), int(d1)))[0]
+            signed = int(i0) & ((1 << 63) - 1)
+            packed.append([*(p if p < (1 << 63) else p - (1 << 64) for p in pointers), int(n), signed, floats, codes])
+            prefix.append(prefix[-1] + (int(n) + _CHUNK - 1) // _CHUNK)
+        # pinned staging + asynchronous upload: building a table must not synchronise the stream
+        host_table = torch.tensor(packed, dtype=torch.int64).pin_memory()
+        host_prefix = torch.tensor(prefix, dtype=torch.int32).pin_memory()
+        self.table = host_table.to(device, non_blocking=True)
+        self.prefix = host_prefix.to(device, non_blocking=True)
+        self.keep.extend((host_table, host_prefix))
+        self.blocks = prefix[-1]
+        self.pointers = tuple(tuple(row[:4]) for row in packed)
+
+    def matches(self, rows):
+        """True when ``rows`` still name the same storage (pointers can change after a re-allocation)."""
+        if len(rows) != len(self.pointers):
+            return False
+        for row, known in zip(rows, self.pointers):
+            current = tuple((t.data_ptr() if isinstance(t, torch.Tensor) else int(t or 0)) for t in row[:4])
+            if tuple(p if p < (1 << 63) else p - (1 << 64) for p in current) != known:
+                return False
+        return True
+
+
+def multi_ema(table, decay):
+    _ops().multi_ema(table.table, table.prefix, table.blocks, float(decay))
+    _count()
+
+
+def multi_adam(table, *, lr, weight_decay, betas, eps, step, rounding="nearest", adamw=True, maximize=False):
+    b1, b2 = betas
+    _ops().multi_adam(table.table, table.prefix, table.blocks, float(lr), float(weight_decay), float(b1), float(b2),
+                      1.0 / (1.0 - b1 ** step), 1.0 / (1.0 - b2 ** step), float(eps), bool(adamw), bool(maximize),
+                      rounding == "stochastic", int(step - 1))
+    _count()
+
+
+def multi_weight_update(table, lr, weight_decay, *, rounding="nearest", step=0):
+    _ops().multi_weight_update(table.table, table.prefix, table.blocks, float(lr), float(weight_decay),
+                               rounding == "stochastic", int(step))
+    _count()
+
+
+def multi_momentum(table, *, tile_size, beta, nesterov=True, loss_scale=1.0, rounding="nearest", step=0):
+    _ops().multi_momentum(table.table, table.prefix, table.blocks, int(tile_size), float(beta), 1.0 / float(loss_scale),
+                          bool(nesterov), rounding == "stochastic", int(step))
+    _count()

@@ -17,7 +17,7 @@ import torch
 from .. import ops
 from ..precision import _dtype, settings
 from .matrix import MatrixOptimizer
-from .orthogonalize import METHODS
+from .orthogonalize import METHODS, OUTPUT_DTYPE
 
 _MODES = {"fast": (256, 3), "balanced": (256, 5), "stable": (128, 5)}
 _MASK63 = (1 << 63) - 1
@@ -138,8 +138,13 @@ class FP8Muon(MatrixOptimizer):
                 and len(_matrix_shape(param, group)) == 2):
             # same-shape matrices are orthogonalised together after the parameter loop
             shape = _matrix_shape(param, group)
-            self._deferred.setdefault((shape, group["ns_method"], group["ns_steps"], param.device), []).append(
+            self._deferred.setdefault((shape, id(group), state["step"], param.device), []).append(
                 (param, grad, state, group, key, master_key))
+            return
+        if not _use_muon(param, group) and self._deferred is not None and param.is_cuda and param.is_contiguous():
+            # vectors of one group that are at the same step share one multi-tensor AdamW launch
+            self._deferred_adam.setdefault((id(group), state["step"], param.device), []).append(
+                (param, grad, state, group, master_key))
             return
         if _use_muon(param, group):
             matrix = self._momentum(param, grad, state, group, key)
@@ -163,32 +168,84 @@ class FP8Muon(MatrixOptimizer):
                             step=state["step"] + 1, rounding=group["master_rounding"], key=master_key)
         state["step"] += 1
 
-    # ------------------------------------------------------------------ batched Newton-Schulz
+    # ------------------------------------------------------------------ batched / multi-tensor tail of the step
     def _begin_local(self):
         self._deferred = {} if self.observer is None else None
+        self._deferred_adam = {}
+
+    def _table(self, name, rows, device):
+        """Cached descriptor table; rebuilt only when a tensor of the set moved."""
+        cached = self._workspace.get(name)
+        if cached is None or not cached.matches(rows):
+            cached = self._workspace[name] = ops.TensorTable(rows, device)
+        return cached
 
     def _finish_local(self):
         deferred, self._deferred = self._deferred, None
+        adam, self._deferred_adam = getattr(self, "_deferred_adam", {}), {}
+        codes = ops._DT
+        for (group_id, step, device), items in adam.items():
+            group = items[0][3]
+            rows = []
+            for param, grad, state, _, master_key in items:
+                if "exp_avg" not in state:
+                    state["exp_avg"] = torch.zeros_like(param, dtype=group["adam_state_dtype"])
+                    state["exp_avg_sq"] = torch.zeros_like(param, dtype=group["adam_state_dtype"])
+                flat = grad if grad.is_contiguous() else grad.contiguous()
+                rows.append((param, flat, state["exp_avg"], state["exp_avg_sq"], param.numel(), master_key, 0.0, 0.0,
+                             codes[param.dtype], codes[flat.dtype] | (codes[state["exp_avg"].dtype] << 8)))
+            table = self._table(("adam", group_id, device), rows, device)
+            ops.multi_adam(table, lr=group["lr"], weight_decay=group["weight_decay"], betas=group["betas"],
+                           eps=group["eps"], step=step + 1, rounding=group["master_rounding"])
+            for _, _, state, _, _ in items:
+                state["step"] += 1
         if not deferred:
             return
-        for (shape, method, steps, device), items in deferred.items():
+        for (shape, group_id, step, device), items in deferred.items():
+            group = items[0][3]
+            rows_, cols_ = shape
+            if group["adjust_lr_fn"] == "match_rms_adamw":
+                update_scale = 0.2 * max(rows_, cols_) ** 0.5
+            else:
+                update_scale = max(1.0, rows_ / cols_) ** 0.5
+            tiled = group["granularity"] == "tile"
             for start in range(0, len(items), self.ns_batch):
                 chunk = items[start:start + self.ns_batch]
                 key = ("stack", shape, device)
                 stack = self._workspace.get(key)
                 if stack is None or stack.shape[0] < len(chunk):
-                    stack = self._workspace[key] = torch.empty((len(chunk), *shape), device=device,
+                    stack = self._workspace[key] = torch.empty((min(self.ns_batch, len(items)), *shape), device=device,
                                                                dtype=torch.bfloat16)
                 stack = stack[:len(chunk)]
-                for slot, (param, grad, state, group, rounding_key, _) in enumerate(chunk):
-                    self._momentum(param, grad, state, group, rounding_key, out=stack[slot])
-                updates = METHODS[method](stack, steps=steps)
-                rows, cols = shape
-                for slot, (param, _, state, group, _, master_key) in enumerate(chunk):
-                    if group["adjust_lr_fn"] == "match_rms_adamw":
-                        scale = 0.2 * max(rows, cols) ** 0.5
-                    else:
-                        scale = max(1.0, rows / cols) ** 0.5
-                    ops.weight_update(param, updates[slot], group["lr"], group["weight_decay"], update_scale=scale,
-                                      rounding=group["master_rounding"], step=state["step"], key=master_key)
+                if tiled:
+                    rows = []
+                    for slot, (param, grad, state, _, rounding_key, _) in enumerate(chunk):
+                        if "momentum_q" not in state:
+                            count, scales = ops.state_sizes(shape, granularity="tile", tile_size=group["tile_size"])
+                            state["momentum_q"] = torch.zeros(count, device=device, dtype=torch.uint8)
+                            state["momentum_scale"] = torch.ones(scales, device=device, dtype=torch.float32)
+                        flat = grad if grad.is_contiguous() else grad.contiguous()
+                        rows.append((flat, state["momentum_q"], state["momentum_scale"], stack[slot], param.numel(),
+                                     rounding_key, 0.0, 0.0, codes[flat.dtype], 0))
+                    table = self._table(("momentum", shape, group_id, start, device), rows, device)
+                    ops.multi_momentum(table, tile_size=group["tile_size"], beta=group["momentum"],
+                                       nesterov=group["nesterov"], rounding=group["rounding"], step=step)
+                else:
+                    for slot, (param, grad, state, _, rounding_key, _) in enumerate(chunk):
+                        self._momentum(param, grad, state, group, rounding_key, out=stack[slot])
+                # a persistent result buffer keeps the addresses in the update table stable across steps
+                out_key = ("ns_out", shape, group["ns_method"], device)
+                result = self._workspace.get(out_key)
+                if result is None or result.shape[0] < len(chunk):
+                    result = self._workspace[out_key] = torch.empty((min(self.ns_batch, len(items)), *shape),
+                                                                    device=device,
+                                                                    dtype=OUTPUT_DTYPE[group["ns_method"]])
+                updates = METHODS[group["ns_method"]](stack, steps=group["ns_steps"], out=result[:len(chunk)])
+                rows = [(param, updates[slot], None, None, param.numel(), master_key, update_scale, 0.0,
+                         codes[param.dtype], codes[updates.dtype])
+                        for slot, (param, _, _, _, _, master_key) in enumerate(chunk)]
+                table = self._table(("update", shape, group_id, start, device), rows, device)
+                ops.multi_weight_update(table, group["lr"], group["weight_decay"], rounding=group["master_rounding"],
+                                        step=step)
+                for _, _, state, _, _, _ in chunk:
                     state["step"] += 1

@@ -41,26 +41,26 @@ def _poly(r):
     return ops.ns_gemm(r, r, alpha=_C, beta=_B, resid=r, symmetric=True)
 
 
-def _standard_2d(matrix, steps, dtype):
+def _standard_2d(matrix, steps, dtype, out=None):
     x, xt, transposed = _prescale(matrix, dtype)
     for step in range(steps):
         gram = ops.ns_gemm(x, x, symmetric=True)
         poly = _poly(gram)
         last = step == steps - 1
         if last and transposed:
-            return ops.ns_gemm(xt, poly, alpha=1.0, beta=_A, resid=xt)        # X^T P = (P X)^T
+            return ops.ns_gemm(xt, poly, alpha=1.0, beta=_A, resid=xt, out=out)        # X^T P = (P X)^T
         if last:
-            return ops.ns_gemm(poly, xt, alpha=1.0, beta=_A, resid=x)
+            return ops.ns_gemm(poly, xt, alpha=1.0, beta=_A, resid=x, out=out)
         new_t = torch.empty_like(xt)
         x = ops.ns_gemm(poly, xt, alpha=1.0, beta=_A, resid=x, out_t=new_t)
         xt = new_t
     return xt if transposed else x
 
 
-def _gram_2d(matrix, steps):
+def _gram_2d(matrix, steps, out=None):
     dtype = torch.float16
     if matrix.shape[-2] == matrix.shape[-1]:
-        return _standard_2d(matrix, steps, dtype)
+        return _standard_2d(matrix, steps, dtype, out)
     x, xt, transposed = _prescale(matrix, dtype)
     segments = [length for length in (min(steps, 2), max(steps - 2, 0)) if length]
     for index, length in enumerate(segments):
@@ -78,9 +78,9 @@ def _gram_2d(matrix, steps):
                 r = ops.ns_gemm(z, rz, alpha=1.0, beta=_A, resid=rz, symmetric=True)
         last = index == len(segments) - 1
         if last and transposed:
-            return ops.ns_gemm(xt, q)                                            # X^T Q = (Q X)^T
+            return ops.ns_gemm(xt, q, out=out)                                   # X^T Q = (Q X)^T
         if last:
-            return ops.ns_gemm(q, xt)
+            return ops.ns_gemm(q, xt, out=out)
         new_t = torch.empty_like(xt)
         x = ops.ns_gemm(q, xt, out_t=new_t)
         xt = new_t
@@ -95,18 +95,27 @@ def _batched(fn, matrix, *args):
     return fn(flat, *args).reshape(matrix.shape)
 
 
-def standard(matrix, steps=5):
-    """bf16 Newton-Schulz; returns the orthogonalised matrix in bf16 with the input's shape."""
+def standard(matrix, steps=5, out=None):
+    """bf16 Newton-Schulz; returns the orthogonalised matrix in bf16 with the input's shape.
+
+    ``out`` (CUDA only): a bf16 tensor of the input's shape (at most one leading batch dimension) that
+    receives the result, so callers can keep a stable address across steps."""
     if not matrix.is_cuda:
         return ops.reference.ns_standard(matrix, steps)
+    if out is not None and matrix.ndim <= 3:
+        return _standard_2d(matrix, steps, torch.bfloat16, out)
     return _batched(_standard_2d, matrix, steps, torch.bfloat16)
 
 
-def gram(matrix, steps=5):
-    """fp16 Gram-matrix Newton-Schulz; returns fp16."""
+def gram(matrix, steps=5, out=None):
+    """fp16 Gram-matrix Newton-Schulz; returns fp16 (``out``: optional fp16 result buffer, CUDA only)."""
     if not matrix.is_cuda:
         return ops.reference.ns_gram(matrix, steps)
+    if out is not None and matrix.ndim <= 3:
+        return _gram_2d(matrix, steps, out)
     return _batched(_gram_2d, matrix, steps)
+
+OUTPUT_DTYPE = {"standard": torch.bfloat16, "gram": torch.float16}
 
 
 def orthogonalize(matrix, *, method="standard", steps=5, autotune=True):

@@ -41,10 +41,21 @@ class EMAState:
     def update(self):
         if not self.decay:
             return
+        pairs = []
         for record in self.store.records:
             source = self._source(record)
             if source is not None:
-                ops.ema_lerp(self.weights[record.name], source, self.decay)
+                pairs.append((self.weights[record.name], source))
+        if pairs and pairs[0][0].is_cuda and all(a.is_contiguous() and b.is_contiguous() for a, b in pairs):
+            # one launch for every average (the sources are the optimizer's master parameters)
+            rows = [(ema, source, None, None, ema.numel(), 0, 0.0, 0.0, ops._DT[ema.dtype], ops._DT[source.dtype])
+                    for ema, source in pairs]
+            if getattr(self, "_table", None) is None or not self._table.matches(rows):
+                self._table = ops.TensorTable(rows, pairs[0][0].device)
+            ops.multi_ema(self._table, self.decay)
+        else:
+            for ema, source in pairs:
+                ops.ema_lerp(ema, source, self.decay)
         self.updates += 1
 
     def state_dict(self):

@@ -192,8 +192,7 @@ class ParameterStore:
                 if layer.rotation_size:
                     from .. import ops
                     master = ops.hadamard64(value)
-                scale = layer.weight_quantizer.scale(master, layer.fp8_dtype, limit)
-                layer.weight_scale.copy_(scale)
+                layer.weight_quantizer.scale(master, layer.fp8_dtype, limit, out=layer.weight_scale)
                 from ..ops.reference import fp8_limit
                 transport.write_fp8_weight(record, master.contiguous(), layer.weight_scale, fp8_limit(layer.fp8_dtype, limit))
             else:
@@ -225,6 +224,16 @@ class ParameterStore:
         if self.transport is not None and record.unit is not None and self.world > 1 and not record.unit.unsharded:
             if self._write_peer(record, value, source):
                 return
+        if self.world == 1 and record.unit is not None and not record.unit.unsharded:
+            # single rank, sharded storage: encode straight into the shard buffer (no staging copy)
+            target = record.unit.local_view(record.entry)[:record.entry.rows].view(record.shape)
+            if layer is not None and layer.weight_dtype == "fp8":
+                layer.quantize_master(value, out=target)
+                layer.clear_weight_cache()
+            else:
+                target.copy_(value)
+            torch.autograd.graph.increment_version(record.parameter)
+            return
         if layer is not None and layer.weight_dtype == "fp8":
             codes = None
             if self.rank == source:

@@ -13,6 +13,7 @@ share (max over ranks reported); ``--layers`` shrinks the set for quick runs.
 from __future__ import annotations
 
 import argparse
+import gc
 import os
 import sys
 
@@ -67,7 +68,8 @@ def main():
                                  step_ms_max_over_ranks=timing.item(), ns_tflop_this_rank=flops / 1e12,
                                  ns_tflops_rate=flops / ms / 1e9,
                                  state_bytes_per_element=1 + 4 / 256))
-            del optimizer, matrices, vectors
+            del optimizer, matrices, vectors, p
+            gc.collect()
             torch.cuda.empty_cache()
     ops.check_status()
     if rank == 0:

@@ -137,7 +137,7 @@ def test_ns_gemm(dtype, m, k):
 
 
 @pytest.mark.parametrize("a_mn,b_mn", [(True, False), (False, True), (True, True)])
-@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (640, 384, 1152), (1008, 528, 2000), (1152, 4608, 4096)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (640, 384, 1152), (1008, 528, 2000), (1152, 4608, 4096), (256, 512, 300)])
 def test_gemm_mn_major_operands(a_mn, b_mn, m, n, k):
     """Operands handed over transposed ([K, M] / [K, N]) are read MN-major in place and give the K-major result."""
     torch.manual_seed(11)

@@ -66,6 +66,7 @@ typedef struct VbGemmDesc {
   // operand layouts: 0 = K-major (A is [M, K], B is [N, K]); 1 = MN-major (A stored as [K, M], B as [K, N]);
   // lda / ldb are always the row pitch of the stored matrix
   int a_mn_major, b_mn_major;
+  int k_mn;              // rows of K actually stored by an MN-major operand (0: K); K - k_mn < 16 rows read as zero
   int no_tma_store;      // 1: LINEAR epilogue writes with per-thread stores instead of the TMA-store path
 } VbGemmDesc;
 

@@ -93,7 +93,10 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t epilogue, int64_
   TORCH_CHECK(batch >= 1 && a.size(0) % batch == 0 && b.size(0) % batch == 0);
   const int64_t k_a = a_mn ? a.size(0) / batch : a.size(1);
   const int64_t k_b = b_mn ? b.size(0) / batch : b.size(1);
-  TORCH_CHECK(k_a == k_b, "K mismatch");
+  // a K-major operand may carry zero padding up to the next 16-byte boundary that the MN-major one lacks
+  const int64_t k_major = a_mn == b_mn ? k_a : (a_mn ? k_b : k_a), k_minor = a_mn == b_mn ? k_b : (a_mn ? k_a : k_b);
+  TORCH_CHECK(k_major >= k_minor && k_major - k_minor < 16 && ((a_mn != b_mn && batch == 1) || k_major == k_minor),
+              "K mismatch");
   TORCH_CHECK(!b_mn || b.size(1) >= n_logical, "MN-major B must hold at least N columns");
   c10::cuda::CUDAGuard guard(a.device());
   VbGemmDesc d{};
@@ -113,7 +116,8 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t epilogue, int64_
   d.batch = (int)batch;
   d.M = (int)(a_mn ? a.size(1) : a.size(0) / batch);
   d.N = (int)n_logical;
-  d.K = (int)k_a;
+  d.K = (int)k_major;
+  d.k_mn = (int)k_minor;
   d.A = a.data_ptr();
   d.lda = a.stride(0);
   d.B = b.data_ptr();

@@ -782,10 +782,10 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream) {
 
   const long long b_rows = (long long)(C::kGatedFwd ? 2 : 1) * d.N * (expert ? d.num_experts : 1) * a.batch;
   CUtensorMap tmA, tmB;
-  int rc = a.a_mn ? make_map_mn(&tmA, d.A, KIND, d.a_fmt, (long long)d.K * a.batch, d.M, d.lda, C::kBK)
+  int rc = a.a_mn ? make_map_mn(&tmA, d.A, KIND, d.a_fmt, (long long)(d.k_mn > 0 ? d.k_mn : d.K) * a.batch, d.M, d.lda, C::kBK)
                   : make_map(&tmA, d.A, KIND, d.a_fmt, (long long)d.M * a.batch, d.K, d.lda, BM);
   if (rc) return rc;
-  rc = a.b_mn ? make_map_mn(&tmB, d.B, KIND, d.b_fmt, (long long)d.K * a.batch, d.N, d.ldb, C::kBK)
+  rc = a.b_mn ? make_map_mn(&tmB, d.B, KIND, d.b_fmt, (long long)(d.k_mn > 0 ? d.k_mn : d.K) * a.batch, d.N, d.ldb, C::kBK)
               : make_map(&tmB, d.B, KIND, d.b_fmt, b_rows, d.K, d.ldb, C::kBBoxRows);
   if (rc) return rc;
   CUtensorMap tmC = tmA;
@@ -819,7 +819,7 @@ extern "C" int vb_gemm(const VbGemmDesc* desc, cudaStream_t stream) {
   const VbGemmDesc& d = *desc;
   if (d.M <= 0 || d.N <= 0 || d.K <= 0) return 0;
   const int elem = d.kind == VB_KIND_F8 ? 1 : 2;
-  if ((d.K * elem) % 16 != 0) return (int)cudaErrorInvalidValue;
+  if ((d.K * elem) % 16 != 0 && !(d.a_mn_major && d.b_mn_major)) return (int)cudaErrorInvalidValue;
   const int sms = sm_count();
   int bn = d.force_bn;
   const bool group = d.group != 0;

@@ -44,7 +44,7 @@ class _NormModulateLinear(torch.autograd.Function):
         q, qt, qscale, mean, rstd = ops.ln_modulate_quantize(
             x2, shift, scale, tokens, eps=eps, history=quantizer.history, index=quantizer.index,
             delayed=quantizer.scaling == "delayed", fp8_dtype=layer.fp8_dtype, quantization_limit=limit,
-            transpose=need_w)
+            transpose=need_w and not layer.in_place_operands)
         quantizer.index += 1
         encoded = SimpleNamespace(q=q, s=qscale, qt=qt, st=qscale)
         y, saved, _ = linear_forward(layer, x2, weight, bias, need_input_grad=True, need_weight_grad=need_w,
@@ -75,7 +75,7 @@ class _ActivationLinear(torch.autograd.Function):
         limit = layer._quantization_limit(max(z2.shape), layer.fp8_dtype)
         q, qt, qscale = ops.activation_quantize(z2, activation, history=quantizer.history, index=quantizer.index,
                                                 delayed=quantizer.scaling == "delayed", fp8_dtype=layer.fp8_dtype,
-                                                quantization_limit=limit, transpose=need_w)
+                                                quantization_limit=limit, transpose=need_w and not layer.in_place_operands)
         quantizer.index += 1
         encoded = SimpleNamespace(q=q, s=qscale, qt=qt, st=qscale)
         y, saved, _ = linear_forward(layer, z2, weight, bias, need_input_grad=True, need_weight_grad=need_w,

@@ -155,9 +155,13 @@ def linear_forward(layer, x, weight, bias, *, need_input_grad, need_weight_grad,
         limit = layer._group_limit(gx, fmt)
     else:
         limit = layer._quantization_limit(max(x.shape), fmt)
+    # per-tensor recipes hand the GEMM the row-wise codes for every product (the tensor core reads a
+    # transposed operand MN-major in place), so no transposed copy of X, dY or W is ever written
+    in_place = layer.in_place_operands
     qx = encoded if encoded is not None else _quantize_activation(
-        layer, x, fmt, gx, layer.input_quantizer, limit, row=True, transposed=save_fp8)
-    w = _weight_operands(layer, weight, need_transpose=need_input_grad and layer.cache_weight_transpose)
+        layer, x, fmt, gx, layer.input_quantizer, limit, row=True, transposed=save_fp8 and not in_place)
+    w = _weight_operands(layer, weight,
+                         need_transpose=need_input_grad and layer.cache_weight_transpose and not in_place)
     aux = None
     if gated is not None:
         group = (gx, gw) if layer._grouped_scaling else None
@@ -171,10 +175,13 @@ def linear_forward(layer, x, weight, bias, *, need_input_grad, need_weight_grad,
     if need_backward:
         saved = SimpleNamespace(x=None, x_scale=None, x_is_fp8=save_fp8, input_scale=qx.s, weight=weight,
                                 weight_scale=w.s, wt=w.qt, wt_scale=w.st, limit=limit, x_dtype=x.dtype,
+                                in_place=in_place, wq=None,
                                 weight_grad_dtype=getattr(weight, "grad_dtype", None) or torch.float32,
                                 bias_grad_dtype=(getattr(bias, "grad_dtype", None) or bias.dtype) if bias is not None else None)
+        if in_place and need_input_grad and layer.weight_dtype != "fp8" and layer.cache_weight_transpose:
+            saved.wq = w.q                              # fast mode: keep this call's codes for dgrad
         if save_fp8:
-            saved.x, saved.x_scale = qx.qt, qx.st
+            saved.x, saved.x_scale = (qx.q, qx.s) if in_place else (qx.qt, qx.st)
         elif need_weight_grad:
             saved.x = x.to(_SAVED[layer.saved_input_dtype])
     return y, saved, aux
@@ -190,6 +197,8 @@ def linear_backward(layer, saved, dy, *, need_input_grad, need_weight_grad, need
     else:
         limit = layer._quantization_limit(max(dy.shape), bfmt)
     dx = dw = db = None
+    if saved.in_place:
+        return _backward_in_place(layer, saved, dy, limit, need_input_grad, need_weight_grad, need_bias_grad, gated, aux)
     # memory mode keeps one FP8 copy of dY alive at a time; fast mode encodes both layouts in one read
     both = need_input_grad and need_weight_grad and layer.mode == "fast"
     qg = _quantize_activation(layer_no_rotation(layer), dy, bfmt, gg, layer.grad_quantizer, limit,
@@ -230,6 +239,46 @@ def linear_backward(layer, saved, dy, *, need_input_grad, need_weight_grad, need
                                 sb_kmajor=True)
         else:
             dw = ops.gemm(qg.qt, xt, qg.st, xt_scale, out_dtype=saved.weight_grad_dtype)
+        if layer.rotation_size:
+            ops.hadamard64(dw, out=dw)
+    if need_bias_grad:
+        db = dy.sum(dim=0, dtype=saved.bias_grad_dtype)
+    return dx, dw, db
+
+
+def _backward_in_place(layer, saved, dy, limit, need_input_grad, need_weight_grad, need_bias_grad, gated, aux):
+    """Per-tensor backward from row-wise codes only: dX = dY W reads W as an MN-major B operand, dW = dY^T X
+    reads both dY and X MN-major."""
+    fmt, bfmt = layer.fp8_dtype, layer.backward_fp8_dtype
+    dx = dw = db = None
+    qg = _quantize_activation(layer_no_rotation(layer), dy, bfmt, None, layer.grad_quantizer, limit, row=True,
+                              transposed=False)
+    if need_input_grad:
+        wq = saved.wq
+        if wq is None and layer.weight_dtype == "fp8":
+            wq = saved.weight
+        elif wq is None:
+            source = ops.hadamard64(saved.weight) if layer.rotation_size else saved.weight
+            wq, _ = ops.quantize(source, saved.weight_scale, fp8_dtype=fmt,
+                                 quantization_limit=layer._quantization_limit(max(source.shape), fmt))
+        if gated is not None and not layer.rotation_size:
+            dx = ops.gated_gemm_backward(qg.q, wq, qg.s, saved.weight_scale, aux, activation=gated,
+                                         out_dtype=saved.x_dtype, wt_mn=True)
+        else:
+            dx = ops.gemm(qg.q, wq, qg.s, saved.weight_scale, out_dtype=saved.x_dtype, b_mn=True)
+            if layer.rotation_size:
+                ops.hadamard64(dx, out=dx)
+            if gated is not None:
+                dx = ops.gated_backward(aux, dx, gated)
+        del wq
+    if need_weight_grad:
+        if saved.x_is_fp8:
+            xq, x_scale = saved.x, saved.x_scale
+        else:
+            enc = _quantize_activation(layer, saved.x, fmt, None, layer.input_quantizer, saved.limit, row=True,
+                                       transposed=False, scale=saved.input_scale)
+            xq, x_scale = enc.q, enc.s
+        dw = ops.gemm(qg.q, xq, qg.s, x_scale, out_dtype=saved.weight_grad_dtype, a_mn=True, b_mn=True)
         if layer.rotation_size:
             ops.hadamard64(dw, out=dw)
     if need_bias_grad:
@@ -403,6 +452,17 @@ class Linear(nn.Module):
             q = (value / expanded).clamp(-limit_value, limit_value).to(self.fp8_dtype)
         return q, s
 
+    @property
+    def in_place_operands(self):
+        """True when every product of this layer runs from row-wise FP8 codes (per-tensor scaling with
+        16-byte aligned rows): the backward GEMMs then read W, X and dY MN-major in place and the layer keeps
+        no transposed weight cache."""
+        return not self._grouped_scaling and self.in_features % 16 == 0 and self.out_features % 16 == 0
+
+    @property
+    def _caches_transpose(self):
+        return self.cache_weight_transpose and not self.in_place_operands
+
     def _transposed_weight(self, weight, scale):
         """W^T codes and scales for dgrad, built from the stored weight without touching its scale state."""
         if self._grouped_scaling:
@@ -468,11 +528,11 @@ class Linear(nn.Module):
                 self.weight_transpose, self.weight_transpose_scale = self._transposed_weight(self.weight,
                                                                                              self.weight_scale)
             return
-        if self.cache_weight_transpose and self.weight_transpose.numel() == 0:
+        if self._caches_transpose and self.weight_transpose.numel() == 0:
             self.weight_transpose = torch.empty((self.in_features, self.out_features), device=master.device,
                                                 dtype=self.fp8_dtype)
         self.quantize_master(master, out=self.weight.data,
-                             out_t=self.weight_transpose if self.cache_weight_transpose else None)
+                             out_t=self.weight_transpose if self._caches_transpose else None)
 
     def dequantize_weight(self):
         """The real-valued weight in the original (unrotated) coordinates, as fp32."""
@@ -502,7 +562,7 @@ class Linear(nn.Module):
     @torch.no_grad()
     def rebuild_weight_cache(self):
         """Recompute the cached W^T from the current codes / scales; W itself is left alone."""
-        if self.cache_weight_transpose and self.weight_dtype == "fp8":
+        if self._caches_transpose and self.weight_dtype == "fp8":
             if self._grouped_scaling:
                 self.weight_transpose, self.weight_transpose_scale = self._transposed_weight(self.weight,
                                                                                              self.weight_scale)

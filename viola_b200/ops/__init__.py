@@ -325,12 +325,15 @@ def gated_gemm_forward(a, w, sa, sw, *, activation, out_dtype, bias=None, save=T
     return h, aux
 
 
-def gated_gemm_backward(dy, wt, sg, st, aux, *, activation, out_dtype, group=None, sg_kmajor=False, st_kmajor=False):
-    """[dG | dU] from d = dY.Wdown (wt = Wdown^T, [H, out]) and the saved aux = [g | u]."""
-    hidden = wt.shape[0]
+def gated_gemm_backward(dy, wt, sg, st, aux, *, activation, out_dtype, group=None, sg_kmajor=False, st_kmajor=False,
+                        wt_mn=False):
+    """[dG | dU] from d = dY.Wdown (wt = Wdown^T, [H, out]) and the saved aux = [g | u].
+
+    ``wt_mn`` (per-tensor scaling only): ``wt`` is Wdown itself ([out, H]), read MN-major in place."""
+    hidden = wt.shape[1] if wt_mn else wt.shape[0]
     if not dy.is_cuda:
         if group is None:
-            d = reference.gemm(dy, wt, sg, st, out_dtype=out_dtype)
+            d = reference.gemm(dy, wt.t() if wt_mn else wt, sg, st, out_dtype=out_dtype)
         else:
             d = reference.group_gemm(dy, wt, sg.t() if sg_kmajor else sg, st.t() if st_kmajor else st, group[0],
                                      group[1], out_dtype=out_dtype)
@@ -343,7 +346,8 @@ def gated_gemm_backward(dy, wt, sg, st, aux, *, activation, out_dtype, group=Non
             d = group_gemm(dy, wt, sg, st, group[0], group[1], out_dtype=out_dtype, sa_kmajor=sg_kmajor,
                            sb_kmajor=st_kmajor)
             return gated_backward(aux, d, activation)
-    _gemm(dy, wt, out, EPI_GATED_BWD, hidden, sa=sg, sb=st, layout=layout, activation=_ACT[activation], aux=aux)
+    _gemm(dy, wt, out, EPI_GATED_BWD, hidden, sa=sg, sb=st, layout=layout, activation=_ACT[activation], aux=aux,
+          b_mn=wt_mn)
     return out
 
 

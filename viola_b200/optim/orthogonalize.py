@@ -9,9 +9,10 @@ Two recurrences with the reference's coefficients and rounding points
 
 Every product is one launch of the warp-specialised tcgen05 kernel with the polynomial fused into
 its epilogue (``alpha * round(acc) + beta * R``).  Gram-side products are symmetric, so only the
-upper-triangular tiles are computed and mirrored.  The kernel consumes K-major operands only, so
-the iterate is carried in both orientations: the third GEMM of a step writes ``X`` row-wise and
-``X^T`` through a coalesced transposed store, which removes every explicit transpose.
+upper-triangular tiles are computed and mirrored.  The iterate is kept in its stored orientation and
+never transposed: the tensor core reads it K-major or MN-major as the product needs (wide ``X``:
+``G = X X^T`` K-major, ``P X`` with ``X`` as the MN-major B operand; tall ``X``: ``G = X^T X`` with
+both operands MN-major, ``X P`` K-major since ``P`` is symmetric).
 """
 
 from __future__ import annotations
@@ -24,16 +25,39 @@ _A, _B, _C = 3.4445, -4.7750, 2.0315
 
 
 def _prescale(matrix, dtype):
-    """(X, X^T) = matrix / (||matrix||_F + 1e-7) rounded to ``dtype``; X is the wide orientation."""
+    """matrix / (||matrix||_F + 1e-7) rounded to ``dtype``, in the input's orientation."""
     rows, cols = matrix.shape[-2:]
-    lead = tuple(matrix.shape[:-2])
     accum = torch.zeros(max(1, matrix.numel() // (rows * cols)), device=matrix.device, dtype=torch.float32)
     source = matrix.contiguous()
     ops.sumsq(source, dtype, accum)
-    straight = torch.empty((*lead, rows, cols), device=matrix.device, dtype=dtype)
-    flipped = torch.empty((*lead, cols, rows), device=matrix.device, dtype=dtype)
-    ops.ns_prescale(source, accum, out=straight, out_t=flipped)
-    return (flipped, straight, True) if rows > cols else (straight, flipped, False)
+    scaled = torch.empty(matrix.shape, device=matrix.device, dtype=dtype)
+    ops.ns_prescale(source, accum, out=scaled)
+    return scaled
+
+
+def _mn_readable(x, k):
+    """Can ``x`` ([.., k, mn]) be read in place as an MN-major operand?  Rows must be 16-byte aligned, and a
+    stack needs whole K blocks per matrix (a partial block would read the next matrix's rows)."""
+    return (x.shape[-1] * x.element_size()) % 16 == 0 and (x.ndim == 2 or k % 64 == 0)
+
+
+def _gram_matrix(x, tall):
+    """The small Gram matrix: X X^T for a wide iterate, X^T X for a tall one."""
+    if not tall:
+        return ops.ns_gemm(x, x, symmetric=True)
+    if _mn_readable(x, x.shape[-2]):
+        return ops.ns_gemm(x, x, symmetric=True, a_mn=True, b_mn=True)
+    flipped = x.mT.contiguous()
+    return ops.ns_gemm(flipped, flipped, symmetric=True)
+
+
+def _apply(p, x, tall, *, beta=0.0, resid=None, out=None):
+    """round(P X) (wide) or round(X P) (tall) for a symmetric P, plus ``beta * resid``."""
+    if tall:
+        return ops.ns_gemm(x, p, alpha=1.0, beta=beta, resid=resid, out=out)
+    if _mn_readable(x, x.shape[-2]):
+        return ops.ns_gemm(p, x, alpha=1.0, beta=beta, resid=resid, out=out, b_mn=True)
+    return ops.ns_gemm(p, x.mT.contiguous(), alpha=1.0, beta=beta, resid=resid, out=out)
 
 
 def _poly(r):
@@ -42,29 +66,23 @@ def _poly(r):
 
 
 def _standard_2d(matrix, steps, dtype, out=None):
-    x, xt, transposed = _prescale(matrix, dtype)
+    x = _prescale(matrix, dtype)
+    tall = matrix.shape[-2] > matrix.shape[-1]
     for step in range(steps):
-        gram = ops.ns_gemm(x, x, symmetric=True)
-        poly = _poly(gram)
-        last = step == steps - 1
-        if last and transposed:
-            return ops.ns_gemm(xt, poly, alpha=1.0, beta=_A, resid=xt, out=out)        # X^T P = (P X)^T
-        if last:
-            return ops.ns_gemm(poly, xt, alpha=1.0, beta=_A, resid=x, out=out)
-        new_t = torch.empty_like(xt)
-        x = ops.ns_gemm(poly, xt, alpha=1.0, beta=_A, resid=x, out_t=new_t)
-        xt = new_t
-    return xt if transposed else x
+        poly = _poly(_gram_matrix(x, tall))
+        x = _apply(poly, x, tall, beta=_A, resid=x, out=out if step == steps - 1 else None)
+    return x
 
 
 def _gram_2d(matrix, steps, out=None):
     dtype = torch.float16
     if matrix.shape[-2] == matrix.shape[-1]:
         return _standard_2d(matrix, steps, dtype, out)
-    x, xt, transposed = _prescale(matrix, dtype)
+    x = _prescale(matrix, dtype)
+    tall = matrix.shape[-2] > matrix.shape[-1]
     segments = [length for length in (min(steps, 2), max(steps - 2, 0)) if length]
     for index, length in enumerate(segments):
-        r = ops.ns_gemm(x, x, symmetric=True)
+        r = _gram_matrix(x, tall)
         q = None
         for i in range(length):
             z = _poly(r)
@@ -76,15 +94,8 @@ def _gram_2d(matrix, steps, out=None):
             if i + 1 < length:
                 rz = ops.ns_gemm(z, r, alpha=1.0, beta=_A, resid=r, symmetric=True)
                 r = ops.ns_gemm(z, rz, alpha=1.0, beta=_A, resid=rz, symmetric=True)
-        last = index == len(segments) - 1
-        if last and transposed:
-            return ops.ns_gemm(xt, q, out=out)                                   # X^T Q = (Q X)^T
-        if last:
-            return ops.ns_gemm(q, xt, out=out)
-        new_t = torch.empty_like(xt)
-        x = ops.ns_gemm(q, xt, out_t=new_t)
-        xt = new_t
-    return xt if transposed else x
+        x = _apply(q, x, tall, out=out if index == len(segments) - 1 else None)
+    return x
 
 
 def _batched(fn, matrix, *args):

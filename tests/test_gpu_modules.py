@@ -240,27 +240,34 @@ def test_graphed_microbatch_matches_eager():
         assert rel_l2(weights_b[name], weights_a[name]) < 1e-3, name
 
 
-def test_producer_fused_linears_match_unfused():
+@pytest.mark.parametrize("stream_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("width", [384, 1152])
+def test_producer_fused_linears_match_unfused(stream_dtype, width):
     from viola_b200.nn import activation_linear, norm_modulate_linear
     from torch.nn import functional as F
     torch.manual_seed(0)
-    batch, tokens, width = 6, 96, 384
+    batch, tokens = 6, 96
     layer = Linear(width, 512).cuda()
-    x = torch.randn(batch, tokens, width, device="cuda", dtype=torch.bfloat16)
-    shift = (torch.randn(batch, width, device="cuda") * 0.3).bfloat16()
-    scale = (torch.randn(batch, width, device="cuda") * 0.3).bfloat16()
+    x = torch.randn(batch, tokens, width, device="cuda", dtype=stream_dtype)
+    # shift / scale are column slices of one adaLN output, as in a transformer block: strided rows
+    mod = (torch.randn(batch, 2 * width, device="cuda") * 0.3).bfloat16()
     dy = torch.randn(batch, tokens, 512, device="cuda", dtype=torch.bfloat16)
     results = []
     for fused in (True, False):
-        xs, sh, sc = (t.clone().requires_grad_(True) for t in (x, shift, scale))
+        xs, ms = x.clone().requires_grad_(True), mod.clone().requires_grad_(True)
+        sh, sc = ms.chunk(2, dim=-1)
         layer.zero_grad()
-        if fused:
-            y = norm_modulate_linear(xs, sh, sc, layer)
-        else:
-            y = layer(torch.addcmul(sh[:, None], F.layer_norm(xs.float(), (width,), eps=1e-6), (1 + sc)[:, None]).bfloat16())
+        launches = ops.launch_count
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            if fused:
+                y = norm_modulate_linear(xs, sh, sc, layer)
+                assert ops.launch_count - launches == 3          # statistics+amax, encode, GEMM: no cast pass
+            else:
+                y = layer(torch.addcmul(sh[:, None], F.layer_norm(xs.float(), (width,), eps=1e-6), (1 + sc)[:, None]))
         y.backward(dy)
-        results.append((y.detach(), xs.grad, sh.grad, sc.grad, layer.weight.grad.clone(), layer.bias.grad.clone()))
-    for name, a, b in zip(("y", "dx", "dshift", "dscale", "dw", "db"), *results):
+        assert xs.grad.dtype == stream_dtype
+        results.append((y.detach(), xs.grad, ms.grad, layer.weight.grad.clone(), layer.bias.grad.clone()))
+    for name, a, b in zip(("y", "dx", "dmod", "dw", "db"), *results):
         assert rel_l2(a, b) < 2e-2, (name, rel_l2(a, b))
     layer2 = Linear(512, width).cuda()
     z = torch.randn(batch * tokens, 512, device="cuda", dtype=torch.bfloat16)
@@ -274,3 +281,28 @@ def test_producer_fused_linears_match_unfused():
         results.append((y.detach(), zs.grad, layer2.weight.grad.clone()))
     for name, a, b in zip(("y", "dz", "dw"), *results):
         assert rel_l2(a, b) < 2e-2, (name, rel_l2(a, b))
+
+
+@pytest.mark.parametrize("stream_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("width", [256, 1152, 2048])
+def test_gated_residual_matches_addcmul(stream_dtype, width):
+    from viola_b200.nn import gated_residual
+    torch.manual_seed(3)
+    batch, tokens = 5, 77
+    x = torch.randn(batch, tokens, width, device="cuda", dtype=stream_dtype)
+    y = torch.randn(batch, tokens, width, device="cuda", dtype=torch.bfloat16)
+    mod = torch.randn(batch, 3 * width, device="cuda").bfloat16()
+    dout = torch.randn(batch, tokens, width, device="cuda", dtype=stream_dtype)
+    results = []
+    for fused in (True, False):
+        xs, ys, ms = (t.clone().requires_grad_(True) for t in (x, y, mod))
+        gate = ms.chunk(3, dim=-1)[1]
+        launches = ops.launch_count
+        out = gated_residual(xs, gate, ys) if fused else torch.addcmul(xs.float(), gate.float()[:, None], ys.float())
+        assert (ops.launch_count - launches == 1) == fused
+        out.backward(dout if fused else dout.float())
+        results.append((out.detach().float(), xs.grad.float(), ys.grad.float(), ms.grad.float()))
+    assert results[0][0].dtype == torch.float32 and rel_l2(results[0][0], results[1][0]) < (4e-3 if stream_dtype == torch.bfloat16 else 1e-6)
+    assert torch.equal(results[0][1], results[1][1])
+    assert rel_l2(results[0][2], results[1][2]) < 4e-3
+    assert rel_l2(results[0][3], results[1][3]) < 1e-2

@@ -121,19 +121,27 @@ int vb_gated_forward(const void* gu, int dtype, int rows, int hidden, int activa
 int vb_gated_backward(const void* gu, const void* dh, int dtype, int rows, int hidden, int activation,
                       void* dgu, cudaStream_t stream);
 
-// ---- producer-fused quantisers (fused.cu): bf16 activations, per-tensor scales ----------
-// mode: 1 = LayerNorm (no affine) + modulate, 2 = GELU(tanh), 3 = SiLU
-int vb_ln_stats_amax(const void* x, int rows, int cols, float eps, const void* mod_shift, const void* mod_scale,
-                     int tokens, float* mean, float* rstd, float* history, int history_len, long long index,
-                     int delayed, float limit, float* scale_out, unsigned int* scratch, cudaStream_t stream);
+// ---- producer-fused quantisers (fused.cu): per-tensor scales ---------------------------------------
+// mode: 1 = LayerNorm (no affine) + modulate, 2 = GELU(tanh), 3 = SiLU.  x_dtype: 0 fp32, 1 bf16 (the residual
+// stream); modulation vectors are bf16 rows of pitch mod_stride (elements), one row per sample of `tokens` rows.
+int vb_ln_stats_amax(const void* x, int x_dtype, int rows, int cols, float eps, const void* mod_shift,
+                     const void* mod_scale, long long mod_stride, int tokens, float* mean, float* rstd, float* history,
+                     int history_len, long long index, int delayed, float limit, float* scale_out,
+                     unsigned int* scratch, cudaStream_t stream);
 int vb_act_amax(const void* z, long long n, int mode, float* history, int history_len, long long index,
                 int delayed, float limit, float* scale_out, unsigned int* scratch, cudaStream_t stream);
-int vb_fused_quantize(const void* x, int rows, int cols, int mode, const float* mean, const float* rstd,
-                      const void* mod_shift, const void* mod_scale, int tokens, const float* scale, float limit,
-                      int fmt, void* q, void* qt, cudaStream_t stream);
-int vb_ln_modulate_backward(const void* dh, const void* x, const float* mean, const float* rstd,
-                            const void* mod_scale, int rows, int cols, int tokens, void* dx, float* dshift,
-                            float* dscale, cudaStream_t stream);
+int vb_fused_quantize(const void* x, int x_dtype, int rows, int cols, int mode, const float* mean, const float* rstd,
+                      const void* mod_shift, const void* mod_scale, long long mod_stride, int tokens,
+                      const float* scale, float limit, int fmt, void* q, void* qt, cudaStream_t stream);
+int vb_ln_modulate_backward(const void* dh, const void* x, int x_dtype, const float* mean, const float* rstd,
+                            const void* mod_scale, long long mod_stride, int rows, int cols, int tokens, void* dx,
+                            float* dshift, float* dscale, cudaStream_t stream);
+// out = x + gate[row / tokens] * y (x, out: x_dtype; y, gate: bf16) and the branch side of its backward:
+// dy = dout * gate (bf16), dgate += per-sample column sums of dout * y (fp32, zero-initialised by the caller)
+int vb_gate_residual(const void* x, int x_dtype, const void* gate, long long gate_stride, const void* y, int rows,
+                     int cols, int tokens, void* out, cudaStream_t stream);
+int vb_gate_residual_backward(const void* dout, int dout_dtype, const void* gate, long long gate_stride, const void* y,
+                              int rows, int cols, int tokens, void* dy, float* dgate, cudaStream_t stream);
 
 // ---- Hadamard-64 rotation --------------------------------------------------------
 int vb_hadamard64(const void* x, int dtype, int rows, int cols, void* out, cudaStream_t stream);

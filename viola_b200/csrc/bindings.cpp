@@ -402,19 +402,29 @@ void gather_pull(const Tensor& entries, at::IntArrayRef heaps, int64_t rank, int
 }
 
 // ---- producer-fused quantisers -------------------------------------------------------------------
+// a per-sample modulation vector: bf16 [samples, cols] with unit column stride (rows may be strided views)
+static int64_t mod_rows(const Tensor& t, const char* name, int64_t cols) {
+  TORCH_CHECK(t.is_cuda() && t.dim() == 2 && t.size(1) == cols && t.stride(1) == 1 && t.scalar_type() == at::kBFloat16,
+              name, " must be a bf16 CUDA [samples, cols] tensor with unit column stride");
+  return t.stride(0);
+}
+static int stream_dtype(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.scalar_type() == at::kFloat || t.scalar_type() == at::kBFloat16, name, " must be fp32 or bf16");
+  return t.scalar_type() == at::kFloat ? 0 : 1;
+}
+
 void ln_stats_amax(const Tensor& x, double eps, const Tensor& shift, const Tensor& scale, int64_t tokens, Tensor mean,
                    Tensor rstd, const OptTensor& history, int64_t index, bool delayed, double limit, Tensor scale_out,
                    Tensor scratch) {
   cuda_contig(x, "x");
-  cuda_contig(shift, "shift");
-  cuda_contig(scale, "scale");
-  TORCH_CHECK(x.dim() == 2 && x.scalar_type() == at::kBFloat16 && shift.scalar_type() == at::kBFloat16 &&
-              scale.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(x.dim() == 2);
+  const int64_t stride = mod_rows(shift, "shift", x.size(1));
+  TORCH_CHECK(mod_rows(scale, "scale", x.size(1)) == stride, "shift and scale must share a row pitch");
   c10::cuda::CUDAGuard guard(x.device());
-  check(vb_ln_stats_amax(x.data_ptr(), (int)x.size(0), (int)x.size(1), (float)eps, shift.data_ptr(), scale.data_ptr(),
-                         (int)tokens, mean.data_ptr<float>(), rstd.data_ptr<float>(), (float*)ptr(history),
-                         history.has_value() ? (int)history->numel() : 0, index, delayed, (float)limit,
-                         scale_out.data_ptr<float>(), (unsigned int*)scratch.data_ptr(), stream()),
+  check(vb_ln_stats_amax(x.data_ptr(), stream_dtype(x, "x"), (int)x.size(0), (int)x.size(1), (float)eps, shift.data_ptr(),
+                         scale.data_ptr(), stride, (int)tokens, mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                         (float*)ptr(history), history.has_value() ? (int)history->numel() : 0, index, delayed,
+                         (float)limit, scale_out.data_ptr<float>(), (unsigned int*)scratch.data_ptr(), stream()),
         "ln_stats_amax");
 }
 
@@ -432,11 +442,17 @@ void fused_quantize(const Tensor& x, int64_t mode, const OptTensor& mean, const 
                     const OptTensor& scale, int64_t tokens, const Tensor& qscale, double limit, int64_t fmt,
                     const OptTensor& q, const OptTensor& qt) {
   cuda_contig(x, "x");
-  TORCH_CHECK(x.dim() == 2 && x.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(x.dim() == 2);
+  int64_t stride = 0;
+  if (mode == 1) {
+    TORCH_CHECK(shift.has_value() && scale.has_value() && mean.has_value() && rstd.has_value());
+    stride = mod_rows(*shift, "shift", x.size(1));
+    TORCH_CHECK(mod_rows(*scale, "scale", x.size(1)) == stride, "shift and scale must share a row pitch");
+  }
   c10::cuda::CUDAGuard guard(x.device());
-  check(vb_fused_quantize(x.data_ptr(), (int)x.size(0), (int)x.size(1), (int)mode, (const float*)ptr(mean),
-                          (const float*)ptr(rstd), ptr(shift), ptr(scale), (int)tokens, qscale.data_ptr<float>(),
-                          (float)limit, (int)fmt, ptr(q), ptr(qt), stream()),
+  check(vb_fused_quantize(x.data_ptr(), stream_dtype(x, "x"), (int)x.size(0), (int)x.size(1), (int)mode,
+                          (const float*)ptr(mean), (const float*)ptr(rstd), ptr(shift), ptr(scale), stride, (int)tokens,
+                          qscale.data_ptr<float>(), (float)limit, (int)fmt, ptr(q), ptr(qt), stream()),
         "fused_quantize");
 }
 
@@ -444,13 +460,44 @@ void ln_modulate_backward(const Tensor& dh, const Tensor& x, const Tensor& mean,
                           int64_t tokens, Tensor dx, Tensor dshift, Tensor dscale) {
   cuda_contig(dh, "dh");
   cuda_contig(x, "x");
-  TORCH_CHECK(dh.scalar_type() == at::kBFloat16 && x.scalar_type() == at::kBFloat16 && dx.scalar_type() == at::kBFloat16);
+  cuda_contig(dx, "dx");
+  TORCH_CHECK(dh.scalar_type() == at::kBFloat16 && dx.scalar_type() == x.scalar_type());
   TORCH_CHECK(dshift.scalar_type() == at::kFloat && dscale.scalar_type() == at::kFloat);
+  const int64_t stride = mod_rows(scale, "scale", x.size(1));
   c10::cuda::CUDAGuard guard(x.device());
-  check(vb_ln_modulate_backward(dh.data_ptr(), x.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
-                                scale.data_ptr(), (int)x.size(0), (int)x.size(1), (int)tokens, dx.data_ptr(),
-                                dshift.data_ptr<float>(), dscale.data_ptr<float>(), stream()),
+  check(vb_ln_modulate_backward(dh.data_ptr(), x.data_ptr(), stream_dtype(x, "x"), mean.data_ptr<float>(),
+                                rstd.data_ptr<float>(), scale.data_ptr(), stride, (int)x.size(0), (int)x.size(1),
+                                (int)tokens, dx.data_ptr(), dshift.data_ptr<float>(), dscale.data_ptr<float>(), stream()),
         "ln_modulate_backward");
+}
+
+void gate_residual(const Tensor& x, const Tensor& gate, const Tensor& y, int64_t tokens, Tensor out) {
+  cuda_contig(x, "x");
+  cuda_contig(y, "y");
+  cuda_contig(out, "out");
+  TORCH_CHECK(x.dim() == 2 && y.sizes() == x.sizes() && out.sizes() == x.sizes());
+  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && out.scalar_type() == x.scalar_type());
+  const int64_t stride = mod_rows(gate, "gate", x.size(1));
+  c10::cuda::CUDAGuard guard(x.device());
+  check(vb_gate_residual(x.data_ptr(), stream_dtype(x, "x"), gate.data_ptr(), stride, y.data_ptr(), (int)x.size(0),
+                         (int)x.size(1), (int)tokens, out.data_ptr(), stream()),
+        "gate_residual");
+}
+
+void gate_residual_backward(const Tensor& dout, const Tensor& gate, const Tensor& y, int64_t tokens, Tensor dy,
+                            Tensor dgate) {
+  cuda_contig(dout, "dout");
+  cuda_contig(y, "y");
+  cuda_contig(dy, "dy");
+  cuda_contig(dgate, "dgate");
+  TORCH_CHECK(dout.dim() == 2 && y.sizes() == dout.sizes() && dy.sizes() == dout.sizes());
+  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && dy.scalar_type() == at::kBFloat16 && dgate.scalar_type() == at::kFloat);
+  const int64_t stride = mod_rows(gate, "gate", dout.size(1));
+  c10::cuda::CUDAGuard guard(dout.device());
+  check(vb_gate_residual_backward(dout.data_ptr(), stream_dtype(dout, "dout"), gate.data_ptr(), stride, y.data_ptr(),
+                                  (int)dout.size(0), (int)dout.size(1), (int)tokens, dy.data_ptr(),
+                                  dgate.data_ptr<float>(), stream()),
+        "gate_residual_backward");
 }
 
 // ---- multi-tensor optimizer kernels ---------------------------------------------------------------
@@ -522,4 +569,6 @@ TORCH_LIBRARY(viola_b200, m) {
   m.def("act_amax", &act_amax);
   m.def("fused_quantize", &fused_quantize);
   m.def("ln_modulate_backward", &ln_modulate_backward);
+  m.def("gate_residual", &gate_residual);
+  m.def("gate_residual_backward", &gate_residual_backward);
 }

@@ -1,4 +1,4 @@
-// Producer-fused quantisers for transformer blocks (sm_100a, bf16 activations).
+// Producer-fused quantisers for transformer blocks (sm_100a; bf16 or fp32 residual stream).
 //
 // The reference quantises the output of LayerNorm/modulate and of GELU in separate passes
 // (viola/nn/linear.py:38-53 is fed by PyTorch LayerNorm / mul / add / gelu kernels in
@@ -9,7 +9,12 @@
 //           vb_act_amax      : global amax of act(z)                               -> FP8 scale
 //   pass 2  vb_fused_quantize: recompute h (or act(z)) from x and emit FP8 codes rowwise and
 //                              transposed; h itself is never written to memory.
-// and the matching backward of LayerNorm+modulate in one kernel (vb_ln_modulate_backward).
+// and the matching backward of LayerNorm+modulate in one kernel (vb_ln_modulate_backward), plus the
+// gated residual x + gate[b] * y with its backward (vb_gate_residual / vb_gate_residual_backward).
+// Rows are walked in 16-byte vectors: a lane owns the 8-element chunks lane, lane + 32, ... of a row.
+#include <mutex>
+#include <set>
+
 #include "api.h"
 #include "common/numerics.cuh"
 
@@ -17,16 +22,46 @@ namespace vb {
 
 enum FusedMode : int { kModeLnModulate = 1, kModeGelu = 2, kModeSilu = 3 };
 
+// tanh-GELU as g * sigmoid(2u), u = sqrt(2/pi) (g + 0.044715 g^3): 0.5 (1 + tanh u) == 1 / (1 + exp(-2u)).
+// One ex2 and one fast reciprocal per element; the ~1e-6 relative error is far below the bf16 rounding
+// that follows.  Saturates cleanly: exp(-2u) -> inf gives 0, -> 0 gives g.
 __device__ __forceinline__ float gelu_tanh(float g) {
-  const float t = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
-  return 0.5f * g * (1.f + t);
+  const float u2 = 1.5957691216057308f * (g + 0.044715f * g * g * g);
+  return __fdividef(g, 1.f + __expf(-u2));
 }
 __device__ __forceinline__ float apply_act(float v, int mode) {
   if (mode == kModeGelu) return gelu_tanh(v);
-  if (mode == kModeSilu) return v / (1.f + __expf(-v));
+  if (mode == kModeSilu) return __fdividef(v, 1.f + __expf(-v));
   return v;
 }
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// 8 consecutive elements <-> fp32 registers (bf16: one 16-byte access, fp32: two)
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 t = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&t);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __bfloat1622float2(h[e]);
+    v[2 * e] = f.x;
+    v[2 * e + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 t;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&t);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+  *reinterpret_cast<uint4*>(p) = t;
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
 
 // amax -> scale with the delayed-scaling history, executed by the last block to finish.
 __device__ __forceinline__ void finish_scale(float block_amax, unsigned int* scratch, float* history, int history_len,
@@ -65,36 +100,44 @@ __device__ __forceinline__ float block_max(float m) {
   return b;
 }
 
-// One warp per row; the row (<= 64 elements per lane) stays in registers between the statistics and
-// the modulated amax.  mod_shift / mod_scale are [samples, cols] in bf16; sample = row / tokens.
-template <int EPL>
+// One warp per row; the row (VPL chunks of 8 elements per lane) stays in registers between the statistics
+// and the modulated amax.  mod_shift / mod_scale are bf16 rows of pitch mod_stride; sample = row / tokens.
+template <typename T, int VPL>
 __global__ void __launch_bounds__(256)
-ln_stats_amax_kernel(const __nv_bfloat16* __restrict__ x, int rows, int cols, float eps,
+ln_stats_amax_kernel(const T* __restrict__ x, int rows, int cols, float eps,
                      const __nv_bfloat16* __restrict__ mod_shift, const __nv_bfloat16* __restrict__ mod_scale,
-                     int tokens, float* __restrict__ mean_out, float* __restrict__ rstd_out, float* history,
-                     int history_len, long long index, int delayed, float limit, float* scale_out,
+                     long long mod_stride, int tokens, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                     float* history, int history_len, long long index, int delayed, float limit, float* scale_out,
                      unsigned int* scratch) {
   const int lane = threadIdx.x & 31;
+  const int chunks = cols >> 3;
   float amax = 0.f;
   for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < rows; row += gridDim.x * 8) {
-    const __nv_bfloat16* xr = x + (long long)row * cols;
-    float v[EPL];
+    const T* xr = x + (long long)row * cols;
+    float v[VPL][8];
     float sum = 0.f;
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) {
-      const int c = e * 32 + lane;
-      v[e] = c < cols ? __bfloat162float(xr[c]) : 0.f;
-      sum += v[e];
+    for (int j = 0; j < VPL; ++j) {
+      const int chunk = lane + 32 * j;
+      if (chunk < chunks) {
+        load8(xr + chunk * 8, v[j]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum += v[j][e];
+      }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
     const float mean = sum / cols;
     float var = 0.f;
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) {
-      const int c = e * 32 + lane;
-      const float d = c < cols ? v[e] - mean : 0.f;
-      var += d * d;
+    for (int j = 0; j < VPL; ++j) {
+      if (lane + 32 * j < chunks) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float d = v[j][e] - mean;
+          var += d * d;
+        }
+      }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
@@ -103,14 +146,17 @@ ln_stats_amax_kernel(const __nv_bfloat16* __restrict__ x, int rows, int cols, fl
       mean_out[row] = mean;
       rstd_out[row] = rstd;
     }
-    const long long mod = (long long)(row / tokens) * cols;
+    const long long mod = (long long)(row / tokens) * mod_stride;
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) {
-      const int c = e * 32 + lane;
-      if (c < cols) {
-        const float normed = (v[e] - mean) * rstd;
-        const float h = round_bf16(fmaf(normed, 1.f + __bfloat162float(mod_scale[mod + c]), __bfloat162float(mod_shift[mod + c])));
-        amax = fmaxf(amax, fabsf(h));
+    for (int j = 0; j < VPL; ++j) {
+      const int chunk = lane + 32 * j;
+      if (chunk < chunks) {
+        float sc[8], sh[8];
+        load8(mod_scale + mod + chunk * 8, sc);
+        load8(mod_shift + mod + chunk * 8, sh);
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          amax = fmaxf(amax, fabsf(round_bf16(fmaf((v[j][e] - mean) * rstd, 1.f + sc[e], sh[e]))));
       }
     }
   }
@@ -142,21 +188,65 @@ struct FusedArgs {
   const float* rstd;
   const __nv_bfloat16* mod_shift;
   const __nv_bfloat16* mod_scale;
+  long long mod_stride;
   int tokens;
 };
 
 __device__ __forceinline__ float fused_value(float v, int r, int c, int cols, const FusedArgs& a) {
   if (a.mode == kModeLnModulate) {
     const float normed = (v - a.mean[r]) * a.rstd[r];
-    const long long mod = (long long)(r / a.tokens) * cols + c;
+    const long long mod = (long long)(r / a.tokens) * a.mod_stride + c;
     return round_bf16(fmaf(normed, 1.f + __bfloat162float(a.mod_scale[mod]), __bfloat162float(a.mod_shift[mod])));
   }
   return round_bf16(apply_act(v, a.mode));
 }
 
-// 64x64 tiles: rowwise and/or transposed FP8 codes of the transformed input (bf16 source).
+// Row-wise codes only: a thread turns 16 consecutive elements into one 16-byte store (cols % 16 == 0).
+template <typename T>
 __global__ void __launch_bounds__(256)
-fused_quantize_kernel(const __nv_bfloat16* __restrict__ x, int rows, int cols, FusedArgs fa,
+fused_quantize_rows_kernel(const T* __restrict__ x, int rows, int cols, FusedArgs fa,
+                           const float* __restrict__ scale_ptr, float limit, int fmt, uint8_t* __restrict__ q) {
+  const float scale = scale_ptr[0];
+  const int per_row = cols >> 4;
+  const long long total = (long long)rows * per_row;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / per_row);
+    const int c = (int)(i - (long long)r * per_row) << 4;
+    float v[2][8];
+    load8(x + (long long)r * cols + c, v[0]);
+    load8(x + (long long)r * cols + c + 8, v[1]);
+    if (fa.mode == kModeLnModulate) {
+      const float mu = fa.mean[r], rs = fa.rstd[r];
+      const long long mod = (long long)(r / fa.tokens) * fa.mod_stride + c;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        float sc[8], sh[8];
+        load8(fa.mod_scale + mod + 8 * j, sc);
+        load8(fa.mod_shift + mod + 8 * j, sh);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[j][e] = round_bf16(fmaf((v[j][e] - mu) * rs, 1.f + sc[e], sh[e]));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[j][e] = round_bf16(apply_act(v[j][e], fa.mode));
+    }
+    uint4 packed;
+    uint16_t* codes = reinterpret_cast<uint16_t*>(&packed);
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        codes[j * 4 + e] = fp8_encode2(scaled_clamp(v[j][2 * e], scale, limit), scaled_clamp(v[j][2 * e + 1], scale, limit), fmt);
+    *reinterpret_cast<uint4*>(q + (long long)r * cols + c) = packed;
+  }
+}
+
+// 64x64 tiles: rowwise and/or transposed FP8 codes of the transformed input.
+template <typename T>
+__global__ void __launch_bounds__(256)
+fused_quantize_kernel(const T* __restrict__ x, int rows, int cols, FusedArgs fa,
                       const float* __restrict__ scale_ptr, float limit, int fmt, uint8_t* __restrict__ q,
                       uint8_t* __restrict__ qt) {
   __shared__ __align__(16) uint8_t tile[64][64 + 16];
@@ -168,20 +258,17 @@ fused_quantize_kernel(const __nv_bfloat16* __restrict__ x, int rows, int cols, F
   if (r < rows && c + 15 < cols && cols % 8 == 0) {
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
-      const uint4 t = *reinterpret_cast<const uint4*>(x + (long long)r * cols + c + j * 8);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&t);
+      float f[8];
+      load8(x + (long long)r * cols + c + j * 8, f);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = __bfloat1622float2(h[e]);
-        codes[j * 8 + 2 * e] = fp8_encode(scaled_clamp(fused_value(f.x, r, c + j * 8 + 2 * e, cols, fa), scale, limit), fmt);
-        codes[j * 8 + 2 * e + 1] = fp8_encode(scaled_clamp(fused_value(f.y, r, c + j * 8 + 2 * e + 1, cols, fa), scale, limit), fmt);
-      }
+      for (int e = 0; e < 8; ++e)
+        codes[j * 8 + e] = fp8_encode(scaled_clamp(fused_value(f[e], r, c + j * 8 + e, cols, fa), scale, limit), fmt);
     }
   } else {
 #pragma unroll
     for (int e = 0; e < 16; ++e) {
       const bool in = r < rows && c + e < cols;
-      const float v = in ? fused_value(__bfloat162float(x[(long long)r * cols + c + e]), r, c + e, cols, fa) : 0.f;
+      const float v = in ? fused_value((float)x[(long long)r * cols + c + e], r, c + e, cols, fa) : 0.f;
       codes[e] = fp8_encode(scaled_clamp(v, scale, limit), fmt);
     }
   }
@@ -216,46 +303,49 @@ fused_quantize_kernel(const __nv_bfloat16* __restrict__ x, int rows, int cols, F
 //   dx     = rstd * (g - mean(g) - xhat * mean(g * xhat)),  g = dh * (1 + scale[b])
 //   dshift[b] += dh,  dscale[b] += dh * xhat        (fp32 atomics into zero-initialised [samples, cols])
 // A block walks `rows_per_block` consecutive rows of ONE sample and reduces dshift / dscale in shared
-// memory first, so the global atomics are one per (block, column).
-template <int EPL>
+// memory first, so the global atomics are one per (block, column).  dx has the dtype of x.
+template <typename T, int VPL>
 __global__ void __launch_bounds__(256)
-ln_modulate_backward_kernel(const __nv_bfloat16* __restrict__ dh, const __nv_bfloat16* __restrict__ x,
+ln_modulate_backward_kernel(const __nv_bfloat16* __restrict__ dh, const T* __restrict__ x,
                             const float* __restrict__ mean, const float* __restrict__ rstd,
-                            const __nv_bfloat16* __restrict__ mod_scale, int rows, int cols, int tokens,
-                            int rows_per_block, __nv_bfloat16* __restrict__ dx, float* __restrict__ dshift,
+                            const __nv_bfloat16* __restrict__ mod_scale, long long mod_stride, int rows, int cols,
+                            int tokens, int rows_per_block, T* __restrict__ dx, float* __restrict__ dshift,
                             float* __restrict__ dscale) {
-  extern __shared__ float partial[];            // [2][cols]
-  float* p_shift = partial;
-  float* p_scale = partial + cols;
-  for (int c = threadIdx.x; c < 2 * cols; c += blockDim.x) partial[c] = 0.f;
-  __syncthreads();
+  extern __shared__ float partial[];            // [8 warps][2][cols], element e of chunk c at e * chunks + c
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int chunks = cols >> 3;
   const int blocks_per_sample = (tokens + rows_per_block - 1) / rows_per_block;
   const int sample = blockIdx.x / blocks_per_sample;
   const int first = sample * tokens + (blockIdx.x % blocks_per_sample) * rows_per_block;
   const int last = min(min(first + rows_per_block, (sample + 1) * tokens), rows);
-  const long long mod = (long long)sample * cols;
-  float acc_shift[EPL], acc_scale[EPL];
+  float acc_shift[VPL][8], acc_scale[VPL][8];
 #pragma unroll
-  for (int e = 0; e < EPL; ++e) acc_shift[e] = acc_scale[e] = 0.f;
+  for (int j = 0; j < VPL; ++j)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc_shift[j][e] = acc_scale[j][e] = 0.f;
+  const __nv_bfloat16* gain_row = mod_scale + (long long)sample * mod_stride;
   for (int row = first + warp; row < last; row += 8) {
     const long long base = (long long)row * cols;
     const float mu = mean[row], rs = rstd[row];
-    float g[EPL], xh[EPL];
+    float g[VPL][8], xh[VPL][8];
     float sum_g = 0.f, sum_gx = 0.f;
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) {
-      const int c = e * 32 + lane;
-      if (c < cols) {
-        const float d = __bfloat162float(dh[base + c]);
-        xh[e] = (__bfloat162float(x[base + c]) - mu) * rs;
-        g[e] = d * (1.f + __bfloat162float(mod_scale[mod + c]));
-        acc_shift[e] += d;
-        acc_scale[e] += d * xh[e];
-        sum_g += g[e];
-        sum_gx += g[e] * xh[e];
-      } else {
-        g[e] = xh[e] = 0.f;
+    for (int j = 0; j < VPL; ++j) {
+      const int chunk = lane + 32 * j;
+      if (chunk < chunks) {
+        float d[8], gain[8];
+        load8(dh + base + chunk * 8, d);
+        load8(x + base + chunk * 8, xh[j]);
+        load8(gain_row + chunk * 8, gain);      // re-read per row (L1 resident) instead of living in registers
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          xh[j][e] = (xh[j][e] - mu) * rs;
+          g[j][e] = d[e] * (1.f + gain[e]);
+          acc_shift[j][e] += d[e];
+          acc_scale[j][e] += d[e] * xh[j][e];
+          sum_g += g[j][e];
+          sum_gx += g[j][e] * xh[j][e];
+        }
       }
     }
 #pragma unroll
@@ -265,23 +355,116 @@ ln_modulate_backward_kernel(const __nv_bfloat16* __restrict__ dh, const __nv_bfl
     }
     const float mean_g = sum_g / cols, mean_gx = sum_gx / cols;
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) {
-      const int c = e * 32 + lane;
-      if (c < cols) dx[base + c] = __float2bfloat16_rn(rs * (g[e] - mean_g - xh[e] * mean_gx));
+    for (int j = 0; j < VPL; ++j) {
+      const int chunk = lane + 32 * j;
+      if (chunk < chunks) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = rs * (g[j][e] - mean_g - xh[j][e] * mean_gx);
+        store8(dx + base + chunk * 8, o);
+      }
     }
   }
+  float* mine = partial + (size_t)warp * 2 * cols;
 #pragma unroll
-  for (int e = 0; e < EPL; ++e) {
-    const int c = e * 32 + lane;
-    if (c < cols) {
-      atomicAdd(&p_shift[c], acc_shift[e]);
-      atomicAdd(&p_scale[c], acc_scale[e]);
+  for (int j = 0; j < VPL; ++j) {
+    const int chunk = lane + 32 * j;
+    if (chunk < chunks) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        mine[e * chunks + chunk] = acc_shift[j][e];            // consecutive lanes -> consecutive banks
+        mine[cols + e * chunks + chunk] = acc_scale[j][e];
+      }
     }
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-    atomicAdd(&dshift[mod + c], p_shift[c]);
-    atomicAdd(&dscale[mod + c], p_scale[c]);
+  const long long mod = (long long)sample * cols;
+  for (int i = threadIdx.x; i < 2 * cols; i += blockDim.x) {
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += partial[(size_t)w * 2 * cols + i];
+    const int which = i >= cols, k = i - which * cols;
+    const int c = (k % chunks) * 8 + k / chunks;
+    atomicAdd((which ? dscale : dshift) + mod + c, total);
+  }
+}
+
+// out = x + gate[b] * y: x / out in T (the residual stream), y and gate in bf16; 8 elements per thread.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gate_residual_kernel(const T* __restrict__ x, const __nv_bfloat16* __restrict__ gate, long long gate_stride,
+                     const __nv_bfloat16* __restrict__ y, int rows, int cols, int tokens, T* __restrict__ out) {
+  const int per_row = cols >> 3;
+  const long long total = (long long)rows * per_row;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / per_row);
+    const int c = (int)(i - (long long)r * per_row) << 3;
+    float xv[8], yv[8], gv[8];
+    load8(x + (long long)r * cols + c, xv);
+    load8(y + (long long)r * cols + c, yv);
+    load8(gate + (long long)(r / tokens) * gate_stride + c, gv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) xv[e] = fmaf(gv[e], yv[e], xv[e]);
+    store8(out + (long long)r * cols + c, xv);
+  }
+}
+
+// Backward of the gated residual for the branch: dy = dout * gate[b] (bf16), dgate[b] += sum over the
+// sample's rows of dout * y (fp32 atomics into a zero-initialised [samples, cols]).  Same block shape as the
+// LayerNorm backward: a block owns rows of one sample and reduces in shared memory first.
+template <typename T, int VPL>
+__global__ void __launch_bounds__(256)
+gate_residual_backward_kernel(const T* __restrict__ dout, const __nv_bfloat16* __restrict__ gate, long long gate_stride,
+                              const __nv_bfloat16* __restrict__ y, int rows, int cols, int tokens, int rows_per_block,
+                              __nv_bfloat16* __restrict__ dy, float* __restrict__ dgate) {
+  extern __shared__ float partial[];            // [8 warps][cols], element e of chunk c at e * chunks + c
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int chunks = cols >> 3;
+  const int blocks_per_sample = (tokens + rows_per_block - 1) / rows_per_block;
+  const int sample = blockIdx.x / blocks_per_sample;
+  const int first = sample * tokens + (blockIdx.x % blocks_per_sample) * rows_per_block;
+  const int last = min(min(first + rows_per_block, (sample + 1) * tokens), rows);
+  float gv[VPL][8], acc[VPL][8];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int chunk = lane + 32 * j;
+    if (chunk < chunks) load8(gate + (long long)sample * gate_stride + chunk * 8, gv[j]);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[j][e] = 0.f;
+  }
+  for (int row = first + warp; row < last; row += 8) {
+    const long long base = (long long)row * cols;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int chunk = lane + 32 * j;
+      if (chunk < chunks) {
+        float d[8], yv[8], o[8];
+        load8(dout + base + chunk * 8, d);
+        load8(y + base + chunk * 8, yv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          o[e] = d[e] * gv[j][e];
+          acc[j][e] = fmaf(d[e], yv[e], acc[j][e]);
+        }
+        store8(dy + base + chunk * 8, o);
+      }
+    }
+  }
+  float* mine = partial + (size_t)warp * cols;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int chunk = lane + 32 * j;
+    if (chunk < chunks) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) mine[e * chunks + chunk] = acc[j][e];
+    }
+  }
+  __syncthreads();
+  for (int k = threadIdx.x; k < cols; k += blockDim.x) {
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += partial[(size_t)w * cols + k];
+    atomicAdd(&dgate[(long long)sample * cols + (k % chunks) * 8 + k / chunks], total);
   }
 }
 
@@ -289,22 +472,57 @@ ln_modulate_backward_kernel(const __nv_bfloat16* __restrict__ dh, const __nv_bfl
 
 using namespace vb;
 
-#define VB_EPL_SWITCH(cols, ...)                                \
-  if ((cols) <= 512) { constexpr int EPL = 16; __VA_ARGS__; }   \
-  else if ((cols) <= 1024) { constexpr int EPL = 32; __VA_ARGS__; } \
-  else if ((cols) <= 1536) { constexpr int EPL = 48; __VA_ARGS__; } \
-  else if ((cols) <= 2048) { constexpr int EPL = 64; __VA_ARGS__; } \
+// chunks of 8 elements per lane for one warp per row; rows up to 2048 elements
+#define VB_VPL_SWITCH(cols, ...)                                       \
+  if ((cols) <= 256) { constexpr int VPL = 1; __VA_ARGS__; }           \
+  else if ((cols) <= 512) { constexpr int VPL = 2; __VA_ARGS__; }      \
+  else if ((cols) <= 768) { constexpr int VPL = 3; __VA_ARGS__; }      \
+  else if ((cols) <= 1024) { constexpr int VPL = 4; __VA_ARGS__; }     \
+  else if ((cols) <= 1280) { constexpr int VPL = 5; __VA_ARGS__; }     \
+  else if ((cols) <= 1536) { constexpr int VPL = 6; __VA_ARGS__; }     \
+  else if ((cols) <= 2048) { constexpr int VPL = 8; __VA_ARGS__; }     \
   else return (int)cudaErrorInvalidValue;
 
-extern "C" int vb_ln_stats_amax(const void* x, int rows, int cols, float eps, const void* mod_shift, const void* mod_scale,
-                                int tokens, float* mean, float* rstd, float* history, int history_len, long long index,
-                                int delayed, float limit, float* scale_out, unsigned int* scratch, cudaStream_t stream) {
-  if (rows <= 0 || cols <= 0 || tokens <= 0) return (int)cudaErrorInvalidValue;
+// Rows of one sample a block walks before it reduces its column sums: as many as still leave about two
+// blocks per SM's worth of work in the grid (the per-block reduction is a fixed cost), at least 8.
+static int pick_rows_per_block(int rows, int tokens) {
+  int rpb = 128;
+  while (rpb > 8 && (long long)(rows / tokens) * ((tokens + rpb - 1) / rpb) < 148LL * 2) rpb >>= 1;
+  return rpb;
+}
+
+// Opt a kernel in, once, to the dynamic shared memory its widest supported row needs (8 warps x 2 x 2048 floats).
+template <typename Kernel>
+static void allow_smem(Kernel kernel) {
+  static std::mutex lock;
+  static std::set<const void*> configured;
+  std::lock_guard<std::mutex> guard(lock);
+  if (configured.insert(reinterpret_cast<const void*>(kernel)).second)
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 2048 * (int)sizeof(float));
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// x_dtype: 0 fp32, 1 bf16 (the dtype codes of numerics.cuh)
+extern "C" int vb_ln_stats_amax(const void* x, int x_dtype, int rows, int cols, float eps, const void* mod_shift,
+                                const void* mod_scale, long long mod_stride, int tokens, float* mean, float* rstd,
+                                float* history, int history_len, long long index, int delayed, float limit,
+                                float* scale_out, unsigned int* scratch, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0 || tokens <= 0 || cols % 8 != 0 || mod_stride % 8 != 0 || x_dtype > kBF16 ||
+      !aligned16(x) || !aligned16(mod_shift) || !aligned16(mod_scale))
+    return (int)cudaErrorInvalidValue;
   const int grid = std::min((rows + 7) / 8, 148 * 8);
-  VB_EPL_SWITCH(cols, (ln_stats_amax_kernel<EPL><<<grid, 256, 0, stream>>>(
-                          (const __nv_bfloat16*)x, rows, cols, eps, (const __nv_bfloat16*)mod_shift,
-                          (const __nv_bfloat16*)mod_scale, tokens, mean, rstd, history, history_len, index, delayed, limit,
-                          scale_out, scratch)));
+  const __nv_bfloat16* sh = (const __nv_bfloat16*)mod_shift;
+  const __nv_bfloat16* sc = (const __nv_bfloat16*)mod_scale;
+  if (x_dtype == kBF16) {
+    VB_VPL_SWITCH(cols, (ln_stats_amax_kernel<__nv_bfloat16, VPL><<<grid, 256, 0, stream>>>(
+                            (const __nv_bfloat16*)x, rows, cols, eps, sh, sc, mod_stride, tokens, mean, rstd, history,
+                            history_len, index, delayed, limit, scale_out, scratch)));
+  } else {
+    VB_VPL_SWITCH(cols, (ln_stats_amax_kernel<float, VPL><<<grid, 256, 0, stream>>>(
+                            (const float*)x, rows, cols, eps, sh, sc, mod_stride, tokens, mean, rstd, history, history_len,
+                            index, delayed, limit, scale_out, scratch)));
+  }
   return (int)cudaGetLastError();
 }
 
@@ -317,26 +535,95 @@ extern "C" int vb_act_amax(const void* z, long long n, int mode, float* history,
   return (int)cudaGetLastError();
 }
 
-extern "C" int vb_fused_quantize(const void* x, int rows, int cols, int mode, const float* mean, const float* rstd,
-                                 const void* mod_shift, const void* mod_scale, int tokens, const float* scale, float limit,
+template <typename T>
+static int launch_fused_quantize(const T* x, int rows, int cols, const FusedArgs& fa, const float* scale, float limit,
                                  int fmt, void* q, void* qt, cudaStream_t stream) {
-  FusedArgs fa{mode, mean, rstd, (const __nv_bfloat16*)mod_shift, (const __nv_bfloat16*)mod_scale, tokens > 0 ? tokens : 1};
-  dim3 grid((cols + 63) / 64, (rows + 63) / 64);
-  fused_quantize_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, rows, cols, fa, scale, limit, fmt, (uint8_t*)q,
-                                                  (uint8_t*)qt);
+  const bool vector_ok = cols % 16 == 0 && aligned16(x) && aligned16(q) &&
+                         (fa.mode != kModeLnModulate ||
+                          (fa.mod_stride % 8 == 0 && aligned16(fa.mod_shift) && aligned16(fa.mod_scale)));
+  if (qt == nullptr && q != nullptr && vector_ok) {
+    const long long total = (long long)rows * (cols / 16);
+    const int grid = (int)std::max<long long>(1, std::min<long long>((total + 255) / 256, 148LL * 16));
+    fused_quantize_rows_kernel<T><<<grid, 256, 0, stream>>>(x, rows, cols, fa, scale, limit, fmt, (uint8_t*)q);
+  } else {
+    if (cols % 8 != 0 || !aligned16(x)) return (int)cudaErrorInvalidValue;
+    dim3 grid((cols + 63) / 64, (rows + 63) / 64);
+    fused_quantize_kernel<T><<<grid, 256, 0, stream>>>(x, rows, cols, fa, scale, limit, fmt, (uint8_t*)q, (uint8_t*)qt);
+  }
   return (int)cudaGetLastError();
 }
 
-extern "C" int vb_ln_modulate_backward(const void* dh, const void* x, const float* mean, const float* rstd,
-                                       const void* mod_scale, int rows, int cols, int tokens, void* dx, float* dshift,
-                                       float* dscale, cudaStream_t stream) {
-  if (rows <= 0 || cols <= 0 || tokens <= 0 || rows % tokens != 0) return (int)cudaErrorInvalidValue;
-  const int rows_per_block = 32;
+extern "C" int vb_fused_quantize(const void* x, int x_dtype, int rows, int cols, int mode, const float* mean,
+                                 const float* rstd, const void* mod_shift, const void* mod_scale, long long mod_stride,
+                                 int tokens, const float* scale, float limit, int fmt, void* q, void* qt,
+                                 cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0 || x_dtype > kBF16) return (int)cudaErrorInvalidValue;
+  FusedArgs fa{mode, mean, rstd, (const __nv_bfloat16*)mod_shift, (const __nv_bfloat16*)mod_scale, mod_stride,
+               tokens > 0 ? tokens : 1};
+  if (x_dtype == kBF16)
+    return launch_fused_quantize((const __nv_bfloat16*)x, rows, cols, fa, scale, limit, fmt, q, qt, stream);
+  return launch_fused_quantize((const float*)x, rows, cols, fa, scale, limit, fmt, q, qt, stream);
+}
+
+extern "C" int vb_ln_modulate_backward(const void* dh, const void* x, int x_dtype, const float* mean, const float* rstd,
+                                       const void* mod_scale, long long mod_stride, int rows, int cols, int tokens,
+                                       void* dx, float* dshift, float* dscale, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0 || tokens <= 0 || rows % tokens != 0 || cols % 8 != 0 || mod_stride % 8 != 0 ||
+      x_dtype > kBF16 || !aligned16(dh) || !aligned16(x) || !aligned16(dx) || !aligned16(mod_scale))
+    return (int)cudaErrorInvalidValue;
+  const int rows_per_block = pick_rows_per_block(rows, tokens);
   const int blocks_per_sample = (tokens + rows_per_block - 1) / rows_per_block;
   const int grid = (rows / tokens) * blocks_per_sample;
-  const size_t smem = 2 * (size_t)cols * sizeof(float);
-  VB_EPL_SWITCH(cols, (ln_modulate_backward_kernel<EPL><<<grid, 256, smem, stream>>>(
-                          (const __nv_bfloat16*)dh, (const __nv_bfloat16*)x, mean, rstd, (const __nv_bfloat16*)mod_scale, rows,
-                          cols, tokens, rows_per_block, (__nv_bfloat16*)dx, dshift, dscale)));
+  const size_t smem = 8 * 2 * (size_t)cols * sizeof(float);
+  const __nv_bfloat16* sc = (const __nv_bfloat16*)mod_scale;
+  if (x_dtype == kBF16) {
+    VB_VPL_SWITCH(cols, (allow_smem(ln_modulate_backward_kernel<__nv_bfloat16, VPL>), ln_modulate_backward_kernel<__nv_bfloat16, VPL><<<grid, 256, smem, stream>>>(
+                            (const __nv_bfloat16*)dh, (const __nv_bfloat16*)x, mean, rstd, sc, mod_stride, rows, cols,
+                            tokens, rows_per_block, (__nv_bfloat16*)dx, dshift, dscale)));
+  } else {
+    VB_VPL_SWITCH(cols, (allow_smem(ln_modulate_backward_kernel<float, VPL>), ln_modulate_backward_kernel<float, VPL><<<grid, 256, smem, stream>>>(
+                            (const __nv_bfloat16*)dh, (const float*)x, mean, rstd, sc, mod_stride, rows, cols, tokens,
+                            rows_per_block, (float*)dx, dshift, dscale)));
+  }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vb_gate_residual(const void* x, int x_dtype, const void* gate, long long gate_stride, const void* y,
+                                int rows, int cols, int tokens, void* out, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0 || tokens <= 0 || cols % 8 != 0 || gate_stride % 8 != 0 || x_dtype > kBF16 ||
+      !aligned16(x) || !aligned16(gate) || !aligned16(y) || !aligned16(out))
+    return (int)cudaErrorInvalidValue;
+  const long long total = (long long)rows * (cols / 8);
+  const int grid = (int)std::max<long long>(1, std::min<long long>((total + 255) / 256, 148LL * 16));
+  if (x_dtype == kBF16)
+    gate_residual_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)gate,
+                                                                  gate_stride, (const __nv_bfloat16*)y, rows, cols, tokens,
+                                                                  (__nv_bfloat16*)out);
+  else
+    gate_residual_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, (const __nv_bfloat16*)gate, gate_stride,
+                                                          (const __nv_bfloat16*)y, rows, cols, tokens, (float*)out);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vb_gate_residual_backward(const void* dout, int dout_dtype, const void* gate, long long gate_stride,
+                                         const void* y, int rows, int cols, int tokens, void* dy, float* dgate,
+                                         cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0 || tokens <= 0 || rows % tokens != 0 || cols % 8 != 0 || gate_stride % 8 != 0 ||
+      dout_dtype > kBF16 || !aligned16(dout) || !aligned16(gate) || !aligned16(y) || !aligned16(dy))
+    return (int)cudaErrorInvalidValue;
+  const int rows_per_block = pick_rows_per_block(rows, tokens);
+  const int blocks_per_sample = (tokens + rows_per_block - 1) / rows_per_block;
+  const int grid = (rows / tokens) * blocks_per_sample;
+  const size_t smem = 8 * (size_t)cols * sizeof(float);
+  const __nv_bfloat16* g = (const __nv_bfloat16*)gate;
+  if (dout_dtype == kBF16) {
+    VB_VPL_SWITCH(cols, (allow_smem(gate_residual_backward_kernel<__nv_bfloat16, VPL>), gate_residual_backward_kernel<__nv_bfloat16, VPL><<<grid, 256, smem, stream>>>(
+                            (const __nv_bfloat16*)dout, g, gate_stride, (const __nv_bfloat16*)y, rows, cols, tokens,
+                            rows_per_block, (__nv_bfloat16*)dy, dgate)));
+  } else {
+    VB_VPL_SWITCH(cols, (allow_smem(gate_residual_backward_kernel<float, VPL>), gate_residual_backward_kernel<float, VPL><<<grid, 256, smem, stream>>>(
+                            (const float*)dout, g, gate_stride, (const __nv_bfloat16*)y, rows, cols, tokens, rows_per_block,
+                            (__nv_bfloat16*)dy, dgate)));
+  }
   return (int)cudaGetLastError();
 }

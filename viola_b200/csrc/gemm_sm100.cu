@@ -405,6 +405,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int n0 = nt * (C::kGatedFwd ? BN / 2 : BN);  // first logical output column
       const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
 
+      // Bias of this tile's columns, fetched before the accumulator wait: lane L keeps column c * 32 + L
+      // of every chunk and the epilogue broadcasts it with a shuffle (zero past N, so no guard later).
+      constexpr bool kHasBias = EPI == VB_EPI_LINEAR || EPI == VB_EPI_GATED_FWD;
+      float bias_reg[kHasBias ? NOUT : 1], bias_reg2[C::kGatedFwd ? NOUT : 1];
+      if constexpr (kHasBias) {
+#pragma unroll
+        for (int c = 0; c < NOUT; ++c) {
+          const int col = n0 + c * 32 + lane;
+          const bool in = args.bias != nullptr && col < args.N;
+          bias_reg[c] = in ? load_elem(args.bias, col, args.bias_dtype) : 0.f;
+          if constexpr (C::kGatedFwd) bias_reg2[c] = in ? load_elem(args.bias, args.N + col, args.bias_dtype) : 0.f;
+        }
+      }
+
       float accr[GROUP ? BN : 1];
       if constexpr (GROUP) {
 #pragma unroll
@@ -490,8 +504,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if constexpr (EPI == VB_EPI_LINEAR) {
           if (args.bias != nullptr) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < args.N) v[j] += load_elem(args.bias, col0 + j, args.bias_dtype);
+            for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, bias_reg[c], j);
           }
           if (!staged) {
             if (row_ok) store_row32(out_base, args.ldo, args.out_dtype, grow, col0, args.N, v);
@@ -560,11 +573,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         } else if constexpr (EPI == VB_EPI_GATED_FWD) {
           if (args.bias != nullptr) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < args.N) {
-                v[j] += load_elem(args.bias, col0 + j, args.bias_dtype);
-                v2[j] += load_elem(args.bias, args.N + col0 + j, args.bias_dtype);
-              }
+            for (int j = 0; j < 32; ++j) {
+              v[j] += __shfl_sync(0xffffffffu, bias_reg[c], j);
+              v2[j] += __shfl_sync(0xffffffffu, bias_reg2[c], j);
+            }
           }
           float h[32];
 #pragma unroll

@@ -17,7 +17,7 @@ import torch
 from torch import nn
 from torch.nn import functional as F
 
-from ..nn import Linear, activation_linear, norm_modulate_linear
+from ..nn import Linear, activation_linear, gated_residual, norm_modulate_linear
 from ..nn.attention import packed_attention
 
 
@@ -31,11 +31,6 @@ def position_embedding(size, width):
 def modulate(x, shift, scale):
     """x * (1 + scale) + shift with per-sample vectors, as one fused multiply-add."""
     return torch.addcmul(shift[:, None], x, (1 + scale)[:, None])
-
-
-def gated_residual(x, gate, y):
-    """x + gate * y with a per-sample gate vector, as one fused multiply-add."""
-    return torch.addcmul(x, gate[:, None], y)
 
 
 class Block(nn.Module):
@@ -120,10 +115,9 @@ class DiT(nn.Module):
     def forward(self, x, t, y):
         """``x`` latents [B, C, H, W]; ``t`` timesteps in [0, 1000); ``y`` labels in [0, classes]."""
         c = self.time(self.timestep_features(t).to(x.dtype)) + self.label(y)
+        # the residual stream stays in the input's dtype (fp32 under autocast, as in experiments/dit.py:72-75):
+        # the fused block kernels read and write it as stored
         x = self.input(x).flatten(2).transpose(1, 2) + self.position.to(x.dtype)
-        if torch.is_autocast_enabled(x.device.type):
-            c = c.to(torch.get_autocast_dtype(x.device.type))
-            x = x.to(torch.get_autocast_dtype(x.device.type))
         for block in self.blocks:
             x = block(x, c)
         shift, scale = self.final_ada(c).chunk(2, -1)

@@ -3,6 +3,6 @@
 from .linear import Linear
 from .mlp import MLP
 from .grouped import GroupedLinear
-from .fused import activation_linear, norm_modulate_linear
+from .fused import activation_linear, gated_residual, norm_modulate_linear
 
-__all__ = ["Linear", "MLP", "GroupedLinear", "norm_modulate_linear", "activation_linear"]
+__all__ = ["Linear", "MLP", "GroupedLinear", "gated_residual", "norm_modulate_linear", "activation_linear"]

@@ -7,8 +7,13 @@ the two passes a per-tensor scale needs anyway (row statistics + amax, then enco
 transposed), and LayerNorm + modulate have a single fused backward kernel.  The reference runs
 these as separate PyTorch kernels in front of ``viola.nn.Linear`` (experiments/dit.py:33-39).
 
-Both fall back to the unfused composition when the fast path does not apply (CPU tensors, non-bf16
-activations, group-scaled or rotated layers, non-FP8 saved inputs, very wide rows).
+``gated_residual(x, gate, y)`` is the other half of an adaLN block, ``x + gate[:, None] * y``, as one
+kernel forward and one backward (branch gradient and per-sample gate gradient from a single read).
+
+The residual stream ``x`` may be fp32 (what autocast leaves it as, experiments/dit.py:60-75) or bf16; it is
+read as stored, so no cast pass runs in front of the LayerNorm.  Everything falls back to the unfused
+composition when the fast path does not apply (CPU tensors, other dtypes, group-scaled or rotated layers,
+non-FP8 saved inputs, very wide rows).
 """
 
 from __future__ import annotations
@@ -22,8 +27,11 @@ from .. import ops
 from .linear import Linear, linear_backward, linear_forward
 
 
-def _eligible(layer, x, max_width=None):
-    return (isinstance(layer, Linear) and x.is_cuda and x.dtype == torch.bfloat16 and not layer._grouped_scaling
+_STREAM_DTYPES = (torch.float32, torch.bfloat16)
+
+
+def _eligible(layer, x, max_width=None, dtypes=(torch.bfloat16,)):
+    return (isinstance(layer, Linear) and x.is_cuda and x.dtype in dtypes and not layer._grouped_scaling
             and not layer.rotation_size and layer.saved_input_dtype == "fp8" and x.shape[-1] % 16 == 0
             and (max_width is None or x.shape[-1] <= max_width))
 
@@ -37,7 +45,6 @@ class _NormModulateLinear(torch.autograd.Function):
     def forward(ctx, x, shift, scale, weight, bias, layer, eps):
         batch, tokens, width = x.shape
         x2 = x.reshape(-1, width).contiguous()
-        shift, scale = shift.contiguous(), scale.contiguous()
         need_w, need_b = ctx.needs_input_grad[3], bias is not None and ctx.needs_input_grad[4]
         quantizer = layer.input_quantizer
         limit = layer._quantization_limit(max(x2.shape), layer.fp8_dtype)
@@ -48,7 +55,7 @@ class _NormModulateLinear(torch.autograd.Function):
         quantizer.index += 1
         encoded = SimpleNamespace(q=q, s=qscale, qt=qt, st=qscale)
         y, saved, _ = linear_forward(layer, x2, weight, bias, need_input_grad=True, need_weight_grad=need_w,
-                                     encoded=encoded)
+                                     encoded=encoded, out_dtype=torch.bfloat16)
         ctx.save_for_backward(x2, scale, mean, rstd)
         ctx.layer, ctx.saved, ctx.shape, ctx.need_b = layer, saved, x.shape, need_b
         ctx.mod_dtypes = (shift.dtype, scale.dtype)
@@ -98,12 +105,24 @@ class _ActivationLinear(torch.autograd.Function):
         return dz.view(ctx.shape), dw, db, None, None
 
 
+def _rows_of(vector, x):
+    """Is ``vector`` a bf16 [batch, width] per-sample row set the kernels can read in place (rows may be strided)?"""
+    return (vector.dim() == 2 and vector.dtype == torch.bfloat16 and vector.shape == (x.shape[0], x.shape[-1])
+            and vector.stride(1) == 1 and vector.stride(0) % 8 == 0 and vector.data_ptr() % 16 == 0)
+
+
 def norm_modulate_linear(x, shift, scale, layer, *, eps=1e-6):
     """``layer(LayerNorm(x) * (1 + scale[:, None]) + shift[:, None])`` for ``x`` [batch, tokens, width]."""
     if x.is_cuda and torch.is_autocast_enabled("cuda"):
         dtype = torch.get_autocast_dtype("cuda")
-        x, shift, scale = x.to(dtype), shift.to(dtype), scale.to(dtype)
-    if _eligible(layer, x, 2048) and x.dim() == 3 and torch.is_grad_enabled() and x.requires_grad:
+        shift, scale = shift.to(dtype), scale.to(dtype)
+        if (dtype == torch.bfloat16 and _eligible(layer, x, 2048, _STREAM_DTYPES) and x.dim() == 3 and _rows_of(shift, x)
+                and _rows_of(scale, x) and shift.stride(0) == scale.stride(0) and torch.is_grad_enabled()
+                and x.requires_grad):
+            return _NormModulateLinear.apply(x, shift, scale, layer.weight, layer.bias, layer, eps)
+        x = x.to(dtype)
+    elif (_eligible(layer, x, 2048) and x.dim() == 3 and _rows_of(shift, x) and _rows_of(scale, x)
+          and shift.stride(0) == scale.stride(0) and torch.is_grad_enabled() and x.requires_grad):
         return _NormModulateLinear.apply(x, shift, scale, layer.weight, layer.bias, layer, eps)
     normed = F.layer_norm(x, (x.shape[-1],), eps=eps)
     return layer(torch.addcmul(shift[:, None], normed, (1 + scale)[:, None]))
@@ -116,3 +135,30 @@ def activation_linear(z, layer, activation="gelu"):
     if _eligible(layer, z) and torch.is_grad_enabled() and z.requires_grad and z.shape[-1] % 16 == 0:
         return _ActivationLinear.apply(z, layer.weight, layer.bias, layer, activation)
     return layer(F.gelu(z, approximate="tanh") if activation == "gelu" else F.silu(z))
+
+
+class _GatedResidual(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gate, y):
+        batch, tokens, width = x.shape
+        y2 = y.reshape(-1, width).contiguous()
+        out = ops.gate_residual(x.reshape(-1, width).contiguous(), gate, y2, tokens)
+        ctx.save_for_backward(gate, y2)
+        ctx.shape = x.shape
+        return out.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dout):
+        gate, y2 = ctx.saved_tensors
+        batch, tokens, width = ctx.shape
+        dy, dgate = ops.gate_residual_backward(dout.reshape(-1, width).contiguous(), gate, y2, tokens)
+        return dout, dgate.to(gate.dtype), dy.view(ctx.shape)
+
+
+def gated_residual(x, gate, y):
+    """``x + gate[:, None] * y`` for ``x`` / ``y`` [batch, tokens, width] and a per-sample ``gate`` [batch, width]."""
+    if (x.is_cuda and x.dim() == 3 and x.dtype in _STREAM_DTYPES and y.dtype == torch.bfloat16 and y.shape == x.shape
+            and _rows_of(gate, x) and x.shape[-1] <= 2048 and x.shape[-1] % 8 == 0 and torch.is_grad_enabled()
+            and (x.requires_grad or y.requires_grad or gate.requires_grad)):
+        return _GatedResidual.apply(x, gate, y)
+    return torch.addcmul(x, gate[:, None], y)

@@ -141,12 +141,15 @@ def _weight_operands(layer, weight, *, need_transpose):
 # ------------------------------------------------------------------------------------------------
 # functional core, shared by Linear and the fused MLP
 # ------------------------------------------------------------------------------------------------
-def linear_forward(layer, x, weight, bias, *, need_input_grad, need_weight_grad, gated=None, encoded=None):
+def linear_forward(layer, x, weight, bias, *, need_input_grad, need_weight_grad, gated=None, encoded=None,
+                   out_dtype=None):
     """y = x W^T + b on 2-D ``x``.  Returns (y, saved, aux) where ``saved`` feeds :func:`linear_backward`.
 
     ``gated`` = activation name turns the GEMM into the fused gate/up epilogue (``aux`` = [g | u]);
-    ``encoded`` = already quantised input (q, s, qt, st) produced by a fused producer.
+    ``encoded`` = already quantised input (q, s, qt, st) produced by a fused producer; ``out_dtype`` = dtype
+    of y and of the input gradient when it differs from ``x.dtype`` (a fused producer reading an fp32 stream).
     """
+    out_dtype = out_dtype or x.dtype
     fmt = layer.fp8_dtype
     need_backward = need_input_grad or need_weight_grad
     save_fp8 = need_weight_grad and layer.saved_input_dtype == "fp8"
@@ -165,16 +168,16 @@ def linear_forward(layer, x, weight, bias, *, need_input_grad, need_weight_grad,
     aux = None
     if gated is not None:
         group = (gx, gw) if layer._grouped_scaling else None
-        y, aux = ops.gated_gemm_forward(qx.q, w.q, qx.s, w.s, activation=gated, out_dtype=x.dtype, bias=bias,
+        y, aux = ops.gated_gemm_forward(qx.q, w.q, qx.s, w.s, activation=gated, out_dtype=out_dtype, bias=bias,
                                         save=need_backward, group=group, sa_kmajor=True)
     elif layer._grouped_scaling:
-        y = ops.group_gemm(qx.q, w.q, qx.s, w.s, gx, gw, out_dtype=x.dtype, bias=bias, sa_kmajor=True)
+        y = ops.group_gemm(qx.q, w.q, qx.s, w.s, gx, gw, out_dtype=out_dtype, bias=bias, sa_kmajor=True)
     else:
-        y = ops.gemm(qx.q, w.q, qx.s, w.s, out_dtype=x.dtype, bias=bias)
+        y = ops.gemm(qx.q, w.q, qx.s, w.s, out_dtype=out_dtype, bias=bias)
     saved = None
     if need_backward:
         saved = SimpleNamespace(x=None, x_scale=None, x_is_fp8=save_fp8, input_scale=qx.s, weight=weight,
-                                weight_scale=w.s, wt=w.qt, wt_scale=w.st, limit=limit, x_dtype=x.dtype,
+                                weight_scale=w.s, wt=w.qt, wt_scale=w.st, limit=limit, x_dtype=out_dtype,
                                 in_place=in_place, wq=None,
                                 weight_grad_dtype=getattr(weight, "grad_dtype", None) or torch.float32,
                                 bias_grad_dtype=(getattr(bias, "grad_dtype", None) or bias.dtype) if bias is not None else None)

@@ -563,9 +563,10 @@ _MODES = {"ln_modulate": 1, "gelu": 2, "silu": 3}
 
 def ln_modulate_quantize(x, shift, scale, tokens, *, eps=1e-6, history=None, index=0, delayed=False,
                          fp8_dtype=torch.float8_e4m3fn, quantization_limit=None, transpose=False):
-    """FP8 codes of ``LN(x) * (1 + scale[b]) + shift[b]`` without materialising it (bf16 CUDA input).
+    """FP8 codes of ``LN(x) * (1 + scale[b]) + shift[b]`` without materialising it (CUDA only).
 
-    ``x`` [rows, cols], ``shift`` / ``scale`` [rows // tokens, cols].  Returns (q, qt or None, qscale, mean, rstd).
+    ``x`` [rows, cols] in fp32 or bf16 (the residual stream is read as stored), ``shift`` / ``scale`` bf16
+    [rows // tokens, cols] (row-strided views are fine).  Returns (q, qt or None, qscale, mean, rstd).
     """
     rows, cols = x.shape
     limit = _limit(fp8_dtype, quantization_limit)
@@ -597,7 +598,7 @@ def activation_quantize(z, activation, *, history=None, index=0, delayed=False, 
 
 
 def ln_modulate_backward(dh, x, mean, rstd, scale, tokens):
-    """Gradients of LN + modulate: returns (dx [rows, cols] bf16, dshift, dscale [samples, cols] fp32)."""
+    """Gradients of LN + modulate: returns (dx [rows, cols] in x's dtype, dshift, dscale [samples, cols] fp32)."""
     rows, cols = x.shape
     dx = torch.empty_like(x)
     dshift = torch.zeros((rows // tokens, cols), device=x.device, dtype=torch.float32)
@@ -605,6 +606,28 @@ def ln_modulate_backward(dh, x, mean, rstd, scale, tokens):
     _ops().ln_modulate_backward(dh, x, mean, rstd, scale, int(tokens), dx, dshift, dscale)
     _count()
     return dx, dshift, dscale
+
+
+def gate_residual(x, gate, y, tokens):
+    """``x + gate[row // tokens] * y`` for a 2-D residual stream ``x`` (fp32 or bf16) and bf16 ``y`` / ``gate``."""
+    if not x.is_cuda:
+        return reference.gate_residual(x, gate, y, tokens)
+    out = torch.empty_like(x)
+    _ops().gate_residual(x, gate, y, int(tokens), out)
+    _count()
+    return out
+
+
+def gate_residual_backward(dout, gate, y, tokens):
+    """Branch gradients of the gated residual: (dy bf16 [rows, cols], dgate fp32 [samples, cols])."""
+    if not dout.is_cuda:
+        return reference.gate_residual_backward(dout, gate, y, tokens)
+    rows, cols = dout.shape
+    dy = torch.empty((rows, cols), device=dout.device, dtype=torch.bfloat16)
+    dgate = torch.zeros((rows // tokens, cols), device=dout.device, dtype=torch.float32)
+    _ops().gate_residual_backward(dout, gate, y, int(tokens), dy, dgate)
+    _count()
+    return dy, dgate
 
 
 # ------------------------------------------------------------------------------ multi-tensor optimizer ops

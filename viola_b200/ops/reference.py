@@ -434,3 +434,18 @@ def wire_unpack(packet, out, tile_size, fp8_dtype, *, reduce=False, accumulate=F
         out.view(-1).add_(flat)
     else:
         out.view(-1).copy_(flat)
+
+
+def gate_residual(x, gate, y, tokens):
+    """x + gate[row // tokens] * y (fp32 arithmetic, result in x's dtype)."""
+    g = gate.float().repeat_interleave(tokens, dim=0)
+    return torch.addcmul(x.float(), g, y.float()).to(x.dtype)
+
+
+def gate_residual_backward(dout, gate, y, tokens):
+    """(dy, dgate) of the gated residual's branch: dy = dout * gate in bf16, dgate = per-sample sums of dout * y."""
+    rows, cols = dout.shape
+    g = gate.float().repeat_interleave(tokens, dim=0)
+    dy = (dout.float() * g).to(torch.bfloat16)
+    dgate = (dout.float() * y.float()).view(rows // tokens, tokens, cols).sum(dim=1)
+    return dy, dgate

@@ -24,7 +24,8 @@ E4M3 = torch.float8_e4m3fn
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--case", required=True,
-                        choices=("gemm_fp8", "gemm_group", "gemm_ns", "quantize", "group_quantize", "momentum", "gated"))
+                        choices=("gemm_fp8", "gemm_group", "gemm_ns", "gemm_ns_apply", "gemm_act_bwd", "quantize",
+                                 "group_quantize", "momentum", "gated"))
     parser.add_argument("--launches", type=int, default=4)
     args = parser.parse_args()
     device = torch.device("cuda")
@@ -53,6 +54,21 @@ def main():
     elif args.case == "gemm_ns":
         x = (torch.randn(28, 1152, 4608, device=device) / 68).bfloat16()
         run = lambda: ops.ns_gemm(x, x, symmetric=True)
+    elif args.case == "gemm_ns_apply":
+        # the third product of a Newton-Schulz step: X' = 3.4445 X + P X for a stack of wide matrices
+        x = (torch.randn(14, 1152, 3456, device=device) / 59).bfloat16()
+        p = (torch.randn(14, 1152, 1152, device=device) / 34).bfloat16()
+        out = torch.empty_like(x)
+        run = lambda: ops.ns_gemm(p, x, alpha=1.0, beta=3.4445, resid=x, out=out, b_mn=True)
+    elif args.case == "gemm_act_bwd":
+        # fc2 dgrad with the activation slope in the epilogue: dZ = (dY W) * act'(z)
+        rows = 16384
+        dy = torch.randn(rows, 1152, device=device).to(torch.float8_e5m2)
+        w = (torch.randn(1152, 4608, device=device) * 0.03).to(E4M3)
+        slope = torch.rand(rows, 4608, device=device).bfloat16()
+        one = torch.ones(1, device=device)
+        amax = ops.amax_word(device)
+        run = lambda: ops.activation_backward_gemm(dy, w, one, one, slope, w_mn=True, amax_out=amax)
     elif args.case == "quantize":
         x = torch.randn(m, 4608, device=device, dtype=torch.bfloat16)
         scale = ops.tensor_scale(x)

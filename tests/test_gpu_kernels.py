@@ -50,6 +50,27 @@ def test_tensor_scale_and_quantize(shape, dtype):
         assert torch.equal(ops.transpose(q).cpu().view(torch.uint8), rqt.view(torch.uint8))
 
 
+@pytest.mark.parametrize("shape", [(300, 256), (4096, 1152), (1000, 4608), (33, 16)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+def test_quantize_rows_with_column_sums(shape, dtype):
+    """Row-wise-only path (16-byte vectors, reciprocal + exact correction instead of a division) gives the same
+    codes as the division oracle, and the fused column sums equal the plain reduction."""
+    torch.manual_seed(7)
+    x = (torch.randn(shape, device=dev()) * 5).to(dtype)
+    x[1, 3], x[2, 5] = float("inf"), float("nan")
+    for fmt, limit in ((E4M3, None), (E5M2, None), (E4M3, 240.0)):
+        scale = ops.tensor_scale(torch.nan_to_num(x, posinf=0.0), fp8_dtype=fmt, quantization_limit=limit)
+        colsum = torch.zeros(shape[1], device=dev())
+        q, _ = ops.quantize(x, scale, fp8_dtype=fmt, quantization_limit=limit, colsum=colsum)
+        rq, _ = ref.quantize(x.cpu(), scale.cpu(), fp8_dtype=fmt, quantization_limit=limit)
+        assert torch.equal(q.cpu().view(torch.uint8), rq.view(torch.uint8))
+        expected = torch.nan_to_num(x.float(), nan=0.0, posinf=0.0).sum(dim=0)
+        got = colsum.clone()
+        got[3] = got[5] = expected[3] = expected[5] = 0          # the inf / nan columns
+        assert rel_l2(got, expected) < 1e-5
+        assert torch.isinf(colsum[3]) and torch.isnan(colsum[5])
+
+
 def test_quantize_preserves_nan():
     x = torch.randn(64, 64, device=dev())
     x[3, 5] = float("nan")

@@ -306,3 +306,70 @@ def test_gated_residual_matches_addcmul(stream_dtype, width):
     assert torch.equal(results[0][1], results[1][1])
     assert rel_l2(results[0][2], results[1][2]) < 4e-3
     assert rel_l2(results[0][3], results[1][3]) < 1e-2
+
+
+@pytest.mark.parametrize("stream_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("activation", ["gelu", "silu"])
+def test_norm_modulate_mlp_matches_unfused(stream_dtype, activation):
+    from viola_b200.nn import norm_modulate_mlp
+    from torch.nn import functional as F
+    torch.manual_seed(0)
+    batch, tokens, width, hidden = 4, 160, 384, 1536
+    fc1, fc2 = Linear(width, hidden).cuda(), Linear(hidden, width).cuda()
+    x = torch.randn(batch, tokens, width, device="cuda", dtype=stream_dtype)
+    mod = (torch.randn(batch, 2 * width, device="cuda") * 0.3).bfloat16()
+    dy = torch.randn(batch, tokens, width, device="cuda", dtype=torch.bfloat16)
+    act = (lambda t: F.gelu(t, approximate="tanh")) if activation == "gelu" else F.silu
+    results = []
+    for fused in (True, False):
+        xs, ms = x.clone().requires_grad_(True), mod.clone().requires_grad_(True)
+        sh, sc = ms.chunk(2, dim=-1)
+        fc1.zero_grad(), fc2.zero_grad()
+        launches = ops.launch_count
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            if fused:
+                y = norm_modulate_mlp(xs, sh, sc, fc1, fc2, activation)
+                assert ops.launch_count - launches == 6
+            else:
+                h = torch.addcmul(sh[:, None], F.layer_norm(xs.float(), (width,), eps=1e-6), (1 + sc)[:, None])
+                y = fc2(act(fc1(h)))
+        launches = ops.launch_count
+        y.backward(dy)
+        if fused:
+            # amax dY, encode dY, dgrad(+act'), wgrad, scale of dZ, encode dZ, dgrad, wgrad, LayerNorm backward
+            assert ops.launch_count - launches == 9
+        results.append((y.detach(), xs.grad, ms.grad, fc1.weight.grad.clone(), fc1.bias.grad.clone(),
+                        fc2.weight.grad.clone(), fc2.bias.grad.clone()))
+    # two FP8 layers deep, and the fused GELU is not bit-identical to torch's: a one-ulp difference in the amax
+    # moves the per-tensor scale and with it many codes, so this bounds noise rather than demanding equality
+    for name, a, b in zip(("y", "dx", "dmod", "dw1", "db1", "dw2", "db2"), *results):
+        assert rel_l2(a, b) < 6e-2, (name, rel_l2(a, b))
+    ops.check_status()
+
+
+def test_activation_backward_gemm_and_gathered_scale():
+    from torch.nn import functional as F
+    torch.manual_seed(1)
+    m, n, k = 1000, 640, 384
+    dy = torch.randn(m, k, device="cuda").to(torch.float8_e5m2)
+    w = (torch.randn(k, n, device="cuda") * 0.1).to(torch.float8_e4m3fn)       # [out, in]: read MN-major
+    z = torch.randn(m, n, device="cuda", dtype=torch.bfloat16) * 2
+    sg, sw = torch.tensor([0.02], device="cuda"), torch.tensor([0.5], device="cuda")
+    for activation in ("gelu", "silu"):
+        # the forward quantiser hands back act'(z) next to the codes of act(z)
+        q, _, qscale, slope = ops.activation_quantize(z, activation, slope=True)
+        zf = z.float().requires_grad_(True)
+        act = F.gelu(zf, approximate="tanh") if activation == "gelu" else F.silu(zf)
+        expected_slope, = torch.autograd.grad(act.sum(), zf)
+        assert (slope.float() - expected_slope).abs().max() < 1e-2 and rel_l2(slope, expected_slope) < 3e-3
+        assert rel_l2(q.float() * qscale, act.detach()) < 4e-2
+        amax = ops.amax_word("cuda")
+        dz = ops.activation_backward_gemm(dy, w, sg, sw, slope, w_mn=True, amax_out=amax)
+        expected = ops.activation_backward_gemm(dy.cpu(), w.cpu(), sg.cpu(), sw.cpu(), slope.cpu(), w_mn=True)
+        assert rel_l2(dz.cpu(), expected) < 1e-5
+        assert amax.view(torch.float32).item() == dz.float().abs().max().item()
+        history = torch.zeros(4, device="cuda")
+        scale = ops.scale_from_amax(amax, history=history, index=0, fp8_dtype=torch.float8_e5m2)
+        torch.testing.assert_close(scale[0], dz.float().abs().max() / 57344, rtol=1e-6, atol=0)
+        assert amax.item() == 0 and history[0].item() == dz.float().abs().max().item()
+    ops.check_status()

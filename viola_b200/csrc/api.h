@@ -14,8 +14,14 @@ extern "C" {
 int vb_amax_scale(const void* x, long long n, int dtype, float* history, int history_len,
                   long long index, int delayed, float limit, float* scale_out, unsigned int* scratch,
                   cudaStream_t stream);
+// scale from an amax that a producer kernel gathered as float bits (see VbGemmDesc::amax_out); zeroes the word
+int vb_scale_from_amax(unsigned int* amax_bits, float* history, int history_len, long long index, int delayed,
+                       float limit, float* scale_out, cudaStream_t stream);
+// colsum (optional, row-wise output only, cols % 16 == 0): fp32 [cols], the column sums of x are ADDED to it, in a
+// fixed order (reproducible).  workspace: 1024 + ceil(rows / 256) * strips * 128 floats with strips =
+// ceil(cols / 128) <= 1024; its first 1024 words (tickets) must be zero on first use and are left zero.
 int vb_quantize(const void* x, int rows, int cols, int dtype, const float* scale, float limit, int fmt,
-                void* q, void* qt, cudaStream_t stream);
+                void* q, void* qt, float* colsum, float* workspace, long long workspace_floats, cudaStream_t stream);
 int vb_transpose_u8(const void* x, int rows, int cols, void* out, cudaStream_t stream);
 int vb_group_encode(const void* x, int rows, int cols, int dtype, int fmt, float limit, void* q, float* s,
                     int gr, int gc, long long s_row, long long s_col, void* qt, float* st, int tgr, int tgc,
@@ -26,7 +32,7 @@ int vb_group_decode(const void* q, const float* s, int rows, int cols, int fmt, 
 // ---- tcgen05 GEMM family -----------------------------------------------------
 // D[M, N] = A[M, K] . B[N, K]^T, both operands K-major (row-major with K contiguous).
 enum VbGemmKind { VB_KIND_F16 = 0, VB_KIND_F8 = 1 };
-enum VbEpilogue { VB_EPI_LINEAR = 0, VB_EPI_AXPBY = 1, VB_EPI_GATED_FWD = 2, VB_EPI_GATED_BWD = 3 };
+enum VbEpilogue { VB_EPI_LINEAR = 0, VB_EPI_AXPBY = 1, VB_EPI_GATED_FWD = 2, VB_EPI_GATED_BWD = 3, VB_EPI_ACT_BWD = 4 };
 enum VbActivation { VB_ACT_SILU = 0, VB_ACT_GELU = 1, VB_ACT_RELU = 2 };
 
 typedef struct VbGemmDesc {
@@ -54,7 +60,10 @@ typedef struct VbGemmDesc {
   int symmetric;         // 1: M == N, only tiles with n_tile >= m_tile are computed and mirrored
   // gated MLP
   int activation;        // VbActivation
-  void* aux; long long ldaux;   // [M, 2N] saved (gate | up) in out dtype (fwd: written, bwd: read)
+  void* aux; long long ldaux;   // [M, 2N] saved (gate | up) in out dtype (fwd: written, bwd: read);
+                                // VB_EPI_ACT_BWD: [M, N] activation slope act'(z) saved by the forward pass,
+                                // out = round(acc) * aux
+  unsigned int* amax_out;       // VB_EPI_ACT_BWD: atomicMax of |out| as float bits (caller zero-initialises)
   // expert GEMM: rows of A are grouped by expert; offsets[e]..offsets[e+1] (device, int32, E+1)
   const int* expert_offsets; int num_experts;
   int* tile_map;         // workspace int32[3 * (ceil(M/128) + E)] when expert_offsets != null
@@ -130,18 +139,26 @@ int vb_ln_stats_amax(const void* x, int x_dtype, int rows, int cols, float eps, 
                      unsigned int* scratch, cudaStream_t stream);
 int vb_act_amax(const void* z, long long n, int mode, float* history, int history_len, long long index,
                 int delayed, float limit, float* scale_out, unsigned int* scratch, cudaStream_t stream);
+// slope (optional, activation modes, row-wise output only): bf16 [rows, cols] that receives act'(x), which is all
+// the backward pass needs of x
 int vb_fused_quantize(const void* x, int x_dtype, int rows, int cols, int mode, const float* mean, const float* rstd,
                       const void* mod_shift, const void* mod_scale, long long mod_stride, int tokens,
-                      const float* scale, float limit, int fmt, void* q, void* qt, cudaStream_t stream);
+                      const float* scale, float limit, int fmt, void* q, void* qt, void* slope, cudaStream_t stream);
+// The per-sample column sums (dshift, dscale, dgate) are reproducible: blocks park their totals in `workspace`
+// (vb_row_block_count(rows, tokens) x (2 * cols | cols) floats) and the last block of a sample (tickets: one zeroed
+// word per sample, left zero) adds them in a fixed order; the outputs are written, not accumulated.
+int vb_row_block_count(int rows, int tokens);
 int vb_ln_modulate_backward(const void* dh, const void* x, int x_dtype, const float* mean, const float* rstd,
                             const void* mod_scale, long long mod_stride, int rows, int cols, int tokens, void* dx,
-                            float* dshift, float* dscale, cudaStream_t stream);
+                            float* dshift, float* dscale, float* workspace, long long workspace_floats,
+                            unsigned int* tickets, int ticket_count, cudaStream_t stream);
 // out = x + gate[row / tokens] * y (x, out: x_dtype; y, gate: bf16) and the branch side of its backward:
-// dy = dout * gate (bf16), dgate += per-sample column sums of dout * y (fp32, zero-initialised by the caller)
+// dy = dout * gate (bf16), dgate = per-sample column sums of dout * y (fp32)
 int vb_gate_residual(const void* x, int x_dtype, const void* gate, long long gate_stride, const void* y, int rows,
                      int cols, int tokens, void* out, cudaStream_t stream);
 int vb_gate_residual_backward(const void* dout, int dout_dtype, const void* gate, long long gate_stride, const void* y,
-                              int rows, int cols, int tokens, void* dy, float* dgate, cudaStream_t stream);
+                              int rows, int cols, int tokens, void* dy, float* dgate, float* workspace,
+                              long long workspace_floats, unsigned int* tickets, int ticket_count, cudaStream_t stream);
 
 // ---- Hadamard-64 rotation --------------------------------------------------------
 int vb_hadamard64(const void* x, int dtype, int rows, int cols, void* out, cudaStream_t stream);

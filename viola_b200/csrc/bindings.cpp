@@ -45,13 +45,27 @@ void amax_scale(const Tensor& x, const OptTensor& history, int64_t index, bool d
         "amax_scale");
 }
 
-void quantize(const Tensor& x, const Tensor& scale, double limit, const OptTensor& q, const OptTensor& qt, int64_t fmt) {
+void quantize(const Tensor& x, const Tensor& scale, double limit, const OptTensor& q, const OptTensor& qt, int64_t fmt,
+              const OptTensor& colsum, const OptTensor& workspace) {
   cuda_contig(x, "x");
   TORCH_CHECK(x.dim() == 2);
+  if (colsum.has_value() && colsum->defined())
+    TORCH_CHECK(colsum->scalar_type() == at::kFloat && colsum->is_contiguous() && colsum->numel() == x.size(1));
   c10::cuda::CUDAGuard guard(x.device());
   check(vb_quantize(x.data_ptr(), (int)x.size(0), (int)x.size(1), dtype_code(x), scale.data_ptr<float>(), (float)limit,
-                    (int)fmt, ptr(q), ptr(qt), stream()),
+                    (int)fmt, ptr(q), ptr(qt), (float*)ptr(colsum), (float*)ptr(workspace),
+                    workspace.has_value() && workspace->defined() ? workspace->numel() : 0, stream()),
         "quantize");
+}
+
+void scale_from_amax(Tensor amax_bits, const OptTensor& history, int64_t index, bool delayed, double limit,
+                     Tensor scale_out) {
+  TORCH_CHECK(amax_bits.is_cuda() && amax_bits.element_size() == 4 && scale_out.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(amax_bits.device());
+  check(vb_scale_from_amax((unsigned int*)amax_bits.data_ptr(), (float*)ptr(history),
+                           history.has_value() && history->defined() ? (int)history->numel() : 0, index, delayed,
+                           (float)limit, scale_out.data_ptr<float>(), stream()),
+        "scale_from_amax");
 }
 
 void transpose_u8(const Tensor& x, Tensor out) {
@@ -86,7 +100,7 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t epilogue, int64_
           const OptTensor& sb, at::IntArrayRef scale_layout, const OptTensor& bias, double alpha, double beta,
           const OptTensor& resid, const OptTensor& out_t, bool symmetric, int64_t activation, const OptTensor& aux,
           const OptTensor& expert_offsets, const OptTensor& tile_map, const OptTensor& status, int64_t force_bn,
-          int64_t batch, bool a_mn, bool b_mn) {
+          int64_t batch, bool a_mn, bool b_mn, const OptTensor& amax_out) {
   // a_mn: ``a`` holds A transposed, i.e. [batch * K, M]; b_mn: ``b`` holds B transposed, [batch * K, N]
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda());
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && out.stride(-1) == 1);
@@ -145,6 +159,8 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t epilogue, int64_
   d.out_t_batch_stride = batch > 1 && d.out_t ? out_t->stride(0) : 0;
   d.symmetric = symmetric;
   d.activation = (int)activation;
+  d.amax_out = (unsigned int*)ptr(amax_out);
+  if (d.amax_out) TORCH_CHECK(amax_out->element_size() == 4 && amax_out->numel() >= 1);
   d.aux = ptr(aux);
   d.ldaux = aux.has_value() && aux->defined() ? aux->stride(0) : 0;
   if (d.aux) TORCH_CHECK(aux->scalar_type() == out.scalar_type(), "aux dtype must match the output");
@@ -440,9 +456,11 @@ void act_amax(const Tensor& z, int64_t mode, const OptTensor& history, int64_t i
 
 void fused_quantize(const Tensor& x, int64_t mode, const OptTensor& mean, const OptTensor& rstd, const OptTensor& shift,
                     const OptTensor& scale, int64_t tokens, const Tensor& qscale, double limit, int64_t fmt,
-                    const OptTensor& q, const OptTensor& qt) {
+                    const OptTensor& q, const OptTensor& qt, const OptTensor& slope) {
   cuda_contig(x, "x");
   TORCH_CHECK(x.dim() == 2);
+  if (slope.has_value() && slope->defined())
+    TORCH_CHECK(slope->scalar_type() == at::kBFloat16 && slope->is_contiguous() && slope->sizes() == x.sizes());
   int64_t stride = 0;
   if (mode == 1) {
     TORCH_CHECK(shift.has_value() && scale.has_value() && mean.has_value() && rstd.has_value());
@@ -452,12 +470,12 @@ void fused_quantize(const Tensor& x, int64_t mode, const OptTensor& mean, const 
   c10::cuda::CUDAGuard guard(x.device());
   check(vb_fused_quantize(x.data_ptr(), stream_dtype(x, "x"), (int)x.size(0), (int)x.size(1), (int)mode,
                           (const float*)ptr(mean), (const float*)ptr(rstd), ptr(shift), ptr(scale), stride, (int)tokens,
-                          qscale.data_ptr<float>(), (float)limit, (int)fmt, ptr(q), ptr(qt), stream()),
+                          qscale.data_ptr<float>(), (float)limit, (int)fmt, ptr(q), ptr(qt), ptr(slope), stream()),
         "fused_quantize");
 }
 
 void ln_modulate_backward(const Tensor& dh, const Tensor& x, const Tensor& mean, const Tensor& rstd, const Tensor& scale,
-                          int64_t tokens, Tensor dx, Tensor dshift, Tensor dscale) {
+                          int64_t tokens, Tensor dx, Tensor dshift, Tensor dscale, Tensor workspace, Tensor tickets) {
   cuda_contig(dh, "dh");
   cuda_contig(x, "x");
   cuda_contig(dx, "dx");
@@ -467,9 +485,13 @@ void ln_modulate_backward(const Tensor& dh, const Tensor& x, const Tensor& mean,
   c10::cuda::CUDAGuard guard(x.device());
   check(vb_ln_modulate_backward(dh.data_ptr(), x.data_ptr(), stream_dtype(x, "x"), mean.data_ptr<float>(),
                                 rstd.data_ptr<float>(), scale.data_ptr(), stride, (int)x.size(0), (int)x.size(1),
-                                (int)tokens, dx.data_ptr(), dshift.data_ptr<float>(), dscale.data_ptr<float>(), stream()),
+                                (int)tokens, dx.data_ptr(), dshift.data_ptr<float>(), dscale.data_ptr<float>(),
+                                workspace.data_ptr<float>(), workspace.numel(), (unsigned int*)tickets.data_ptr(),
+                                (int)tickets.numel(), stream()),
         "ln_modulate_backward");
 }
+
+int64_t row_block_count(int64_t rows, int64_t tokens) { return vb_row_block_count((int)rows, (int)tokens); }
 
 void gate_residual(const Tensor& x, const Tensor& gate, const Tensor& y, int64_t tokens, Tensor out) {
   cuda_contig(x, "x");
@@ -485,7 +507,7 @@ void gate_residual(const Tensor& x, const Tensor& gate, const Tensor& y, int64_t
 }
 
 void gate_residual_backward(const Tensor& dout, const Tensor& gate, const Tensor& y, int64_t tokens, Tensor dy,
-                            Tensor dgate) {
+                            Tensor dgate, Tensor workspace, Tensor tickets) {
   cuda_contig(dout, "dout");
   cuda_contig(y, "y");
   cuda_contig(dy, "dy");
@@ -496,7 +518,8 @@ void gate_residual_backward(const Tensor& dout, const Tensor& gate, const Tensor
   c10::cuda::CUDAGuard guard(dout.device());
   check(vb_gate_residual_backward(dout.data_ptr(), stream_dtype(dout, "dout"), gate.data_ptr(), stride, y.data_ptr(),
                                   (int)dout.size(0), (int)dout.size(1), (int)tokens, dy.data_ptr(),
-                                  dgate.data_ptr<float>(), stream()),
+                                  dgate.data_ptr<float>(), workspace.data_ptr<float>(), workspace.numel(),
+                                  (unsigned int*)tickets.data_ptr(), (int)tickets.numel(), stream()),
         "gate_residual_backward");
 }
 
@@ -535,6 +558,7 @@ TORCH_LIBRARY(viola_b200, m) {
   m.def("amax_scale", &amax_scale);
   m.def("quantize", &quantize);
   m.def("transpose_u8", &transpose_u8);
+  m.def("scale_from_amax", &scale_from_amax);
   m.def("group_encode", &group_encode);
   m.def("group_decode", &group_decode);
   m.def("gemm", &gemm);
@@ -569,6 +593,7 @@ TORCH_LIBRARY(viola_b200, m) {
   m.def("act_amax", &act_amax);
   m.def("fused_quantize", &fused_quantize);
   m.def("ln_modulate_backward", &ln_modulate_backward);
+  m.def("row_block_count", &row_block_count);
   m.def("gate_residual", &gate_residual);
   m.def("gate_residual_backward", &gate_residual_backward);
 }

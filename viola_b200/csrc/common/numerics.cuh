@@ -37,6 +37,25 @@ __device__ __forceinline__ float scaled_clamp(float v, float inv_or_scale_div, f
   return (q != q) ? q : fminf(fmaxf(q, -limit), limit);
 }
 
+// v / scale for many v and one scale: a reciprocal computed once, then per element one multiply and one
+// Newton correction whose residual is exact under FMA; the quotient is the correctly rounded one (what the
+// division instruction sequence computes), at three instructions instead of a dozen.  +-inf and NaN pass through.
+struct Divisor {
+  float scale, inv;
+};
+__device__ __forceinline__ Divisor make_divisor(float scale) { return Divisor{scale, __frcp_rn(scale)}; }
+__device__ __forceinline__ float divide(float v, const Divisor& d) {
+  const float q = v * d.inv;
+  const float r = fmaf(-q, d.scale, v);
+  return fabsf(q) <= 3.0e38f ? fmaf(r, d.inv, q) : q;
+}
+// clamp(v / scale, +-limit) with NaN preserved; `clamp` is false when the limit is the format's largest finite
+// value, which the saturating conversion enforces by itself.
+__device__ __forceinline__ float scaled_clamp(float v, const Divisor& d, float limit, bool clamp) {
+  const float q = divide(v, d);
+  return (!clamp || q != q) ? q : fminf(fmaxf(q, -limit), limit);
+}
+
 __host__ __device__ __forceinline__ uint32_t mulhi32(uint32_t a, uint32_t b) {
 #ifdef __CUDA_ARCH__
   return __umulhi(a, b);

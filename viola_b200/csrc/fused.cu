@@ -29,6 +29,18 @@ __device__ __forceinline__ float gelu_tanh(float g) {
   const float u2 = 1.5957691216057308f * (g + 0.044715f * g * g * g);
   return __fdividef(g, 1.f + __expf(-u2));
 }
+// act(v) and act'(v) from one exponential.  GELU: with s = sigmoid(2u), 1 - tanh^2 u = 4 s (1 - s).
+__device__ __forceinline__ float apply_act_with_slope(float v, int mode, float& slope) {
+  if (mode == kModeGelu) {
+    const float v2 = v * v;
+    const float s = __fdividef(1.f, 1.f + __expf(-1.5957691216057308f * v * fmaf(0.044715f, v2, 1.f)));
+    slope = fmaf(1.5957691216057308f * v * s * (1.f - s), fmaf(0.134145f, v2, 1.f), s);
+    return v * s;
+  }
+  const float s = __fdividef(1.f, 1.f + __expf(-v));
+  slope = s * fmaf(v, 1.f - s, 1.f);
+  return v * s;
+}
 __device__ __forceinline__ float apply_act(float v, int mode) {
   if (mode == kModeGelu) return gelu_tanh(v);
   if (mode == kModeSilu) return __fdividef(v, 1.f + __expf(-v));
@@ -205,8 +217,10 @@ __device__ __forceinline__ float fused_value(float v, int r, int c, int cols, co
 template <typename T>
 __global__ void __launch_bounds__(256)
 fused_quantize_rows_kernel(const T* __restrict__ x, int rows, int cols, FusedArgs fa,
-                           const float* __restrict__ scale_ptr, float limit, int fmt, uint8_t* __restrict__ q) {
-  const float scale = scale_ptr[0];
+                           const float* __restrict__ scale_ptr, float limit, int fmt, uint8_t* __restrict__ q,
+                           __nv_bfloat16* __restrict__ slope_out) {
+  const Divisor scale = make_divisor(scale_ptr[0]);
+  const bool clamp = limit < fp8_max(fmt);
   const int per_row = cols >> 4;
   const long long total = (long long)rows * per_row;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -226,6 +240,14 @@ fused_quantize_rows_kernel(const T* __restrict__ x, int rows, int cols, FusedArg
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[j][e] = round_bf16(fmaf((v[j][e] - mu) * rs, 1.f + sc[e], sh[e]));
       }
+    } else if (slope_out != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        float slope[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[j][e] = round_bf16(apply_act_with_slope(v[j][e], fa.mode, slope[e]));
+        store8(slope_out + (long long)r * cols + c + 8 * j, slope);
+      }
     } else {
 #pragma unroll
       for (int j = 0; j < 2; ++j)
@@ -238,7 +260,8 @@ fused_quantize_rows_kernel(const T* __restrict__ x, int rows, int cols, FusedArg
     for (int j = 0; j < 2; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e)
-        codes[j * 4 + e] = fp8_encode2(scaled_clamp(v[j][2 * e], scale, limit), scaled_clamp(v[j][2 * e + 1], scale, limit), fmt);
+        codes[j * 4 + e] = fp8_encode2(scaled_clamp(v[j][2 * e], scale, limit, clamp),
+                                       scaled_clamp(v[j][2 * e + 1], scale, limit, clamp), fmt);
     *reinterpret_cast<uint4*>(q + (long long)r * cols + c) = packed;
   }
 }
@@ -299,30 +322,66 @@ fused_quantize_kernel(const T* __restrict__ x, int rows, int cols, FusedArgs fa,
   }
 }
 
+// Reproducible per-sample column sums.  Every block of a sample stores its `width` column totals in `workspace`
+// (block-major); the last block of the sample to get here (ticket in `tickets[sample]`, left at zero) adds the
+// blocks in ascending order and writes the result, so the sums do not depend on scheduling and the outputs
+// need no zero-initialisation.  `partial` = [8 warps][width] shared-memory slices with element i of the totals
+// at `slot(i)`; `emit(i, total)` stores one finished column sum.
+template <typename Slot, typename Emit>
+__device__ __forceinline__ void ordered_sample_sums(const float* partial, int width, int sample, int blocks_per_sample,
+                                                    float* __restrict__ workspace, unsigned int* __restrict__ tickets,
+                                                    Slot slot, Emit emit) {
+  __shared__ bool last_block;
+  float* mine = workspace + (long long)blockIdx.x * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += partial[(size_t)w * width + slot(i)];
+    mine[i] = total;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    last_block = atomicAdd(&tickets[sample], 1u) == (unsigned)blocks_per_sample - 1;
+    if (last_block) tickets[sample] = 0u;
+  }
+  __syncthreads();
+  if (!last_block) return;
+  __threadfence();
+  const float* first = workspace + (long long)sample * blocks_per_sample * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float total = 0.f;
+    for (int b = 0; b < blocks_per_sample; ++b) total += __ldcg(first + (long long)b * width + i);
+    emit(i, total);
+  }
+}
+
 // Backward of h = LN(x) * (1 + scale[b]) + shift[b] for one warp per row:
 //   dx     = rstd * (g - mean(g) - xhat * mean(g * xhat)),  g = dh * (1 + scale[b])
-//   dshift[b] += dh,  dscale[b] += dh * xhat        (fp32 atomics into zero-initialised [samples, cols])
-// A block walks `rows_per_block` consecutive rows of ONE sample and reduces dshift / dscale in shared
-// memory first, so the global atomics are one per (block, column).  dx has the dtype of x.
+//   dshift[b] = sum dh,  dscale[b] = sum dh * xhat     (fp32 [samples, cols], reproducible, see above)
+// A block walks `rows_per_block` consecutive rows of ONE sample.  Each warp keeps its running column sums in
+// its own shared-memory slice (element e of chunk c at e * chunks + c, so a warp's accesses are conflict
+// free) rather than in registers: that halves the register count and lets two blocks share an SM, which is
+// what a latency-bound streaming kernel needs.  dx has the dtype of x.
 template <typename T, int VPL>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 ln_modulate_backward_kernel(const __nv_bfloat16* __restrict__ dh, const T* __restrict__ x,
                             const float* __restrict__ mean, const float* __restrict__ rstd,
                             const __nv_bfloat16* __restrict__ mod_scale, long long mod_stride, int rows, int cols,
                             int tokens, int rows_per_block, T* __restrict__ dx, float* __restrict__ dshift,
-                            float* __restrict__ dscale) {
-  extern __shared__ float partial[];            // [8 warps][2][cols], element e of chunk c at e * chunks + c
+                            float* __restrict__ dscale, float* __restrict__ workspace,
+                            unsigned int* __restrict__ tickets) {
+  extern __shared__ float partial[];            // [8 warps][2][cols]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int chunks = cols >> 3;
   const int blocks_per_sample = (tokens + rows_per_block - 1) / rows_per_block;
   const int sample = blockIdx.x / blocks_per_sample;
   const int first = sample * tokens + (blockIdx.x % blocks_per_sample) * rows_per_block;
   const int last = min(min(first + rows_per_block, (sample + 1) * tokens), rows);
-  float acc_shift[VPL][8], acc_scale[VPL][8];
-#pragma unroll
-  for (int j = 0; j < VPL; ++j)
-#pragma unroll
-    for (int e = 0; e < 8; ++e) acc_shift[j][e] = acc_scale[j][e] = 0.f;
+  float* my_shift = partial + (size_t)warp * 2 * cols;
+  float* my_scale = my_shift + cols;
+  for (int i = lane; i < 2 * cols; i += 32) my_shift[i] = 0.f;
+  __syncwarp();
   const __nv_bfloat16* gain_row = mod_scale + (long long)sample * mod_stride;
   for (int row = first + warp; row < last; row += 8) {
     const long long base = (long long)row * cols;
@@ -336,13 +395,13 @@ ln_modulate_backward_kernel(const __nv_bfloat16* __restrict__ dh, const T* __res
         float d[8], gain[8];
         load8(dh + base + chunk * 8, d);
         load8(x + base + chunk * 8, xh[j]);
-        load8(gain_row + chunk * 8, gain);      // re-read per row (L1 resident) instead of living in registers
+        load8(gain_row + chunk * 8, gain);      // L1 resident
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           xh[j][e] = (xh[j][e] - mu) * rs;
           g[j][e] = d[e] * (1.f + gain[e]);
-          acc_shift[j][e] += d[e];
-          acc_scale[j][e] += d[e] * xh[j][e];
+          my_shift[e * chunks + chunk] += d[e];
+          my_scale[e * chunks + chunk] += d[e] * xh[j][e];
           sum_g += g[j][e];
           sum_gx += g[j][e] * xh[j][e];
         }
@@ -365,28 +424,13 @@ ln_modulate_backward_kernel(const __nv_bfloat16* __restrict__ dh, const T* __res
       }
     }
   }
-  float* mine = partial + (size_t)warp * 2 * cols;
-#pragma unroll
-  for (int j = 0; j < VPL; ++j) {
-    const int chunk = lane + 32 * j;
-    if (chunk < chunks) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        mine[e * chunks + chunk] = acc_shift[j][e];            // consecutive lanes -> consecutive banks
-        mine[cols + e * chunks + chunk] = acc_scale[j][e];
-      }
-    }
-  }
   __syncthreads();
   const long long mod = (long long)sample * cols;
-  for (int i = threadIdx.x; i < 2 * cols; i += blockDim.x) {
-    float total = 0.f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) total += partial[(size_t)w * 2 * cols + i];
-    const int which = i >= cols, k = i - which * cols;
-    const int c = (k % chunks) * 8 + k / chunks;
-    atomicAdd((which ? dscale : dshift) + mod + c, total);
-  }
+  // totals are indexed [shift columns | scale columns]; column c lives at slice position (c % 8) * chunks + c / 8
+  ordered_sample_sums(
+      partial, 2 * cols, sample, blocks_per_sample, workspace, tickets,
+      [=](int i) { const int which = i >= cols, c = i - which * cols; return which * cols + (c & 7) * chunks + (c >> 3); },
+      [=](int i, float total) { (i >= cols ? dscale + mod - cols : dshift + mod)[i] = total; });
 }
 
 // out = x + gate[b] * y: x / out in T (the residual stream), y and gate in bf16; 8 elements per thread.
@@ -409,14 +453,14 @@ gate_residual_kernel(const T* __restrict__ x, const __nv_bfloat16* __restrict__ 
   }
 }
 
-// Backward of the gated residual for the branch: dy = dout * gate[b] (bf16), dgate[b] += sum over the
-// sample's rows of dout * y (fp32 atomics into a zero-initialised [samples, cols]).  Same block shape as the
-// LayerNorm backward: a block owns rows of one sample and reduces in shared memory first.
+// Backward of the gated residual for the branch: dy = dout * gate[b] (bf16), dgate[b] = sum over the sample's
+// rows of dout * y (fp32 [samples, cols], reproducible).  Same block shape as the LayerNorm backward.
 template <typename T, int VPL>
 __global__ void __launch_bounds__(256)
 gate_residual_backward_kernel(const T* __restrict__ dout, const __nv_bfloat16* __restrict__ gate, long long gate_stride,
                               const __nv_bfloat16* __restrict__ y, int rows, int cols, int tokens, int rows_per_block,
-                              __nv_bfloat16* __restrict__ dy, float* __restrict__ dgate) {
+                              __nv_bfloat16* __restrict__ dy, float* __restrict__ dgate, float* __restrict__ workspace,
+                              unsigned int* __restrict__ tickets) {
   extern __shared__ float partial[];            // [8 warps][cols], element e of chunk c at e * chunks + c
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int chunks = cols >> 3;
@@ -460,12 +504,10 @@ gate_residual_backward_kernel(const T* __restrict__ dout, const __nv_bfloat16* _
     }
   }
   __syncthreads();
-  for (int k = threadIdx.x; k < cols; k += blockDim.x) {
-    float total = 0.f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) total += partial[(size_t)w * cols + k];
-    atomicAdd(&dgate[(long long)sample * cols + (k % chunks) * 8 + k / chunks], total);
-  }
+  float* out_row = dgate + (long long)sample * cols;
+  ordered_sample_sums(
+      partial, cols, sample, blocks_per_sample, workspace, tickets,
+      [=](int c) { return (c & 7) * chunks + (c >> 3); }, [=](int c, float total) { out_row[c] = total; });
 }
 
 }  // namespace vb
@@ -537,15 +579,18 @@ extern "C" int vb_act_amax(const void* z, long long n, int mode, float* history,
 
 template <typename T>
 static int launch_fused_quantize(const T* x, int rows, int cols, const FusedArgs& fa, const float* scale, float limit,
-                                 int fmt, void* q, void* qt, cudaStream_t stream) {
+                                 int fmt, void* q, void* qt, void* slope, cudaStream_t stream) {
   const bool vector_ok = cols % 16 == 0 && aligned16(x) && aligned16(q) &&
                          (fa.mode != kModeLnModulate ||
                           (fa.mod_stride % 8 == 0 && aligned16(fa.mod_shift) && aligned16(fa.mod_scale)));
   if (qt == nullptr && q != nullptr && vector_ok) {
     const long long total = (long long)rows * (cols / 16);
     const int grid = (int)std::max<long long>(1, std::min<long long>((total + 255) / 256, 148LL * 16));
-    fused_quantize_rows_kernel<T><<<grid, 256, 0, stream>>>(x, rows, cols, fa, scale, limit, fmt, (uint8_t*)q);
+    if (slope != nullptr && (fa.mode == kModeLnModulate || !aligned16(slope))) return (int)cudaErrorInvalidValue;
+    fused_quantize_rows_kernel<T><<<grid, 256, 0, stream>>>(x, rows, cols, fa, scale, limit, fmt, (uint8_t*)q,
+                                                            (__nv_bfloat16*)slope);
   } else {
+    if (slope != nullptr) return (int)cudaErrorInvalidValue;
     if (cols % 8 != 0 || !aligned16(x)) return (int)cudaErrorInvalidValue;
     dim3 grid((cols + 63) / 64, (rows + 63) / 64);
     fused_quantize_kernel<T><<<grid, 256, 0, stream>>>(x, rows, cols, fa, scale, limit, fmt, (uint8_t*)q, (uint8_t*)qt);
@@ -555,19 +600,21 @@ static int launch_fused_quantize(const T* x, int rows, int cols, const FusedArgs
 
 extern "C" int vb_fused_quantize(const void* x, int x_dtype, int rows, int cols, int mode, const float* mean,
                                  const float* rstd, const void* mod_shift, const void* mod_scale, long long mod_stride,
-                                 int tokens, const float* scale, float limit, int fmt, void* q, void* qt,
+                                 int tokens, const float* scale, float limit, int fmt, void* q, void* qt, void* slope,
                                  cudaStream_t stream) {
   if (rows <= 0 || cols <= 0 || x_dtype > kBF16) return (int)cudaErrorInvalidValue;
   FusedArgs fa{mode, mean, rstd, (const __nv_bfloat16*)mod_shift, (const __nv_bfloat16*)mod_scale, mod_stride,
                tokens > 0 ? tokens : 1};
   if (x_dtype == kBF16)
-    return launch_fused_quantize((const __nv_bfloat16*)x, rows, cols, fa, scale, limit, fmt, q, qt, stream);
-  return launch_fused_quantize((const float*)x, rows, cols, fa, scale, limit, fmt, q, qt, stream);
+    return launch_fused_quantize((const __nv_bfloat16*)x, rows, cols, fa, scale, limit, fmt, q, qt, slope, stream);
+  return launch_fused_quantize((const float*)x, rows, cols, fa, scale, limit, fmt, q, qt, slope, stream);
 }
 
 extern "C" int vb_ln_modulate_backward(const void* dh, const void* x, int x_dtype, const float* mean, const float* rstd,
                                        const void* mod_scale, long long mod_stride, int rows, int cols, int tokens,
-                                       void* dx, float* dshift, float* dscale, cudaStream_t stream) {
+                                       void* dx, float* dshift, float* dscale, float* workspace,
+                                       long long workspace_floats, unsigned int* tickets, int ticket_count,
+                                       cudaStream_t stream) {
   if (rows <= 0 || cols <= 0 || tokens <= 0 || rows % tokens != 0 || cols % 8 != 0 || mod_stride % 8 != 0 ||
       x_dtype > kBF16 || !aligned16(dh) || !aligned16(x) || !aligned16(dx) || !aligned16(mod_scale))
     return (int)cudaErrorInvalidValue;
@@ -575,17 +622,27 @@ extern "C" int vb_ln_modulate_backward(const void* dh, const void* x, int x_dtyp
   const int blocks_per_sample = (tokens + rows_per_block - 1) / rows_per_block;
   const int grid = (rows / tokens) * blocks_per_sample;
   const size_t smem = 8 * 2 * (size_t)cols * sizeof(float);
+  if (workspace == nullptr || tickets == nullptr || workspace_floats < (long long)grid * 2 * cols || ticket_count < rows / tokens)
+    return (int)cudaErrorInvalidValue;
   const __nv_bfloat16* sc = (const __nv_bfloat16*)mod_scale;
   if (x_dtype == kBF16) {
     VB_VPL_SWITCH(cols, (allow_smem(ln_modulate_backward_kernel<__nv_bfloat16, VPL>), ln_modulate_backward_kernel<__nv_bfloat16, VPL><<<grid, 256, smem, stream>>>(
                             (const __nv_bfloat16*)dh, (const __nv_bfloat16*)x, mean, rstd, sc, mod_stride, rows, cols,
-                            tokens, rows_per_block, (__nv_bfloat16*)dx, dshift, dscale)));
+                            tokens, rows_per_block, (__nv_bfloat16*)dx, dshift, dscale, workspace, tickets)));
   } else {
     VB_VPL_SWITCH(cols, (allow_smem(ln_modulate_backward_kernel<float, VPL>), ln_modulate_backward_kernel<float, VPL><<<grid, 256, smem, stream>>>(
                             (const __nv_bfloat16*)dh, (const float*)x, mean, rstd, sc, mod_stride, rows, cols, tokens,
-                            rows_per_block, (float*)dx, dshift, dscale)));
+                            rows_per_block, (float*)dx, dshift, dscale, workspace, tickets)));
   }
   return (int)cudaGetLastError();
+}
+
+// number of blocks the two row-block backward kernels launch (the reduction workspace holds one row of column
+// totals per block)
+extern "C" int vb_row_block_count(int rows, int tokens) {
+  if (rows <= 0 || tokens <= 0 || rows % tokens != 0) return 0;
+  const int rows_per_block = pick_rows_per_block(rows, tokens);
+  return (rows / tokens) * ((tokens + rows_per_block - 1) / rows_per_block);
 }
 
 extern "C" int vb_gate_residual(const void* x, int x_dtype, const void* gate, long long gate_stride, const void* y,
@@ -607,7 +664,8 @@ extern "C" int vb_gate_residual(const void* x, int x_dtype, const void* gate, lo
 
 extern "C" int vb_gate_residual_backward(const void* dout, int dout_dtype, const void* gate, long long gate_stride,
                                          const void* y, int rows, int cols, int tokens, void* dy, float* dgate,
-                                         cudaStream_t stream) {
+                                         float* workspace, long long workspace_floats, unsigned int* tickets,
+                                         int ticket_count, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0 || tokens <= 0 || rows % tokens != 0 || cols % 8 != 0 || gate_stride % 8 != 0 ||
       dout_dtype > kBF16 || !aligned16(dout) || !aligned16(gate) || !aligned16(y) || !aligned16(dy))
     return (int)cudaErrorInvalidValue;
@@ -615,15 +673,17 @@ extern "C" int vb_gate_residual_backward(const void* dout, int dout_dtype, const
   const int blocks_per_sample = (tokens + rows_per_block - 1) / rows_per_block;
   const int grid = (rows / tokens) * blocks_per_sample;
   const size_t smem = 8 * (size_t)cols * sizeof(float);
+  if (workspace == nullptr || tickets == nullptr || workspace_floats < (long long)grid * cols || ticket_count < rows / tokens)
+    return (int)cudaErrorInvalidValue;
   const __nv_bfloat16* g = (const __nv_bfloat16*)gate;
   if (dout_dtype == kBF16) {
     VB_VPL_SWITCH(cols, (allow_smem(gate_residual_backward_kernel<__nv_bfloat16, VPL>), gate_residual_backward_kernel<__nv_bfloat16, VPL><<<grid, 256, smem, stream>>>(
                             (const __nv_bfloat16*)dout, g, gate_stride, (const __nv_bfloat16*)y, rows, cols, tokens,
-                            rows_per_block, (__nv_bfloat16*)dy, dgate)));
+                            rows_per_block, (__nv_bfloat16*)dy, dgate, workspace, tickets)));
   } else {
     VB_VPL_SWITCH(cols, (allow_smem(gate_residual_backward_kernel<float, VPL>), gate_residual_backward_kernel<float, VPL><<<grid, 256, smem, stream>>>(
                             (const float*)dout, g, gate_stride, (const __nv_bfloat16*)y, rows, cols, tokens, rows_per_block,
-                            (__nv_bfloat16*)dy, dgate)));
+                            (__nv_bfloat16*)dy, dgate, workspace, tickets)));
   }
   return (int)cudaGetLastError();
 }

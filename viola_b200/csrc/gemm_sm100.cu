@@ -34,7 +34,7 @@ namespace vb {
 
 constexpr int BM = 128;
 constexpr int BK_BYTES = 128;  // one 128-byte swizzle span along K per stage
-constexpr int kThreads = 192;
+constexpr int kThreads = 192;   // warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 epilogue (+ warp 6: slab loader)
 
 struct GemmArgs {
   int M, N, K;
@@ -64,7 +64,10 @@ struct GemmArgs {
   // batched mode: `batch` independent problems stacked along the rows of A, B and the outputs
   int batch, tiles_per_batch;
   long long b_rows_per_batch, out_bs, resid_bs, out_t_bs;
+  unsigned int* amax_out;
   int tma_store;        // LINEAR epilogue: stage in shared memory and write with TMA
+  int epi_stage;        // AXPBY residual / ACT_BWD slope arrives through the TMA slab ring
+  int epi_store;        // AXPBY / ACT_BWD result leaves through the slab ring (TMA store)
   int a_mn, b_mn;       // operand stored MN-major: A as [K, M] / B as [K, N] (row-major, MN contiguous)
   int* status;
 };
@@ -165,6 +168,82 @@ __device__ __forceinline__ void load_row32(const void* base, long long ld, int d
   for (int j = 0; j < 32; ++j) v[j] = (col0 + j < ncols) ? load_elem(base, off + j, dt) : 0.f;
 }
 
+// One row (32 16-bit columns = 64 bytes) of an epilogue slab: rows are 64 bytes apart and the 16-byte pieces of
+// a row sit at piece ^ ((row >> 1) & 3) (SWIZZLE_64B), which also spreads a warp's accesses over all banks.
+__device__ __forceinline__ uint4* slab_piece(uint8_t* slab, int row_in_tile, int piece) {
+  return reinterpret_cast<uint4*>(slab + row_in_tile * 64 + ((piece ^ ((row_in_tile >> 1) & 3)) << 4));
+}
+__device__ __forceinline__ void load_slab32(uint8_t* slab, int row_in_tile, int dt, float (&v)[32]) {
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const uint4 t = *slab_piece(slab, row_in_tile, p);
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float2 f;
+      if (dt == 1) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e]));
+      else f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+      v[8 * p + 2 * e] = f.x;
+      v[8 * p + 2 * e + 1] = f.y;
+    }
+  }
+}
+__device__ __forceinline__ void store_slab32(uint8_t* slab, int row_in_tile, int dt, const float (&v)[32]) {
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    uint4 t;
+    t.x = pack2(v[8 * p + 0], v[8 * p + 1], dt);
+    t.y = pack2(v[8 * p + 2], v[8 * p + 3], dt);
+    t.z = pack2(v[8 * p + 4], v[8 * p + 5], dt);
+    t.w = pack2(v[8 * p + 6], v[8 * p + 7], dt);
+    *slab_piece(slab, row_in_tile, p) = t;
+  }
+}
+
+// Lean in-place epilogue for one slab row (32 columns), specialised on the 16-bit type so no per-element dtype
+// branch survives: v = scaled accumulator; the slab holds the operand x (or nothing) and receives
+//   AXPBY  : round(alpha * round(v) + beta * x)
+//   ACT_BWD: round(round(v) * x), with max |result| tracked as float bits (NaN orders above +inf)
+template <int DT>
+__device__ __forceinline__ uint32_t pack_round2(float a, float b) {
+  if constexpr (DT == 1) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&t);
+  } else {
+    __half2 t = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&t);
+  }
+}
+template <int DT>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+  if constexpr (DT == 1) return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  else return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+template <int EPI, int DT>
+__device__ __forceinline__ void slab_row_epilogue(const float (&v)[32], uint8_t* slab, int row_in_tile, bool has_operand,
+                                                  float alpha, float beta, uint32_t& amax_bits) {
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    uint4* ptr = slab_piece(slab, row_in_tile, p);
+    const uint4 in = has_operand ? *ptr : make_uint4(0u, 0u, 0u, 0u);
+    const uint32_t w[4] = {in.x, in.y, in.z, in.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 d = unpack2<DT>(pack_round2<DT>(v[8 * p + 2 * e], v[8 * p + 2 * e + 1]));
+      const float2 x = unpack2<DT>(w[e]);
+      if constexpr (EPI == VB_EPI_AXPBY) {
+        o[e] = pack_round2<DT>(alpha * d.x + beta * x.x, alpha * d.y + beta * x.y);
+      } else {
+        o[e] = pack_round2<DT>(d.x * x.x, d.y * x.y);
+        const float2 f = unpack2<DT>(o[e]);
+        amax_bits = max(amax_bits, max(__float_as_uint(f.x) & 0x7fffffffu, __float_as_uint(f.y) & 0x7fffffffu));
+      }
+    }
+    *ptr = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 __device__ __forceinline__ float act_fn(float g, int act) {
   if (act == VB_ACT_SILU) return g / (1.f + __expf(-g));
   if (act == VB_ACT_RELU) return fmaxf(g, 0.f);
@@ -209,12 +288,22 @@ struct Config {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr bool kTmaStore = EPI == VB_EPI_LINEAR;   // epilogue staged in smem and written by TMA
   static constexpr int kStoreBytes = kTmaStore ? 4 * 2 * 4096 : 0;   // 4 warps x 2 buffers x (32 rows x 128 B)
+  // AXPBY and ACT_BWD epilogues (16-bit output, optional 16-bit [M, N] operand: the residual / the activation
+  // slope) run through a ring of 128-row x 32-column slabs in shared memory, one per output chunk: the
+  // producer warp TMA-loads the operand slab while the tile's MMAs run, each epilogue warp rewrites its 32
+  // rows of the slab in place with the result and TMA-stores them.  Plain loads issued after the accumulator
+  // wait would expose a memory round trip per chunk, and per-thread row stores write half sectors.
+  static constexpr bool kEpiSlab = (EPI == VB_EPI_AXPBY || EPI == VB_EPI_ACT_BWD) && !GROUP;
+  static constexpr int kEpiSlabs = 4;
+  static constexpr int kCtaThreads = kEpiSlab ? kThreads + 32 : kThreads;   // a seventh warp feeds the slab ring
+  static constexpr int kEpiSlabBytes = BM * 64;
+  static constexpr int kEpiBytes = kEpiSlab ? kEpiSlabs * kEpiSlabBytes : 0;
   static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? ((GROUP && kTmaStore) ? 5 : 6) : 8);
   static constexpr int kAcc = GROUP ? (512 / BN > 4 ? 4 : 512 / BN) : 2;
   static constexpr int kTmemCols = kAcc * BN;
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kSbStage = GROUP ? 4 * 2 * BN * (int)sizeof(float) : 0;  // per-warp staged B scales
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kSbStage + kStoreBytes + 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kSbStage + kStoreBytes + kEpiBytes + 1024;
   static_assert(kSmemBytes <= 232448, "dynamic shared memory limit of sm_100");
   static constexpr int kElemBytes = KIND == VB_KIND_F8 ? 1 : 2;
   static constexpr int kBK = BK_BYTES / kElemBytes;  // elements per K-block
@@ -225,9 +314,9 @@ struct Config {
 };
 
 template <int KIND, int BN, bool GROUP, int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__((Config<KIND, BN, GROUP, EPI>::kCtaThreads), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const __grid_constant__ CUtensorMap tmC, const GemmArgs args) {
+            const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD, const GemmArgs args) {
   using C = Config<KIND, BN, GROUP, EPI>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -237,12 +326,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint64_t* empty_bar = bars + C::kStages;           // [kStages]
   uint64_t* tmem_full = bars + 2 * C::kStages;       // [kAcc]
   uint64_t* tmem_empty = tmem_full + C::kAcc;        // [kAcc]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + C::kAcc);
+  uint64_t* epi_full = tmem_empty + C::kAcc;         // [kEpiSlabs]
+  uint64_t* epi_empty = epi_full + C::kEpiSlabs;     // [kEpiSlabs]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_empty + C::kEpiSlabs);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* sb_stage = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes + C::kBarrierBytes);
   // epilogue staging for TMA stores: the stage ring is a multiple of 1024 bytes and the barrier and
   // scale areas are 1024 / 4096 bytes, so this region keeps the 1024-byte alignment the swizzle needs
   uint8_t* store_stage = smem + C::kStages * C::kStageBytes + C::kBarrierBytes + C::kSbStage;
+  uint8_t* epi_stage = store_stage + C::kStoreBytes;   // epilogue slab ring (1024-byte aligned)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -255,6 +347,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     for (int i = 0; i < C::kAcc; ++i) {
       mbar_init(&tmem_full[i], 1);
       mbar_init(&tmem_empty[i], 4);
+    }
+    for (int i = 0; i < C::kEpiSlabs; ++i) {
+      mbar_init(&epi_full[i], 1);
+      mbar_init(&epi_empty[i], 4);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -375,6 +471,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1; }
       }
     }
+  } else if (warp == 6) {
+    // ------------------------------ slab loader --------------------------------
+    // Feeds the epilogue's operand slabs (AXPBY residual, ACT_BWD slope) on its own, so a full slab ring never
+    // holds back the main-loop producer; it runs up to kEpiSlabs chunks ahead of the epilogue.
+    if constexpr (C::kEpiSlab) {
+      if (args.epi_stage) {
+        int eslot = 0;
+        uint32_t ephase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
+          int mt, nt;
+          const int bi = t / args.tiles_per_batch;
+          tile_coords(args, t - bi * args.tiles_per_batch, mt, nt);
+          for (int c = 0; c < BN / 32 && nt * BN + c * 32 < args.N; ++c) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&epi_empty[eslot], ephase ^ 1, abort_flag, args.status, kTimeoutEmpty));
+            if (!ok) break;
+            if (lane == 0) {
+              mbar_expect_tx(&epi_full[eslot], C::kEpiSlabBytes);
+              tma_load_2d(epi_stage + eslot * C::kEpiSlabBytes, &tmC, &epi_full[eslot], nt * BN + c * 32,
+                          bi * args.M + mt * BM);
+            }
+            __syncwarp();
+            if (++eslot == C::kEpiSlabs) { eslot = 0; ephase ^= 1; }
+          }
+        }
+      }
+    }
   } else {
     // ------------------------------ epilogue ----------------------------------
     const int quad = warp & 3;            // TMEM lane quadrant this warp may read
@@ -382,6 +505,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    float out_amax = 0.f;                 // VB_EPI_ACT_BWD: running |out| maximum of this thread
+    uint32_t amax_bits = 0;               // ... and the same gathered as float bits by the slab path
+    int eslot = 0, prev_slot = -1;        // epilogue slab ring: position, phase, slot awaiting release
+    uint32_t ephase = 0;
     constexpr int NCHUNK = BN / 32;
     constexpr int NOUT = C::kGatedFwd ? NCHUNK / 2 : NCHUNK;  // output chunks per tile
     for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
@@ -474,7 +601,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
       const float alpha_pt = GROUP ? 1.f
                                    : (args.sa != nullptr ? args.sa[0] : 1.f) * (args.sb != nullptr ? args.sb[0] : 1.f);
-#pragma unroll
+#pragma unroll(C::kEpiSlab ? 1 : NOUT)
       for (int c = 0; c < NOUT; ++c) {
         float v[32];
         float v2[C::kGatedFwd ? 32 : 1];
@@ -500,7 +627,53 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         const int col0 = n0 + c * 32;
         const bool staged = C::kTmaStore && args.tma_store != 0;
-        if (col0 >= args.N && !staged) continue;  // warp-uniform
+        if (col0 >= args.N && !staged) continue;  // warp-uniform; the producer skips these chunks too
+        // slab ring: this chunk's slot holds the operand (once epi_full fires) and then the result
+        uint8_t* slab = nullptr;
+        if constexpr (C::kEpiSlab) {
+          if (args.epi_stage || args.epi_store) {
+            slab = epi_stage + eslot * C::kEpiSlabBytes;
+            if (args.epi_stage) {
+              ok = __all_sync(0xffffffffu, mbar_wait(&epi_full[eslot], ephase, abort_flag, args.status, kTimeoutFull));
+              if (!ok) break;
+            } else {
+              // result staging only: the slot was last used kEpiSlabs chunks ago by this warp's own store
+              if (lane == 0) tma_store_wait_read<C::kEpiSlabs - 1>();
+              __syncwarp();
+            }
+          }
+        }
+        // after the body: store the rewritten rows, then hand the PREVIOUS chunk's slot back to the producer
+        // (its store has had this chunk's time to finish reading shared memory)
+        auto finish_slab = [&]() {
+          if constexpr (C::kEpiSlab) {
+            if (slab == nullptr) return;
+            if (args.epi_store) {
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                if (mt * BM + quad * 32 < args.M)   // rows past M are clipped by the map; a warp wholly past it stores nothing
+                  tma_store_2d(&tmD, slab + quad * 32 * 64, col0, (int)(bi * args.M) + mt * BM + quad * 32);
+                tma_store_commit();
+              }
+            }
+            if (args.epi_stage) {
+              if (args.epi_store) {
+                if (prev_slot >= 0) {
+                  if (lane == 0) {
+                    tma_store_wait_read<1>();
+                    mbar_arrive(&epi_empty[prev_slot]);
+                  }
+                }
+                prev_slot = eslot;
+              } else {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&epi_empty[eslot]);
+              }
+            }
+            if (++eslot == C::kEpiSlabs) { eslot = 0; ephase ^= 1; }
+          }
+        };
         if constexpr (EPI == VB_EPI_LINEAR) {
           if (args.bias != nullptr) {
 #pragma unroll
@@ -551,8 +724,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
           }
         } else if constexpr (EPI == VB_EPI_AXPBY) {
+          if (slab != nullptr && args.epi_store && (args.epi_stage || resid_base == nullptr)) {
+            uint32_t unused = 0;
+            if (args.out_dtype == 1)
+              slab_row_epilogue<EPI, 1>(v, slab, row_in_tile, args.epi_stage != 0, args.alpha, args.beta, unused);
+            else
+              slab_row_epilogue<EPI, 2>(v, slab, row_in_tile, args.epi_stage != 0, args.alpha, args.beta, unused);
+            finish_slab();
+            continue;
+          }
           float res[32];
-          if (resid_base != nullptr && row_ok) load_row32(resid_base, args.ldr, args.out_dtype, grow, col0, args.N, res);
+          if (slab != nullptr && args.epi_stage) load_slab32(slab, row_in_tile, args.out_dtype, res);
+          else if (resid_base != nullptr && row_ok) load_row32(resid_base, args.ldr, args.out_dtype, grow, col0, args.N, res);
           else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) res[j] = 0.f;
@@ -560,7 +743,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             v[j] = round_to(args.alpha * round_to(v[j], args.out_dtype) + args.beta * res[j], args.out_dtype);
-          if (row_ok) store_row32(out_base, args.ldo, args.out_dtype, grow, col0, args.N, v);
+          if (slab != nullptr && args.epi_store) store_slab32(slab, row_in_tile, args.out_dtype, v);   // TMA clips
+          else if (row_ok) store_row32(out_base, args.ldo, args.out_dtype, grow, col0, args.N, v);
           void* tbase = out_t_base;
           long long tld = args.ldot;
           if (args.symmetric && mt != nt) { tbase = out_base; tld = args.ldo; }
@@ -599,6 +783,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               store_row32(up_base, args.ldaux, args.out_dtype, grow, col0, args.N, v2);
             }
           }
+        } else if constexpr (EPI == VB_EPI_ACT_BWD) {  // v = d; aux = act'(z) saved by the forward; out = d * aux, with its amax
+          if (slab != nullptr && args.epi_store && args.epi_stage) {
+            if (args.out_dtype == 1) slab_row_epilogue<EPI, 1>(v, slab, row_in_tile, true, 0.f, 0.f, amax_bits);
+            else slab_row_epilogue<EPI, 2>(v, slab, row_in_tile, true, 0.f, 0.f, amax_bits);
+            finish_slab();
+            continue;
+          }
+          {
+            float z[32], o[32];
+            if (slab != nullptr && args.epi_stage) load_slab32(slab, row_in_tile, args.out_dtype, z);
+            else if (row_ok) load_row32(args.aux, args.ldaux, args.out_dtype, grow, col0, args.N, z);
+            else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) z[j] = 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              o[j] = round_to(round_to(v[j], args.out_dtype) * z[j], args.out_dtype);
+              if (row_ok && col0 + j < args.N) out_amax = fmaxf(out_amax, (o[j] != o[j]) ? INFINITY : fabsf(o[j]));
+            }
+            if (slab != nullptr && args.epi_store) store_slab32(slab, row_in_tile, args.out_dtype, o);
+            else if (row_ok) store_row32(args.out, args.ldo, args.out_dtype, grow, col0, args.N, o);
+          }
         } else {  // VB_EPI_GATED_BWD: v = d; aux = [g | u]; out = [dG | dU]
           if (row_ok) {
             float g[32], u[32], dg[32], du[32];
@@ -619,6 +826,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             store_row32(out_up, args.ldo, args.out_dtype, grow, col0, args.N, du);
           }
         }
+        finish_slab();
       }
       if constexpr (!GROUP) {
         tc_fence_before_sync();
@@ -626,6 +834,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (lane == 0) mbar_arrive(&tmem_empty[acc]);
         if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1; }
       }
+    }
+    if constexpr (C::kEpiSlab) {
+      if (lane == 0) tma_store_wait_all();   // stores read this CTA's shared memory until they finish
+    }
+    if constexpr (EPI == VB_EPI_ACT_BWD) {
+      // non-negative floats order like their bit patterns (+inf, the stand-in for NaN, included)
+      uint32_t m = max(__float_as_uint(out_amax), min(amax_bits, 0x7f800000u));   // NaN counts as +inf
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+      if (lane == 0 && args.amax_out != nullptr) atomicMax(args.amax_out, m);
     }
   }
 
@@ -725,6 +943,22 @@ static int make_map_mn(CUtensorMap* map, const void* base, int kind, int fmt, lo
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+// Tensor map of a 16-bit [rows, cols] matrix moved in epilogue slabs: box = 32 columns (64 bytes) x box_rows rows,
+// 64B swizzle (128 rows for the operand load, 32 for one warp's result store).
+static int make_slab_map(CUtensorMap* map, const void* base, int dtype, long long rows, long long cols, long long ld_elems,
+                         int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return (int)cudaErrorNotSupported;
+  CUtensorMapDataType dt = dtype == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)(ld_elems * 2)};
+  cuuint32_t box[2] = {32, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
 // Output tensor map for the TMA-store epilogue: box = 128 bytes of columns x 32 rows, 128B swizzle.
 static int make_out_map(CUtensorMap* map, void* base, int out_dtype, long long rows, long long cols, long long ld_elems) {
   EncodeTiledFn fn = get_encode_fn();
@@ -784,6 +1018,7 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream) {
   a.sb_shift = d.sb_shift; a.k_shift = d.k_shift;
   a.out = d.out; a.out_dtype = d.out_dtype; a.ldo = d.ldo;
   a.bias = d.bias; a.bias_dtype = d.bias_dtype;
+  a.amax_out = d.amax_out;
   a.alpha = d.alpha; a.beta = d.beta; a.resid = d.resid; a.ldr = d.ldr;
   a.out_t = d.out_t; a.ldot = d.ldot; a.symmetric = d.symmetric;
   a.activation = d.activation; a.aux = d.aux; a.ldaux = d.ldaux;
@@ -808,6 +1043,21 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream) {
         make_out_map(&tmC, d.out, d.out_dtype, d.M, d.N, d.ldo) == 0)
       a.tma_store = 1;
   }
+  CUtensorMap tmD = tmA;
+  if constexpr (C::kEpiSlab) {
+    auto usable = [](const void* p, long long ld) { return p != nullptr && (reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld * 2) % 16 == 0; };
+    const void* src = EPI == VB_EPI_AXPBY ? d.resid : d.aux;
+    const long long ld = EPI == VB_EPI_AXPBY ? d.ldr : d.ldaux;
+    const long long bs = EPI == VB_EPI_AXPBY ? d.resid_batch_stride : 0;
+    // a stack is moved as one [batch * M, N] matrix: it must be dense, and whole tiles per matrix for the store
+    if (d.out_dtype != 0 && usable(src, ld) && (a.batch == 1 || bs == (long long)d.M * ld) &&
+        make_slab_map(&tmC, src, d.out_dtype, (long long)d.M * a.batch, d.N, ld, BM) == 0)
+      a.epi_stage = 1;
+    if (d.out_dtype != 0 && usable(d.out, d.ldo) && !d.symmetric && d.out_t == nullptr &&
+        (a.batch == 1 || (d.M % BM == 0 && d.out_batch_stride == (long long)d.M * d.ldo)) &&
+        make_slab_map(&tmD, d.out, d.out_dtype, (long long)d.M * a.batch, d.N, d.ldo, 32) == 0)
+      a.epi_store = 1;
+  }
   if (expert) {
     expert_tile_map_kernel<<<1, 32, 0, stream>>>(d.expert_offsets, d.num_experts, a.num_m_tiles, d.tile_map);
   }
@@ -819,7 +1069,7 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream) {
     configured = true;
   }
   const int grid = std::min(a.num_tiles, sm_count());
-  kernel<<<grid, kThreads, C::kSmemBytes, stream>>>(tmA, tmB, tmC, a);
+  kernel<<<grid, C::kCtaThreads, C::kSmemBytes, stream>>>(tmA, tmB, tmC, tmD, a);
   return (int)cudaGetLastError();
 }
 
@@ -856,6 +1106,10 @@ extern "C" int vb_gemm(const VbGemmDesc* desc, cudaStream_t stream) {
       case VB_EPI_GATED_BWD:
         if (group) { VB_LAUNCH(VB_KIND_F8, 128, true, VB_EPI_GATED_BWD); }
         VB_LAUNCH(VB_KIND_F8, 128, false, VB_EPI_GATED_BWD);
+      case VB_EPI_ACT_BWD:
+        if (group || d.aux == nullptr) return (int)cudaErrorInvalidValue;
+        if (bn == 256) { VB_LAUNCH(VB_KIND_F8, 256, false, VB_EPI_ACT_BWD); }
+        VB_LAUNCH(VB_KIND_F8, 128, false, VB_EPI_ACT_BWD);
       default:
         return (int)cudaErrorInvalidValue;
     }

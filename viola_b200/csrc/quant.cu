@@ -180,6 +180,74 @@ __global__ void __launch_bounds__(256) quantize_kernel(const typename Src<DT>::T
   }
 }
 
+// Row-wise codes only, optionally with the fp32 column sums of the source (the bias gradient when the source
+// is an output gradient).  A block walks a panel of `panel_rows` rows x 128 columns: thread t owns the 16
+// columns (t & 7) * 16 of rows (t >> 3) + 32 i and keeps 16 running sums.  Column sums are reproducible: every
+// block stores its panel's sums in `workspace`, and the last block to finish a 128-column strip (ticket in
+// the first 1024 words of the workspace, self-resetting) adds the panels in ascending order into
+// `colsum`.  Needs cols % 16 == 0 and 16-byte aligned x / q.
+template <int DT>
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const typename Src<DT>::T* __restrict__ x, int rows,
+                                                            int cols, const float* __restrict__ scale_ptr,
+                                                            float limit, int fmt, uint8_t* __restrict__ q,
+                                                            float* __restrict__ colsum, int panel_rows,
+                                                            float* __restrict__ workspace) {
+  constexpr int V = Src<DT>::kVec;
+  __shared__ float red[32][128 + 8];   // row pitch 136 floats: a warp's 4 rows x 8 groups land in 32 banks
+  const Divisor scale = make_divisor(scale_ptr[0]);
+  const bool clamp = limit < fp8_max(fmt);
+  const int group = threadIdx.x & 7, lane_row = threadIdx.x >> 3;
+  const int c = blockIdx.x * 128 + group * 16;
+  const int r_begin = blockIdx.y * panel_rows, r_end = min(rows, r_begin + panel_rows);
+  float sums[16];
+#pragma unroll
+  for (int e = 0; e < 16; ++e) sums[e] = 0.f;
+  if (c < cols) {
+    for (int r = r_begin + lane_row; r < r_end; r += 32) {
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16 / V; ++j) Src<DT>::load(x + (long long)r * cols + c + j * V, *reinterpret_cast<float(*)[V]>(&v[j * V]));
+      uint4 packed;
+      uint16_t* codes = reinterpret_cast<uint16_t*>(&packed);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        sums[2 * e] += v[2 * e];
+        sums[2 * e + 1] += v[2 * e + 1];
+        codes[e] = fp8_encode2(scaled_clamp(v[2 * e], scale, limit, clamp), scaled_clamp(v[2 * e + 1], scale, limit, clamp), fmt);
+      }
+      *reinterpret_cast<uint4*>(q + (long long)r * cols + c) = packed;
+    }
+  }
+  if (colsum == nullptr) return;
+#pragma unroll
+  for (int e = 0; e < 16; ++e) red[lane_row][e * 8 + group] = sums[e];
+  __syncthreads();
+  const int strip_cols = gridDim.x * 128;
+  unsigned int* tickets = reinterpret_cast<unsigned int*>(workspace);
+  float* partial = workspace + 1024;                            // [panels][strip_cols]
+  const int col = blockIdx.x * 128 + (threadIdx.x & 7) * 16 + (threadIdx.x >> 3);
+  if (threadIdx.x < 128) {
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) total += red[i][threadIdx.x];
+    partial[(long long)blockIdx.y * strip_cols + col] = total;
+  }
+  __shared__ bool last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    last = atomicAdd(&tickets[blockIdx.x], 1u) == gridDim.y - 1;
+    if (last) tickets[blockIdx.x] = 0u;
+  }
+  __syncthreads();
+  if (last && threadIdx.x < 128 && col < cols) {
+    __threadfence();
+    float total = 0.f;
+    for (int p = 0; p < (int)gridDim.y; ++p) total += __ldcg(&partial[(long long)p * strip_cols + col]);   // other blocks' stores: read at L2
+    colsum[col] += total;
+  }
+}
+
 __global__ void __launch_bounds__(256) transpose_u8_kernel(const uint8_t* __restrict__ x, int rows,
                                                            int cols, uint8_t* __restrict__ out) {
   __shared__ __align__(16) uint8_t tile[64][64 + 16];
@@ -414,8 +482,55 @@ extern "C" int vb_amax_scale(const void* x, long long n, int dtype, float* histo
   return (int)cudaGetLastError();
 }
 
+// amax (float bits gathered by a producer's epilogue with atomicMax) -> scale, with the delayed-scaling
+// history; re-zeroes the gather word for the next producer.
+__global__ void scale_from_amax_kernel(unsigned int* __restrict__ amax_bits, float* __restrict__ history,
+                                       int history_len, long long index, int delayed, float limit,
+                                       float* __restrict__ scale_out) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const float amax = __uint_as_float(amax_bits[0]);
+  amax_bits[0] = 0u;
+  float chosen = amax;
+  if (history != nullptr) {
+    if (delayed && index != 0) {
+      float old = 0.f;
+      for (int i = 0; i < history_len; ++i) old = fmaxf(old, history[i]);
+      chosen = old;
+    }
+    history[index % history_len] = amax;
+  }
+  scale_out[0] = fmaxf(chosen, 1e-30f) / limit;
+}
+
+extern "C" int vb_scale_from_amax(unsigned int* amax_bits, float* history, int history_len, long long index,
+                                  int delayed, float limit, float* scale_out, cudaStream_t stream) {
+  scale_from_amax_kernel<<<1, 32, 0, stream>>>(amax_bits, history, history_len, index, delayed, limit, scale_out);
+  return (int)cudaGetLastError();
+}
+
 extern "C" int vb_quantize(const void* x, int rows, int cols, int dtype, const float* scale, float limit,
-                           int fmt, void* q, void* qt, cudaStream_t stream) {
+                           int fmt, void* q, void* qt, float* colsum, float* workspace, long long workspace_floats,
+                           cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  const bool vector_ok = cols % 16 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                         (reinterpret_cast<uintptr_t>(q) & 15) == 0;
+  if (qt == nullptr && q != nullptr && vector_ok) {
+    // panels tall enough to amortise the column reduction, short enough to fill the machine
+    const int col_blocks = (cols + 127) / 128;
+    int panel_rows = 512;
+    while (panel_rows > 32 && (long long)col_blocks * ((rows + panel_rows - 1) / panel_rows) < 148LL * 8) panel_rows >>= 1;
+    if (colsum != nullptr) {
+      panel_rows = 256;   // fixed, so the caller can size the workspace: 1024 + panels * strips * 128 floats
+      const long long need = 1024 + (long long)((rows + 255) / 256) * col_blocks * 128;
+      if (workspace == nullptr || workspace_floats < need || col_blocks > 1024) return (int)cudaErrorInvalidValue;
+    }
+    dim3 grid(col_blocks, (rows + panel_rows - 1) / panel_rows);
+    VB_DISPATCH_DT(dtype, (quantize_rows_kernel<DT><<<grid, 256, 0, stream>>>(
+                              reinterpret_cast<const Src<DT>::T*>(x), rows, cols, scale, limit, fmt,
+                              reinterpret_cast<uint8_t*>(q), colsum, panel_rows, workspace)));
+    return (int)cudaGetLastError();
+  }
+  if (colsum != nullptr) return (int)cudaErrorInvalidValue;   // column sums ride on the row-wise path only
   dim3 grid((cols + 63) / 64, (rows + 63) / 64);
   VB_DISPATCH_DT(dtype, (quantize_kernel<DT><<<grid, 256, 0, stream>>>(
                             reinterpret_cast<const Src<DT>::T*>(x), rows, cols, scale, limit, fmt,

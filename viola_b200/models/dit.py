@@ -17,7 +17,7 @@ import torch
 from torch import nn
 from torch.nn import functional as F
 
-from ..nn import Linear, activation_linear, gated_residual, norm_modulate_linear
+from ..nn import Linear, gated_residual, norm_modulate_linear, norm_modulate_mlp
 from ..nn.attention import packed_attention
 
 
@@ -49,12 +49,12 @@ class Block(nn.Module):
     def forward(self, x, c):
         s1, a1, g1, s2, a2, g2 = self.ada(F.silu(c)).chunk(6, dim=-1)
         b, n, d = x.shape
-        # LayerNorm + modulate are folded into the FP8 quantiser of qkv / fc1, GELU into that of fc2
+        # LayerNorm + modulate are folded into the FP8 quantiser of qkv / fc1, GELU into that of fc2 (forward)
+        # and into the fc2 dgrad epilogue (backward)
         qkv = norm_modulate_linear(x, s1, a1, self.qkv, eps=self.norm1.eps)
         h = packed_attention(qkv.view(b, n, 3, self.heads, d // self.heads))
         x = gated_residual(x, g1, self.proj(h))
-        h = norm_modulate_linear(x, s2, a2, self.fc1, eps=self.norm2.eps)
-        return gated_residual(x, g2, activation_linear(h, self.fc2, "gelu"))
+        return gated_residual(x, g2, norm_modulate_mlp(x, s2, a2, self.fc1, self.fc2, "gelu", eps=self.norm2.eps))
 
 
 class DiT(nn.Module):

@@ -105,6 +105,73 @@ class _ActivationLinear(torch.autograd.Function):
         return dz.view(ctx.shape), dw, db, None, None
 
 
+class _NormModulateMLP(torch.autograd.Function):
+    """fc2(act(fc1(LN(x) * (1 + scale) + shift))) as one autograd node.
+
+    Forward: statistics + amax, encode, GEMM, activation amax, encode, GEMM (the normalised and the activated
+    tensors are never written; the second encode also emits act'(z), which replaces z as the saved tensor).
+    Backward: dY is encoded once (bias gradient from the same pass); the fc2 dgrad epilogue multiplies by the
+    saved slope and gathers the amax of dZ, so dZ is written once and read once (encode + bias gradient); then
+    both wgrads, the fc1 dgrad and the fused LayerNorm backward."""
+
+    @staticmethod
+    def forward(ctx, x, shift, scale, w1, b1, w2, b2, fc1, fc2, activation, eps):
+        batch, tokens, width = x.shape
+        x2 = x.reshape(-1, width).contiguous()
+        need = ctx.needs_input_grad
+        q1, limit1 = fc1.input_quantizer, fc1._quantization_limit(max(x2.shape), fc1.fp8_dtype)
+        q, _, qscale, mean, rstd = ops.ln_modulate_quantize(
+            x2, shift, scale, tokens, eps=eps, history=q1.history, index=q1.index, delayed=q1.scaling == "delayed",
+            fp8_dtype=fc1.fp8_dtype, quantization_limit=limit1)
+        q1.index += 1
+        z, saved1, _ = linear_forward(fc1, x2, w1, b1, need_input_grad=True, need_weight_grad=need[3],
+                                      encoded=SimpleNamespace(q=q, s=qscale, qt=None, st=qscale),
+                                      out_dtype=torch.bfloat16)
+        q2, limit2 = fc2.input_quantizer, fc2._quantization_limit(max(z.shape), fc2.fp8_dtype)
+        qa, _, ascale, slope = ops.activation_quantize(z, activation, history=q2.history, index=q2.index,
+                                                       delayed=q2.scaling == "delayed", fp8_dtype=fc2.fp8_dtype,
+                                                       quantization_limit=limit2, slope=True)
+        q2.index += 1
+        y, saved2, _ = linear_forward(fc2, z, w2, b2, need_input_grad=True, need_weight_grad=need[5],
+                                      encoded=SimpleNamespace(q=qa, s=ascale, qt=None, st=ascale))
+        ctx.save_for_backward(x2, scale, mean, rstd, slope)       # act'(z) stands in for z in the backward
+        ctx.layers, ctx.saved, ctx.shape = (fc1, fc2), (saved1, saved2), x.shape
+        ctx.need_bias = (b1 is not None and need[4], b2 is not None and need[6])
+        ctx.mod_dtypes = (shift.dtype, scale.dtype)
+        return y.reshape(batch, tokens, -1)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, scale, mean, rstd, slope = ctx.saved_tensors
+        fc1, fc2 = ctx.layers
+        saved1, saved2 = ctx.saved
+        need = ctx.needs_input_grad
+        dy2 = dy.reshape(-1, fc2.out_features).contiguous()
+        amax = ops.amax_word(dy2.device)
+        dz, dw2, db2 = linear_backward(fc2, saved2, dy2, need_input_grad=True, need_weight_grad=need[5],
+                                       need_bias_grad=ctx.need_bias[1], act=(slope, amax))
+        dh, dw1, db1 = linear_backward(fc1, saved1, dz, need_input_grad=True, need_weight_grad=need[3],
+                                       need_bias_grad=ctx.need_bias[0], grad_amax=amax)
+        del dz
+        dx, dshift, dscale = ops.ln_modulate_backward(dh, x2, mean, rstd, scale, ctx.shape[1])
+        return (dx.view(ctx.shape), dshift.to(ctx.mod_dtypes[0]), dscale.to(ctx.mod_dtypes[1]), dw1, db1, dw2, db2,
+                None, None, None, None)
+
+
+def norm_modulate_mlp(x, shift, scale, fc1, fc2, activation="gelu", *, eps=1e-6):
+    """``fc2(act(fc1(LayerNorm(x) * (1 + scale[:, None]) + shift[:, None])))`` for ``x`` [batch, tokens, width]."""
+    if (x.is_cuda and torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16
+            and x.dim() == 3 and torch.is_grad_enabled() and x.requires_grad
+            and _eligible(fc1, x, 2048, _STREAM_DTYPES) and fc1.in_place_operands
+            and isinstance(fc2, Linear) and fc2.in_place_operands and not fc2.rotation_size
+            and fc2.saved_input_dtype == "fp8"):
+        shift, scale = shift.to(torch.bfloat16), scale.to(torch.bfloat16)
+        if _rows_of(shift, x) and _rows_of(scale, x) and shift.stride(0) == scale.stride(0):
+            return _NormModulateMLP.apply(x, shift, scale, fc1.weight, fc1.bias, fc2.weight, fc2.bias, fc1, fc2,
+                                          activation, eps)
+    return activation_linear(norm_modulate_linear(x, shift, scale, fc1, eps=eps), fc2, activation)
+
+
 def _rows_of(vector, x):
     """Is ``vector`` a bf16 [batch, width] per-sample row set the kernels can read in place (rows may be strided)?"""
     return (vector.dim() == 2 and vector.dtype == torch.bfloat16 and vector.shape == (x.shape[0], x.shape[-1])

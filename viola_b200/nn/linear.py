@@ -47,6 +47,14 @@ class _Quantizer(nn.Module):
         self.index += 1
         return result
 
+    def scale_gathered(self, amax_bits, fp8_dtype=torch.float8_e4m3fn, quantization_limit=None):
+        """Same bookkeeping as :meth:`scale` for an amax that a producer kernel already gathered (float bits)."""
+        result = ops.scale_from_amax(amax_bits, history=self.history, index=self.index,
+                                     delayed=self.scaling == "delayed", fp8_dtype=fp8_dtype,
+                                     quantization_limit=quantization_limit)
+        self.index += 1
+        return result
+
     def get_extra_state(self):
         return {"index": self.index, "scaling": self.scaling}
 
@@ -66,8 +74,9 @@ def _pow2_scales(scale):
 # ------------------------------------------------------------------------------------------------
 # quantisation helpers (activation side)
 # ------------------------------------------------------------------------------------------------
-def _quantize_activation(layer, x, fmt, group, quantizer, limit, *, row, transposed, scale=None):
-    """Returns SimpleNamespace(q, s, qt, st).  Per-tensor recipes share one scale for both layouts."""
+def _quantize_activation(layer, x, fmt, group, quantizer, limit, *, row, transposed, scale=None, colsum=None):
+    """Returns SimpleNamespace(q, s, qt, st).  Per-tensor recipes share one scale for both layouts; ``colsum``
+    (per-tensor only) receives the fp32 column sums of ``x`` from the same pass."""
     result = SimpleNamespace(q=None, s=None, qt=None, st=None)
     if layer._grouped_scaling:
         if row and transposed:
@@ -84,7 +93,8 @@ def _quantize_activation(layer, x, fmt, group, quantizer, limit, *, row, transpo
         x = ops.hadamard64(x)
     if scale is None:
         scale = quantizer.scale(x, fmt, limit)
-    q, qt = ops.quantize(x, scale, rowwise=row, transpose=transposed, fp8_dtype=fmt, quantization_limit=limit)
+    q, qt = ops.quantize(x, scale, rowwise=row, transpose=transposed, fp8_dtype=fmt, quantization_limit=limit,
+                         colsum=colsum)
     result.q = q if row else None
     result.qt = qt if transposed else None
     result.s = result.st = scale
@@ -190,8 +200,15 @@ def linear_forward(layer, x, weight, bias, *, need_input_grad, need_weight_grad,
     return y, saved, aux
 
 
-def linear_backward(layer, saved, dy, *, need_input_grad, need_weight_grad, need_bias_grad, gated=None, aux=None):
-    """Returns (dx, dw, db).  ``gated``: dx becomes [dG | dU] through the fused derivative epilogue."""
+def linear_backward(layer, saved, dy, *, need_input_grad, need_weight_grad, need_bias_grad, gated=None, aux=None,
+                    act=None, grad_amax=None):
+    """Returns (dx, dw, db).  ``gated``: dx becomes [dG | dU] through the fused derivative epilogue.
+
+    Layers with :attr:`Linear.in_place_operands` additionally take ``act=(slope, amax_bits)``: the layer's input
+    was ``activation(z)`` with ``slope = activation'(z)``, and dx becomes the gradient of ``z`` straight from the
+    dgrad epilogue, its amax gathered into ``amax_bits``; and ``grad_amax`` = such a gathered amax of ``dy``
+    itself (skips the amax pass).
+    """
     fmt, bfmt = layer.fp8_dtype, layer.backward_fp8_dtype
     gg, gx, gw = layer.grad_group_shape, layer.input_group_shape, layer.weight_group_shape
     grouped = layer._grouped_scaling
@@ -201,7 +218,9 @@ def linear_backward(layer, saved, dy, *, need_input_grad, need_weight_grad, need
         limit = layer._quantization_limit(max(dy.shape), bfmt)
     dx = dw = db = None
     if saved.in_place:
-        return _backward_in_place(layer, saved, dy, limit, need_input_grad, need_weight_grad, need_bias_grad, gated, aux)
+        return _backward_in_place(layer, saved, dy, limit, need_input_grad, need_weight_grad, need_bias_grad, gated, aux,
+                                  act, grad_amax)
+    assert act is None and grad_amax is None, "fused activation backward needs in-place operands"
     # memory mode keeps one FP8 copy of dY alive at a time; fast mode encodes both layouts in one read
     both = need_input_grad and need_weight_grad and layer.mode == "fast"
     qg = _quantize_activation(layer_no_rotation(layer), dy, bfmt, gg, layer.grad_quantizer, limit,
@@ -249,13 +268,17 @@ def linear_backward(layer, saved, dy, *, need_input_grad, need_weight_grad, need
     return dx, dw, db
 
 
-def _backward_in_place(layer, saved, dy, limit, need_input_grad, need_weight_grad, need_bias_grad, gated, aux):
+def _backward_in_place(layer, saved, dy, limit, need_input_grad, need_weight_grad, need_bias_grad, gated, aux,
+                       act=None, grad_amax=None):
     """Per-tensor backward from row-wise codes only: dX = dY W reads W as an MN-major B operand, dW = dY^T X
     reads both dY and X MN-major."""
     fmt, bfmt = layer.fp8_dtype, layer.backward_fp8_dtype
     dx = dw = db = None
+    # the bias gradient (column sums of dY) comes out of the pass that encodes dY
+    db_sum = torch.zeros(dy.shape[1], device=dy.device, dtype=torch.float32) if need_bias_grad else None
+    grad_scale = layer.grad_quantizer.scale_gathered(grad_amax, bfmt, limit) if grad_amax is not None else None
     qg = _quantize_activation(layer_no_rotation(layer), dy, bfmt, None, layer.grad_quantizer, limit, row=True,
-                              transposed=False)
+                              transposed=False, colsum=db_sum, scale=grad_scale)
     if need_input_grad:
         wq = saved.wq
         if wq is None and layer.weight_dtype == "fp8":
@@ -264,7 +287,10 @@ def _backward_in_place(layer, saved, dy, limit, need_input_grad, need_weight_gra
             source = ops.hadamard64(saved.weight) if layer.rotation_size else saved.weight
             wq, _ = ops.quantize(source, saved.weight_scale, fp8_dtype=fmt,
                                  quantization_limit=layer._quantization_limit(max(source.shape), fmt))
-        if gated is not None and not layer.rotation_size:
+        if act is not None:
+            assert not layer.rotation_size and gated is None
+            dx = ops.activation_backward_gemm(qg.q, wq, qg.s, saved.weight_scale, act[0], w_mn=True, amax_out=act[1])
+        elif gated is not None and not layer.rotation_size:
             dx = ops.gated_gemm_backward(qg.q, wq, qg.s, saved.weight_scale, aux, activation=gated,
                                          out_dtype=saved.x_dtype, wt_mn=True)
         else:
@@ -285,7 +311,7 @@ def _backward_in_place(layer, saved, dy, limit, need_input_grad, need_weight_gra
         if layer.rotation_size:
             ops.hadamard64(dw, out=dw)
     if need_bias_grad:
-        db = dy.sum(dim=0, dtype=saved.bias_grad_dtype)
+        db = db_sum.to(saved.bias_grad_dtype)
     return dx, dw, db
 
 

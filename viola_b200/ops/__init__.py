@@ -28,7 +28,7 @@ _load_error = None
 FP8_DTYPES = (torch.float8_e4m3fn, torch.float8_e5m2)
 _FMT = {torch.float8_e4m3fn: 0, torch.float8_e5m2: 1}
 _ACT = {"silu": 0, "gelu": 1, "relu": 2}
-EPI_LINEAR, EPI_AXPBY, EPI_GATED_FWD, EPI_GATED_BWD = 0, 1, 2, 3
+EPI_LINEAR, EPI_AXPBY, EPI_GATED_FWD, EPI_GATED_BWD, EPI_ACT_BWD = 0, 1, 2, 3, 4
 _NO_GROUP = (0, 0, 0, 0, 0, 0, 0)
 
 launch_count = 0  # number of library kernels launched through this layer (bench bookkeeping)
@@ -77,6 +77,47 @@ def _amax_scratch(device):
     return buffer
 
 
+_amax_words = {}
+
+
+def amax_word(device):
+    """Per-(device, stream) uint32[1] that producer epilogues gather an amax into (float bits); the consumer
+    (:func:`scale_from_amax`) re-zeroes it, so one word serves every producer / consumer pair on a stream."""
+    key = (torch.device(device), torch.cuda.current_stream(device).cuda_stream if torch.device(device).type == "cuda" else 0)
+    word = _amax_words.get(key)
+    if word is None:
+        word = _amax_words[key] = torch.zeros(1, device=device, dtype=torch.int32)
+    return word
+
+
+_colsum_space = {}
+
+
+def _colsum_workspace(device, rows, cols):
+    """Per-(device, stream) fp32 scratch of the reproducible column-sum reduction (tickets + per-panel sums)."""
+    strips = (cols + 127) // 128
+    need = 1024 + ((rows + 255) // 256) * strips * 128
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    buffer = _colsum_space.get(key)
+    if buffer is None or buffer.numel() < need:
+        buffer = _colsum_space[key] = torch.zeros(max(need, 1 << 20), device=device, dtype=torch.float32)
+    return buffer
+
+
+_sum_space = {}
+
+
+def _sample_sum_workspace(device, rows, tokens, width):
+    """(workspace, tickets) of the reproducible per-sample column sums, per (device, stream)."""
+    need = _ops().row_block_count(int(rows), int(tokens)) * width
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    entry = _sum_space.get(key)
+    if entry is None or entry[0].numel() < need or entry[1].numel() < rows // tokens:
+        entry = _sum_space[key] = (torch.empty(max(need, 1 << 22), device=device, dtype=torch.float32),
+                                   torch.zeros(max(rows // tokens, 4096), device=device, dtype=torch.int32))
+    return entry
+
+
 def status_word(device):
     """Per-device int32[8] error word written by bounded waits inside the kernels."""
     device = torch.device(device)
@@ -123,17 +164,26 @@ def tensor_scale(x, *, history=None, index=0, delayed=False, fp8_dtype=torch.flo
 
 
 def quantize(x, scale, *, rowwise=True, transpose=False, fp8_dtype=torch.float8_e4m3fn, out=None, out_t=None,
-             quantization_limit=None):
+             quantization_limit=None, colsum=None):
+    """FP8 codes of ``x / scale`` row-wise and / or transposed.  ``colsum`` (fp32 [cols], zero-initialised by the
+    caller) additionally receives the column sums of ``x``: on CUDA they come out of the same read when only
+    row-wise codes are asked for (the bias gradient of a linear layer's output gradient)."""
     if not x.is_cuda:
+        if colsum is not None:
+            colsum.add_(x.detach().float().sum(dim=0))
         return reference.quantize(x, scale, rowwise=rowwise, transpose=transpose, fp8_dtype=fp8_dtype, out=out,
                                   out_t=out_t, quantization_limit=quantization_limit)
     x = x.detach().contiguous()
+    if colsum is not None and (transpose or out_t is not None or x.shape[1] % 16 or x.data_ptr() % 16):
+        colsum.add_(x.float().sum(dim=0))
+        colsum = None
     empty = None
     q = out if out is not None else (torch.empty(x.shape, device=x.device, dtype=fp8_dtype) if rowwise else None)
     qt = out_t if out_t is not None else (
         torch.empty(x.shape[::-1], device=x.device, dtype=fp8_dtype) if transpose else None)
     if q is not None or qt is not None:
-        _ops().quantize(x, scale, _limit(fp8_dtype, quantization_limit), q, qt, _FMT[fp8_dtype])
+        workspace = _colsum_workspace(x.device, *x.shape) if colsum is not None else None
+        _ops().quantize(x, scale, _limit(fp8_dtype, quantization_limit), q, qt, _FMT[fp8_dtype], colsum, workspace)
         _count()
     if q is None or qt is None:
         empty = torch.empty((0, 0), device=x.device, dtype=fp8_dtype)
@@ -173,13 +223,13 @@ def _check_mn(t):
 
 def _gemm(a, b, out, epilogue, n_logical, *, sa=None, sb=None, layout=_NO_GROUP, bias=None, alpha=1.0, beta=0.0,
           resid=None, out_t=None, symmetric=False, activation=0, aux=None, expert_offsets=None, tile_map=None,
-          force_bn=0, batch=1, a_mn=False, b_mn=False):
+          force_bn=0, batch=1, a_mn=False, b_mn=False, amax_out=None):
     multiple = 16 if a.element_size() == 1 else 8
     a = _check_mn(a) if a_mn else _pad_k(a, multiple)
     b = _check_mn(b) if b_mn else _pad_k(b, multiple)
     _ops().gemm(a, b, out, epilogue, n_logical, sa, sb, list(layout), bias, float(alpha), float(beta), resid, out_t,
                 bool(symmetric), int(activation), aux, expert_offsets, tile_map, status_word(a.device), int(force_bn),
-                int(batch), bool(a_mn), bool(b_mn))
+                int(batch), bool(a_mn), bool(b_mn), amax_out)
     _count(2 if expert_offsets is not None else 1)
     return out
 
@@ -349,6 +399,43 @@ def gated_gemm_backward(dy, wt, sg, st, aux, *, activation, out_dtype, group=Non
     _gemm(dy, wt, out, EPI_GATED_BWD, hidden, sa=sg, sb=st, layout=layout, activation=_ACT[activation], aux=aux,
           b_mn=wt_mn)
     return out
+
+
+def activation_backward_gemm(dy, w, sg, sw, slope, *, w_mn=False, amax_out=None):
+    """``dz = round(dy @ W) * slope`` in ``slope``'s dtype: the input gradient of ``act(z) @ W^T`` through the
+    activation, from the dgrad GEMM's epilogue (per-tensor scales); ``slope`` = ``act'(z)`` saved by the forward
+    (:func:`activation_quantize`).  ``w`` is W^T ([in, out], K-major) or, with ``w_mn``, W itself ([out, in]).
+    ``amax_out`` (int32 [1], zero-initialised) gathers ``max |dz|`` as float bits; :func:`scale_from_amax` turns
+    it into an FP8 scale without another pass over ``dz``."""
+    if not dy.is_cuda:
+        d = reference.gemm(dy, w.t() if w_mn else w, sg, sw, out_dtype=slope.dtype).float()
+        dz = (d * slope.float()).to(slope.dtype)
+        if amax_out is not None:
+            amax_out.copy_(torch.maximum(amax_out.view(torch.float32), dz.float().abs().max().reshape(1)).view(amax_out.dtype))
+        return dz
+    n = w.shape[1] if w_mn else w.shape[0]
+    out = torch.empty((dy.shape[0], n), device=dy.device, dtype=slope.dtype)
+    return _gemm(dy, w, out, EPI_ACT_BWD, n, sa=sg, sb=sw, aux=slope, b_mn=w_mn, amax_out=amax_out)
+
+
+def scale_from_amax(amax_bits, *, history=None, index=0, delayed=False, fp8_dtype=torch.float8_e4m3fn,
+                    quantization_limit=None, out=None):
+    """FP8 scale from an amax gathered as float bits by a producer kernel; the gather word is re-zeroed."""
+    limit = _limit(fp8_dtype, quantization_limit)
+    if not amax_bits.is_cuda:
+        amax = amax_bits.view(torch.float32).clone()
+        amax_bits.zero_()
+        chosen = amax
+        if history is not None:
+            if delayed and index != 0:
+                chosen = history.max().reshape(1)
+            history[index % history.numel()] = amax[0]
+        result = torch.clamp(chosen, min=1e-30) / limit
+        return result if out is None else out.copy_(result)
+    scale = out if out is not None else torch.empty(1, device=amax_bits.device, dtype=torch.float32)
+    _ops().scale_from_amax(amax_bits, history, int(index), bool(delayed), limit, scale)
+    _count()
+    return scale
 
 
 def gated_forward(gu, activation):
@@ -577,14 +664,16 @@ def ln_modulate_quantize(x, shift, scale, tokens, *, eps=1e-6, history=None, ind
                          qscale, _amax_scratch(x.device))
     q = torch.empty((rows, cols), device=x.device, dtype=fp8_dtype)
     qt = torch.empty((cols, rows), device=x.device, dtype=fp8_dtype) if transpose else None
-    _ops().fused_quantize(x, 1, mean, rstd, shift, scale, int(tokens), qscale, limit, _FMT[fp8_dtype], q, qt)
+    _ops().fused_quantize(x, 1, mean, rstd, shift, scale, int(tokens), qscale, limit, _FMT[fp8_dtype], q, qt, None)
     _count(2)
     return q, qt, qscale, mean, rstd
 
 
 def activation_quantize(z, activation, *, history=None, index=0, delayed=False, fp8_dtype=torch.float8_e4m3fn,
-                        quantization_limit=None, transpose=False):
-    """FP8 codes of ``act(z)`` (gelu / silu) without materialising it.  Returns (q, qt or None, qscale)."""
+                        quantization_limit=None, transpose=False, slope=False):
+    """FP8 codes of ``act(z)`` (gelu / silu) without materialising it.  Returns (q, qt or None, qscale), plus
+    ``act'(z)`` in bf16 when ``slope`` is set (row-wise codes only): the backward pass then needs neither ``z``
+    nor another transcendental."""
     rows, cols = z.shape
     limit = _limit(fp8_dtype, quantization_limit)
     qscale = torch.empty(1, device=z.device, dtype=torch.float32)
@@ -592,18 +681,20 @@ def activation_quantize(z, activation, *, history=None, index=0, delayed=False, 
     _ops().act_amax(z, mode, history, int(index), bool(delayed), limit, qscale, _amax_scratch(z.device))
     q = torch.empty((rows, cols), device=z.device, dtype=fp8_dtype)
     qt = torch.empty((cols, rows), device=z.device, dtype=fp8_dtype) if transpose else None
-    _ops().fused_quantize(z, mode, None, None, None, None, 1, qscale, limit, _FMT[fp8_dtype], q, qt)
+    slope_out = torch.empty_like(z) if slope else None
+    _ops().fused_quantize(z, mode, None, None, None, None, 1, qscale, limit, _FMT[fp8_dtype], q, qt, slope_out)
     _count(2)
-    return q, qt, qscale
+    return (q, qt, qscale, slope_out) if slope else (q, qt, qscale)
 
 
 def ln_modulate_backward(dh, x, mean, rstd, scale, tokens):
     """Gradients of LN + modulate: returns (dx [rows, cols] in x's dtype, dshift, dscale [samples, cols] fp32)."""
     rows, cols = x.shape
     dx = torch.empty_like(x)
-    dshift = torch.zeros((rows // tokens, cols), device=x.device, dtype=torch.float32)
-    dscale = torch.zeros_like(dshift)
-    _ops().ln_modulate_backward(dh, x, mean, rstd, scale, int(tokens), dx, dshift, dscale)
+    dshift = torch.empty((rows // tokens, cols), device=x.device, dtype=torch.float32)
+    dscale = torch.empty_like(dshift)
+    workspace, tickets = _sample_sum_workspace(x.device, rows, tokens, 2 * cols)
+    _ops().ln_modulate_backward(dh, x, mean, rstd, scale, int(tokens), dx, dshift, dscale, workspace, tickets)
     _count()
     return dx, dshift, dscale
 
@@ -624,8 +715,9 @@ def gate_residual_backward(dout, gate, y, tokens):
         return reference.gate_residual_backward(dout, gate, y, tokens)
     rows, cols = dout.shape
     dy = torch.empty((rows, cols), device=dout.device, dtype=torch.bfloat16)
-    dgate = torch.zeros((rows // tokens, cols), device=dout.device, dtype=torch.float32)
-    _ops().gate_residual_backward(dout, gate, y, int(tokens), dy, dgate)
+    dgate = torch.empty((rows // tokens, cols), device=dout.device, dtype=torch.float32)
+    workspace, tickets = _sample_sum_workspace(dout.device, rows, tokens, cols)
+    _ops().gate_residual_backward(dout, gate, y, int(tokens), dy, dgate, workspace, tickets)
     _count()
     return dy, dgate
 

@@ -50,6 +50,31 @@ __device__ __forceinline__ bool wait_flag_budget(const int* flag, int expected, 
   }
 }
 
+// One resident warp that sleeps between polls: the stand-alone wait launched in front of a kernel whose every
+// block would otherwise sit on an SM polling (a polling warp shares an issue port with the tensor-core
+// kernels' epilogue warps and slowed them by up to 1.8x).  expected = *generation + delta; values < 1 mean
+// "nothing to wait for yet".
+__global__ void wait_generation_kernel(const int* flags, int count, int skip, const int* generation_ptr, int delta,
+                                       long long budget, int* status) {
+  if (threadIdx.x != 0) return;
+  const int expected = *generation_ptr + delta;
+  if (expected < 1) return;
+  const long long start = clock64();
+  for (int r = 0; r < count; ++r) {
+    if (r == skip) continue;
+    uint32_t polls = 0;
+    while (true) {
+      const int seen = ld_acquire_sys(flags + r);
+      if (seen >= expected) break;
+      __nanosleep(400);
+      if ((++polls & 15u) == 0 && clock64() - start > budget) {
+        report(status, kTimeoutPeerFlag, seen);
+        return;
+      }
+    }
+  }
+}
+
 // Block-wide: thread 0 waits on up to `count` flags (skipping index `skip`), everyone learns the result.
 __device__ __forceinline__ bool block_wait_flags(const int* flags, int count, int skip, int expected, long long budget,
                                                  int* status) {
@@ -406,6 +431,7 @@ extern "C" int vb_reduce_push_fp8(const float* bucket, long long n, int tile, in
                                   long long wait_clocks, int max_blocks, int* status, cudaStream_t stream) {
   const long long tiles = (n + tile - 1) / tile;
   const int grid = blocks_for(tiles, max_blocks);
+  wait_generation_kernel<<<1, 32, 0, stream>>>(ack_flag, 1, -1, generation, -1, wait_clocks, status);
   VB_TILE_SWITCH(tile, (reduce_push_kernel<T><<<grid, 256, 0, stream>>>(bucket, n, fmt, (uint8_t*)dst_codes, dst_scales, dst_flag,
                                                                        ack_flag, generation, counter, wait_clocks, status)));
   return (int)cudaGetLastError();
@@ -418,6 +444,7 @@ extern "C" int vb_reduce_accumulate_fp8(const float* bucket, long long n, int ti
                                         cudaStream_t stream) {
   const long long tiles = (n + tile - 1) / tile;
   const int grid = blocks_for(tiles, max_blocks);
+  wait_generation_kernel<<<1, 32, 0, stream>>>(flags, peers->world, peers->rank, generation, 0, wait_clocks, status);
   VB_TILE_SWITCH(tile, (reduce_accumulate_kernel<T><<<grid, 256, 0, stream>>>(bucket, n, fmt, (const uint8_t*)recv, slot_stride,
                                                                              scales_offset, flags, make_peers(peers), ack_offset,
                                                                              generation, accum, counter, wait_clocks, status)));
@@ -437,9 +464,14 @@ extern "C" int vb_allreduce_requant_fp8(float* value, long long n, int tile, int
   VB_TILE_SWITCH(tile, {
     allreduce_push_kernel<T><<<grid_all, 256, 0, stream>>>(value, n, groups, fmt, p, a2a_offset, slot, a2a_flag_offset,
                                                           generation, counters);
+    // stand-alone single-warp waits in front of the kernels whose blocks would otherwise all poll
+    wait_flags_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<const int*>(p.heap[p.rank] + a2a_flag_offset), world, p.rank,
+                                            generation, wait_clocks, status);
     allreduce_reduce_kernel<T><<<grid_own, 256, 0, stream>>>(value, n, groups, fmt, p, a2a_offset, gather_offset, slot,
                                                             a2a_flag_offset, gather_flag_offset, generation, counters + 1,
                                                             wait_clocks, status);
+    wait_flags_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<const int*>(p.heap[p.rank] + gather_flag_offset), world, p.rank,
+                                            generation, wait_clocks, status);
     allreduce_unpack_kernel<T><<<grid_all, 256, 0, stream>>>(value, n, groups, fmt, p, gather_offset, slot, gather_flag_offset,
                                                             generation, wait_clocks, status);
   });

@@ -93,7 +93,7 @@ class violaEngine:  # noqa: N801 - public name kept identical to the reference
         try:
             from .symm import PeerTransport
             return PeerTransport(self, fp8_format=communication["fp8_format"], tile_size=communication["fp8_tile_size"],
-                                 fp8=communication["dtype"] == "fp8", overlap=communication.get("overlap", True))
+                                 fp8=communication["dtype"] == "fp8", overlap=communication.get("overlap", False))
         except Exception:
             if backend == "p2p":
                 raise

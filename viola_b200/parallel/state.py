@@ -34,7 +34,7 @@ class DistributedState:
                                        communication_dtype=communication["dtype"], bucket_mb=communication["bucket_mb"],
                                        fp8_format=communication["fp8_format"],
                                        fp8_tile_size=communication["fp8_tile_size"], shard=self.sharding["gradients"],
-                                       defer_reduction=sharder is not None and transport is None,
+                                       defer_reduction=(sharder is not None and transport is None) or (transport is not None and not transport.overlap),
                                        transport=transport)
         for position, record in enumerate(self.parameters.records):
             self.gradients.bind(position, record.parameter)

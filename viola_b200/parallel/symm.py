@@ -68,8 +68,10 @@ class PeerTransport:
             raise RuntimeError("peer transport supports up to 16 ranks on one node")
         self.group, self.rank, self.world, self.device = engine.group, engine.rank, engine.world_size, engine.device
         self.fmt, self.tile, self.fp8 = _FMT[fp8_format], tile_size, fp8
-        self.max_blocks, self.wait_clocks = max_blocks, wait_clocks
         self.overlap = overlap
+        # Overlapped communication shares the GPU with compute, so its kernels stay narrow; without overlap they
+        # run alone after backward and take the whole GPU (a 25 MB bucket then costs microseconds, not hundreds).
+        self.max_blocks, self.wait_clocks = (max_blocks if overlap else 296), wait_clocks
         self.stream = torch.cuda.Stream(device=self.device) if overlap else None
         self.status = ops.status_word(self.device)
         self.counters = torch.zeros(64, device=self.device, dtype=torch.int32)
@@ -166,7 +168,11 @@ class PeerTransport:
         return index, self.staging[index]
 
     def begin_microbatch(self):
-        """Advance the generation all of this microbatch's buckets signal with (captured in CUDA graphs)."""
+        """Advance the generation all of this microbatch's buckets signal with (captured in CUDA graphs).
+
+        The kernels read the counter when they run, so it may only move once the side stream has finished the
+        previous microbatch's kernels."""
+        self.synchronize()
         self.micro_counter.add_(1)
 
     def forget_events(self):

@@ -24,8 +24,9 @@ E4M3 = torch.float8_e4m3fn
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--case", required=True,
-                        choices=("gemm_fp8", "gemm_group", "gemm_ns", "gemm_ns_apply", "gemm_act_bwd", "quantize",
-                                 "group_quantize", "momentum", "gated"))
+                        choices=("gemm_fp8", "gemm_group", "gemm_ns", "gemm_ns_apply", "gemm_act_bwd", "gemm_wgrad",
+                                 "gemm_expert", "quantize", "quantize_rows", "group_quantize", "momentum", "gated",
+                                 "ln_quantize", "gelu_quantize", "ln_backward", "gate_backward"))
     parser.add_argument("--launches", type=int, default=4)
     args = parser.parse_args()
     device = torch.device("cuda")
@@ -69,6 +70,44 @@ def main():
         one = torch.ones(1, device=device)
         amax = ops.amax_word(device)
         run = lambda: ops.activation_backward_gemm(dy, w, one, one, slope, w_mn=True, amax_out=amax)
+    elif args.case == "gemm_wgrad":
+        # dW = dY^T X for the attention projection: 1152x1152 output, K = 32768 tokens, both operands MN-major
+        dy = torch.randn(m, 1152, device=device).to(torch.float8_e5m2)
+        xq = torch.randn(m, 1152, device=device).to(E4M3)
+        one = torch.ones(1, device=device)
+        run = lambda: ops.gemm(dy, xq, one, one, out_dtype=torch.float32, a_mn=True, b_mn=True)
+    elif args.case == "gemm_expert":
+        experts, tokens, width, hidden = 8, 1024, 4096, 14336
+        x = torch.randn(experts * tokens, width, device=device, dtype=torch.bfloat16)
+        w = torch.randn(experts, hidden, width, device=device, dtype=torch.bfloat16) * 0.02
+        offsets = torch.arange(0, experts * tokens + 1, tokens, device=device, dtype=torch.int32)
+        sx, sw = ops.tensor_scale(x), ops.tensor_scale(w)
+        qx, _ = ops.quantize(x, sx)
+        qw, _ = ops.quantize(w.view(-1, width), sw)
+        run = lambda: ops.expert_gemm(qx, qw.view(experts, hidden, width), offsets, sx, sw, out_dtype=torch.bfloat16)
+    elif args.case == "quantize_rows":
+        # output-gradient encode of a linear layer: row-wise e5m2 codes plus the bias gradient (column sums)
+        x = torch.randn(m, 4608, device=device, dtype=torch.bfloat16)
+        scale = ops.tensor_scale(x, fp8_dtype=torch.float8_e5m2)
+        colsum = torch.zeros(4608, device=device)
+        run = lambda: ops.quantize(x, scale, fp8_dtype=torch.float8_e5m2, colsum=colsum)
+    elif args.case in ("ln_quantize", "ln_backward", "gate_backward"):
+        tokens, width = 256, 1152
+        x = torch.randn(m, width, device=device)                      # fp32 residual stream
+        mod = (torch.randn(m // tokens, 3 * width, device=device) * 0.3).bfloat16()
+        shift, scale, gate = mod.chunk(3, dim=-1)
+        if args.case == "ln_quantize":
+            run = lambda: ops.ln_modulate_quantize(x, shift, scale, tokens)
+        elif args.case == "ln_backward":
+            _, _, _, mean, rstd = ops.ln_modulate_quantize(x, shift, scale, tokens)
+            dh = torch.randn(m, width, device=device, dtype=torch.bfloat16)
+            run = lambda: ops.ln_modulate_backward(dh, x, mean, rstd, scale, tokens)
+        else:
+            y = torch.randn(m, width, device=device, dtype=torch.bfloat16)
+            run = lambda: ops.gate_residual_backward(x, gate, y, tokens)
+    elif args.case == "gelu_quantize":
+        z = torch.randn(m, 4608, device=device, dtype=torch.bfloat16)
+        run = lambda: ops.activation_quantize(z, "gelu", slope=True)
     elif args.case == "quantize":
         x = torch.randn(m, 4608, device=device, dtype=torch.bfloat16)
         scale = ops.tensor_scale(x)

@@ -106,7 +106,8 @@ def worker(rank, world, port, flags, directory, results):
                       LOCAL_RANK=str(rank))
     torch.manual_seed(7 if rank == 0 else 99)       # ranks start different: prepare_model must synchronise
     config = dict(device="cpu", mixed_precision="no", gradient_accumulation_steps=2,
-                  sharding=dict(parameters=flags[0], gradients=flags[1], optimizer=flags[2], ema=flags[3]),
+                  sharding=dict(parameters=flags[0], gradients=flags[1], optimizer=flags[2], ema=flags[3],
+                                resident=flags[4] if len(flags) > 4 else "auto"),
                   communication=dict(dtype="fp32"), ema=dict(decay=0.9999))
     engine = viola.violaEngine(config)
     model = engine.prepare_model(Net())
@@ -179,7 +180,8 @@ def run_world(target, world, *args):
 
 
 @pytest.mark.parametrize("flags", [(True, True, True, True), (False, False, False, False), (False, True, True, False),
-                                   (True, False, True, True), (False, True, False, True), (True, True, False, False)])
+                                   (True, False, True, True), (False, True, False, True), (True, True, False, False),
+                                   (True, True, True, True, True)])      # last: gathered parameters kept resident
 def test_two_rank_plumbing(flags):
     with tempfile.TemporaryDirectory() as directory:
         assert len(run_world(worker, 2, flags, directory)) == 2

@@ -9,6 +9,8 @@ blocks}``, ``precision{master_weight_dtype, gradient_dtype, master_rounding, mas
 ``"p2p"`` or ``"nccl"`` — and ``communication.overlap``: true runs the gradient reduction on a side stream bucket by
 bucket while backward is still producing gradients; false (default) runs it once backward is done, with kernels
 that take the whole GPU (measured faster at 2-8 GPUs: the narrow overlapped kernels cost more than they hide).
+``sharding.resident`` (``"auto"`` / true / false) keeps the gathered copy of sharded parameters allocated between
+uses when it is small next to the device memory.
 """
 
 from __future__ import annotations
@@ -43,7 +45,8 @@ def read_config(config=None):
         "num_processes": 1,
         "mixed_precision": "bf16",
         "gradient_accumulation_steps": 1,
-        "sharding": {"parameters": False, "gradients": False, "optimizer": True, "ema": True, "blocks": None},
+        "sharding": {"parameters": False, "gradients": False, "optimizer": True, "ema": True, "blocks": None,
+                     "resident": "auto"},
         "precision": {"master_weight_dtype": policy["master_weight_dtype"],
                       "gradient_dtype": policy["gradient_dtype"] or torch.float32,
                       "master_rounding": policy["master_rounding"],

@@ -83,7 +83,21 @@ class violaEngine:  # noqa: N801 - public name kept identical to the reference
         self.transport = self._make_transport()
         self.state = DistributedState(self.model, optimizer, self, self.sharder, self.transport)
         self.optimizer, self.ema = optimizer, self.state.ema
+        self._choose_resident_parameters()
         return optimizer
+
+    def _choose_resident_parameters(self):
+        """``sharding.resident``: keep the gathered parameters allocated between uses.  ``"auto"`` does so on a GPU
+        when one full copy takes at most an eighth of its memory (an FP8 DiT-XL/2 is 0.7 GB of 180 GB): the shards
+        stay the storage of record, the gather runs once per optimizer step instead of four times per unit."""
+        if self.sharder is None:
+            return
+        mode = self.config["sharding"].get("resident", "auto")
+        if mode == "auto":
+            mode = (self.device.type == "cuda"
+                    and self.sharder.full_bytes() <= torch.cuda.get_device_properties(self.device).total_memory // 8)
+        if mode:
+            self.sharder.set_resident(True)
 
     def _make_transport(self):
         communication = self.config["communication"]

@@ -161,7 +161,9 @@ class ParameterStore:
                     stacked[:entry.rows].copy_(payload.reshape(entry.shape))
                     chunks = list(_wire(stacked.view(self.world, entry.shard_rows, *entry.shape[1:])).unbind(0))
                 dist.scatter(_wire(local), chunks, src=src, group=self.group)
-            if unit.unsharded:       # keep a live gathered copy coherent (e.g. inside ema_scope)
+            if unit.resident:
+                unit.stale = True    # refreshed in one go by end_writes()
+            elif unit.unsharded:     # keep a live gathered copy coherent (e.g. inside ema_scope)
                 if self.world > 1:
                     unit.full_view(entry).copy_(self.full(record).view(entry.shape))
                 else:
@@ -179,6 +181,8 @@ class ParameterStore:
         """Publish this rank's stores and wait (bounded, on the stream) for every owner's."""
         if self.transport is not None and self.world > 1:
             self.transport.publish_step()
+        if self.sharder is not None:
+            self.sharder.refresh()
 
     @torch.no_grad()
     def _write_peer(self, record, value, source):
@@ -278,10 +282,7 @@ class ParameterStore:
             self._local_storage(record).copy_(values[record.name])
             torch.autograd.graph.increment_version(record.parameter)
         if self.sharder is not None:
-            for unit in self.sharder.units.values():
-                if unit.unsharded:
-                    unit.unsharded = False
-                    unit.unshard()
+            self.sharder.refresh()
 
     # ------------------------------------------------------------------ full-model state dicts
     @torch.no_grad()
@@ -321,6 +322,10 @@ class ParameterStore:
         finally:
             if self.sharder is not None:
                 self.sharder.reshard_all()
+        if self.sharder is not None and self.world > 1:
+            dist.barrier(group=self.group)       # every rank's slab is in place before anyone gathers again
+        if self.sharder is not None:
+            self.sharder.refresh()
         del sharded
         extras = [dict((name, saved[f"{name}._extra_state" if name else "_extra_state"])
                        for name in extra_states(self.model)) if self.rank == 0 else None]

@@ -66,6 +66,8 @@ class ShardedUnit:
     shard: torch.Tensor = None
     full: torch.Tensor = None
     unsharded: bool = True
+    resident: bool = False         # keep the gathered copy between uses (it is refreshed after every write-back)
+    stale: bool = False            # the shards changed since ``full`` was gathered
     pending_gradients: int = 0
     gatherer: object = None        # optional callable(unit) that fills ``full`` from peer memory
 
@@ -90,7 +92,7 @@ class ShardedUnit:
 
     @torch.no_grad()
     def unshard(self):
-        if self.unsharded:
+        if self.unsharded and not self.stale:
             return
         storage = self.full.untyped_storage()
         if storage.size() == 0:
@@ -106,10 +108,11 @@ class ShardedUnit:
                 else:
                     dist.all_gather_into_tensor(target, source, group=self.group)
         self.unsharded = True
+        self.stale = False
 
     @torch.no_grad()
     def reshard(self):
-        if not self.unsharded:
+        if not self.unsharded or self.resident:
             return
         self.full.untyped_storage().resize_(0)
         self.unsharded = False
@@ -152,6 +155,7 @@ class ParameterSharder:
     def __init__(self, model, group, rank, world, *, blocks=None):
         self.model, self.group, self.rank, self.world = model, group, rank, world
         self.in_backward = False
+        self.resident = False
         self.units = {}
         self.by_parameter = {}
         self.handles = []
@@ -232,6 +236,36 @@ class ParameterSharder:
         self.in_backward = False
         for unit in self.units.values():
             unit.reshard()
+
+    def set_resident(self, resident=True):
+        """Resident mode keeps every unit's gathered parameters allocated: forward and backward of every
+        microbatch then read local memory, and the gather runs once per write-back (``refresh``) instead of twice
+        per unit per microbatch.  Costs one full copy of the parameters per rank."""
+        self.resident = resident
+        for unit in self.units.values():
+            unit.resident = resident
+        if resident:
+            self.unshard_all()
+        else:
+            self.reshard_all()
+
+    def full_bytes(self):
+        return sum(unit.full.numel() for unit in self.units.values())
+
+    def invalidate(self):
+        """The shards were written (optimizer write-back, EMA swap, state load): gathered copies are out of date."""
+        for unit in self.units.values():
+            unit.stale = True
+
+    def refresh(self):
+        """After a write-back: re-gather right away in resident mode, else leave it to the next use."""
+        self.invalidate()
+        if self.resident:
+            self.unshard_all()
+        else:
+            for unit in self.units.values():
+                if unit.unsharded:
+                    unit.unshard()
 
     def unshard_all(self):
         for unit in self.units.values():

@@ -208,7 +208,14 @@ momentum16_kernel(const void* __restrict__ grad, int gdt, void* __restrict__ mom
   }
 }
 
-// sum of squares of x rounded to `round_dt` first (Newton-Schulz normalises the bf16/fp16 copy)
+// sum of squares of x rounded to `round_dt` first (Newton-Schulz normalises the bf16/fp16 copy).  Reproducible:
+// every block parks its partial sum, the last block of a tensor (ticket, self-resetting) adds them in block order.
+// The scratch is file-scope device memory shared by all launches, which therefore must not overlap in time
+// (the optimizer issues them on one stream); at most kSumsqBatch tensors x kSumsqBlocks blocks per launch.
+constexpr int kSumsqBlocks = 256, kSumsqBatch = 1024;
+static __device__ float g_sumsq_partial[kSumsqBatch * kSumsqBlocks];
+static __device__ unsigned int g_sumsq_ticket[kSumsqBatch];
+
 __global__ void __launch_bounds__(256)
 sumsq_kernel(const void* __restrict__ x, int dt, int round_dt, long long n, float* __restrict__ accum) {
   // blockIdx.y selects one of gridDim.y stacked tensors of n elements each
@@ -224,12 +231,22 @@ sumsq_kernel(const void* __restrict__ x, int dt, int round_dt, long long n, floa
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
   __shared__ float red[8];
+  __shared__ bool last;
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
   __syncthreads();
   if (threadIdx.x == 0) {
     float t = 0.f;
     for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += red[i];
-    atomicAdd(accum, t);
+    g_sumsq_partial[blockIdx.y * kSumsqBlocks + blockIdx.x] = t;
+    __threadfence();
+    last = atomicAdd(&g_sumsq_ticket[blockIdx.y], 1u) == gridDim.x - 1;
+    if (last) {
+      g_sumsq_ticket[blockIdx.y] = 0u;
+      __threadfence();
+      float total = 0.f;
+      for (int b = 0; b < (int)gridDim.x; ++b) total += __ldcg(&g_sumsq_partial[blockIdx.y * kSumsqBlocks + b]);
+      *accum += total;
+    }
   }
 }
 
@@ -456,8 +473,13 @@ extern "C" int vb_momentum16(const void* grad, int grad_dtype, void* momentum, i
 extern "C" int vb_sumsq(const void* x, int dtype, long long n, float* accum, int batch, cudaStream_t stream) {
   // `dtype` packs the storage dtype in the low byte and the rounding dtype in the next byte.
   if (n <= 0 || batch <= 0) return 0;
-  dim3 grid(std::min(grid_for(n, 1024), 256), batch);
-  sumsq_kernel<<<grid, 256, 0, stream>>>(x, dtype & 0xff, (dtype >> 8) & 0xff, n, accum);
+  const int esize = (dtype & 0xff) == kF32 ? 4 : 2;
+  for (int first = 0; first < batch; first += kSumsqBatch) {       // the scratch holds kSumsqBatch tensors per launch
+    const int count = std::min(batch - first, kSumsqBatch);
+    dim3 grid(std::min(grid_for(n, 1024), kSumsqBlocks), count);
+    sumsq_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const char*>(x) + (long long)first * n * esize, dtype & 0xff,
+                                           (dtype >> 8) & 0xff, n, accum + first);
+  }
   return (int)cudaGetLastError();
 }
 

@@ -225,10 +225,15 @@ class ParameterStore:
     def write(self, record, value, source):
         """Owner ``source`` holds the new real-valued ``value``; update the compute storage everywhere."""
         layer = record.layer
-        if self.transport is not None and record.unit is not None and self.world > 1 and not record.unit.unsharded:
+        # the shards are the storage of record: write them directly unless a live gathered copy must stay
+        # coherent (a resident copy is refreshed in one go by end_writes())
+        direct = record.unit is not None and (not record.unit.unsharded or record.unit.resident)
+        if self.transport is not None and direct and self.world > 1:
             if self._write_peer(record, value, source):
+                record.unit.stale = True
                 return
-        if self.world == 1 and record.unit is not None and not record.unit.unsharded:
+        if self.world == 1 and direct:
+            record.unit.stale = True
             # single rank, sharded storage: encode straight into the shard buffer (no staging copy)
             target = record.unit.local_view(record.entry)[:record.entry.rows].view(record.shape)
             if layer is not None and layer.weight_dtype == "fp8":

@@ -92,3 +92,44 @@ def test_hadamard_is_orthogonal_and_self_inverse():
     h = ref.hadamard64_matrix()
     torch.testing.assert_close(h @ h, torch.eye(64), atol=1e-6, rtol=0)
     torch.testing.assert_close(h, h.t())
+
+
+def test_block_fusion_ops_on_cpu():
+    """CPU paths of the transformer-block ops: gated residual, activation-slope GEMM, gathered amax, column sums."""
+    from viola_b200 import ops
+    from torch.nn import functional as F
+    torch.manual_seed(4)
+    rows, cols, tokens = 24, 32, 6
+    x = torch.randn(rows, cols, requires_grad=True)
+    y = torch.randn(rows, cols).bfloat16().requires_grad_(True)
+    gate = torch.randn(rows // tokens, cols).bfloat16().requires_grad_(True)
+    out = ops.gate_residual(x.detach(), gate.detach(), y.detach(), tokens)
+    expected = x + gate.float().repeat_interleave(tokens, dim=0) * y.float()
+    torch.testing.assert_close(out, expected.detach())
+    dout = torch.randn(rows, cols)
+    expected.backward(dout)
+    dy, dgate = ops.gate_residual_backward(dout, gate.detach(), y.detach(), tokens)
+    torch.testing.assert_close(dy.float(), y.grad.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(dgate, gate.grad.float(), rtol=2e-2, atol=2e-2)
+
+    z = torch.randn(rows, cols).bfloat16()
+    zf = z.float().requires_grad_(True)
+    slope, = torch.autograd.grad(F.gelu(zf, approximate="tanh").sum(), zf)
+    slope = slope.bfloat16()
+    dyq = torch.randn(rows, 16).to(torch.float8_e5m2)
+    w = (torch.randn(16, cols) * 0.1).to(E4M3)
+    one = torch.ones(1)
+    amax = torch.zeros(1, dtype=torch.int32)
+    dz = ops.activation_backward_gemm(dyq, w, one, one, slope, w_mn=True, amax_out=amax)
+    reference = ((dyq.float() @ w.float()).bfloat16().float() * slope.float()).bfloat16()
+    torch.testing.assert_close(dz.float(), reference.float())
+    assert amax.view(torch.float32).item() == dz.float().abs().max().item()
+    history = torch.zeros(4)
+    scale = ops.scale_from_amax(amax, history=history, index=1, fp8_dtype=torch.float8_e5m2)
+    assert amax.item() == 0 and history[1].item() == dz.float().abs().max().item()
+    torch.testing.assert_close(scale, dz.float().abs().max().reshape(1) / 57344)
+
+    colsum = torch.zeros(cols)
+    q, _ = ops.quantize(x.detach(), torch.tensor([0.05]), colsum=colsum)
+    torch.testing.assert_close(colsum, x.detach().sum(dim=0))
+    assert q.shape == x.shape

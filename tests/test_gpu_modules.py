@@ -363,6 +363,15 @@ def test_activation_backward_gemm_and_gathered_scale():
         expected_slope, = torch.autograd.grad(act.sum(), zf)
         assert (slope.float() - expected_slope).abs().max() < 1e-2 and rel_l2(slope, expected_slope) < 3e-3
         assert rel_l2(q.float() * qscale, act.detach()) < 4e-2
+        # the amax pass looks at three extreme inputs only; it must still find the true maximum of |act(z)|,
+        # also when every input sits in the negative lobe, and report +inf for a NaN
+        torch.testing.assert_close(qscale[0] * 448, act.detach().bfloat16().float().abs().max(), rtol=8e-3, atol=0)
+        lobe = -torch.rand(64, 256, device="cuda", dtype=torch.bfloat16) * 6
+        _, _, lobe_scale = ops.activation_quantize(lobe, activation)
+        lobe_act = F.gelu(lobe.float(), approximate="tanh") if activation == "gelu" else F.silu(lobe.float())
+        torch.testing.assert_close(lobe_scale[0] * 448, lobe_act.bfloat16().float().abs().max(), rtol=8e-3, atol=0)
+        lobe[5, 7] = float("nan")
+        assert torch.isinf(ops.activation_quantize(lobe, activation)[2]).all()
         amax = ops.amax_word("cuda")
         dz = ops.activation_backward_gemm(dy, w, sg, sw, slope, w_mn=True, amax_out=amax)
         expected = ops.activation_backward_gemm(dy.cpu(), w.cpu(), sg.cpu(), sw.cpu(), slope.cpu(), w_mn=True)

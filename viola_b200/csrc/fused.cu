@@ -175,23 +175,104 @@ ln_stats_amax_kernel(const T* __restrict__ x, int rows, int cols, float eps,
   finish_scale(block_max(amax), scratch, history, history_len, index, delayed, limit, scale_out);
 }
 
+// amax of act(z) without evaluating act per element.  tanh-GELU and SiLU fall from 0 to one minimum at z0 and
+// rise from there, so |act| over a set is largest at one of three points: the largest z, the smallest z >= z0, or
+// the largest z < z0.  The pass therefore tracks two maxima and one minimum (no transcendental: the exact amax pass
+// was bound by the exponential unit, not by memory), and the last block evaluates act at those three points with
+// the very function the encode pass uses.  A NaN anywhere gives amax = +inf, as in the other amax kernels.
+// Partials go through file-scope device scratch: launches of this kernel must not overlap (one stream).
+constexpr int kActAmaxBlocks = 148 * 8;
+static __device__ float g_act_partial[kActAmaxBlocks * 4];
+
 __global__ void __launch_bounds__(256)
 act_amax_kernel(const __nv_bfloat16* __restrict__ z, long long n, int mode, float* history, int history_len,
                 long long index, int delayed, float limit, float* scale_out, unsigned int* scratch) {
-  float m = 0.f;
+  const float z0 = mode == kModeGelu ? -0.75179f : -1.27846f;
+  float zmax = -INFINITY, zleft = -INFINITY, zright = INFINITY, bad = 0.f;
+  auto see = [&](float v) {
+    zmax = fmaxf(zmax, v);
+    if (v < z0) zleft = fmaxf(zleft, v);
+    else zright = fminf(zright, v);
+    if (v != v) bad = 1.f;
+  };
   const long long nvec = n / 8;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
-    const uint4 t = reinterpret_cast<const uint4*>(z)[i];
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&t);
+    float v[8];
+    load8(z + i * 8, v);
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 f = __bfloat1622float2(h[e]);
-      m = fmaxf(m, fmaxf(fabsf(round_bf16(apply_act(f.x, mode))), fabsf(round_bf16(apply_act(f.y, mode)))));
-    }
+    for (int e = 0; e < 8; ++e) see(v[e]);
   }
   for (long long i = nvec * 8 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
-    m = fmaxf(m, fabsf(round_bf16(apply_act(__bfloat162float(z[i]), mode))));
-  finish_scale(block_max(m), scratch, history, history_len, index, delayed, limit, scale_out);
+    see(__bfloat162float(z[i]));
+  // block reduction of (zmax, zleft, zright, bad)
+  __shared__ float part[8][4];
+  __shared__ bool last;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    zmax = fmaxf(zmax, __shfl_xor_sync(0xffffffffu, zmax, o));
+    zleft = fmaxf(zleft, __shfl_xor_sync(0xffffffffu, zleft, o));
+    zright = fminf(zright, __shfl_xor_sync(0xffffffffu, zright, o));
+    bad = fmaxf(bad, __shfl_xor_sync(0xffffffffu, bad, o));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    float* p = part[threadIdx.x >> 5];
+    p[0] = zmax; p[1] = zleft; p[2] = zright; p[3] = bad;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) {
+      zmax = fmaxf(zmax, part[w][0]); zleft = fmaxf(zleft, part[w][1]);
+      zright = fminf(zright, part[w][2]); bad = fmaxf(bad, part[w][3]);
+    }
+    float* mine = g_act_partial + blockIdx.x * 4;
+    mine[0] = zmax; mine[1] = zleft; mine[2] = zright; mine[3] = bad;
+    __threadfence();
+    last = atomicAdd(&scratch[1], 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!last) return;
+  // the last block folds every block's partial: strided over its threads, then the same block reduction again
+  __threadfence();
+  zmax = zleft = -INFINITY; zright = INFINITY; bad = 0.f;
+  for (int b = threadIdx.x; b < (int)gridDim.x; b += blockDim.x) {
+    const float* other = g_act_partial + b * 4;
+    zmax = fmaxf(zmax, __ldcg(other)); zleft = fmaxf(zleft, __ldcg(other + 1));
+    zright = fminf(zright, __ldcg(other + 2)); bad = fmaxf(bad, __ldcg(other + 3));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    zmax = fmaxf(zmax, __shfl_xor_sync(0xffffffffu, zmax, o));
+    zleft = fmaxf(zleft, __shfl_xor_sync(0xffffffffu, zleft, o));
+    zright = fminf(zright, __shfl_xor_sync(0xffffffffu, zright, o));
+    bad = fmaxf(bad, __shfl_xor_sync(0xffffffffu, bad, o));
+  }
+  __syncthreads();                     // part[] is reused
+  if ((threadIdx.x & 31) == 0) {
+    float* p = part[threadIdx.x >> 5];
+    p[0] = zmax; p[1] = zleft; p[2] = zright; p[3] = bad;
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  for (int w = 1; w < (int)(blockDim.x >> 5); ++w) {
+    zmax = fmaxf(zmax, part[w][0]); zleft = fmaxf(zleft, part[w][1]);
+    zright = fminf(zright, part[w][2]); bad = fmaxf(bad, part[w][3]);
+  }
+  scratch[1] = 0u;
+  float amax = 0.f;
+  if (zmax > -INFINITY) amax = fmaxf(amax, fabsf(round_bf16(apply_act(zmax, mode))));
+  if (zleft > -INFINITY) amax = fmaxf(amax, fabsf(round_bf16(apply_act(zleft, mode))));
+  if (zright < INFINITY) amax = fmaxf(amax, fabsf(round_bf16(apply_act(zright, mode))));
+  if (bad != 0.f) amax = INFINITY;
+  float chosen = amax;
+  if (history != nullptr) {
+    if (delayed && index != 0) {
+      float old = 0.f;
+      for (int i = 0; i < history_len; ++i) old = fmaxf(old, history[i]);
+      chosen = old;
+    }
+    history[index % history_len] = amax;
+  }
+  scale_out[0] = fmaxf(chosen, 1e-30f) / limit;
 }
 
 struct FusedArgs {
@@ -350,9 +431,17 @@ __device__ __forceinline__ void ordered_sample_sums(const float* partial, int wi
   __threadfence();
   const float* first = workspace + (long long)sample * blocks_per_sample * width;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float total = 0.f;
-    for (int b = 0; b < blocks_per_sample; ++b) total += __ldcg(first + (long long)b * width + i);
-    emit(i, total);
+    // four independent chains keep the loads in flight; the order of additions is still fixed
+    float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;
+    int b = 0;
+    for (; b + 4 <= blocks_per_sample; b += 4) {
+      t0 += __ldcg(first + (long long)b * width + i);
+      t1 += __ldcg(first + (long long)(b + 1) * width + i);
+      t2 += __ldcg(first + (long long)(b + 2) * width + i);
+      t3 += __ldcg(first + (long long)(b + 3) * width + i);
+    }
+    for (; b < blocks_per_sample; ++b) t0 += __ldcg(first + (long long)b * width + i);
+    emit(i, (t0 + t1) + (t2 + t3));
   }
 }
 
@@ -530,6 +619,8 @@ using namespace vb;
 static int pick_rows_per_block(int rows, int tokens) {
   int rpb = 128;
   while (rpb > 8 && (long long)(rows / tokens) * ((tokens + rpb - 1) / rpb) < 148LL * 2) rpb >>= 1;
+  // ... but no more than eight blocks per sample: the last block of a sample adds all of them up
+  while (rpb < 128 && (tokens + rpb - 1) / rpb > 8) rpb <<= 1;
   return rpb;
 }
 
@@ -571,7 +662,7 @@ extern "C" int vb_ln_stats_amax(const void* x, int x_dtype, int rows, int cols, 
 extern "C" int vb_act_amax(const void* z, long long n, int mode, float* history, int history_len, long long index,
                            int delayed, float limit, float* scale_out, unsigned int* scratch, cudaStream_t stream) {
   if (n <= 0) return (int)cudaErrorInvalidValue;
-  const int grid = (int)std::max<long long>(1, std::min<long long>((n / 8 + 255) / 256 / 4, 148 * 8));
+  const int grid = (int)std::max<long long>(1, std::min<long long>((n / 8 + 255) / 256 / 4, kActAmaxBlocks));
   act_amax_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)z, n, mode, history, history_len, index, delayed, limit,
                                             scale_out, scratch);
   return (int)cudaGetLastError();

@@ -44,7 +44,8 @@ def test_precision_policy_and_public_names():
 
 def test_config_defaults_and_one_level_merge(tmp_path):
     config = read_config(dict(sharding=dict(parameters=True), ema=dict(decay=0.5), device="cpu"))
-    assert config["sharding"] == dict(parameters=True, gradients=False, optimizer=True, ema=True, blocks=None)
+    assert config["sharding"] == dict(parameters=True, gradients=False, optimizer=True, ema=True, blocks=None,
+                                      resident="auto")
     assert config["communication"]["bucket_mb"] == 25 and config["communication"]["fp8_tile_size"] == 256
     assert config["ema"] == dict(decay=0.5, dtype="fp32") and config["device"] == "cpu"
     path = tmp_path / "engine.yaml"

@@ -382,3 +382,31 @@ def test_activation_backward_gemm_and_gathered_scale():
         torch.testing.assert_close(scale[0], dz.float().abs().max() / 57344, rtol=1e-6, atol=0)
         assert amax.item() == 0 and history[0].item() == dz.float().abs().max().item()
     ops.check_status()
+
+
+@pytest.mark.parametrize("stream_dtype", [torch.bfloat16, torch.float32])
+def test_carried_stream_gradient_is_added_in_the_layernorm_backward(stream_dtype):
+    """x -> (LN-mod-linear(x), x carried) -> carried + gate * y: same gradients as the two-branch autograd graph."""
+    from viola_b200.nn import gated_residual, norm_modulate_linear
+    torch.manual_seed(2)
+    batch, tokens, width = 4, 128, 384
+    layer = Linear(width, width).cuda()
+    x = torch.randn(batch, tokens, width, device="cuda", dtype=stream_dtype)
+    mod = (torch.randn(batch, 3 * width, device="cuda") * 0.3).bfloat16()
+    dout = torch.randn(batch, tokens, width, device="cuda", dtype=stream_dtype)
+    results = []
+    for carry in (True, False):
+        xs, ms = x.clone().requires_grad_(True), mod.clone().requires_grad_(True)
+        sh, sc, gate = ms.chunk(3, dim=-1)
+        layer.zero_grad()
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            if carry:
+                y, stream = norm_modulate_linear(xs, sh, sc, layer, carry=True)
+            else:
+                y, stream = norm_modulate_linear(xs, sh, sc, layer), xs
+            out = gated_residual(stream, gate, y)
+        out.backward(dout)
+        results.append((out.detach(), xs.grad, ms.grad, layer.weight.grad.clone()))
+    assert torch.equal(results[0][0], results[1][0])
+    assert rel_l2(results[0][1], results[1][1]) < (4e-3 if stream_dtype == torch.bfloat16 else 1e-6)
+    assert torch.equal(results[0][2], results[1][2]) and torch.equal(results[0][3], results[1][3])

@@ -149,7 +149,8 @@ int vb_fused_quantize(const void* x, int x_dtype, int rows, int cols, int mode, 
 // word per sample, left zero) adds them in a fixed order; the outputs are written, not accumulated.
 int vb_row_block_count(int rows, int tokens);
 int vb_ln_modulate_backward(const void* dh, const void* x, int x_dtype, const float* mean, const float* rstd,
-                            const void* mod_scale, long long mod_stride, int rows, int cols, int tokens, void* dx,
+                            const void* mod_scale, long long mod_stride, int rows, int cols, int tokens,
+                            const void* grad_in /* optional, x's dtype: added to dx */, void* dx,
                             float* dshift, float* dscale, float* workspace, long long workspace_floats,
                             unsigned int* tickets, int ticket_count, cudaStream_t stream);
 // out = x + gate[row / tokens] * y (x, out: x_dtype; y, gate: bf16) and the branch side of its backward:

@@ -475,17 +475,20 @@ void fused_quantize(const Tensor& x, int64_t mode, const OptTensor& mean, const 
 }
 
 void ln_modulate_backward(const Tensor& dh, const Tensor& x, const Tensor& mean, const Tensor& rstd, const Tensor& scale,
-                          int64_t tokens, Tensor dx, Tensor dshift, Tensor dscale, Tensor workspace, Tensor tickets) {
+                          int64_t tokens, const OptTensor& grad_in, Tensor dx, Tensor dshift, Tensor dscale, Tensor workspace,
+                          Tensor tickets) {
   cuda_contig(dh, "dh");
   cuda_contig(x, "x");
   cuda_contig(dx, "dx");
   TORCH_CHECK(dh.scalar_type() == at::kBFloat16 && dx.scalar_type() == x.scalar_type());
+  if (grad_in.has_value() && grad_in->defined())
+    TORCH_CHECK(grad_in->is_contiguous() && grad_in->scalar_type() == x.scalar_type() && grad_in->sizes() == x.sizes());
   TORCH_CHECK(dshift.scalar_type() == at::kFloat && dscale.scalar_type() == at::kFloat);
   const int64_t stride = mod_rows(scale, "scale", x.size(1));
   c10::cuda::CUDAGuard guard(x.device());
   check(vb_ln_modulate_backward(dh.data_ptr(), x.data_ptr(), stream_dtype(x, "x"), mean.data_ptr<float>(),
                                 rstd.data_ptr<float>(), scale.data_ptr(), stride, (int)x.size(0), (int)x.size(1),
-                                (int)tokens, dx.data_ptr(), dshift.data_ptr<float>(), dscale.data_ptr<float>(),
+                                (int)tokens, ptr(grad_in), dx.data_ptr(), dshift.data_ptr<float>(), dscale.data_ptr<float>(),
                                 workspace.data_ptr<float>(), workspace.numel(), (unsigned int*)tickets.data_ptr(),
                                 (int)tickets.numel(), stream()),
         "ln_modulate_backward");

@@ -457,8 +457,8 @@ __global__ void __launch_bounds__(256, 2)
 ln_modulate_backward_kernel(const __nv_bfloat16* __restrict__ dh, const T* __restrict__ x,
                             const float* __restrict__ mean, const float* __restrict__ rstd,
                             const __nv_bfloat16* __restrict__ mod_scale, long long mod_stride, int rows, int cols,
-                            int tokens, int rows_per_block, T* __restrict__ dx, float* __restrict__ dshift,
-                            float* __restrict__ dscale, float* __restrict__ workspace,
+                            int tokens, int rows_per_block, const T* __restrict__ grad_in, T* __restrict__ dx,
+                            float* __restrict__ dshift, float* __restrict__ dscale, float* __restrict__ workspace,
                             unsigned int* __restrict__ tickets) {
   extern __shared__ float partial[];            // [8 warps][2][cols]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -507,8 +507,13 @@ ln_modulate_backward_kernel(const __nv_bfloat16* __restrict__ dh, const T* __res
       const int chunk = lane + 32 * j;
       if (chunk < chunks) {
         float o[8];
+        if (grad_in != nullptr) load8(grad_in + base + chunk * 8, o);     // gradient arriving on the residual path
+        else {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = rs * (g[j][e] - mean_g - xh[j][e] * mean_gx);
+          for (int e = 0; e < 8; ++e) o[e] = 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] += rs * (g[j][e] - mean_g - xh[j][e] * mean_gx);
         store8(dx + base + chunk * 8, o);
       }
     }
@@ -703,11 +708,11 @@ extern "C" int vb_fused_quantize(const void* x, int x_dtype, int rows, int cols,
 
 extern "C" int vb_ln_modulate_backward(const void* dh, const void* x, int x_dtype, const float* mean, const float* rstd,
                                        const void* mod_scale, long long mod_stride, int rows, int cols, int tokens,
-                                       void* dx, float* dshift, float* dscale, float* workspace,
+                                       const void* grad_in, void* dx, float* dshift, float* dscale, float* workspace,
                                        long long workspace_floats, unsigned int* tickets, int ticket_count,
                                        cudaStream_t stream) {
   if (rows <= 0 || cols <= 0 || tokens <= 0 || rows % tokens != 0 || cols % 8 != 0 || mod_stride % 8 != 0 ||
-      x_dtype > kBF16 || !aligned16(dh) || !aligned16(x) || !aligned16(dx) || !aligned16(mod_scale))
+      x_dtype > kBF16 || !aligned16(dh) || !aligned16(x) || !aligned16(dx) || !aligned16(mod_scale) || !aligned16(grad_in))
     return (int)cudaErrorInvalidValue;
   const int rows_per_block = pick_rows_per_block(rows, tokens);
   const int blocks_per_sample = (tokens + rows_per_block - 1) / rows_per_block;
@@ -719,11 +724,12 @@ extern "C" int vb_ln_modulate_backward(const void* dh, const void* x, int x_dtyp
   if (x_dtype == kBF16) {
     VB_VPL_SWITCH(cols, (allow_smem(ln_modulate_backward_kernel<__nv_bfloat16, VPL>), ln_modulate_backward_kernel<__nv_bfloat16, VPL><<<grid, 256, smem, stream>>>(
                             (const __nv_bfloat16*)dh, (const __nv_bfloat16*)x, mean, rstd, sc, mod_stride, rows, cols,
-                            tokens, rows_per_block, (__nv_bfloat16*)dx, dshift, dscale, workspace, tickets)));
+                            tokens, rows_per_block, (const __nv_bfloat16*)grad_in, (__nv_bfloat16*)dx, dshift, dscale,
+                            workspace, tickets)));
   } else {
     VB_VPL_SWITCH(cols, (allow_smem(ln_modulate_backward_kernel<float, VPL>), ln_modulate_backward_kernel<float, VPL><<<grid, 256, smem, stream>>>(
                             (const __nv_bfloat16*)dh, (const float*)x, mean, rstd, sc, mod_stride, rows, cols, tokens,
-                            rows_per_block, (float*)dx, dshift, dscale, workspace, tickets)));
+                            rows_per_block, (const float*)grad_in, (float*)dx, dshift, dscale, workspace, tickets)));
   }
   return (int)cudaGetLastError();
 }

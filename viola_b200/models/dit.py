@@ -51,10 +51,13 @@ class Block(nn.Module):
         b, n, d = x.shape
         # LayerNorm + modulate are folded into the FP8 quantiser of qkv / fc1, GELU into that of fc2 (forward)
         # and into the fc2 dgrad epilogue (backward)
-        qkv = norm_modulate_linear(x, s1, a1, self.qkv, eps=self.norm1.eps)
+        # ``carry``: the residual connection takes x back from the fused function, so that its gradient is added
+        # inside the LayerNorm backward kernel
+        qkv, x = norm_modulate_linear(x, s1, a1, self.qkv, eps=self.norm1.eps, carry=True)
         h = packed_attention(qkv.view(b, n, 3, self.heads, d // self.heads))
         x = gated_residual(x, g1, self.proj(h))
-        return gated_residual(x, g2, norm_modulate_mlp(x, s2, a2, self.fc1, self.fc2, "gelu", eps=self.norm2.eps))
+        h, x = norm_modulate_mlp(x, s2, a2, self.fc1, self.fc2, "gelu", eps=self.norm2.eps, carry=True)
+        return gated_residual(x, g2, h)
 
 
 class DiT(nn.Module):

@@ -36,6 +36,13 @@ def _eligible(layer, x, max_width=None, dtypes=(torch.bfloat16,)):
             and (max_width is None or x.shape[-1] <= max_width))
 
 
+def _stream_grad(dstream, x2):
+    """The gradient that arrived for the carried stream, as the 2-D tensor the LayerNorm backward adds in."""
+    if dstream is None:
+        return None
+    return dstream.reshape(x2.shape).to(x2.dtype).contiguous()
+
+
 def _needs(ctx, positions):
     return [ctx.needs_input_grad[p] for p in positions]
 
@@ -59,16 +66,20 @@ class _NormModulateLinear(torch.autograd.Function):
         ctx.save_for_backward(x2, scale, mean, rstd)
         ctx.layer, ctx.saved, ctx.shape, ctx.need_b = layer, saved, x.shape, need_b
         ctx.mod_dtypes = (shift.dtype, scale.dtype)
-        return y.reshape(batch, tokens, -1)
+        ctx.set_materialize_grads(False)
+        # second output: the stream itself, for the residual connection that follows (see ``carry``)
+        return y.reshape(batch, tokens, -1), x.view_as(x)
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dstream):
         x2, scale, mean, rstd = ctx.saved_tensors
         layer = ctx.layer
+        if dy is None:
+            return (dstream, None, None, None, None, None, None)
         dy2 = dy.reshape(-1, layer.out_features).contiguous()
         dh, dw, db = linear_backward(layer, ctx.saved, dy2, need_input_grad=True, need_weight_grad=ctx.needs_input_grad[3],
                                      need_bias_grad=ctx.need_b)
-        dx, dshift, dscale = ops.ln_modulate_backward(dh, x2, mean, rstd, scale, ctx.shape[1])
+        dx, dshift, dscale = ops.ln_modulate_backward(dh, x2, mean, rstd, scale, ctx.shape[1], _stream_grad(dstream, x2))
         return (dx.view(ctx.shape), dshift.to(ctx.mod_dtypes[0]), dscale.to(ctx.mod_dtypes[1]), dw, db, None, None)
 
 
@@ -138,10 +149,13 @@ class _NormModulateMLP(torch.autograd.Function):
         ctx.layers, ctx.saved, ctx.shape = (fc1, fc2), (saved1, saved2), x.shape
         ctx.need_bias = (b1 is not None and need[4], b2 is not None and need[6])
         ctx.mod_dtypes = (shift.dtype, scale.dtype)
-        return y.reshape(batch, tokens, -1)
+        ctx.set_materialize_grads(False)
+        return y.reshape(batch, tokens, -1), x.view_as(x)
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dstream):
+        if dy is None:
+            return (dstream,) + (None,) * 10
         x2, scale, mean, rstd, slope = ctx.saved_tensors
         fc1, fc2 = ctx.layers
         saved1, saved2 = ctx.saved
@@ -153,13 +167,17 @@ class _NormModulateMLP(torch.autograd.Function):
         dh, dw1, db1 = linear_backward(fc1, saved1, dz, need_input_grad=True, need_weight_grad=need[3],
                                        need_bias_grad=ctx.need_bias[0], grad_amax=amax)
         del dz
-        dx, dshift, dscale = ops.ln_modulate_backward(dh, x2, mean, rstd, scale, ctx.shape[1])
+        dx, dshift, dscale = ops.ln_modulate_backward(dh, x2, mean, rstd, scale, ctx.shape[1], _stream_grad(dstream, x2))
         return (dx.view(ctx.shape), dshift.to(ctx.mod_dtypes[0]), dscale.to(ctx.mod_dtypes[1]), dw1, db1, dw2, db2,
                 None, None, None, None)
 
 
-def norm_modulate_mlp(x, shift, scale, fc1, fc2, activation="gelu", *, eps=1e-6):
-    """``fc2(act(fc1(LayerNorm(x) * (1 + scale[:, None]) + shift[:, None])))`` for ``x`` [batch, tokens, width]."""
+def norm_modulate_mlp(x, shift, scale, fc1, fc2, activation="gelu", *, eps=1e-6, carry=False):
+    """``fc2(act(fc1(LayerNorm(x) * (1 + scale[:, None]) + shift[:, None])))`` for ``x`` [batch, tokens, width].
+
+    ``carry=True`` returns ``(result, x)``: use the returned ``x`` for the residual connection that follows.  Its
+    gradient then reaches the LayerNorm backward kernel, which adds it to its own input gradient in the same pass
+    (instead of autograd summing the two branches with a separate kernel)."""
     if (x.is_cuda and torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16
             and x.dim() == 3 and torch.is_grad_enabled() and x.requires_grad
             and _eligible(fc1, x, 2048, _STREAM_DTYPES) and fc1.in_place_operands
@@ -167,9 +185,11 @@ def norm_modulate_mlp(x, shift, scale, fc1, fc2, activation="gelu", *, eps=1e-6)
             and fc2.saved_input_dtype == "fp8"):
         shift, scale = shift.to(torch.bfloat16), scale.to(torch.bfloat16)
         if _rows_of(shift, x) and _rows_of(scale, x) and shift.stride(0) == scale.stride(0):
-            return _NormModulateMLP.apply(x, shift, scale, fc1.weight, fc1.bias, fc2.weight, fc2.bias, fc1, fc2,
-                                          activation, eps)
-    return activation_linear(norm_modulate_linear(x, shift, scale, fc1, eps=eps), fc2, activation)
+            result, stream = _NormModulateMLP.apply(x, shift, scale, fc1.weight, fc1.bias, fc2.weight, fc2.bias, fc1,
+                                                    fc2, activation, eps)
+            return (result, stream) if carry else result
+    result = activation_linear(norm_modulate_linear(x, shift, scale, fc1, eps=eps), fc2, activation)
+    return (result, x) if carry else result
 
 
 def _rows_of(vector, x):
@@ -178,21 +198,28 @@ def _rows_of(vector, x):
             and vector.stride(1) == 1 and vector.stride(0) % 8 == 0 and vector.data_ptr() % 16 == 0)
 
 
-def norm_modulate_linear(x, shift, scale, layer, *, eps=1e-6):
-    """``layer(LayerNorm(x) * (1 + scale[:, None]) + shift[:, None])`` for ``x`` [batch, tokens, width]."""
+def norm_modulate_linear(x, shift, scale, layer, *, eps=1e-6, carry=False):
+    """``layer(LayerNorm(x) * (1 + scale[:, None]) + shift[:, None])`` for ``x`` [batch, tokens, width].
+    ``carry=True`` returns ``(result, x)`` as in :func:`norm_modulate_mlp`."""
+    stream = x
+    fused = False
     if x.is_cuda and torch.is_autocast_enabled("cuda"):
         dtype = torch.get_autocast_dtype("cuda")
         shift, scale = shift.to(dtype), scale.to(dtype)
-        if (dtype == torch.bfloat16 and _eligible(layer, x, 2048, _STREAM_DTYPES) and x.dim() == 3 and _rows_of(shift, x)
-                and _rows_of(scale, x) and shift.stride(0) == scale.stride(0) and torch.is_grad_enabled()
-                and x.requires_grad):
-            return _NormModulateLinear.apply(x, shift, scale, layer.weight, layer.bias, layer, eps)
-        x = x.to(dtype)
-    elif (_eligible(layer, x, 2048) and x.dim() == 3 and _rows_of(shift, x) and _rows_of(scale, x)
-          and shift.stride(0) == scale.stride(0) and torch.is_grad_enabled() and x.requires_grad):
-        return _NormModulateLinear.apply(x, shift, scale, layer.weight, layer.bias, layer, eps)
-    normed = F.layer_norm(x, (x.shape[-1],), eps=eps)
-    return layer(torch.addcmul(shift[:, None], normed, (1 + scale)[:, None]))
+        fused = (dtype == torch.bfloat16 and _eligible(layer, x, 2048, _STREAM_DTYPES) and x.dim() == 3
+                 and _rows_of(shift, x) and _rows_of(scale, x) and shift.stride(0) == scale.stride(0)
+                 and torch.is_grad_enabled() and x.requires_grad)
+        if not fused:
+            x = x.to(dtype)
+    else:
+        fused = (_eligible(layer, x, 2048) and x.dim() == 3 and _rows_of(shift, x) and _rows_of(scale, x)
+                 and shift.stride(0) == scale.stride(0) and torch.is_grad_enabled() and x.requires_grad)
+    if fused:
+        result, stream = _NormModulateLinear.apply(x, shift, scale, layer.weight, layer.bias, layer, eps)
+    else:
+        normed = F.layer_norm(x, (x.shape[-1],), eps=eps)
+        result = layer(torch.addcmul(shift[:, None], normed, (1 + scale)[:, None]))
+    return (result, stream) if carry else result
 
 
 def activation_linear(z, layer, activation="gelu"):

@@ -687,14 +687,15 @@ def activation_quantize(z, activation, *, history=None, index=0, delayed=False, 
     return (q, qt, qscale, slope_out) if slope else (q, qt, qscale)
 
 
-def ln_modulate_backward(dh, x, mean, rstd, scale, tokens):
-    """Gradients of LN + modulate: returns (dx [rows, cols] in x's dtype, dshift, dscale [samples, cols] fp32)."""
+def ln_modulate_backward(dh, x, mean, rstd, scale, tokens, grad_in=None):
+    """Gradients of LN + modulate: returns (dx [rows, cols] in x's dtype, dshift, dscale [samples, cols] fp32).
+    ``grad_in`` (x's shape and dtype) is added to dx: the gradient that reaches x along the residual path."""
     rows, cols = x.shape
     dx = torch.empty_like(x)
     dshift = torch.empty((rows // tokens, cols), device=x.device, dtype=torch.float32)
     dscale = torch.empty_like(dshift)
     workspace, tickets = _sample_sum_workspace(x.device, rows, tokens, 2 * cols)
-    _ops().ln_modulate_backward(dh, x, mean, rstd, scale, int(tokens), dx, dshift, dscale, workspace, tickets)
+    _ops().ln_modulate_backward(dh, x, mean, rstd, scale, int(tokens), grad_in, dx, dshift, dscale, workspace, tickets)
     _count()
     return dx, dshift, dscale
 

@@ -599,6 +599,9 @@ class Linear(nn.Module):
                 self.weight_transpose = ops.transpose(self.weight)
 
     def clear_weight_cache(self):
+        if self.weight_transpose.numel() == 0 and (not hasattr(self, "weight_transpose_scale")
+                                                  or self.weight_transpose_scale.numel() == 0):
+            return                      # nothing cached (the usual case on the write-back path)
         self.weight_transpose = self.weight_transpose.new_empty((0, 0))
         if hasattr(self, "weight_transpose_scale"):
             self.weight_transpose_scale = self.weight_transpose_scale.new_empty((0, 0))

@@ -49,7 +49,7 @@ def main():
             wire = n * (1 + 4 / tile)
             # ---- reduce to owner ----
             owner = 0
-            transport = PeerTransport(engine, tile_size=tile, max_blocks=64)
+            transport = PeerTransport(engine, tile_size=tile, overlap=False)   # full-width kernels, as the engine runs them
             accum = torch.zeros(n, device=device) if rank == owner else None
             transport.attach_gradients([(owner, [], n)], [accum], n)
             transport.finalize()
@@ -87,7 +87,7 @@ def main():
                                  note="time includes the fp32 staging copy on every rank"))
             del transport, library
             # ---- all-reduce with requantisation ----
-            transport = PeerTransport(engine, tile_size=tile, max_blocks=128)
+            transport = PeerTransport(engine, tile_size=tile, overlap=False)
             transport.attach_all_reduce(n)
             transport.finalize()
             transport.finalize_all_reduce()

@@ -1,6 +1,9 @@
 // tcgen05 / TMEM / TMA GEMM family for sm_100a.
 //
-//   D[M, N] = A[M, K] . B[N, K]^T     (both operands K-major)
+//   D[M, N] = A[M, K] . B[N, K]^T
+//
+// Either operand may be K-major (as written) or MN-major (the tensor holds the transpose, [K, M] / [K, N]); the
+// producer then loads 128-byte-of-MN x K-row boxes and the UMMA descriptors use the MN-major SWIZZLE_128B form.
 //
 // One persistent, warp-specialised kernel template covers every GEMM-shaped op in
 // the library:
@@ -17,9 +20,12 @@
 //   * Newton-Schulz GEMMs in bf16 / fp16 with the two polynomial epilogues, an
 //     optional transposed second output and a symmetric-output mode
 //                                                     [viola/optim/_orthogonalize_kernels.py:16-50]
+//   * dgrad through an activation: D = round(A . B^T) * slope with the amax of D gathered on the fly
 //
 // Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer (one elected lane)
-// and TMEM owner, warps 2-5 = epilogue (TMEM lane quadrant = warp % 4).
+// and TMEM owner, warps 2-5 = epilogue (TMEM lane quadrant = warp % 4); the AXPBY and ACT_BWD
+// epilogues add warp 6, which TMA-loads their second operand into a ring of 128x32 slabs that the
+// epilogue warps rewrite in place and TMA-store (LINEAR stages and TMA-stores its tile per warp).
 // Pipeline: smem ring (full/empty mbarriers, TMA complete_tx / tcgen05.commit) and a
 // TMEM accumulator ring (tmem_full via tcgen05.commit, tmem_empty via epilogue arrive).
 // TMA loads are never cluster-multicast.  Every wait is bounded (common/ptx.cuh).

@@ -270,3 +270,23 @@ def checkpoint_worker(rank, world, port, directory):
 def test_checkpoint_directory_layout():
     with tempfile.TemporaryDirectory() as directory:
         run_world(checkpoint_worker, 2, directory)
+
+
+def test_phase_tracing_is_inert_by_default_and_times_when_enabled():
+    from viola_b200 import utils
+    with utils.phase("anything"):
+        pass
+    assert utils.phase_times() == {}
+    utils.enable_timing(True)
+    try:
+        with utils.phase("optimizer"):
+            sum(range(1000))
+        with utils.phase("optimizer"):
+            pass
+        with utils.phase("ema"):
+            pass
+        times = utils.phase_times()
+        assert set(times) == {"optimizer", "ema"} and times["optimizer"] >= 0.0
+        assert utils.phase_times() == {}
+    finally:
+        utils.enable_timing(False)

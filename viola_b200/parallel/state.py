@@ -12,6 +12,7 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from ..utils.trace import phase
 from .config import dtype as to_dtype
 from .ema import EMAState
 from .gradients import GradientState
@@ -53,13 +54,16 @@ class DistributedState:
     def backward(self, loss):
         self.gradients.begin_backward()
         try:
-            loss.backward()
+            with phase("backward"):
+                loss.backward()
         finally:
-            self.gradients.finish_backward()
+            with phase("reduce"):
+                self.gradients.finish_backward()
 
     @torch.no_grad()
     def step(self, divisor):
-        active = self.gradients.reduce(divisor)
+        with phase("reduce"):
+            active = self.gradients.reduce(divisor)
         if not any(active):
             self.zero_grad()
             return False
@@ -72,11 +76,14 @@ class DistributedState:
                 optimizer.step_was_skipped = True
                 self.zero_grad()
                 return False
-        self.optimizer.materialize()
-        self.optimizer.attach_gradients(self.gradients, active)
-        self.optimizer.step()
-        self.optimizer.writeback(active)
-        self.ema.update()
+        with phase("optimizer"):
+            self.optimizer.materialize()
+            self.optimizer.attach_gradients(self.gradients, active)
+            self.optimizer.step()
+        with phase("writeback"):
+            self.optimizer.writeback(active)
+        with phase("ema"):
+            self.ema.update()
         self.zero_grad()
         return True
 

@@ -263,8 +263,11 @@ class _GraphedMicrobatch:
         if engine.transport is not None:
             engine.transport.forget_events()
         self.graph = torch.cuda.CUDAGraph()
+        from .. import ops
+        before = ops.launch_count
         with torch.cuda.graph(self.graph):
             self.static_loss = self._run()
+        self.captured_launches = ops.launch_count - before      # library kernels inside one replay
         if engine.transport is not None:
             engine.transport.forget_events()
         self.marks = engine.state.gradients.capture_marks()
@@ -280,8 +283,12 @@ class _GraphedMicrobatch:
         self.calls += 1
         if self.graph is None and self.calls <= self.eager_calls:
             return self._run()
-        if self.graph is None:
+        captured_now = self.graph is None
+        if captured_now:
             self._capture()          # capturing records the work without running it: replay right away
         engine.state.gradients.replay_marks(self.marks)
         self.graph.replay()
+        if not captured_now:         # the capture itself already counted its kernels once
+            from .. import ops
+            ops._count(self.captured_launches)                   # keep ops.launch_count = kernels actually launched
         return self.static_loss

@@ -49,6 +49,9 @@ def parse():
     parser.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
     parser.add_argument("--scaling", default="current", choices=("current", "delayed", "grouped"))
     parser.add_argument("--backend", default="auto", choices=("auto", "p2p", "nccl"))
+    parser.add_argument("--ref-microbatch", type=int, default=0,
+                        help="reference arm only: images per microbatch (raises the accumulation steps above the "
+                             "named config's 2 to keep the global batch); 0 = the named config")
     parser.add_argument("--no-e2e", action="store_true")
     parser.add_argument("--no-graph", action="store_true", help="run every microbatch eagerly (no CUDA graph)")
     return parser.parse_args()
@@ -241,6 +244,33 @@ def run_ours(args):
     dist.destroy_process_group()
 
 
+REFERENCE_SHIM = "sys.modules alias tilelang.cuda[.intrinsics] -> tilelang.intrinsics (harness only)"
+
+
+def alias_tilelang_intrinsics():
+    """Make ``tilelang.cuda.intrinsics`` importable on a TileLang that ships the same classes elsewhere.
+
+    The reference's kernel modules do ``from tilelang.cuda.intrinsics import TensorCoreIntrinEmitter``
+    (its pinned TileLang 0.1.15 layout); TileLang 0.1.9 exposes that class as
+    ``tilelang.intrinsics.TensorCoreIntrinEmitter``.  Two ``sys.modules`` entries in this harness bridge
+    the two layouts; nothing under ``baseline/_ref`` is edited.  Returns True when the alias was needed.
+    """
+    import importlib
+    import types
+    try:
+        importlib.import_module("tilelang.cuda.intrinsics")
+        return False
+    except ImportError:
+        pass
+    intrinsics = importlib.import_module("tilelang.intrinsics")
+    package = types.ModuleType("tilelang.cuda")
+    package.__path__ = []
+    package.intrinsics = intrinsics
+    sys.modules["tilelang.cuda"] = package
+    sys.modules["tilelang.cuda.intrinsics"] = intrinsics
+    return True
+
+
 def run_reference(args):
     """The unmodified reference package from baseline/_ref, driven through its own engine."""
     rank = int(os.environ.get("RANK", 0))
@@ -248,19 +278,26 @@ def run_reference(args):
 
     def unavailable(reason):
         if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": reason}), flush=True)
+            print(json.dumps({"impl": "reference", "unavailable": reason, "shim": REFERENCE_SHIM}), flush=True)
         return 0
 
     if not os.path.isdir(os.path.join(reference_root, "viola")):
         return unavailable("baseline/_ref is not installed (pip --no-index --no-deps --target baseline/_ref)")
+    # JIT results of the reference's TileLang kernels are kept beside the install, so a box that
+    # receives this folder with a warm cache does not compile them again
+    os.environ.setdefault("TILELANG_CACHE_DIR", os.path.join(reference_root, "tilelang_cache"))
     sys.path.insert(0, reference_root)
+    if "RANK" not in os.environ:       # single process without a launcher: the reference engine reads env://
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29534")
+        os.environ.update(RANK="0", WORLD_SIZE="1", LOCAL_RANK="0")
     try:
+        shimmed = alias_tilelang_intrinsics()
         import viola  # noqa: F401  (the reference package)
     except Exception as error:
-        return unavailable(f"import viola failed: {type(error).__name__}: {str(error).splitlines()[0][:160]} "
-                           "(reference pins tilelang==0.1.15; this image ships tilelang 0.1.9)")
+        return unavailable(f"import viola failed: {type(error).__name__}: {str(error).splitlines()[0][:160]}")
     from baseline.reference_arm import run
-    return run(args, unavailable)
+    return run(args, unavailable, REFERENCE_SHIM if shimmed else None)
 
 
 if __name__ == "__main__":

@@ -22,7 +22,7 @@ OBJ = ROOT / "build"
 TARGET = ROOT / "_C.so"
 
 CUDA_SOURCES = ["quant.cu", "gemm_sm100.cu", "optim.cu", "codec.cu", "comm.cu", "fused.cu", "multi.cu", "noalloc.cu"]
-CPP_SOURCES = ["bindings.cpp", "runtime.cpp"]
+CPP_SOURCES = ["bindings.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -203,6 +203,13 @@ int vb_quantize_push(const void* master, int master_dtype, long long rows, long 
                      long long dst_offset, long long shard_rows, int max_blocks, cudaStream_t stream);
 int vb_byte_push(const void* src, long long bytes, const VbPeerTable* peers, long long dst_offset,
                  long long shard_bytes, int max_blocks, cudaStream_t stream);
+// Path 4, fused: the whole write-back of an owner in two launches over a device table of 128-byte rows
+// {master, ema, amax slot, n, slab_elems, dst_offset, header_offset, base_index, limit, history_len,
+//  master_dtype, ema_dtype, mode, out_dtype}: (A) EMA lerp + per-tensor amax, (B) scale + encode / cast +
+// stores into the rank that holds each row slab + header (scale, history slot) into every rank.
+// prefix: int32[rows + 1] prefix sums of 4096-element chunks; amax slots must be zero on entry.
+int vb_multi_writeback(const void* table, const int* prefix, int rows, int blocks, float decay, int with_ema,
+                       const VbPeerTable* peers, long long calls, cudaStream_t stream);
 // flags[rank] = value on every peer (and optionally on this rank); bounded wait on local flags
 int vb_signal(const VbPeerTable* peers, long long flag_offset, int value, int include_self, cudaStream_t stream);
 int vb_wait_flags(const int* flags, int count, int skip, int expected, long long wait_clocks, int* status,

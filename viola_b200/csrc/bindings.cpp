@@ -394,6 +394,18 @@ void byte_push(const Tensor& src, at::IntArrayRef heaps, int64_t rank, int64_t d
         "byte_push");
 }
 
+void multi_writeback(const Tensor& table, const Tensor& prefix, int64_t blocks, double decay, bool with_ema,
+                     at::IntArrayRef heaps, int64_t rank, int64_t calls) {
+  TORCH_CHECK(table.is_cuda() && table.scalar_type() == at::kLong && table.is_contiguous() && table.numel() % 16 == 0,
+              "write-back table must be a contiguous CUDA int64 tensor of 16-word rows");
+  TORCH_CHECK(prefix.is_cuda() && prefix.scalar_type() == at::kInt && prefix.numel() == table.numel() / 16 + 1);
+  c10::cuda::CUDAGuard guard(table.device());
+  VbPeerTable peers = peer_table(heaps, rank);
+  check(vb_multi_writeback(table.data_ptr(), prefix.data_ptr<int>(), (int)(table.numel() / 16), (int)blocks, (float)decay,
+                           with_ema ? 1 : 0, &peers, calls, stream()),
+        "multi_writeback");
+}
+
 void signal(at::IntArrayRef heaps, int64_t rank, int64_t flag_offset, int64_t value, bool include_self) {
   VbPeerTable table = peer_table(heaps, rank);
   check(vb_signal(&table, flag_offset, (int)value, include_self, stream()), "signal");
@@ -585,6 +597,7 @@ TORCH_LIBRARY(viola_b200, m) {
   m.def("allreduce_requant_fp8", &allreduce_requant_fp8);
   m.def("quantize_push", &quantize_push);
   m.def("byte_push", &byte_push);
+  m.def("multi_writeback", &multi_writeback);
   m.def("signal", &signal);
   m.def("wait_flags", &wait_flags);
   m.def("gather_pull", &gather_pull);

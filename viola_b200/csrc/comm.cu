@@ -90,16 +90,22 @@ __device__ __forceinline__ bool block_wait_flags(const int* flags, int count, in
 }
 
 // Last block to arrive (after every thread fenced its peer stores) gets `true`; the counter resets itself.
-__device__ __forceinline__ bool last_block_done(unsigned int* counter) {
+// The counter word carries the number of arrived blocks in its low 24 bits and a "some block gave up"
+// mark in bit 31: every block takes a ticket whether or not its wait succeeded, so one timed-out launch
+// leaves the counter at zero for the next one, and the last block returns false when any block failed
+// (the caller then publishes nothing).
+__device__ __forceinline__ bool last_block_done(unsigned int* counter, bool ok = true) {
   __shared__ bool last;
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
-    const unsigned int ticket = atomicAdd(counter, 1u);
-    last = ticket == gridDim.x - 1;
+    const unsigned int ticket = atomicAdd(counter, ok ? 1u : (1u | 0x80000000u));
+    const bool failed = !ok || (ticket & 0x80000000u) != 0u;
+    last = (ticket & 0x00ffffffu) == gridDim.x - 1;
     if (last) {
       *counter = 0u;
       __threadfence_system();
+      last = !failed;
     }
   }
   __syncthreads();
@@ -118,12 +124,15 @@ reduce_push_kernel(const float* __restrict__ bucket, long long n, int fmt, uint8
   // signals a fresh value on every replay.
   const int generation = *generation_ptr;
   // The owner must have consumed the previous generation of this slot before it is overwritten.
-  if (generation > 1 && !block_wait_flags(ack_flag, 1, -1, generation - 1, budget, status)) return;
+  // A block whose wait ran out skips its share of the data but still takes its ticket below, so the
+  // self-resetting counter ends at zero; the flag is then not raised (the failure is in the status word).
+  const bool ready = generation <= 1 || block_wait_flags(ack_flag, 1, -1, generation - 1, budget, status);
   const long long tiles = (n + TILE - 1) / TILE;
   const int lane = threadIdx.x & 31;
-  for (long long t = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); t < tiles; t += (long long)gridDim.x * 8)
-    pack_tile<TILE>(bucket, t * TILE, n, fmt, dst_codes + t * TILE, dst_scales + t, lane);
-  if (last_block_done(counter) && threadIdx.x == 0) st_release_sys(dst_flag, generation);
+  if (ready)
+    for (long long t = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); t < tiles; t += (long long)gridDim.x * 8)
+      pack_tile<TILE>(bucket, t * TILE, n, fmt, dst_codes + t * TILE, dst_scales + t, lane);
+  if (last_block_done(counter, ready) && threadIdx.x == 0) st_release_sys(dst_flag, generation);
 }
 
 // Quantise-dequantise of the owner's own contribution with exactly the codec's arithmetic.
@@ -145,10 +154,10 @@ reduce_accumulate_kernel(const float* __restrict__ bucket, long long n, int fmt,
                          const int* generation_ptr, float* __restrict__ accum, unsigned int* counter, long long budget,
                          int* status) {
   const int generation = *generation_ptr;
-  if (!block_wait_flags(flags, peers.world, peers.rank, generation, budget, status)) return;
+  const bool ready = block_wait_flags(flags, peers.world, peers.rank, generation, budget, status);
   const long long tiles = (n + TILE - 1) / TILE;
   const int lane = threadIdx.x & 31;
-  for (long long t = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); t < tiles; t += (long long)gridDim.x * 8) {
+  for (long long t = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); ready && t < tiles; t += (long long)gridDim.x * 8) {
     float own[TILE / 32], result[TILE / 32];
     load_tile<TILE>(bucket, t * TILE, n, lane, own);
     fake_quantize_tile<TILE>(own, fmt);
@@ -166,7 +175,7 @@ reduce_accumulate_kernel(const float* __restrict__ bucket, long long n, int fmt,
     }
     store_tile<TILE>(accum, t * TILE, n, lane, result, true);
   }
-  if (last_block_done(counter) && threadIdx.x < peers.world && (int)threadIdx.x != peers.rank)
+  if (last_block_done(counter, ready) && threadIdx.x < peers.world && (int)threadIdx.x != peers.rank)
     st_release_sys(reinterpret_cast<int*>(peers.heap[threadIdx.x] + ack_offset), generation);
 }
 
@@ -200,11 +209,11 @@ allreduce_reduce_kernel(const float* __restrict__ value, long long n, int groups
                         long long gather_offset, long long slot, long long a2a_flag_offset, long long gather_flag_offset,
                         int generation, unsigned int* counter, long long budget, int* status) {
   const int* flags = reinterpret_cast<const int*>(peers.heap[peers.rank] + a2a_flag_offset);
-  if (!block_wait_flags(flags, peers.world, peers.rank, generation, budget, status)) return;
+  const bool ready = block_wait_flags(flags, peers.world, peers.rank, generation, budget, status);
   const long long width = (long long)groups * TILE;
   const int lane = threadIdx.x & 31;
   const uint8_t* recv = peers.heap[peers.rank] + a2a_offset;
-  for (long long g = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); g < groups; g += (long long)gridDim.x * 8) {
+  for (long long g = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); ready && g < groups; g += (long long)gridDim.x * 8) {
     float own[TILE / 32], partial[TILE / 32];
     load_tile<TILE>(value, peers.rank * width + g * TILE, n, lane, own);
     fake_quantize_tile<TILE>(own, fmt);
@@ -245,7 +254,7 @@ allreduce_reduce_kernel(const float* __restrict__ value, long long n, int groups
       if (lane == 0) reinterpret_cast<float*>(base + width)[g] = scale;
     }
   }
-  if (last_block_done(counter) && threadIdx.x < peers.world)
+  if (last_block_done(counter, ready) && threadIdx.x < peers.world)
     st_release_sys(reinterpret_cast<int*>(peers.heap[threadIdx.x] + gather_flag_offset) + peers.rank, generation);
 }
 
@@ -298,6 +307,149 @@ quantize_push_kernel(const void* __restrict__ master, int mdt, long long rows, l
       *reinterpret_cast<uint32_t*>(peers.heap[d] + dst_offset + (i4 - (long long)d * shard_rows * cols)) = word;
     }
   }
+}
+
+// ------------------------------------------------------------------------------------------
+// path 4, whole write-back of an owner in two launches over a device-resident table
+// ------------------------------------------------------------------------------------------
+// One row per parameter this rank owns.  The reference does, per parameter and per step: amax -> scale ->
+// quantise on the owner, scatter / broadcast of the codes, three small broadcasts (scale, amax history,
+// call index) with a host sync, and later a separate EMA lerp (viola/distributed/parameters.py:121-147,
+// viola/distributed/ema.py:100-113).  Here launch A reads every owned master once (EMA lerp + per-tensor
+// amax), launch B reads it again (from L2 for all but the largest sets), encodes and stores the codes into
+// the row slab of whichever rank holds those rows, and stores the layer header (scale, history slot) into
+// every rank's copy of it.
+struct WriteDesc {
+  long long master;         // pointer: the updated master weight (fp32 / bf16 / fp16), contiguous
+  long long ema;            // pointer: its running average, or 0
+  long long amax;           // pointer: one uint32 slot (float bits), zeroed by the host before launch A
+  long long n;              // elements
+  long long slab_elems;     // elements per destination row slab (shard rows x row length); rank = element / slab_elems
+  long long dst_offset;     // byte offset of this parameter's slab inside every rank's heap
+  long long header_offset;  // byte offset of [scale, history[0..len)] inside every rank's heap, or -1
+  long long base_index;     // quantizer call index when the table was built
+  float limit;              // quantisation limit of FP8 rows
+  int history_len;
+  int master_dtype, ema_dtype;
+  int mode;                 // 0 = e4m3 codes, 1 = e5m2 codes, 2 = cast to out_dtype
+  int out_dtype;
+  long long reserved[5];
+};
+static_assert(sizeof(WriteDesc) == 128, "write-back descriptor is 16 x 8 bytes");
+
+constexpr int kWriteChunk = 4096;
+
+__device__ __forceinline__ int find_row(const int* __restrict__ prefix, int rows, int block) {
+  int lo = 0, hi = rows;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (prefix[mid] <= block) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// Launch A: ema <- decay * ema + (1 - decay) * master (when the row has an average and with_ema) and the
+// per-tensor amax of FP8 rows (NaN ignored, as the stand-alone amax kernel does).
+__global__ void __launch_bounds__(256)
+writeback_amax_kernel(const WriteDesc* __restrict__ table, const int* __restrict__ prefix, int rows, float decay,
+                      int with_ema) {
+  const int t = find_row(prefix, rows, blockIdx.x);
+  const WriteDesc d = table[t];
+  const long long begin = (long long)(blockIdx.x - prefix[t]) * kWriteChunk;
+  const long long end = min(begin + kWriteChunk, d.n);
+  const void* master = reinterpret_cast<const void*>(d.master);
+  void* ema = with_ema ? reinterpret_cast<void*>(d.ema) : nullptr;
+  if (ema == nullptr && d.mode == 2) return;
+  float m = 0.f;
+  const bool vec = d.master_dtype == kF32 && (d.master & 15) == 0 && (ema == nullptr || (d.ema_dtype == kF32 && (d.ema & 15) == 0));
+  if (vec) {
+    const long long vend = begin + ((end - begin) & ~3LL);
+    for (long long i = begin + 4LL * threadIdx.x; i < vend; i += 4LL * blockDim.x) {
+      const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(master) + i);
+      if (ema != nullptr) {
+        float4 e = *reinterpret_cast<float4*>(reinterpret_cast<float*>(ema) + i);
+        e.x = fmaf(1.f - decay, v.x, e.x * decay);
+        e.y = fmaf(1.f - decay, v.y, e.y * decay);
+        e.z = fmaf(1.f - decay, v.z, e.z * decay);
+        e.w = fmaf(1.f - decay, v.w, e.w * decay);
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(ema) + i) = e;
+      }
+      m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+    }
+    for (long long i = vend + threadIdx.x; i < end; i += blockDim.x) {
+      const float v = reinterpret_cast<const float*>(master)[i];
+      if (ema != nullptr) reinterpret_cast<float*>(ema)[i] = fmaf(1.f - decay, v, reinterpret_cast<float*>(ema)[i] * decay);
+      m = fmaxf(m, fabsf(v));
+    }
+  } else {
+    for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
+      const float v = load_as_float(master, i, d.master_dtype);
+      if (ema != nullptr) store_from_float(ema, i, d.ema_dtype, fmaf(1.f - decay, v, load_as_float(ema, i, d.ema_dtype) * decay));
+      m = fmaxf(m, fabsf(v));
+    }
+  }
+  if (d.mode == 2) return;
+  m = warp_max(m);
+  __shared__ float warp_m[8];
+  if ((threadIdx.x & 31) == 0) warp_m[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float b = 0.f;
+    for (int i = 0; i < 8; ++i) b = fmaxf(b, warp_m[i]);
+    atomicMax(reinterpret_cast<unsigned int*>(d.amax), __float_as_uint(b));   // non-negative floats order like uints
+  }
+}
+
+__device__ __forceinline__ uint8_t* slab_address(const Peers& peers, const WriteDesc& d, long long element, int bytes_per_element) {
+  const int rank = d.slab_elems > 0 ? (int)(element / d.slab_elems) : 0;
+  const long long local = element - (long long)rank * d.slab_elems;
+  return peers.heap[rank] + d.dst_offset + local * bytes_per_element;
+}
+
+// Launch B: scale = max(amax, 1e-30) / limit (current scaling); codes = round(clamp(master / scale)) stored into
+// the slab of the rank that holds each row; the first block of a row also stores the header everywhere.
+// `calls` = write-backs since the table was built (the history slot is (base_index + calls) % history_len).
+__global__ void __launch_bounds__(256)
+writeback_push_kernel(const WriteDesc* __restrict__ table, const int* __restrict__ prefix, int rows, Peers peers,
+                      long long calls) {
+  const int t = find_row(prefix, rows, blockIdx.x);
+  const WriteDesc d = table[t];
+  const long long begin = (long long)(blockIdx.x - prefix[t]) * kWriteChunk;
+  const long long end = min(begin + kWriteChunk, d.n);
+  const void* master = reinterpret_cast<const void*>(d.master);
+  if (d.mode == 2) {
+    const int width = d.out_dtype == kF32 ? 4 : 2;
+    for (long long i = begin + threadIdx.x; i < end; i += blockDim.x)
+      store_from_float(slab_address(peers, d, i, width), 0, d.out_dtype, load_as_float(master, i, d.master_dtype));
+    return;
+  }
+  const float amax = __uint_as_float(*reinterpret_cast<const unsigned int*>(d.amax));
+  const float scale = fmaxf(amax, 1e-30f) / d.limit;
+  if (blockIdx.x == prefix[t] && d.header_offset >= 0 && (int)threadIdx.x < peers.world) {
+    float* header = reinterpret_cast<float*>(peers.heap[threadIdx.x] + d.header_offset);
+    header[0] = scale;
+    if (d.history_len > 0) header[1 + (int)((d.base_index + calls) % d.history_len)] = amax;
+  }
+  const bool vec = d.master_dtype == kF32 && (d.master & 15) == 0 && (d.slab_elems % 16) == 0 && (d.dst_offset % 16) == 0;
+  long long i = begin;
+  if (vec) {
+    const long long vend = begin + ((end - begin) & ~15LL);
+    for (long long j = begin + 16LL * threadIdx.x; j < vend; j += 16LL * blockDim.x) {
+      uint32_t words[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(master) + j + 4 * q);
+        words[q] = (uint32_t)fp8_encode(scaled_clamp(v.x, scale, d.limit), d.mode)
+                 | (uint32_t)fp8_encode(scaled_clamp(v.y, scale, d.limit), d.mode) << 8
+                 | (uint32_t)fp8_encode(scaled_clamp(v.z, scale, d.limit), d.mode) << 16
+                 | (uint32_t)fp8_encode(scaled_clamp(v.w, scale, d.limit), d.mode) << 24;
+      }
+      *reinterpret_cast<uint4*>(slab_address(peers, d, j, 1)) = make_uint4(words[0], words[1], words[2], words[3]);
+    }
+    i = vend;
+  }
+  for (long long j = i + threadIdx.x; j < end; j += blockDim.x)
+    *slab_address(peers, d, j, 1) = fp8_encode(scaled_clamp(load_as_float(master, j, d.master_dtype), scale, d.limit), d.mode);
 }
 
 // Plain byte push of an already encoded payload (16-byte vectors): full copy to everyone or one slab per rank.
@@ -518,5 +670,16 @@ extern "C" int vb_gather_pull(const void* entries, int num_entries, const VbPeer
   const int grid = (int)std::min<long long>(total_pieces, max_blocks);
   gather_pull_kernel<<<grid, 256, 0, stream>>>((const GatherEntry*)entries, num_entries, make_peers(peers), shard_region_offset,
                                                (uint8_t*)full, piece_prefix, piece_counts, panel_flags, generation);
+  return (int)cudaGetLastError();
+}
+
+// Fused owner write-back (see WriteDesc).  `amax_slots` (uint32 per row, referenced by the table) must be zero on
+// entry; they are left holding the amax bits.  With world == 1 and peers->buffers[0] == nullptr the offsets of the
+// table are absolute addresses, which lets a single process without a symmetric heap use the same kernels.
+extern "C" int vb_multi_writeback(const void* table, const int* prefix, int rows, int blocks, float decay, int with_ema,
+                                  const VbPeerTable* peers, long long calls, cudaStream_t stream) {
+  if (blocks <= 0 || rows <= 0) return 0;
+  writeback_amax_kernel<<<blocks, 256, 0, stream>>>((const WriteDesc*)table, prefix, rows, decay, with_ema);
+  writeback_push_kernel<<<blocks, 256, 0, stream>>>((const WriteDesc*)table, prefix, rows, make_peers(peers), calls);
   return (int)cudaGetLastError();
 }

@@ -144,6 +144,67 @@ def check_status(device=None):
                                f"(block {values[1]}, warp {values[2]}, detail {values[3]}) on {dev}")
 
 
+def status_message(values, device="?"):
+    """Text for a non-zero status word ``[code, block, warp, detail, ...]``."""
+    return (f"viola_b200 kernel reported: {_STATUS_NAMES.get(int(values[0]), int(values[0]))} "
+            f"(block {int(values[1])}, warp {int(values[2])}, detail {int(values[3])}) on {device}")
+
+
+class StatusMonitor:
+    """Reads a device's kernel status word without stalling the training loop.
+
+    ``snapshot()`` enqueues a copy of the word into pinned host memory behind the work issued so far;
+    ``poll()`` looks at the latest snapshot that has completed (it never waits) and raises when a kernel
+    recorded a failure.  A loop that calls ``poll()`` then ``snapshot()`` once per step therefore learns of
+    a timed-out wait one step late but pays no synchronisation; ``check()`` is the synchronising form for
+    places that write something durable (checkpoints) or shut down.  ``pending`` lets a test or a host-side
+    fault model put a code in without any GPU work.
+    """
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.pending = 0                  # host-injected code, reported by the next poll()/check()
+        self._host = self._event = None
+        if self.device.type == "cuda":
+            self._host = torch.zeros(8, dtype=torch.int32).pin_memory()
+            self._event = torch.cuda.Event()
+            self._armed = False
+
+    def local_code(self):
+        """The code this rank would report right now without waiting for the GPU."""
+        if self.pending:
+            return int(self.pending)
+        if self._host is not None and self._armed and self._event.query():
+            return int(self._host[0])
+        return 0
+
+    def snapshot(self):
+        if self._host is None:
+            return
+        self._host.copy_(status_word(self.device), non_blocking=True)
+        self._event.record(torch.cuda.current_stream(self.device))
+        self._armed = True
+
+    def poll(self):
+        code = self.local_code()
+        if code:
+            self.raise_for(code)
+
+    def check(self):
+        if self.pending:
+            self.raise_for(self.pending)
+        if self._host is not None:
+            check_status(self.device)
+
+    def raise_for(self, code, rank=None):
+        values = [code, 0, 0, 0]
+        if self._host is not None and int(self._host[0]) == code:
+            values = self._host.tolist()
+        self.pending = 0
+        where = f"{self.device}" if rank is None else f"rank {rank}"
+        raise RuntimeError(status_message(values, where))
+
+
 def _limit(dtype, limit):
     return reference.fp8_limit(dtype, limit)
 
@@ -789,3 +850,68 @@ def multi_momentum(table, *, tile_size, beta, nesterov=True, loss_scale=1.0, rou
     _ops().multi_momentum(table.table, table.prefix, table.blocks, int(tile_size), float(beta), 1.0 / float(loss_scale),
                           bool(nesterov), rounding == "stochastic", int(step))
     _count()
+
+
+class WritebackTable:
+    """Device-resident table for :func:`multi_writeback` (16 int64 words per owned parameter).
+
+    ``rows``: dicts with ``master`` (tensor), ``ema`` (tensor or None), ``n``, ``slab_elems``, ``dst_offset``,
+    ``header_offset`` (-1 for none), ``base_index``, ``limit``, ``history_len``, ``mode`` (0 e4m3, 1 e5m2, 2 cast)
+    and ``out_dtype`` (torch dtype, cast rows only).  One uint32 amax slot per row is allocated here.
+    """
+
+    def __init__(self, rows, device):
+        import struct
+        self.rows = len(rows)
+        self.amax = torch.zeros(max(1, len(rows)), device=device, dtype=torch.int32)
+        self.keep = [row["master"] for row in rows] + [row["ema"] for row in rows if row.get("ema") is not None]
+        base = self.amax.data_ptr()
+        packed, prefix = [], [0]
+
+        def pair(a, b, first_float=False):
+            return struct.unpack("<q", struct.pack("<fi" if first_float else "<ii", a, b))[0]
+
+        def signed(value):
+            return value if value < (1 << 63) else value - (1 << 64)
+
+        for position, row in enumerate(rows):
+            master, ema = row["master"], row.get("ema")
+            packed.append([signed(master.data_ptr()), signed(ema.data_ptr()) if ema is not None else 0,
+                           signed(base + 4 * position), int(row["n"]), int(row["slab_elems"]),
+                           signed(int(row["dst_offset"])), signed(int(row["header_offset"])) if row["header_offset"] >= 0 else -1,
+                           int(row["base_index"]),
+                           pair(float(row.get("limit", 448.0)), int(row.get("history_len", 0)), first_float=True),
+                           pair(_DT[master.dtype], _DT[ema.dtype] if ema is not None else 0),
+                           pair(int(row["mode"]), _DT.get(row.get("out_dtype"), 0)), 0, 0, 0, 0, 0])
+            prefix.append(prefix[-1] + (int(row["n"]) + _CHUNK - 1) // _CHUNK)
+        host_table = torch.tensor(packed, dtype=torch.int64).reshape(-1).pin_memory() if packed else torch.zeros(0, dtype=torch.int64)
+        host_prefix = torch.tensor(prefix, dtype=torch.int32).pin_memory()
+        self.table = host_table.to(device, non_blocking=True)
+        self.prefix = host_prefix.to(device, non_blocking=True)
+        self.keep.extend((host_table, host_prefix))
+        self.blocks = prefix[-1]
+        self.pointers = tuple((row[0], row[1]) for row in packed)
+
+    def matches(self, rows):
+        if len(rows) != len(self.pointers):
+            return False
+        for row, (master, ema) in zip(rows, self.pointers):
+            if (row["master"].data_ptr() & ((1 << 64) - 1)) != (master & ((1 << 64) - 1)):
+                return False
+            current = row["ema"].data_ptr() if row.get("ema") is not None else 0
+            if (current & ((1 << 64) - 1)) != (ema & ((1 << 64) - 1)):
+                return False
+        return True
+
+
+def multi_writeback(table, *, heaps, rank, calls, decay=0.0, with_ema=False):
+    """Owner write-back of every row of ``table`` in two launches (amax + EMA, then encode + peer stores).
+
+    ``heaps``: every rank's symmetric-heap base address (``[0]`` with absolute offsets for a single process).
+    ``calls``: write-backs since the table was built (selects the amax-history slot)."""
+    if not table.rows:
+        return
+    table.amax.zero_()
+    _ops().multi_writeback(table.table, table.prefix, table.blocks, float(decay), bool(with_ema), list(heaps), int(rank),
+                           int(calls))
+    _count(2)

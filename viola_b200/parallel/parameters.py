@@ -108,8 +108,12 @@ class ParameterStore:
         self.by_parameter = {r.parameter: r for r in self.records}
         self.local = [r for r in self.records if r.owner == rank]
         self.hooks = []
+        self._tables = {}              # fused write-back tables by purpose ("step", "ema", ...)
+        self._local_headers = None     # single process: [scale, amax history] of each FP8 layer, contiguous
         if self.transport is not None:
             self.transport.attach_parameters(sharder, self.records)
+        elif sharder is not None and world == 1 and self.records and self.records[0].parameter.is_cuda:
+            self._make_local_headers()
 
     def metadata(self):
         return [dict(name=r.name, index=r.index, shape=r.shape, dtype=r.dtype, owner=r.owner, placement=r.placement)
@@ -170,12 +174,110 @@ class ParameterStore:
                     unit.full_view(entry).copy_(local[:entry.rows].view(entry.shape))
         torch.autograd.graph.increment_version(record.parameter)
 
+    # ------------------------------------------------------------------ fused write-back (one table, two launches)
+    def _make_local_headers(self):
+        """Single process, sharded storage: give every per-tensor FP8 layer one contiguous ``[scale, history]``
+        block so that the table-driven write-back kernel can update both with one address (with several ranks
+        the transport keeps these blocks in the symmetric heap)."""
+        layers = [r for r in self.records if r.layer is not None and r.layer.weight_dtype == "fp8"
+                  and not r.layer._grouped_scaling and r.layer.weight_quantizer.history.numel() + 1 <= 32]
+        if not layers:
+            return
+        block = torch.zeros(len(layers), 32, device=layers[0].parameter.device, dtype=torch.float32)
+        self._local_headers = {}
+        for row, record in zip(block, layers):
+            layer, length = record.layer, record.layer.weight_quantizer.history.numel()
+            row[0:1].copy_(layer.weight_scale)
+            row[1:1 + length].copy_(layer.weight_quantizer.history)
+            layer.weight_scale = row[0:1]
+            layer.weight_quantizer.history = row[1:1 + length]
+            self._local_headers[record.index] = row.data_ptr()
+
+    def _header_address(self, record):
+        if self.transport is not None:
+            found = self.transport.header_offset.get(record.index)
+            return None if found is None else found[0]
+        return None if self._local_headers is None else self._local_headers.get(record.index)
+
+    def _fusable(self, record):
+        """True when the table-driven kernels can write this record (same answer on every rank)."""
+        from .. import ops
+        unit = record.unit
+        if unit is None or not record.parameter.is_cuda or (unit.unsharded and not unit.resident):
+            return False
+        if self.world > 1 and self.transport is None:
+            return False
+        layer = record.layer
+        if layer is not None and layer.weight_dtype == "fp8":
+            return (not layer._grouped_scaling and not layer.rotation_size
+                    and layer.weight_quantizer.scaling == "current" and self._header_address(record) is not None)
+        return record.dtype in ops._DT
+
+    def _table_row(self, record, value, average):
+        from .. import ops
+        from ..ops.reference import fp8_limit
+        unit, entry, layer = record.unit, record.entry, record.layer
+        element = torch.empty((), dtype=record.dtype).element_size()
+        base = unit.heap_offset if self.transport is not None else unit.shard.data_ptr()
+        row = dict(master=value, ema=average, n=value.numel(), slab_elems=entry.shard_rows * (entry.row_bytes // element),
+                   dst_offset=base + entry.shard_offset, header_offset=-1, base_index=0, limit=448.0, history_len=0,
+                   mode=2, out_dtype=record.dtype)
+        if layer is not None and layer.weight_dtype == "fp8":
+            limit = layer._quantization_limit(max(layer.in_features, layer.out_features), layer.fp8_dtype)
+            row.update(mode=ops._FMT[layer.fp8_dtype], limit=fp8_limit(layer.fp8_dtype, limit),
+                       header_offset=self._header_address(record), history_len=layer.weight_quantizer.history.numel(),
+                       base_index=layer.weight_quantizer.index)
+        return row
+
+    @torch.no_grad()
+    def write_many(self, records, values, *, averages=None, decay=0.0, purpose="step"):
+        """Write-back of many records at once.  ``values[index]`` is the new real-valued tensor on the owner of
+        the record with that index.  Records the fused kernels can handle go through one device table (two
+        launches on each owner for all of them, EMA lerp of ``averages[name]`` included when given); the rest
+        take :meth:`write`.  Every rank must call this with the same ``records``."""
+        from .. import ops
+        self.begin_writes()
+        fused = [r for r in records if self._fusable(r)]
+        fused_ids = {id(r) for r in fused}
+        owned = [r for r in fused if r.owner == self.rank and values.get(r.index) is not None
+                 and values[r.index].is_contiguous() and values[r.index].dtype in ops._DT]
+        if len(owned) != sum(1 for r in fused if r.owner == self.rank):
+            fused, fused_ids, owned = [], set(), []          # an owner cannot serve its rows: use the per-record path
+        with_ema = bool(averages) and bool(decay)
+        if owned:
+            rows = [self._table_row(r, values[r.index], averages.get(r.name) if with_ema else None) for r in owned]
+            cached = self._tables.get(purpose)
+            valid = (cached is not None and cached["table"].matches(rows)
+                     and all(row["base_index"] == base + cached["calls"] or row["mode"] == 2
+                             for row, base in zip(rows, cached["bases"])))
+            if not valid:
+                cached = self._tables[purpose] = dict(table=ops.WritebackTable(rows, owned[0].parameter.device),
+                                                      bases=[row["base_index"] for row in rows], calls=0)
+            if self.transport is not None:
+                self.transport.write_table(cached["table"], calls=cached["calls"], decay=decay, with_ema=with_ema)
+            else:
+                ops.multi_writeback(cached["table"], heaps=[0], rank=0, calls=cached["calls"], decay=decay,
+                                    with_ema=with_ema)
+            cached["calls"] += 1
+        for record in fused:
+            layer = record.layer
+            if layer is not None and layer.weight_dtype == "fp8":
+                layer.weight_quantizer.index += 1
+                layer.clear_weight_cache()
+            record.unit.stale = True
+            torch.autograd.graph.increment_version(record.parameter)
+        for record in records:
+            if id(record) not in fused_ids:
+                self.write(record, values.get(record.index), record.owner)
+        self.end_writes()
+        return with_ema and len(fused) == len(records)
+
     # ------------------------------------------------------------------ peer-memory write path
     def begin_writes(self):
-        """Cross-rank barrier before owners overwrite storage that peers may still be reading."""
+        """Cross-rank barrier (on the stream, no host wait) before owners overwrite storage that peers may
+        still be reading."""
         if self.transport is not None and self.world > 1:
-            token = torch.zeros(1, device=self.records[0].parameter.device)
-            dist.all_reduce(token, group=self.group)
+            self.transport.barrier()
 
     def end_writes(self):
         """Publish this rank's stores and wait (bounded, on the stream) for every owner's."""
@@ -283,11 +385,14 @@ class ParameterStore:
 
     @torch.no_grad()
     def restore(self, values):
+        """Put a :meth:`snapshot` back.  With peer-memory storage this is a write like any other: no rank may
+        overwrite its slab while a peer still gathers from it, and no rank may gather before every slab is
+        back, hence the same barrier / publish bracket as an optimizer write-back."""
+        self.begin_writes()
         for record in self.records:
             self._local_storage(record).copy_(values[record.name])
             torch.autograd.graph.increment_version(record.parameter)
-        if self.sharder is not None:
-            self.sharder.refresh()
+        self.end_writes()
 
     # ------------------------------------------------------------------ full-model state dicts
     @torch.no_grad()

@@ -19,8 +19,10 @@ identical layout everywhere so that ``(rank, offset)`` names the same object on 
 
 The kernels run on a side stream ordered against the compute stream with events.  Cross-rank
 ordering uses generation counters in the heap; every device-side wait is bounded and reports
-through the status word (``ops.check_status``).  The step's usage-flag all-reduce is the barrier
-between "everyone finished reading the old weights" and "owners overwrite them".
+through the status word (``ops.check_status``).  Each rank's per-step message (its status word and
+which parameters produced a gradient) is stored into every rank's heap and followed by a flag; the
+bounded on-stream wait for all of those flags doubles as the barrier between "everyone finished reading
+the old weights" and "owners overwrite them", so a step contains no NCCL call and no host wait.
 """
 
 from __future__ import annotations
@@ -315,6 +317,91 @@ class PeerTransport:
                             8 * self.max_blocks)
         ops._count()
         return True
+
+    # ------------------------------------------------------------------ per-step message + barrier
+    def attach_usage(self, count):
+        """Reserve one message slot per rank: ``[status code, non-finite flag, used[0..count)]`` as int32."""
+        self.usage_words = 2 + count
+        self.usage_slot = _align(4 * self.usage_words, 16)
+        self.request("usage", self.usage_slot * self.world)
+        self.usage_generation = 0
+        self.barrier_generation = 0
+
+    def finalize_usage(self):
+        self.usage_flag_offset = self.flags("usage", self.world)
+        self.barrier_flag_offset = self.flags("barrier", self.world)
+        self.usage_message = torch.zeros(self.usage_slot // 4, device=self.device, dtype=torch.int32)
+        self.usage_staging = torch.zeros(self.usage_words, dtype=torch.int32).pin_memory()
+        self.usage_host = torch.zeros(self.world * self.usage_slot // 4, dtype=torch.int32).pin_memory()
+        self.usage_event = torch.cuda.Event()
+        self.usage_armed = False
+
+    def exchange_usage(self, used, *, bad=None, injected=0):
+        """Send this rank's step message to every rank and enqueue the wait for everyone's.
+
+        ``used``: list of bools (one per parameter record); ``bad``: optional device int32[1] non-finite flag;
+        ``injected``: a host-side status code to report instead of the device word (fault tests).
+        The host first waits for the *previous* step's exchange to land (which bounds how far the host can run
+        ahead of the GPU to one step and frees the pinned buffers for reuse) and raises, on every rank alike, if
+        any rank reported a kernel failure in it.  It does not wait for this step's exchange; :meth:`read_usage`
+        does when the caller needs the answer now."""
+        previous = self.read_usage(wait=True)
+        if previous is not None:
+            self.raise_for_codes(previous[0])
+        staging = self.usage_staging
+        staging[0] = int(injected)
+        staging[1] = 0
+        staging[2:] = torch.tensor(used, dtype=torch.int32)
+        message = self.usage_message
+        message[:self.usage_words].copy_(staging, non_blocking=True)
+        if not injected:
+            message[0:1].copy_(self.status[0:1])
+        if bad is not None:
+            message[1:2].copy_(bad.reshape(1))
+        self.usage_generation += 1
+        base = self.offsets["usage"]
+        self._ops.byte_push(message.view(torch.uint8), self.pointers, self.rank, base + self.rank * self.usage_slot, 0, 1)
+        self._ops.signal(self.pointers, self.rank, self.usage_flag_offset, self.usage_generation, True)
+        self._ops.wait_flags(self.local_pointer(self.usage_flag_offset), self.world, -1, self.usage_generation,
+                             self.wait_clocks, self.status)
+        self.usage_host.copy_(self.heap.view(base, self.world * self.usage_slot).view(torch.int32), non_blocking=True)
+        self.usage_event.record(torch.cuda.current_stream(self.device))
+        self.usage_armed = True
+        ops._count(3)
+
+    def read_usage(self, *, wait):
+        """``(codes, bad, used)`` per rank from the latest completed exchange, or None when it has not landed yet
+        (``wait=False``).  ``codes[r]`` is rank r's status code, ``used`` the element-wise OR over ranks."""
+        if not self.usage_armed:
+            return None
+        if wait:
+            self.usage_event.synchronize()
+        elif not self.usage_event.query():
+            return None
+        table = self.usage_host.view(self.world, self.usage_slot // 4)
+        codes = table[:, 0].tolist()
+        bad = bool(table[:, 1].max().item())
+        used = table[:, 2:self.usage_words].max(dim=0).values.bool().tolist()
+        return codes, bad, used
+
+    def raise_for_codes(self, codes):
+        for rank, code in enumerate(codes):
+            if code:
+                self.usage_armed = False
+                raise RuntimeError(f"rank {rank}: {ops.status_message([code, 0, 0, 0], f'rank {rank}')}; the step that "
+                                   "followed it did not see that rank's data, stop and resume from a checkpoint")
+
+    def barrier(self):
+        """On-stream barrier over all ranks (signal + bounded wait); the host does not wait."""
+        self.barrier_generation += 1
+        self._ops.signal(self.pointers, self.rank, self.barrier_flag_offset, self.barrier_generation, True)
+        self._ops.wait_flags(self.local_pointer(self.barrier_flag_offset), self.world, -1, self.barrier_generation,
+                             self.wait_clocks, self.status)
+        ops._count(2)
+
+    def write_table(self, table, *, calls, decay=0.0, with_ema=False):
+        """Fused owner write-back of a :class:`viola_b200.ops.WritebackTable` whose offsets are heap offsets."""
+        ops.multi_writeback(table, heaps=self.pointers, rank=self.rank, calls=calls, decay=decay, with_ema=with_ema)
 
     def publish_step(self):
         """Owner side done: tell every rank; then wait until every owner's stores for this step landed."""

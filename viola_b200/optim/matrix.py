@@ -1,16 +1,28 @@
-"""Base class for optimizers whose update rule needs a whole logical matrix.
+"""``MatrixOptimizer``: base class for update rules that need a whole logical matrix (Muon and relatives).
 
-Subclasses implement ``_step_local(parameter, gradient, state, group, index)`` on ordinary full
-tensors.  Plain parameters are updated in place; DTensor parameters (Replicate or Shard on a 1-D
-mesh) are processed in owner rounds: gather gradient and weight to the owner, update there, write
-the result back into the existing layout.  ``shard_state=False`` keeps replicated state but still
-writes back from one source so stochastic / FP8 results agree bit for bit.  Behaviour and
-checkpoint keys follow the reference base class (viola/optim/matrix.py:13-135).
+A subclass writes one method, ``_step_local(parameter, gradient, state, group, index)``, which updates a
+full ordinary tensor in place.  This class does the rest:
+
+* plain tensors are handed to ``_step_local`` directly (``_begin_local`` / ``_finish_local`` bracket that
+  pass so a subclass can collect same-shape matrices and run them as one batched launch);
+* DTensor parameters (``Replicate`` or ``Shard`` on a 1-D mesh) have per-tensor owners
+  (:class:`~viola_b200.parallel.partition.MatrixPartition`).  They are worked through in rounds of one
+  tensor per owner: the gradient and the weight are assembled on the owner, updated there, and the result
+  is written back into the existing layout, so every rank is busy in every round.  With
+  ``shard_state=False`` every rank assembles and updates every tensor (replicated state), but the value
+  that is written back still comes from the owner alone, which keeps stochastic and FP8 results bit-identical;
+* ``skip_nonfinite=True`` makes all ranks agree (one flag, one reduction per mesh) to skip a step whose
+  gradients contain Inf / NaN; ``step_was_skipped`` tells hooks about it;
+* ``group["viola_parameter_indices"]`` (set by the engine) replaces positional indices, so Philox keys stay
+  the same under any sharding layout;
+* ``state_dict`` carries the ownership layout as ``viola_dtensor`` and ``load_state_dict`` refuses another
+  layout and keeps every state tensor's own dtype (raw uint8 momentum, bf16 Adam moments), which the stock
+  loader would cast to the parameter dtype.
+
+Behaviour and checkpoint keys follow the reference base class (viola/optim/matrix.py:13-135).
 """
 
 from __future__ import annotations
-
-from abc import abstractmethod
 
 import torch
 import torch.distributed as dist
@@ -23,16 +35,23 @@ except Exception:  # pragma: no cover
     DTensor = ()
 
 
+def _local(tensor):
+    return tensor.to_local() if isinstance(tensor, DTensor) else tensor
+
+
 class MatrixOptimizer(torch.optim.Optimizer):
     def __init__(self, params, defaults, *, shard_state=True, skip_nonfinite=False):
-        self.shard_state = shard_state
-        self.skip_nonfinite = skip_nonfinite
+        self.shard_state, self.skip_nonfinite = shard_state, skip_nonfinite
         self.step_was_skipped = False
         self._partition = None
         super().__init__(params, defaults)
-        self.register_state_dict_post_hook(self._save_partition)
-        self.register_load_state_dict_pre_hook(self._before_load)
-        self.register_load_state_dict_post_hook(self._after_load)
+
+    # ------------------------------------------------------------------ ownership
+    @property
+    def partition(self):
+        if self._partition is None:
+            self._partition = MatrixPartition(p for group in self.param_groups for p in group["params"])
+        return self._partition
 
     def add_param_group(self, group):
         if self._partition is not None and self._partition.owners:
@@ -40,31 +59,40 @@ class MatrixOptimizer(torch.optim.Optimizer):
         super().add_param_group(group)
         self._partition = None
 
-    @property
-    def partition(self):
-        if self._partition is None:
-            self._partition = MatrixPartition(p for g in self.param_groups for p in g["params"])
-        return self._partition
-
-    @abstractmethod
+    # ------------------------------------------------------------------ subclass interface
     def _step_local(self, parameter, gradient, state, group, index):
         """Update one full parameter in place; ``index`` is stable across sharding layouts."""
         raise NotImplementedError
 
-    def _has_nonfinite(self):
-        bad = False
+    def _begin_local(self):
+        """Called before the plain-tensor parameters are visited (subclasses may start batching)."""
+
+    def _finish_local(self):
+        """Called after the plain-tensor parameters were visited, before DTensor owner rounds."""
+
+    # ------------------------------------------------------------------ the step
+    def _work_items(self):
+        """(parameter, group, stable index) for every parameter that has a gradient."""
+        position = 0
         for group in self.param_groups:
-            for param in group["params"]:
-                if param.grad is None:
-                    continue
-                grad = param.grad.to_local() if isinstance(param.grad, DTensor) else param.grad
-                if not torch.isfinite(grad).all():
-                    bad = True
-        for mesh in self.partition.meshes:          # all ranks must agree before anyone skips
-            flag = torch.tensor(int(bad), device=mesh.device_type, dtype=torch.int32)
-            dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=mesh.get_group())
-            bad = bool(flag.item())
-        return bad
+            stable = group.get("viola_parameter_indices")
+            for slot, parameter in enumerate(group["params"]):
+                index = position if stable is None else stable[slot]
+                position += 1
+                if parameter.grad is not None:
+                    yield parameter, group, index
+
+    def _gradients_nonfinite(self):
+        """One device-side flag over all local gradients, then one MAX reduction per mesh so ranks agree."""
+        flags = [torch.isfinite(_local(p.grad)).all().logical_not() for p, _, _ in self._work_items()]
+        bad = torch.stack(flags).any() if flags else None
+        for mesh in self.partition.meshes:
+            vote = torch.zeros((), device=mesh.device_type, dtype=torch.int32)
+            if bad is not None:
+                vote += bad.to(device=vote.device, dtype=torch.int32)
+            dist.all_reduce(vote, op=dist.ReduceOp.MAX, group=mesh.get_group())
+            bad = vote.bool()
+        return bool(bad) if bad is not None else False
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -73,80 +101,66 @@ class MatrixOptimizer(torch.optim.Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
-        if self.skip_nonfinite and self._has_nonfinite():
+        if self.skip_nonfinite and self._gradients_nonfinite():
             self.step_was_skipped = True
             return loss
-        distributed, running = {}, 0
+        owned_elsewhere = {}
         self._begin_local()
-        for group in self.param_groups:
-            indices = group.get("viola_parameter_indices")
-            for position, param in enumerate(group["params"]):
-                index = indices[position] if indices is not None else running
-                running += 1
-                if param.grad is None:
-                    continue
-                if isinstance(param, DTensor):
-                    distributed[param] = (group, index)
-                else:
-                    self._step_local(param, param.grad, self.state[param], group, index)
+        for parameter, group, index in self._work_items():
+            if isinstance(parameter, DTensor):
+                owned_elsewhere[parameter] = (group, index)
+            else:
+                self._step_local(parameter, parameter.grad, self.state[parameter], group, index)
         self._finish_local()
-        if distributed:
-            for batch in self.partition.batches:
-                self._step_batch(batch, distributed)
+        if owned_elsewhere:
+            for round_ in self.partition.batches:
+                self._owner_round([p for p in round_ if p in owned_elsewhere], owned_elsewhere)
         return loss
 
-    def _begin_local(self):
-        """Called before the plain-tensor parameters are visited (subclasses may start batching)."""
-
-    def _finish_local(self):
-        """Called after the plain-tensor parameters were visited, before DTensor owner rounds."""
-
-    def _step_batch(self, batch, contexts):
+    def _owner_round(self, parameters, contexts):
+        """One tensor per owner: assemble, update on the owner(s), write back from the owner."""
         from ..parallel.communication import gather_to_owner, replicate_tensor, write_from_owner
-        work = []
-        for param in batch:
-            if param not in contexts:
-                continue
-            owner = self.partition.owner(param)
+        assembled = []
+        for parameter in parameters:
+            owner = self.partition.owner(parameter)
             if self.shard_state:
-                gradient, value = gather_to_owner(param.grad, owner), gather_to_owner(param, owner)
+                weight, gradient = gather_to_owner(parameter, owner), gather_to_owner(parameter.grad, owner)
             else:
-                gradient, value = replicate_tensor(param.grad), replicate_tensor(param)
-            if value is not None:
-                value = value.contiguous()
-            work.append((param, value, gradient, owner))
-        for param, value, gradient, _ in work:
-            if value is not None:
-                group, index = contexts[param]
-                self._step_local(value, gradient.contiguous(), self.state[param], group, index)
-        for param, value, _, owner in work:
-            write_from_owner(param, value, owner)
+                weight, gradient = replicate_tensor(parameter), replicate_tensor(parameter.grad)
+            assembled.append((parameter, owner, None if weight is None else weight.contiguous(), gradient))
+        for parameter, _, weight, gradient in assembled:
+            if weight is not None:
+                group, index = contexts[parameter]
+                self._step_local(weight, gradient.contiguous(), self.state[parameter], group, index)
+        for parameter, owner, weight, _ in assembled:
+            write_from_owner(parameter, weight, owner)
 
-    # ------------------------------------------------------------------ checkpoint hooks
-    def _save_partition(self, optimizer, state):
-        if self.partition.owners:
-            state["viola_dtensor"] = dict(shard_state=self.shard_state, partition=self.partition.state_dict())
+    # ------------------------------------------------------------------ checkpoints
+    def _layout(self):
+        if not self.partition.owners:
+            return {}
+        return {"shard_state": self.shard_state, "partition": self.partition.state_dict()}
+
+    def state_dict(self):
+        state = super().state_dict()
+        layout = self._layout()
+        if layout:
+            state["viola_dtensor"] = layout
         return state
 
-    def _before_load(self, optimizer, saved):
-        saved = dict(saved)
-        layout = saved.pop("viola_dtensor", {})
-        expected = (dict(shard_state=self.shard_state, partition=self.partition.state_dict())
-                    if self.partition.owners else {})
-        if layout != expected:
+    def load_state_dict(self, state_dict):
+        if state_dict.get("viola_dtensor", {}) != self._layout():
             raise RuntimeError("matrix-optimizer checkpoint ownership / layout differs from this run")
-        # torch would cast every floating state tensor to the parameter dtype; keep raw FP8 momentum
-        # bytes and independently chosen Adam state dtypes by loading tensors ourselves.
-        self._loading = {pid: {k: v for k, v in state.items() if isinstance(v, torch.Tensor)}
-                         for pid, state in saved["state"].items()}
-        self._loading_groups = saved["param_groups"]
-        stripped = {pid: {k: v for k, v in state.items() if not isinstance(v, torch.Tensor)}
-                    for pid, state in saved["state"].items()}
-        return dict(saved, state=stripped)
-
-    def _after_load(self, optimizer):
-        for old, group in zip(self._loading_groups, self.param_groups):
-            for pid, param in zip(old["params"], group["params"]):
-                for name, value in self._loading.get(pid, {}).items():
-                    self.state[param][name] = value.to(device=param.device, copy=True)
-        del self._loading, self._loading_groups
+        incoming = {key: value for key, value in state_dict.items() if key != "viola_dtensor"}
+        # split the per-parameter state: scalars go through the stock loader, tensors are re-attached
+        # afterwards exactly as saved (torch would cast floating tensors to the parameter dtype)
+        tensors, scalars = {}, {}
+        for saved_id, entries in incoming["state"].items():
+            tensors[saved_id] = {k: v for k, v in entries.items() if isinstance(v, torch.Tensor)}
+            scalars[saved_id] = {k: v for k, v in entries.items() if not isinstance(v, torch.Tensor)}
+        super().load_state_dict({**incoming, "state": scalars})
+        saved_groups = incoming["param_groups"]
+        for saved_group, group in zip(saved_groups, self.param_groups):
+            for saved_id, parameter in zip(saved_group["params"], group["params"]):
+                for name, value in tensors.get(saved_id, {}).items():
+                    self.state[parameter][name] = value.to(device=parameter.device, copy=True)

@@ -14,6 +14,15 @@ from .. import ops
 
 
 class EMAState:
+    """The engine's running average of the master weights.
+
+    Placement: with ``shard`` each rank averages the records it owns (no communication at all); without it
+    every rank averages every record and receives the owners' masters each step.  ``update`` is one
+    multi-tensor launch; when the step's write-back already folded the lerp into its kernels the engine calls
+    :meth:`mark_updated` instead.  ``apply`` pushes the averages into the compute weights through the same
+    owner write-back an optimizer step uses, so FP8 codes and scales are identical on all ranks.
+    """
+
     def __init__(self, store, optimizer, *, decay=0, dtype=torch.float32, shard=True):
         if not 0 <= decay < 1:
             raise ValueError("ema decay must be in [0, 1)")
@@ -21,133 +30,142 @@ class EMAState:
         self.decay, self.dtype, self.shard = decay, dtype, shard
         self.updates = 0
         self.weights = {}
-        if not decay:
-            return
-        self.optimizer.materialize()
-        for record in store.records:
-            source = self._source(record)
-            if source is not None:
-                self.weights[record.name] = source.to(dtype=dtype, copy=True)
-        self.optimizer.release()
+        self._table = None
+        if decay:
+            optimizer.materialize()
+            for record, master in self._tracked():
+                self.weights[record.name] = master.to(dtype=dtype, copy=True)
+            optimizer.release()
 
-    def _source(self, record):
-        if not self.shard:
-            return self.optimizer.full_value(record)
-        if record.owner == self.store.rank:
-            return self.optimizer.parameters[record.index].detach()
-        return None
+    def _tracked(self):
+        """(record, current master) for every record this rank averages; communicates when replicated."""
+        for record in self.store.records:
+            if not self.shard:
+                yield record, self.optimizer.full_value(record)
+            elif record.owner == self.store.rank:
+                yield record, self.optimizer.parameters[record.index].detach()
+
+    @property
+    def fusable(self):
+        """The averages sit beside the owners' masters, so the write-back kernels can update them in passing."""
+        return bool(self.decay) and self.shard
+
+    def mark_updated(self):
+        self.updates += 1
 
     @torch.no_grad()
     def update(self):
         if not self.decay:
             return
-        pairs = []
-        for record in self.store.records:
-            source = self._source(record)
-            if source is not None:
-                pairs.append((self.weights[record.name], source))
-        if pairs and pairs[0][0].is_cuda and all(a.is_contiguous() and b.is_contiguous() for a, b in pairs):
-            # one launch for every average (the sources are the optimizer's master parameters)
-            rows = [(ema, source, None, None, ema.numel(), 0, 0.0, 0.0, ops._DT[ema.dtype], ops._DT[source.dtype])
-                    for ema, source in pairs]
-            if getattr(self, "_table", None) is None or not self._table.matches(rows):
+        pairs = [(self.weights[record.name], master) for record, master in self._tracked()]
+        on_gpu = bool(pairs) and pairs[0][0].is_cuda and all(a.is_contiguous() and m.is_contiguous() for a, m in pairs)
+        if on_gpu:
+            rows = [(average, master, None, None, average.numel(), 0, 0.0, 0.0, ops._DT[average.dtype], ops._DT[master.dtype])
+                    for average, master in pairs]
+            if self._table is None or not self._table.matches(rows):
                 self._table = ops.TensorTable(rows, pairs[0][0].device)
             ops.multi_ema(self._table, self.decay)
         else:
-            for ema, source in pairs:
-                ops.ema_lerp(ema, source, self.decay)
+            for average, master in pairs:
+                ops.ema_lerp(average, master, self.decay)
         self.updates += 1
+
+    @torch.no_grad()
+    def apply(self):
+        """Overwrite the compute weights with the averages (used inside ``ema_scope``)."""
+        values = {record.index: self.weights[record.name] for record in self.store.records
+                  if record.name in self.weights}
+        self.store.write_many(list(self.store.records), values, purpose="ema")
 
     def state_dict(self):
         if not self.decay:
             return {}
-        return dict(decay=self.decay, dtype=self.dtype, shard=self.shard, updates=self.updates, weights=self.weights)
+        return {"decay": self.decay, "dtype": self.dtype, "shard": self.shard, "updates": self.updates,
+                "weights": self.weights}
 
     @torch.no_grad()
     def load_state_dict(self, state):
         if not self.decay:
             return
-        if state["dtype"] != self.dtype or state["shard"] != self.shard:
+        if (state["dtype"], state["shard"]) != (self.dtype, self.shard):
             raise RuntimeError("checkpoint EMA dtype / placement differs from this run")
-        if state["weights"].keys() != self.weights.keys():
+        if set(state["weights"]) != set(self.weights):
             raise RuntimeError("checkpoint EMA covers different parameters")
         self.decay, self.updates = state["decay"], state["updates"]
-        for name, average in self.weights.items():
-            average.copy_(state["weights"][name])
+        for name, saved in state["weights"].items():
+            self.weights[name].copy_(saved)
 
-    @torch.no_grad()
-    def apply(self):
-        """Write the averages into the compute weights (through the owners, like an optimizer step)."""
-        self.store.begin_writes()
-        for record in self.store.records:
-            self.store.write(record, self.weights.get(record.name), record.owner)
-        self.store.end_writes()
+
+def _average_placement(source):
+    """Where the average of a DTensor lives: row-sharded for replicated tensors with rows, else as the source."""
+    from torch.distributed.tensor import Replicate, Shard
+    (placement,) = source.placements
+    if isinstance(placement, Replicate):
+        return Shard(0) if source.ndim else placement
+    if isinstance(placement, Shard):
+        return placement
+    raise ValueError("parameters must be Replicate or Shard")
 
 
 class ShardedEMA:
-    """EMA bound to ``optimizer.step`` for DTensor parameters on a 1-D mesh; ``decay=0`` allocates nothing.
+    """Stand-alone EMA for DTensor parameters on a 1-D mesh, updated from an ``optimizer.step`` post-hook.
 
-    ``parameters`` is a module or an iterable of ``(name, DTensor)``.  Replicated parameters keep a
-    ``Shard(0)`` average (local row slice, no communication); sharded parameters keep their placement.
-    With ``bind_optimizer`` in use the average tracks the master weights.
+    ``parameters``: a module or ``(name, DTensor)`` pairs.  A replicated parameter's average is kept as its
+    local row slice (``Shard(0)``), so the state is one copy across the mesh and the update needs no
+    communication; sharded parameters keep their placement.  After ``bind_optimizer`` the average follows the
+    master weights.  ``decay=0`` allocates nothing and installs no hook.  Steps the optimizer skipped
+    (``step_was_skipped``) do not advance the average.  (viola/distributed/ema.py:7-75)
     """
 
     def __init__(self, parameters, optimizer, *, decay=0, dtype=torch.float32):
-        from torch.distributed.tensor import DTensor, Replicate, Shard
+        from torch.distributed.tensor import DTensor
         if not 0 <= decay < 1:
             raise ValueError("ema decay must be in [0, 1)")
         self.decay, self.dtype, self.updates = decay, dtype, 0
         self.weights, self._sources, self._hook = {}, {}, None
-        if decay == 0:
+        if not decay:
             return
-        pairs = parameters.named_parameters() if isinstance(parameters, torch.nn.Module) else parameters
+        named = parameters.named_parameters() if isinstance(parameters, torch.nn.Module) else parameters
         binding = getattr(optimizer, "_viola_linear_masters", None)
-        masters = {id(p): master for p, master, _ in binding.pairs} if binding is not None else {}
-        for name, param in pairs:
-            if not param.requires_grad:
+        master_of = {id(b.parameter): b.master for b in binding.bindings} if binding is not None else {}
+        for name, parameter in named:
+            if not parameter.requires_grad:
                 continue
-            source = masters.get(id(param), param)
+            source = master_of.get(id(parameter), parameter)
             if not isinstance(source, DTensor) or source.device_mesh.ndim != 1:
                 raise ValueError("ShardedEMA expects DTensor parameters on a 1-D mesh")
-            placement, = source.placements
-            if not isinstance(placement, (Replicate, Shard)):
-                raise ValueError("parameters must be Replicate or Shard")
-            if isinstance(placement, Replicate) and source.ndim:
-                placement = Shard(0)
+            placement = _average_placement(source)
             self._sources[name] = source
             self.weights[name] = source.detach().redistribute(placements=[placement]).to(dtype=dtype, copy=True)
-        self._hook = optimizer.register_step_post_hook(self._after_step)
-
-    def _after_step(self, optimizer, args, kwargs):
-        if not getattr(optimizer, "step_was_skipped", False):
-            self.update()
+        self._hook = optimizer.register_step_post_hook(
+            lambda opt, args, kwargs: None if getattr(opt, "step_was_skipped", False) else self.update())
 
     @torch.no_grad()
     def update(self):
-        if self.decay == 0:
+        if not self.decay:
             return
         for name, average in self.weights.items():
-            source = self._sources[name].detach().redistribute(placements=average.placements)
             local = average.to_local()
             if local.numel():
-                ops.ema_lerp(local, source.to_local().to(self.dtype), self.decay)
+                fresh = self._sources[name].detach().redistribute(placements=average.placements).to_local()
+                ops.ema_lerp(local, fresh.to(self.dtype), self.decay)
         self.updates += 1
 
     def state_dict(self):
-        if self.decay == 0:
+        if not self.decay:
             return {}
-        return dict(decay=self.decay, updates=self.updates, dtype=self.dtype, weights=self.weights)
+        return {"decay": self.decay, "updates": self.updates, "dtype": self.dtype, "weights": self.weights}
 
     @torch.no_grad()
     def load_state_dict(self, state):
-        if self.decay == 0:
+        if not self.decay:
             return
-        if state["dtype"] != self.dtype or state["weights"].keys() != self.weights.keys():
+        if state["dtype"] != self.dtype or set(state["weights"]) != set(self.weights):
             raise RuntimeError("checkpoint EMA differs from this instance")
         self.decay, self.updates = state["decay"], state["updates"]
-        for name, saved in state["weights"].items():
-            current = self.weights[name]
-            current.to_local().copy_(saved.redistribute(placements=current.placements).to_local())
+        for name, average in self.weights.items():
+            incoming = state["weights"][name].redistribute(placements=average.placements)
+            average.to_local().copy_(incoming.to_local())
 
     def close(self):
         if self._hook is not None:

@@ -100,18 +100,37 @@ class violaEngine:  # noqa: N801 - public name kept identical to the reference
             self.sharder.set_resident(True)
 
     def _make_transport(self):
+        """The peer-memory transport when it can work here, else None (collectives).
+
+        ``communication.backend``: ``"nccl"`` never tries; ``"p2p"`` raises when peer memory cannot be set up;
+        ``"auto"`` (default) probes it: every rank allocates and rendezvouses a small symmetric buffer, the
+        outcomes are combined with a MIN all-reduce so that all ranks take the same branch, and a fallback is
+        reported with its reason instead of passing silently."""
         communication = self.config["communication"]
         backend = communication.get("backend", "auto")
+        self.transport_reason = None
         if self.world_size == 1 or self.device.type != "cuda" or backend == "nccl":
             return None
+        reason = None
         try:
-            from .symm import PeerTransport
-            return PeerTransport(self, fp8_format=communication["fp8_format"], tile_size=communication["fp8_tile_size"],
-                                 fp8=communication["dtype"] == "fp8", overlap=communication.get("overlap", False))
-        except Exception:
+            from .symm import PeerTransport, probe_peer_memory
+            if self.world_size > 16:
+                raise RuntimeError("more than 16 ranks")
+            probe_peer_memory(self.group, self.device)
+        except Exception as error:                        # noqa: BLE001 - any failure means "use collectives"
+            reason = f"{type(error).__name__}: {str(error).splitlines()[0][:200] if str(error) else ''}"
+        verdict = torch.tensor([0 if reason else 1], device=self.device, dtype=torch.int32)
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN, group=self.group)
+        if not int(verdict.item()):
+            self.transport_reason = reason or "another rank could not map peer memory"
             if backend == "p2p":
-                raise
+                raise RuntimeError(f"communication.backend='p2p' but peer memory is unavailable: {self.transport_reason}")
+            import warnings
+            warnings.warn("viola_b200: peer-memory transport unavailable, falling back to NCCL collectives "
+                          f"({self.transport_reason})", RuntimeWarning, stacklevel=2)
             return None
+        return PeerTransport(self, fp8_format=communication["fp8_format"], tile_size=communication["fp8_tile_size"],
+                             fp8=communication["dtype"] == "fp8", overlap=communication.get("overlap", False))
 
     def prepare_dataloader(self, loader):
         return prepare_dataloader(loader, rank=self.rank, world_size=self.world_size)
@@ -230,10 +249,13 @@ class violaEngine:  # noqa: N801 - public name kept identical to the reference
         return checkpoint.load(self, path, scheduler=scheduler)
 
     def close(self):
-        if self.state is not None:
-            self.state.close()
-        if self.transport is not None:
-            self.transport.close()
+        """Remove hooks, drain the side stream and report a kernel failure that nothing has reported yet."""
+        try:
+            if self.state is not None:
+                self.state.close()
+        finally:
+            if self.transport is not None:
+                self.transport.close()
 
 
 class _GraphedMicrobatch:

@@ -27,8 +27,10 @@ from .fp8 import FP8Communication
 
 class GradientState:
     def __init__(self, store, *, gradient_dtype, communication_dtype=None, bucket_mb=25, fp8_format="e4m3",
-                 fp8_tile_size=256, shard=False, defer_reduction=False, transport=None):
+                 fp8_tile_size=256, shard=False, defer_reduction=False, transport=None, monitor=None):
         self.store = store
+        self.monitor = monitor
+        self.mailbox = transport          # per-step usage / status exchange, whatever moves the gradients
         self.records = store.records
         self.rank, self.world, self.group = store.rank, store.world, store.group
         self.shard = shard and self.world > 1
@@ -173,31 +175,55 @@ class GradientState:
         self.in_backward = False
 
     # ------------------------------------------------------------------ step-time reduction
+    def _agree_on_usage(self):
+        """Which records produced a gradient on any rank (``active``), with every rank's kernel status riding
+        along so that a recorded failure raises everywhere in the same step.
+
+        Peer-memory transport: each rank stores its message into all heaps and the host does not wait; when
+        every local record was used the answer is "all" whatever the peers say, so the host only waits in the
+        rare step with locally unused parameters.  Collective transports: one MAX all-reduce.
+        """
+        count = len(self.records)
+        code = self.monitor.local_code() if self.monitor is not None else 0
+        if self.world == 1:
+            if code:
+                self.monitor.raise_for(code)
+            return list(self.used)
+        if self.mailbox is not None:
+            self.mailbox.exchange_usage(self.used, injected=self.monitor.pending if self.monitor is not None else 0)
+            if self.monitor is not None:
+                self.monitor.pending = 0
+            if all(self.used):
+                return [True] * count
+            codes, _, used = self.mailbox.read_usage(wait=True)
+            self.mailbox.raise_for_codes(codes)
+            return used
+        message = torch.tensor([code, *self.used], device=self.accumulator.device, dtype=torch.int32)
+        dist.all_reduce(message, op=dist.ReduceOp.MAX, group=self.group)
+        values = message.tolist()
+        if values[0]:
+            self.monitor.raise_for(values[0], rank="(some)")
+        return [bool(v) for v in values[1:]]
+
     @torch.no_grad()
     def reduce(self, divisor):
         """Agree on which parameters were used anywhere, finish replicated reductions, normalise."""
-        if self.world > 1:
-            used = torch.tensor(self.used, device=self.accumulator.device, dtype=torch.int32)
-            dist.all_reduce(used, op=dist.ReduceOp.MAX, group=self.group)
-            active = used.bool().tolist()
-            if not self.shard:
-                for bucket in self.bucket_slices:      # bucket-ordered accumulator: reduce in place, no staging
-                    if self.transport is not None:
-                        self.transport.all_reduce(bucket)
-                    elif self.fp8 is not None and bucket.dtype == torch.float32:
-                        self.fp8.all_reduce(bucket)
-                    elif self.fp8 is not None:
-                        buffer = self.buffer[:bucket.numel()].copy_(bucket)
-                        self.fp8.all_reduce(buffer)
-                        bucket.copy_(buffer)
-                    elif bucket.dtype == self.dtype:
-                        dist.all_reduce(bucket, group=self.group)
+        active = self._agree_on_usage()
+        if self.world > 1 and not self.shard:
+            for bucket in self.bucket_slices:          # bucket-ordered accumulator: reduce in place, no staging
+                if self.transport is not None:
+                    self.transport.all_reduce(bucket)
+                elif self.fp8 is not None and bucket.dtype == torch.float32:
+                    self.fp8.all_reduce(bucket)
+                elif self.fp8 is None and bucket.dtype == self.dtype:
+                    dist.all_reduce(bucket, group=self.group)
+                else:                                  # wire dtype differs from the accumulator's
+                    staged = self.buffer[:bucket.numel()].copy_(bucket)
+                    if self.fp8 is not None:
+                        self.fp8.all_reduce(staged)
                     else:
-                        buffer = self.buffer[:bucket.numel()].copy_(bucket)
-                        dist.all_reduce(buffer, group=self.group)
-                        bucket.copy_(buffer)
-        else:
-            active = list(self.used)
+                        dist.all_reduce(staged, group=self.group)
+                    bucket.copy_(staged)
         if self.transport is not None:
             self.transport.synchronize()
         self.accumulator.div_(divisor)

@@ -172,20 +172,19 @@ class ParameterSharder:
                     continue
                 # selected units are disjoint subtrees; the root unit takes what is left (including
                 # parameters tied across units, whose units were dropped from the selection)
-                if True:
-                    claimed.add(id(param))
-                    shape = tuple(param.shape)
-                    rows = shape[0] if shape else 1
-                    row_elems = 1
-                    for extent in shape[1:]:
-                        row_elems *= extent
-                    entry = ShardEntry(prefix + local_name, param, shape if shape else (1,), param.dtype, rows,
-                                       (rows + world - 1) // world, row_elems * param.element_size(), shard_offset,
-                                       full_offset)
-                    unit.entries.append(entry)
-                    shard_offset = _align(shard_offset + entry.shard_bytes)
-                    full_offset = _align(full_offset + world * entry.shard_bytes)
-                    self.by_parameter[param] = (unit, entry)
+                claimed.add(id(param))
+                shape = tuple(param.shape)
+                rows = shape[0] if shape else 1
+                row_elems = 1
+                for extent in shape[1:]:
+                    row_elems *= extent
+                entry = ShardEntry(prefix + local_name, param, shape if shape else (1,), param.dtype, rows,
+                                   (rows + world - 1) // world, row_elems * param.element_size(), shard_offset,
+                                   full_offset)
+                unit.entries.append(entry)
+                shard_offset = _align(shard_offset + entry.shard_bytes)
+                full_offset = _align(full_offset + world * entry.shard_bytes)
+                self.by_parameter[param] = (unit, entry)
             if not unit.entries:
                 continue
             device = unit.entries[0].parameter.device

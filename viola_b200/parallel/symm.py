@@ -41,6 +41,16 @@ def _align(value, alignment=256):
     return (value + alignment - 1) // alignment * alignment
 
 
+def probe_peer_memory(group, device):
+    """Allocate and rendezvous a small symmetric buffer; raises where peer mapping does not work (ranks on
+    different nodes, GPUs without peer access, a torch build without symmetric memory)."""
+    import torch.distributed._symmetric_memory as symm_mem
+    probe = symm_mem.empty(4096, dtype=torch.uint8, device=device)
+    handle = symm_mem.rendezvous(probe, group)
+    if len(handle.buffer_ptrs) != handle.world_size:
+        raise RuntimeError("symmetric-memory rendezvous returned an incomplete peer table")
+
+
 class SymmetricHeap:
     def __init__(self, nbytes, group, device):
         import torch.distributed._symmetric_memory as symm_mem
@@ -86,8 +96,6 @@ class PeerTransport:
         self.step_generation = 0
         ops.load()
         self._ops = torch.ops.viola_b200
-        # probe early so that "auto" can fall back before any layout depends on the heap
-        import torch.distributed._symmetric_memory as symm_mem  # noqa: F401
 
     # ------------------------------------------------------------------ layout
     def request(self, name, nbytes):
@@ -152,8 +160,10 @@ class PeerTransport:
             owned_counts[owner] += 1
         self.request("grad_receive", max(per_owner) if per_owner else 0)
         self._max_owned = max(owned_counts) if owned_counts else 0
-        self.staging = [torch.empty(capacity, device=self.device, dtype=torch.float32) for _ in range(4)]
-        self.staging_events = [None] * 4
+        # staging buffers rotate only when reduction overlaps backward; after-backward reduction needs one
+        count = 4 if self.overlap else 1
+        self.staging = [torch.empty(capacity, device=self.device, dtype=torch.float32) for _ in range(count)]
+        self.staging_events = [None] * count
         self.staging_cursor = 0
 
     def finalize_gradients(self):

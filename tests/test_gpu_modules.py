@@ -410,3 +410,48 @@ def test_carried_stream_gradient_is_added_in_the_layernorm_backward(stream_dtype
     assert torch.equal(results[0][0], results[1][0])
     assert rel_l2(results[0][1], results[1][1]) < (4e-3 if stream_dtype == torch.bfloat16 else 1e-6)
     assert torch.equal(results[0][2], results[1][2]) and torch.equal(results[0][3], results[1][3])
+
+
+def test_table_driven_writeback_matches_the_per_tensor_kernels():
+    """``ops.multi_writeback`` (EMA lerp + amax, then scale + encode + stores) against amax_scale + quantize + lerp."""
+    from viola_b200 import ops
+    device = torch.device("cuda")
+    torch.manual_seed(3)
+    shapes = [(1152, 1152), (96, 64), (37, 20), (256, 48)]
+    masters = [torch.randn(s, device=device) * (0.02 * (i + 1)) for i, s in enumerate(shapes)]
+    masters[2] = masters[2].to(torch.bfloat16)                      # a 16-bit master takes the scalar path
+    averages = [torch.randn(s, device=device) for s in shapes]
+    averages[2] = None
+    expected_averages = [None if a is None else a.clone() for a in averages]
+    headers = torch.zeros(len(shapes), 32, device=device)
+    codes = [torch.zeros(m.numel() + 64, device=device, dtype=torch.uint8) for m in masters]
+    plain = torch.zeros(shapes[3][0] * shapes[3][1], device=device, dtype=torch.bfloat16)
+    rows = []
+    for i, master in enumerate(masters):
+        rows.append(dict(master=master, ema=averages[i], n=master.numel(), slab_elems=master.numel(),
+                         dst_offset=codes[i].data_ptr(), header_offset=headers[i].data_ptr(), base_index=5, limit=448.0,
+                         history_len=16, mode=0, out_dtype=None))
+    rows[3].update(mode=2, out_dtype=torch.bfloat16, dst_offset=plain.data_ptr(), header_offset=-1)
+    table = ops.WritebackTable(rows, device)
+    decay = 0.99
+    for call in range(2):
+        ops.multi_writeback(table, heaps=[0], rank=0, calls=call, decay=decay, with_ema=True)
+        for i, master in enumerate(masters):
+            if expected_averages[i] is not None:
+                ops.ema_lerp(expected_averages[i], master, decay)
+                assert torch.equal(averages[i], expected_averages[i]), i
+            if i == 3:
+                assert torch.equal(plain.view(shapes[3]), master.to(torch.bfloat16))
+                continue
+            history = torch.zeros(16, device=device)
+            scale = ops.tensor_scale(master, history=history, index=5 + call, fp8_dtype=torch.float8_e4m3fn)
+            q, _ = ops.quantize(master, scale, fp8_dtype=torch.float8_e4m3fn)
+            assert torch.equal(codes[i][:master.numel()].view(master.shape), q.view(torch.uint8)), (i, call)
+            assert not codes[i][master.numel():].any()
+            assert headers[i][0].item() == scale.item()
+            slot = (5 + call) % 16
+            assert headers[i][1 + slot].item() == history[slot].item() and history[slot].item() > 0
+        for master in masters:                                       # a second round on changed weights
+            master.mul_(1.5)
+    torch.cuda.synchronize()
+    ops.check_status()

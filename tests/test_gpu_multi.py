@@ -157,11 +157,81 @@ def training_worker(rank, world, port, backend, directory, results):
     torch.cuda.synchronize()
     ops.check_status()
     weights = engine.state.parameters.model_state_dict()
+    store = engine.state.parameters
+
+    def one_step(step):
+        for micro in range(2):
+            generator = torch.Generator(device=engine.device).manual_seed(100 * step + 10 * micro + rank)
+            latents = torch.randn(4, 4, 32, 32, device=engine.device, generator=generator)
+            labels = torch.randint(0, 1000, (4,), device=engine.device, generator=generator)
+            timesteps = torch.randint(0, 1000, (4,), device=engine.device, generator=generator)
+            noise = torch.randn(4, 4, 32, 32, device=engine.device, generator=generator)
+            with engine.accumulate():
+                with engine.autocast():
+                    value = diffusion_loss(model, schedule, latents, labels, timesteps, noise)
+                engine.backward(value)
+        assert engine.step()
+        return value.item()
+
+    # every rank holds the same FP8 codes, scale, amax history and call index after the owners' write-back
+    for record in store.records:
+        layer = record.layer
+        if layer is None or layer.weight_dtype != "fp8":
+            continue
+        header = torch.cat((layer.weight_scale.reshape(-1).float(), layer.weight_quantizer.history.float(),
+                            torch.tensor([float(layer.weight_quantizer.index)], device=engine.device)))
+        everyone = [torch.empty_like(header) for _ in range(world)]
+        dist.all_gather(everyone, header)
+        assert all(torch.equal(everyone[0], other) for other in everyone), record.name
+    # the peer-memory gather fills the full buffers with exactly what an all-gather of the shards gives
+    if engine.sharder is not None:
+        for unit in engine.sharder.units.values():
+            unit.stale = True
+            unit.unshard()
+            for entry in unit.entries:
+                shard = unit.shard[entry.shard_offset:entry.shard_offset + entry.shard_bytes].clone()
+                expected = torch.empty(world * entry.shard_bytes, device=engine.device, dtype=torch.uint8)
+                dist.all_gather_into_tensor(expected, shard)
+                got = unit.full[entry.full_offset:entry.full_offset + world * entry.shard_bytes]
+                assert torch.equal(got, expected), (unit.name, entry.name)
+            unit.reshard()
+    # evaluation under the averages leaves the compute weights bit-identical
+    before = store.snapshot()
+    generator = torch.Generator(device=engine.device).manual_seed(4242)
+    probe = [torch.randn(4, 4, 32, 32, device=engine.device, generator=generator),
+             torch.randint(0, 1000, (4,), device=engine.device, generator=generator),
+             torch.randint(0, 1000, (4,), device=engine.device, generator=generator),
+             torch.randn(4, 4, 32, 32, device=engine.device, generator=generator)]
+    with engine.ema_scope():
+        with engine.autocast():
+            averaged_loss = diffusion_loss(model, schedule, *probe).item()
+    after = store.snapshot()
+    assert all(torch.equal(before[name], after[name]) for name in before)
+    # save, run on, reload, run the same step again: identical bits
+    path = os.path.join(directory, f"checkpoint-{backend}")
+    engine.save_checkpoint(path)
+    first = one_step(7)
+    weights_first = store.snapshot()
+    engine.load_checkpoint(path)
+    second = one_step(7)
+    weights_second = store.snapshot()
+    assert first == second
+    assert all(torch.equal(weights_first[name], weights_second[name]) for name in weights_first)
+    torch.cuda.synchronize()
+    ops.check_status()
+    if backend == "p2p":
+        # a failure code on one rank (put in on the host) reaches every rank with the next step's exchange
+        if rank == 1:
+            engine.state.monitor.pending = 5
+        one_step(8)
+        with pytest.raises(RuntimeError, match="rank 1.*peer flag"):
+            one_step(9)
+        torch.cuda.synchronize()
     engine.close()
     dist.barrier()
     dist.destroy_process_group()
     if rank == 0:
-        torch.save((losses, {k: v.float() for k, v in weights.items() if isinstance(v, torch.Tensor)}),
+        torch.save((losses + [averaged_loss], {k: v.float() for k, v in weights.items() if isinstance(v, torch.Tensor)}),
                    os.path.join(directory, f"{backend}.pt"))
     results.put(rank)
 
@@ -183,6 +253,38 @@ def test_engine_peer_backend_matches_collective_backend():
     assert losses_a == pytest.approx(losses_b, rel=2e-2)
     for name in weights_a:
         assert rel_l2(weights_b[name], weights_a[name]) < 2e-2, name
+
+
+def test_timed_out_push_leaves_the_ticket_counter_clean():
+    """A reduce push whose acknowledgement never comes gives up, reports, and leaves the shared ticket counter at
+    zero, so the next push (whose acknowledgement is there) completes and raises its flag."""
+    from viola_b200 import ops
+    ops.load()
+    device = torch.device("cuda", 0)
+    n, tile = 300_000, 256
+    tiles = (n + tile - 1) // tile
+    bucket = torch.randn(n, device=device)
+    codes = torch.zeros(tiles * tile, device=device, dtype=torch.uint8)
+    scales = torch.zeros(tiles, device=device)
+    flag = torch.zeros(1, device=device, dtype=torch.int32)
+    ack = torch.zeros(1, device=device, dtype=torch.int32)
+    generation = torch.full((1,), 2, device=device, dtype=torch.int32)      # expects ack >= 1, which nobody wrote
+    counter = torch.zeros(1, device=device, dtype=torch.int32)
+    status = ops.status_word(device)
+
+    def push():
+        torch.ops.viola_b200.reduce_push_fp8(bucket, tile, 0, codes.data_ptr(), scales.data_ptr(), flag.data_ptr(),
+                                             ack.data_ptr(), generation, counter, 2_000_000, 64, status)
+        torch.cuda.synchronize()
+
+    push()
+    with pytest.raises(RuntimeError, match="peer flag"):
+        ops.check_status(device)
+    assert counter.item() == 0 and flag.item() == 0 and not codes.any()
+    ack.fill_(1)
+    push()
+    ops.check_status(device)
+    assert counter.item() == 0 and flag.item() == 2 and codes.any()
 
 
 def test_bounded_wait_reports_and_returns():

@@ -96,7 +96,9 @@ class DistributedState:
 
     @torch.no_grad()
     def step(self, divisor):
-        self.monitor.poll()                              # last step's snapshot, never a wait
+        # A status code recorded since the last step travels with the usage agreement inside reduce(), so
+        # that with several ranks all of them raise in the same step instead of one leaving the others
+        # inside a collective.
         with phase("reduce"):
             active = self.gradients.reduce(divisor)
         updated = any(active)

@@ -54,6 +54,10 @@ def parse():
                              "named config's 2 to keep the global batch); 0 = the named config")
     parser.add_argument("--no-e2e", action="store_true")
     parser.add_argument("--no-graph", action="store_true", help="run every microbatch eagerly (no CUDA graph)")
+    parser.add_argument("--resident", default="auto", choices=("auto", "true", "false"),
+                        help="sharding.resident: keep gathered parameters between uses (auto: when one copy is small)")
+    parser.add_argument("--overlap", action="store_true", help="communication.overlap: reduce buckets during backward")
+    parser.add_argument("--no-phases", action="store_true", help="skip the extra untimed steps that measure phase times")
     return parser.parse_args()
 
 
@@ -113,10 +117,11 @@ def model_options(name):
 
 def engine_config(args):
     return dict(num_processes=args.gpus, mixed_precision="bf16", gradient_accumulation_steps=ACCUMULATION,
-                sharding=dict(parameters=True, gradients=True, optimizer=True, ema=True),
+                sharding=dict(parameters=True, gradients=True, optimizer=True, ema=True,
+                              resident={"auto": "auto", "true": True, "false": False}[args.resident]),
                 precision=dict(master_weight_dtype="fp32", gradient_dtype="fp32"),
                 communication=dict(dtype="fp8", bucket_mb=25, fp8_format="e4m3", fp8_tile_size=256,
-                                   backend=args.backend),
+                                   backend=args.backend, overlap=args.overlap),
                 ema=dict(decay=0.9999, dtype="fp32"))
 
 
@@ -134,12 +139,41 @@ def synthetic_batches(count, micro_batch, seed, pinned):
     return batches
 
 
+def phase_breakdown(engine, train_step, *, resident_batches, steps, world):
+    """Per-phase device milliseconds of a step, from CUDA events around the engine's phases during ``steps`` extra
+    steps after the timed regions (these steps are not part of any reported throughput).
+
+    ``fp8muon_ms_per_step`` is the optimizer phase (momentum, Newton-Schulz, weight and AdamW updates);
+    ``exposed_comm_ms_per_step`` adds up what communication costs on the compute stream of this rank outside the
+    captured microbatches: the step's usage / status exchange and replicated-gradient reduction (``reduce``), the
+    owners' write-back with its barriers and the parameter re-gather (``writeback``).  Reduction kernels inside a
+    captured microbatch are part of ``microbatch``.  Maxima over ranks."""
+    import torch
+    import torch.distributed as dist
+    from viola_b200 import utils
+    from viola_b200.utils.trace import phase
+    utils.enable_timing(True)
+    for index in range(steps):
+        with phase("step_total"):
+            train_step(resident_batches[index * ACCUMULATION:(index + 1) * ACCUMULATION], False)
+    times = utils.phase_times()
+    utils.enable_timing(False)
+    names = ("step_total", "microbatch", "backward", "reduce", "optimizer", "writeback", "ema")
+    values = torch.tensor([times.get(name, 0.0) / steps for name in names], device=engine.device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(values, op=dist.ReduceOp.MAX)
+    per_phase = {name: round(v, 3) for name, v in zip(names, values.tolist()) if v}
+    return {"phases_ms_per_step": per_phase, "fp8muon_ms_per_step": per_phase.get("optimizer"),
+            "exposed_comm_ms_per_step": round(per_phase.get("reduce", 0.0) + per_phase.get("writeback", 0.0), 3)}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
     import viola_b200 as viola
     from viola_b200 import ops
     from viola_b200.models import DiT, NoiseSchedule, diffusion_loss, muon_parameter_groups
+    from viola_b200.utils.trace import phase
 
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -162,18 +196,19 @@ def run_ours(args):
 
     total_steps = args.warmup + args.steps
     host = synthetic_batches(total_steps * ACCUMULATION, micro_batch, 100 + rank, pinned=True)
-    resident = [tuple(t.to(device) for t in items) for items in host]
+    resident_list = [tuple(t.to(device) for t in items) for items in host]
 
     def microbatch_loss(latents, labels, timesteps, noise):
         return diffusion_loss(model, schedule, latents, labels, timesteps, noise)
 
-    graphed = None if args.no_graph else engine.graph_microbatch(microbatch_loss, *resident[0])
+    graphed = None if args.no_graph else engine.graph_microbatch(microbatch_loss, *resident_list[0])
 
     def train_step(microbatches, from_host):
         last = None
         for items in microbatches:
             if graphed is not None:
-                last = graphed(*items)              # pinned host tensors are copied H2D asynchronously inside
+                with phase("microbatch"):
+                    last = graphed(*items)          # pinned host tensors are copied H2D asynchronously inside
                 continue
             if from_host:
                 items = tuple(t.to(device, non_blocking=True) for t in items)
@@ -186,7 +221,7 @@ def run_ours(args):
         return last
 
     def timed(from_host):
-        source = host if from_host else resident
+        source = host if from_host else resident_list
         for step in range(args.warmup):
             loss = train_step(source[step * ACCUMULATION:(step + 1) * ACCUMULATION], from_host)
             if from_host:
@@ -215,6 +250,9 @@ def run_ours(args):
 
     device_ms, clocks, launches, loss_value = timed(from_host=False)
     ops.check_status()
+    transport = "peer memory (fused NVLink kernels, no NCCL on the step)" if engine.transport is not None else (
+        "none (single GPU)" if world == 1 else f"NCCL collectives ({engine.transport_reason or 'requested'})")
+    resident = bool(engine.sharder is not None and engine.sharder.resident)
     result = {
         "metric": "DiT-XL/2 training images/sec" if args.model == "xl_2" else f"{model_name} training images/sec",
         "value": args.global_batch * args.steps / (device_ms / 1000.0),
@@ -227,7 +265,8 @@ def run_ours(args):
                    "optimizer": "FP8Muon(balanced, standard NS) + AdamW", "ema": 0.9999,
                    "grad_comm": "fp8 e4m3 tile 256, 25 MB buckets",
                    "cache": "fresh inputs every step; per-microbatch activations exceed L2 by >100x",
-                   "cuda_graph": graphed is not None},
+                   "cuda_graph": graphed is not None, "transport": transport,
+                   "gathered_parameters_resident": resident, "comm_overlap": bool(args.overlap)},
         "clocks": clocks, "gpu_launches": launches, "final_loss": loss_value,
     }
     if not args.no_e2e:
@@ -237,6 +276,9 @@ def run_ours(args):
                          "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": 4,
                          "timing": "host wall clock around K steps incl. pinned H2D copies and loss.item(), max over ranks",
                          "clocks": e2e_clocks}
+    if not args.no_phases:
+        result.update(phase_breakdown(engine, train_step, resident_batches=resident_list,
+                                      steps=2, world=world))
     engine.close()
     if rank == 0:
         print(json.dumps(result), flush=True)

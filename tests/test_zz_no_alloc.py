@@ -38,14 +38,18 @@ def test_no_alloc_scale_matches_regular_entry_point_twice():
     stream = torch.cuda.current_stream(device).cuda_stream
     cases = [(torch.randn(3_000_001, device=device) * 7.0, 0, 448.0),
              (torch.randn(777, 513, device=device).bfloat16() * 0.01, 1, 57344.0)]
-    for tensor, code, limit in cases:
+    for call, (tensor, code, limit) in enumerate(cases):
         out = torch.zeros(1, device=device)
         message = ctypes.create_string_buffer(256)
+        torch.cuda.synchronize(device)
         allocated = torch.cuda.memory_allocated(device)
+        free_before, _ = torch.cuda.mem_get_info(device)          # the driver's view: sees a cudaMalloc inside the library
         status = function(tensor.data_ptr(), tensor.numel(), code, limit, out.data_ptr(), stream, message, 256)
         assert status == 0, message.value
         torch.cuda.synchronize(device)
         assert torch.cuda.memory_allocated(device) == allocated
+        if call:         # the first call on a device may load the module that holds the scratch array
+            assert torch.cuda.mem_get_info(device)[0] == free_before
         fmt = torch.float8_e4m3fn if limit == 448.0 else torch.float8_e5m2
         expected = ops.tensor_scale(tensor, fp8_dtype=fmt)
         torch.testing.assert_close(out, expected, rtol=1e-6, atol=0)
@@ -60,4 +64,10 @@ def test_no_alloc_scale_rejects_oversized_input():
     status = function(small.data_ptr(), MAX_ELEMENTS + 1, 0, 448.0, out.data_ptr(),
                       torch.cuda.current_stream(device).cuda_stream, message, 256)
     assert status != 0 and b"exceeds" in message.value
+    assert out.item() == 0.0
+    for bad in (0.0, -1.0, float("nan"), float("inf")):
+        status = function(small.data_ptr(), 16, 0, bad, out.data_ptr(), torch.cuda.current_stream(device).cuda_stream,
+                          message, 256)
+        assert status != 0 and b"limit" in message.value
+    torch.cuda.synchronize(device)
     assert out.item() == 0.0

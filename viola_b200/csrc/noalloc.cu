@@ -74,6 +74,9 @@ extern "C" int vb_tensor_scale_noalloc(const void* x, long long n, int dtype, fl
   if (dtype < 0 || dtype > 2)
     return fail((int)cudaErrorInvalidValue, "vb_tensor_scale_noalloc: dtype must be 0 (fp32), 1 (bf16) or 2 (fp16)",
                 error_message, error_capacity);
+  if (!(limit > 0.0f) || limit > 3.0e38f)       // also catches NaN: a scale of amax / limit must be finite and positive
+    return fail((int)cudaErrorInvalidValue, "vb_tensor_scale_noalloc: limit must be a finite number greater than 0",
+                error_message, error_capacity);
   if (n > VB_NOALLOC_MAX_ELEMENTS) {
     char text[192];
     std::snprintf(text, sizeof(text), "vb_tensor_scale_noalloc: n = %lld exceeds the built-in scratch limit of %lld elements",

@@ -18,7 +18,8 @@ extern "C" {
 // Largest input this entry point accepts (elements).  Bigger inputs are rejected, never truncated.
 #define VB_NOALLOC_MAX_ELEMENTS (4096LL * 8192LL)
 
-// scale_out[0] = max(amax(|x|), 1e-30) / limit for the n elements at x (dtype: 0 fp32, 1 bf16, 2 fp16).
+// scale_out[0] = max(amax(|x|), 1e-30) / limit for the n elements at x (dtype: 0 fp32, 1 bf16, 2 fp16);
+// limit must be finite and greater than 0 (448 for e4m3, 57344 for e5m2, or a reduced range).
 //
 //  * x and scale_out are device pointers supplied by the caller; nothing else is needed.
 //  * The scratch (4096 partial maxima + one ticket counter, 16.6 KB) is a file-scope device array

@@ -394,3 +394,76 @@ def test_hadamard64_and_misc():
     expected = ema * 0.999 + master * (1 - 0.999)
     ops.ema_lerp(ema, master, 0.999)
     torch.testing.assert_close(ema, expected, rtol=1e-6, atol=1e-7)
+
+
+# ------------------------------------------------------------------------------------------------ MXFP8 (hardware block scaling)
+@pytest.mark.parametrize("shape", [(128, 128, 128), (256, 384, 512), (200, 136, 160), (1024, 1152, 4608)])
+@pytest.mark.parametrize("formats", [(torch.float8_e4m3fn, torch.float8_e4m3fn), (torch.float8_e5m2, torch.float8_e4m3fn)])
+def test_mx_gemm_matches_dequantised_product(shape, formats):
+    """tcgen05 block-scaled MMA with UE8M0 scales in tensor memory against the fp32 product of the decoded operands
+    (bound of checks/check_grouped_linear.py:42 for fp32 accumulation and output)."""
+    m, n, k = shape
+    torch.manual_seed(m + n + k)
+    a = (torch.randn(m, k, device="cuda") * 2).to(formats[0])
+    b = (torch.randn(n, k, device="cuda") * 2).to(formats[1])
+    groups = (k + 31) // 32
+    sa = torch.randint(118, 134, (m, groups), device="cuda", dtype=torch.uint8)        # 2^-9 .. 2^6
+    sb = torch.randint(118, 134, (n, groups), device="cuda", dtype=torch.uint8)
+    bias = torch.randn(n, device="cuda")
+    out = ops.mx_gemm(a, b, ops.mx_pack_scales(sa, m, k), ops.mx_pack_scales(sb, n, k), out_dtype=torch.float32, bias=bias)
+    torch.cuda.synchronize()
+    ops.check_status()
+    expected = ref.mx_gemm(a, b, sa, sb, out_dtype=torch.float32, bias=bias)
+    assert rel_l2(out, expected) < 2e-5
+    half = ops.mx_gemm(a, b, ops.mx_pack_scales(sa, m, k), ops.mx_pack_scales(sb, n, k), out_dtype=torch.bfloat16)
+    assert rel_l2(half, ref.mx_gemm(a, b, sa, sb, out_dtype=torch.float32)) < 4e-3
+
+
+def test_mx_scales_from_fp32_powers_of_two_and_weight_blocks():
+    """Packing accepts fp32 powers of two in either storage order and 32 x 32 weight blocks (one scale per 32 rows)."""
+    m, n, k = 256, 192, 256
+    torch.manual_seed(5)
+    a = torch.randn(m, k, device="cuda").to(torch.float8_e4m3fn)
+    b = torch.randn(n, k, device="cuda").to(torch.float8_e4m3fn)
+    ea = torch.randint(120, 131, (m, k // 32), device="cuda", dtype=torch.uint8)
+    eb = torch.randint(120, 131, (n // 32, k // 32), device="cuda", dtype=torch.uint8)
+    fa, fb = torch.exp2(ea.float() - 127), torch.exp2(eb.float() - 127)
+    sfa = ops.mx_pack_scales(fa.t().contiguous(), m, k, kmajor=True)                    # K-block-major fp32
+    sfb = ops.mx_pack_scales(fb, n, k, group_rows=32)
+    assert torch.equal(sfa, ops.mx_pack_scales(ea, m, k))
+    out = ops.mx_gemm(a, b, sfa, sfb, out_dtype=torch.float32)
+    expected = ref.mx_gemm(a, b, ea, eb.repeat_interleave(32, 0), out_dtype=torch.float32)
+    assert rel_l2(out, expected) < 2e-5
+
+
+@pytest.mark.parametrize("transposed", [False, True])
+def test_power_of_two_group_encode_matches_oracle(transposed):
+    x = torch.randn(300, 416, device="cuda", dtype=torch.bfloat16) * 3
+    x[7, 40:72] = 0                                                    # an all-zero group
+    x[9, :32] = torch.tensor(2.0 ** 5)                                 # amax / limit exactly representable
+    q, s = ops.group_quantize(x, torch.float8_e4m3fn, (1, 32), transposed=transposed, pow2=True)
+    rq, rs = ref.group_quantize(x.cpu(), torch.float8_e4m3fn, (1, 32), transposed=transposed, pow2=True)
+    assert torch.equal(s.cpu(), rs) and torch.equal(q.cpu().view(torch.uint8), rq.view(torch.uint8))
+    exponent = (s.view(torch.int32) >> 23) & 0xff
+    assert torch.equal(torch.exp2(exponent.float() - 127), s)          # every scale is a power of two
+
+
+def test_mxfp8_linear_runs_on_the_block_scaled_path_and_matches_cpu():
+    from viola_b200.nn import Linear
+    torch.manual_seed(11)
+    layer = Linear(256, 384, scaling="mxfp8", device="cuda", dtype=torch.bfloat16)
+    x = torch.randn(512, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    before = ops.launch_count
+    y = layer(x)
+    y.float().square().mean().backward()
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert ops.launch_count > before
+    clone = Linear(256, 384, scaling="mxfp8", device="cpu", dtype=torch.bfloat16)
+    clone.load_state_dict({k: v.cpu() if isinstance(v, torch.Tensor) else v for k, v in layer.state_dict().items()})
+    xc = x.detach().cpu().requires_grad_(True)
+    yc = clone(xc)
+    yc.float().square().mean().backward()
+    assert rel_l2(y.detach().cpu(), yc.detach()) < 1e-2
+    assert rel_l2(x.grad.cpu(), xc.grad) < 2e-2
+    assert rel_l2(layer.weight.grad.cpu(), clone.weight.grad) < 2e-2

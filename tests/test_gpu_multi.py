@@ -131,14 +131,18 @@ def training_worker(rank, world, port, backend, directory, results):
     import viola_b200 as viola
     from viola_b200 import ops
     from viola_b200.models import DiT, NoiseSchedule, diffusion_loss, muon_parameter_groups
+    label = backend
+    backend, _, variant = backend.partition(":")
+    resident = False if variant == "gathered-per-use" else "auto"
     config = dict(mixed_precision="bf16", gradient_accumulation_steps=2,
-                  sharding=dict(parameters=True, gradients=True, optimizer=True, ema=True),
+                  sharding=dict(parameters=True, gradients=True, optimizer=True, ema=True, resident=resident),
                   communication=dict(dtype="fp8", backend=backend, bucket_mb=1), ema=dict(decay=0.999))
     engine = viola.violaEngine(config)
     torch.manual_seed(0)
     model = engine.prepare_model(DiT(width=256, depth=3, heads=4, patch=2))
     engine.prepare_optimizer(lambda params: viola.optim.FP8Muon(muon_parameter_groups(model, lr=1e-3)))
     assert (engine.transport is not None) == (backend == "p2p")
+    assert engine.sharder.resident == (resident == "auto")
     schedule = NoiseSchedule(device=engine.device)
     losses = []
     for step in range(3):
@@ -208,7 +212,7 @@ def training_worker(rank, world, port, backend, directory, results):
     after = store.snapshot()
     assert all(torch.equal(before[name], after[name]) for name in before)
     # save, run on, reload, run the same step again: identical bits
-    path = os.path.join(directory, f"checkpoint-{backend}")
+    path = os.path.join(directory, f"checkpoint-{label.replace(':', '-')}")
     engine.save_checkpoint(path)
     first = one_step(7)
     weights_first = store.snapshot()
@@ -232,7 +236,7 @@ def training_worker(rank, world, port, backend, directory, results):
     dist.destroy_process_group()
     if rank == 0:
         torch.save((losses + [averaged_loss], {k: v.float() for k, v in weights.items() if isinstance(v, torch.Tensor)}),
-                   os.path.join(directory, f"{backend}.pt"))
+                   os.path.join(directory, f"{label}.pt"))
     results.put(rank)
 
 
@@ -245,7 +249,7 @@ def test_fused_collectives_match_oracle():
 def test_engine_peer_backend_matches_collective_backend():
     outputs = {}
     with tempfile.TemporaryDirectory() as directory:
-        for backend in ("nccl", "p2p"):
+        for backend in ("nccl", "p2p", "p2p:gathered-per-use"):
             launch(training_worker, 2, backend, directory)
             outputs[backend] = torch.load(os.path.join(directory, f"{backend}.pt"), weights_only=False)
     losses_a, weights_a = outputs["nccl"]
@@ -253,6 +257,10 @@ def test_engine_peer_backend_matches_collective_backend():
     assert losses_a == pytest.approx(losses_b, rel=2e-2)
     for name in weights_a:
         assert rel_l2(weights_b[name], weights_a[name]) < 2e-2, name
+    # gathering every unit per use (next unit prefetched on a side stream) computes exactly what resident copies do
+    losses_c, weights_c = outputs["p2p:gathered-per-use"]
+    assert losses_b == losses_c
+    assert all(torch.equal(weights_b[name], weights_c[name]) for name in weights_b)
 
 
 def test_timed_out_push_leaves_the_ticket_counter_clean():

@@ -133,3 +133,18 @@ def test_block_fusion_ops_on_cpu():
     q, _ = ops.quantize(x.detach(), torch.tensor([0.05]), colsum=colsum)
     torch.testing.assert_close(colsum, x.detach().sum(dim=0))
     assert q.shape == x.shape
+
+
+def test_power_of_two_scale_rule_is_exact():
+    """MXFP8 scales are the smallest power of two >= amax / limit, with no logarithm rounding at the boundaries."""
+    from viola_b200.ops import reference
+    values = torch.tensor([1.0, 1.0 + 2 ** -23, 0.75, 0.5, 0.5 - 2 ** -25, 3e-30, 2.0 ** -126, 448.0])
+    expected = torch.tensor([1.0, 2.0, 1.0, 0.5, 0.5, 2.0 ** -98, 2.0 ** -126, 512.0])
+    assert torch.equal(reference.ceil_pow2(values), expected)
+    x = torch.randn(64, 96) * 5
+    q, s = reference.group_quantize(x, torch.float8_e4m3fn, (1, 32), pow2=True)
+    assert torch.equal(torch.exp2(torch.round(torch.log2(s))), s)
+    plain = reference.group_quantize(x, torch.float8_e4m3fn, (1, 32))[1]
+    assert ((s >= plain) & (s < 2 * plain)).all()
+    decoded = reference.group_dequantize(q, s, (1, 32))
+    assert ((decoded - x).abs() <= 0.0625 * x.abs() + 1e-6 + s.repeat_interleave(32, 1) * 2 ** -9).all()

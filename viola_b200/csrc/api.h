@@ -25,7 +25,7 @@ int vb_quantize(const void* x, int rows, int cols, int dtype, const float* scale
 int vb_transpose_u8(const void* x, int rows, int cols, void* out, cudaStream_t stream);
 int vb_group_encode(const void* x, int rows, int cols, int dtype, int fmt, float limit, void* q, float* s,
                     int gr, int gc, long long s_row, long long s_col, void* qt, float* st, int tgr, int tgc,
-                    long long st_row, long long st_col, cudaStream_t stream);
+                    long long st_row, long long st_col, int pow2 /* 1: round every scale up to a power of two (MXFP8) */, cudaStream_t stream);
 int vb_group_decode(const void* q, const float* s, int rows, int cols, int fmt, int gr, int gc,
                     long long s_row, long long s_col, float* out, cudaStream_t stream);
 
@@ -80,6 +80,20 @@ typedef struct VbGemmDesc {
 } VbGemmDesc;
 
 int vb_gemm(const VbGemmDesc* desc, cudaStream_t stream);
+
+// ---- MXFP8: hardware block-scaled GEMM (mxfp8_gemm_sm100.cu) ---------------------------------
+// out[m, n] = sum_k (A[m, k] * 2^(sfa[m, k/32] - 127)) * (B[n, k] * 2^(sfb[n, k/32] - 127)) (+ bias[n]);
+// A [M, K], B [N, K]: e4m3 (fmt 0) / e5m2 (fmt 1) codes, K contiguous, row pitches lda / ldb bytes (multiples of 16).
+// sfa_tiled / sfb_tiled: UE8M0 scale bytes in the tiled layout written by vb_mx_pack_scales
+// (vb_mx_scale_bytes(rows, K) bytes each, 16-byte aligned).  out_dtype: 0 fp32, 1 bf16, 2 fp16.
+long long vb_mx_scale_bytes(long long rows, long long k);
+// scales: one fp32 power of two (is_bytes = 0) or one UE8M0 byte (is_bytes = 1) per (row >> row_shift, 32 K elements),
+// element (r, g) at scales[(r >> row_shift) * row_stride + g * group_stride].
+int vb_mx_pack_scales(const void* scales, int is_bytes, long long row_stride, long long group_stride, int rows, int k,
+                      int row_shift, uint8_t* out, cudaStream_t stream);
+int vb_mx_gemm(const void* a, long long lda, int a_fmt, const void* b, long long ldb, int b_fmt,
+               const uint8_t* sfa_tiled, const uint8_t* sfb_tiled, int M, int N, int K, void* out, int out_dtype,
+               long long ldo, const void* bias, int bias_dtype, int* status, cudaStream_t stream);
 
 // ---- optimizer kernels ---------------------------------------------------------
 int vb_momentum_1d(const void* grad, int grad_dtype, long long n, const uint8_t* old_q,

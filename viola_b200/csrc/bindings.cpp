@@ -77,13 +77,13 @@ void transpose_u8(const Tensor& x, Tensor out) {
 
 void group_encode(const Tensor& x, int64_t fmt, double limit, const OptTensor& q, const OptTensor& s, int64_t gr,
                   int64_t gc, int64_t s_row, int64_t s_col, const OptTensor& qt, const OptTensor& st, int64_t tgr,
-                  int64_t tgc, int64_t st_row, int64_t st_col) {
+                  int64_t tgc, int64_t st_row, int64_t st_col, bool pow2) {
   cuda_contig(x, "x");
   TORCH_CHECK(x.dim() == 2 && gc >= 32 && (!qt.has_value() || tgc >= 32), "group columns must be >= 32");
   c10::cuda::CUDAGuard guard(x.device());
   check(vb_group_encode(x.data_ptr(), (int)x.size(0), (int)x.size(1), dtype_code(x), (int)fmt, (float)limit, ptr(q),
                         (float*)ptr(s), (int)gr, (int)gc, s_row, s_col, ptr(qt), (float*)ptr(st), (int)tgr, (int)tgc,
-                        st_row, st_col, stream()),
+                        st_row, st_col, pow2 ? 1 : 0, stream()),
         "group_encode");
 }
 
@@ -318,6 +318,35 @@ void wire_unpack(const Tensor& packet, int64_t row_stride, int64_t rows, int64_t
   check(vb_wire_unpack((const uint8_t*)packet.data_ptr(), row_stride, (int)rows, (int)groups, (int)tile, (int)fmt,
                        reduce, out.data_ptr<float>(), out.numel(), accumulate, stream()),
         "wire_unpack");
+}
+
+// ---- MXFP8 hardware block-scaled GEMM --------------------------------------------------------------
+Tensor mx_pack_scales(const Tensor& scales, int64_t row_stride, int64_t group_stride, int64_t rows, int64_t k,
+                      int64_t row_shift) {
+  TORCH_CHECK(scales.is_cuda() && (scales.scalar_type() == at::kFloat || scales.scalar_type() == at::kByte),
+              "scales must be a CUDA fp32 or uint8 tensor");
+  c10::cuda::CUDAGuard guard(scales.device());
+  Tensor out = at::empty({vb_mx_scale_bytes(rows, k)}, scales.options().dtype(at::kByte));
+  check(vb_mx_pack_scales(scales.data_ptr(), scales.scalar_type() == at::kByte ? 1 : 0, row_stride, group_stride, (int)rows,
+                          (int)k, (int)row_shift, out.data_ptr<uint8_t>(), stream()),
+        "mx_pack_scales");
+  return out;
+}
+
+void mx_gemm(const Tensor& a, int64_t a_fmt, const Tensor& b, int64_t b_fmt, const Tensor& sfa, const Tensor& sfb, Tensor out,
+             const OptTensor& bias, Tensor status) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "A [M, K], B [N, K]");
+  TORCH_CHECK(a.element_size() == 1 && b.element_size() == 1 && a.stride(1) == 1 && b.stride(1) == 1, "FP8 codes, K contiguous");
+  TORCH_CHECK(out.dim() == 2 && out.size(0) == a.size(0) && out.size(1) == b.size(0) && out.stride(1) == 1);
+  TORCH_CHECK(sfa.numel() == vb_mx_scale_bytes(a.size(0), a.size(1)) && sfb.numel() == vb_mx_scale_bytes(b.size(0), b.size(1)),
+              "scale tensors must come from mx_pack_scales for these operands");
+  c10::cuda::CUDAGuard guard(a.device());
+  const bool has_bias = bias.has_value() && bias->defined();
+  check(vb_mx_gemm(a.data_ptr(), a.stride(0), (int)a_fmt, b.data_ptr(), b.stride(0), (int)b_fmt, sfa.data_ptr<uint8_t>(),
+                   sfb.data_ptr<uint8_t>(), (int)a.size(0), (int)b.size(0), (int)a.size(1), out.data_ptr(), dtype_code(out),
+                   out.stride(0), has_bias ? bias->data_ptr() : nullptr, has_bias ? dtype_code(*bias) : 0,
+                   (int*)status.data_ptr(), stream()),
+        "mx_gemm");
 }
 
 // ---- peer-memory kernels -----------------------------------------------------------------------
@@ -598,6 +627,8 @@ TORCH_LIBRARY(viola_b200, m) {
   m.def("quantize_push", &quantize_push);
   m.def("byte_push", &byte_push);
   m.def("multi_writeback", &multi_writeback);
+  m.def("mx_pack_scales", &mx_pack_scales);
+  m.def("mx_gemm", &mx_gemm);
   m.def("signal", &signal);
   m.def("wait_flags", &wait_flags);
   m.def("gather_pull", &gather_pull);

@@ -15,11 +15,17 @@
 //           (viola/distributed/fp8.py:48-65): reduce-scatter by push, second quantisation fused
 //           with the all-gather push, dequantise.
 //   path 3  parameter gather     vb_gather_pull: one kernel pulls every peer's row slab of every
-//           parameter of a unit into the local full buffers and raises one flag per (parameter,
-//           source rank); the consuming tcgen05 GEMM waits on those flags inside its TMA producer.
-//   path 4  owner write-back     vb_quantize_push: master -> (EMA lerp) -> FP8 codes written straight
-//           into every rank's weight storage (replicated) or into the owning rank's row slab
-//           (sharded); vb_byte_push for already encoded payloads; vb_signal / vb_wait_flags.
+//           parameter of a unit into the local full buffers (local slab first) and raises one flag
+//           per (parameter, source rank).  The consuming GEMMs are ordered after it by a stream
+//           event, not by polling those flags: a kernel that spins on a flag which a separate
+//           launch on the same GPU has to write is not guaranteed to ever see that launch run.
+//           The host starts the gather of the next sharding unit on a side stream while the
+//           current unit computes, which hides it (viola/distributed/fsdp.py:67 gathers in line).
+//   path 4  owner write-back     vb_multi_writeback: every master an owner holds, in two launches over a
+//           device table: EMA lerp + per-tensor amax, then scale + FP8 encode (or cast) + 16-byte
+//           stores into the row slab of whichever rank holds those rows + the layer header (scale,
+//           amax history slot) into every rank.  vb_quantize_push / vb_byte_push are the
+//           single-tensor forms; vb_signal / vb_wait_flags build the on-stream barriers.
 //
 // Waits on flags another GPU writes are bounded (``wait_clocks``); on expiry the kernel records
 // kTimeoutPeerFlag in the status word and returns without touching the data.

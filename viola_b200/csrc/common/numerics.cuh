@@ -31,6 +31,15 @@ __device__ __forceinline__ uint16_t fp8_encode2(float a, float b, int fmt) {
                                             fmt == kE4M3 ? __NV_E4M3 : __NV_E5M2);
 }
 
+// Smallest power of two >= s for a positive finite s (exactly: exponent bumped when the mantissa is non-zero);
+// the MXFP8 recipe stores scales as UE8M0 exponents.  Inf / NaN pass through.
+__device__ __forceinline__ float ceil_pow2(float s) {
+  const uint32_t bits = __float_as_uint(s);
+  const uint32_t exponent = (bits >> 23) & 0xffu;
+  if (exponent == 0xffu) return s;
+  return __uint_as_float((exponent + ((bits & 0x7fffffu) != 0u ? 1u : 0u)) << 23);
+}
+
 // clamp(v / scale, +-limit) with NaN preserved (fminf/fmaxf would drop it).
 __device__ __forceinline__ float scaled_clamp(float v, float inv_or_scale_div, float limit) {
   float q = v / inv_or_scale_div;

@@ -294,7 +294,7 @@ __global__ void __launch_bounds__(256)
 group_encode_kernel(const typename Src<DT>::T* __restrict__ x, int rows, int cols, int fmt, float limit,
                     uint8_t* __restrict__ q, float* __restrict__ s, int gr, int gc, long long s_row,
                     long long s_col, uint8_t* __restrict__ qt, float* __restrict__ st, int tgr, int tgc,
-                    long long st_row, long long st_col) {
+                    long long st_row, long long st_col, int pow2) {
   constexpr int TS = 128;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float (*tile)[TS + 1] = reinterpret_cast<float (*)[TS + 1]>(smem_raw);  // 128 x 129 floats
@@ -334,6 +334,7 @@ group_encode_kernel(const typename Src<DT>::T* __restrict__ x, int rows, int col
     // Groups wider than the tile need a cross-CTA amax; those shapes use the generic kernel.
     for (int g = threadIdx.x; g < ngroups; g += blockDim.x) {
       float sc_v = fmaxf(gscale[g], 1e-30f) / limit;
+      if (pow2) sc_v = ceil_pow2(sc_v);
       gscale[g] = sc_v;
       int gy = g / ngc, gx = g % ngc;
       int orow0 = (pass == 0 ? r0 : c0) + gy * er, ocol0 = (pass == 0 ? c0 : r0) + gx * ec;
@@ -376,7 +377,7 @@ group_encode_kernel(const typename Src<DT>::T* __restrict__ x, int rows, int col
 template <int DT>
 __global__ void __launch_bounds__(256)
 row128_encode_kernel(const typename Src<DT>::T* __restrict__ x, int rows, int cols, int fmt, float limit,
-                     uint8_t* __restrict__ q, float* __restrict__ s, long long s_row, long long s_col) {
+                     uint8_t* __restrict__ q, float* __restrict__ s, long long s_row, long long s_col, int pow2) {
   const int groups_per_row = cols / 128;
   const long long total = (long long)rows * groups_per_row;
   const int lane = threadIdx.x & 31;
@@ -403,7 +404,8 @@ row128_encode_kernel(const typename Src<DT>::T* __restrict__ x, int rows, int co
     float m = fmaxf(fmaxf(abs_nan_to_inf(v[0]), abs_nan_to_inf(v[1])),
                     fmaxf(abs_nan_to_inf(v[2]), abs_nan_to_inf(v[3])));
     m = warp_max(m);
-    const float sc = fmaxf(m, 1e-30f) / limit;
+    float sc = fmaxf(m, 1e-30f) / limit;
+    if (pow2) sc = ceil_pow2(sc);
     uint32_t packed = 0;
 #pragma unroll
     for (int e = 0; e < 4; ++e) packed |= (uint32_t)fp8_encode(scaled_clamp(v[e], sc, limit), fmt) << (8 * e);
@@ -417,7 +419,7 @@ template <int DT>
 __global__ void __launch_bounds__(128)
 group_encode_generic_kernel(const typename Src<DT>::T* __restrict__ x, int rows, int cols, int fmt,
                             float limit, int transposed, uint8_t* __restrict__ q, float* __restrict__ s,
-                            int gr, int gc, long long s_row, long long s_col) {
+                            int gr, int gc, long long s_row, long long s_col, int pow2) {
   // output coordinates: (orows, ocols) = transposed ? (cols, rows) : (rows, cols)
   const int orows = transposed ? cols : rows, ocols = transposed ? rows : cols;
   const int ngc = (ocols + gc - 1) / gc;
@@ -436,7 +438,8 @@ group_encode_generic_kernel(const typename Src<DT>::T* __restrict__ x, int rows,
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
   __syncthreads();
   m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-  const float sc = fmaxf(m, 1e-30f) / limit;
+  float sc = fmaxf(m, 1e-30f) / limit;
+  if (pow2) sc = ceil_pow2(sc);
   if (threadIdx.x == 0) s[(long long)gy * s_row + (long long)gx * s_col] = sc;
   for (int e = threadIdx.x; e < count; e += blockDim.x) {
     int y = gy * gr + e / gc, xx = gx * gc + e % gc;
@@ -547,10 +550,10 @@ extern "C" int vb_transpose_u8(const void* x, int rows, int cols, void* out, cud
 
 extern "C" int vb_group_encode(const void* x, int rows, int cols, int dtype, int fmt, float limit, void* q,
                                float* s, int gr, int gc, long long s_row, long long s_col, void* qt,
-                               float* st, int tgr, int tgc, long long st_row, long long st_col,
+                               float* st, int tgr, int tgc, long long st_row, long long st_col, int pow2,
                                cudaStream_t stream) {
-  auto pow2 = [](int v) { return v > 0 && (v & (v - 1)) == 0; };
-  if (!pow2(gr) || !pow2(gc) || (qt != nullptr && (!pow2(tgr) || !pow2(tgc))))
+  auto is_pow2 = [](int v) { return v > 0 && (v & (v - 1)) == 0; };
+  if (!is_pow2(gr) || !is_pow2(gc) || (qt != nullptr && (!is_pow2(tgr) || !is_pow2(tgc))))
     return (int)cudaErrorInvalidValue;
   const bool tile_ok = gr <= 128 && gc <= 128 && (qt == nullptr || (tgr <= 128 && tgc <= 128));
   const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 3) == 0;
@@ -559,7 +562,7 @@ extern "C" int vb_group_encode(const void* x, int rows, int cols, int dtype, int
     int blocks = (int)std::min<long long>((groups + 7) / 8, 148 * 16);
     VB_DISPATCH_DT(dtype, (row128_encode_kernel<DT><<<blocks, 256, 0, stream>>>(
                               reinterpret_cast<const Src<DT>::T*>(x), rows, cols, fmt, limit,
-                              reinterpret_cast<uint8_t*>(q), s, s_row, s_col)));
+                              reinterpret_cast<uint8_t*>(q), s, s_row, s_col, pow2)));
     return (int)cudaGetLastError();
   }
   if (tile_ok) {
@@ -570,7 +573,7 @@ extern "C" int vb_group_encode(const void* x, int rows, int cols, int dtype, int
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       kernel<<<grid, 256, smem, stream>>>(reinterpret_cast<const Src<DT>::T*>(x), rows, cols, fmt, limit,
                                           reinterpret_cast<uint8_t*>(q), s, gr, gc, s_row, s_col,
-                                          reinterpret_cast<uint8_t*>(qt), st, tgr, tgc, st_row, st_col);
+                                          reinterpret_cast<uint8_t*>(qt), st, tgr, tgc, st_row, st_col, pow2);
     });
     return (int)cudaGetLastError();
   }
@@ -578,13 +581,13 @@ extern "C" int vb_group_encode(const void* x, int rows, int cols, int dtype, int
     int groups = ((rows + gr - 1) / gr) * ((cols + gc - 1) / gc);
     VB_DISPATCH_DT(dtype, (group_encode_generic_kernel<DT><<<groups, 128, 0, stream>>>(
                               reinterpret_cast<const Src<DT>::T*>(x), rows, cols, fmt, limit, 0,
-                              reinterpret_cast<uint8_t*>(q), s, gr, gc, s_row, s_col)));
+                              reinterpret_cast<uint8_t*>(q), s, gr, gc, s_row, s_col, pow2)));
   }
   if (qt != nullptr) {
     int groups = ((cols + tgr - 1) / tgr) * ((rows + tgc - 1) / tgc);
     VB_DISPATCH_DT(dtype, (group_encode_generic_kernel<DT><<<groups, 128, 0, stream>>>(
                               reinterpret_cast<const Src<DT>::T*>(x), rows, cols, fmt, limit, 1,
-                              reinterpret_cast<uint8_t*>(qt), st, tgr, tgc, st_row, st_col)));
+                              reinterpret_cast<uint8_t*>(qt), st, tgr, tgc, st_row, st_col, pow2)));
   }
   return (int)cudaGetLastError();
 }

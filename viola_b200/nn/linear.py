@@ -11,7 +11,8 @@ rowwise+transposed quantisers) and is shared with the fused gated MLP.
 
 Scaling recipes: ``current`` / ``delayed`` = one fp32 scale per tensor; ``grouped`` = one fp32 scale
 per (rows x cols) group, K-groups of 128 and wider run the two-level-accumulation tcgen05 kernel,
-other shapes decode to bf16 first; ``mxfp8`` = power-of-two (UE8M0-representable) group scales.
+other shapes decode to bf16 first; ``mxfp8`` = power-of-two (UE8M0) scales per 32 K elements, chosen by the
+encode kernel and applied by the tensor core (``tcgen05.mma.kind::mxf8f6f4.block_scale``).
 The accumulator is always fp32 in tensor memory; ``accum_dtype='fp16'`` only keeps its documented
 effect on the quantisation range (``_quantization_limit``).
 """
@@ -67,10 +68,6 @@ def transpose_group(group):
     return tuple(group[::-1]) if group[0] >= 32 else tuple(group)
 
 
-def _pow2_scales(scale):
-    return torch.exp2(torch.ceil(torch.log2(scale)))
-
-
 # ------------------------------------------------------------------------------------------------
 # quantisation helpers (activation side)
 # ------------------------------------------------------------------------------------------------
@@ -79,15 +76,15 @@ def _quantize_activation(layer, x, fmt, group, quantizer, limit, *, row, transpo
     (per-tensor only) receives the fp32 column sums of ``x`` from the same pass."""
     result = SimpleNamespace(q=None, s=None, qt=None, st=None)
     if layer._grouped_scaling:
+        pow2 = layer._native_scaling          # MXFP8: every scale a power of two, chosen inside the encode kernel
         if row and transposed:
             result.q, result.s, result.qt, result.st = ops.group_quantize_pair(x, fmt, group, group, limit=limit,
-                                                                               kmajor=True)
+                                                                               kmajor=True, pow2=pow2)
         elif row:
-            result.q, result.s = ops.group_quantize(x, fmt, group, limit=limit, kmajor=True)
+            result.q, result.s = ops.group_quantize(x, fmt, group, limit=limit, kmajor=True, pow2=pow2)
         elif transposed:
-            result.qt, result.st = ops.group_quantize(x, fmt, group, limit=limit, transposed=True, kmajor=True)
-        if layer._native_scaling:
-            _requantize_pow2(layer, x, fmt, group, limit, result)
+            result.qt, result.st = ops.group_quantize(x, fmt, group, limit=limit, transposed=True, kmajor=True,
+                                                      pow2=pow2)
         return result
     if layer.rotation_size:
         x = ops.hadamard64(x)
@@ -99,23 +96,6 @@ def _quantize_activation(layer, x, fmt, group, quantizer, limit, *, row, transpo
     result.qt = qt if transposed else None
     result.s = result.st = scale
     return result
-
-
-def _requantize_pow2(layer, x, fmt, group, limit, result):
-    """MXFP8 recipe: round every group scale up to a power of two and re-encode with it."""
-    limit_value = ops.reference.fp8_limit(fmt, limit)
-    value = x.detach().float()
-    for transposed, q_name, s_name in ((False, "q", "s"), (True, "qt", "st")):
-        scale = getattr(result, s_name)
-        if scale is None:
-            continue
-        source = value.t() if transposed else value
-        pow2 = _pow2_scales(scale.t())            # scales are K-block-major: back to [rows/gr, cols/gc]
-        expanded = pow2.repeat_interleave(group[0], 0).repeat_interleave(group[1], 1)[:source.shape[0], :source.shape[1]]
-        codes = source / expanded
-        codes = torch.where(torch.isnan(codes), codes, codes.clamp(-limit_value, limit_value)).to(fmt)
-        setattr(result, q_name, codes.contiguous())
-        setattr(result, s_name, pow2.t().contiguous())
 
 
 def _weight_operands(layer, weight, *, need_transpose):
@@ -181,7 +161,8 @@ def linear_forward(layer, x, weight, bias, *, need_input_grad, need_weight_grad,
         y, aux = ops.gated_gemm_forward(qx.q, w.q, qx.s, w.s, activation=gated, out_dtype=out_dtype, bias=bias,
                                         save=need_backward, group=group, sa_kmajor=True)
     elif layer._grouped_scaling:
-        y = ops.group_gemm(qx.q, w.q, qx.s, w.s, gx, gw, out_dtype=out_dtype, bias=bias, sa_kmajor=True)
+        y = ops.group_gemm(qx.q, w.q, qx.s, w.s, gx, gw, out_dtype=out_dtype, bias=bias, sa_kmajor=True,
+                           mx=layer._native_scaling)
     else:
         y = ops.gemm(qx.q, w.q, qx.s, w.s, out_dtype=out_dtype, bias=bias)
     saved = None
@@ -236,7 +217,7 @@ def linear_backward(layer, saved, dy, *, need_input_grad, need_weight_grad, need
         else:
             if grouped:
                 dx = ops.group_gemm(qg.q, wt, qg.s, wt_scale, gg, transpose_group(gw), out_dtype=saved.x_dtype,
-                                    sa_kmajor=True)
+                                    sa_kmajor=True, mx=layer._native_scaling)
             else:
                 dx = ops.gemm(qg.q, wt, qg.s, wt_scale, out_dtype=saved.x_dtype)
             if layer.rotation_size:
@@ -258,7 +239,7 @@ def linear_backward(layer, saved, dy, *, need_input_grad, need_weight_grad, need
             xt, xt_scale = enc.qt, enc.st
         if grouped:
             dw = ops.group_gemm(qg.qt, xt, qg.st, xt_scale, gg, gx, out_dtype=saved.weight_grad_dtype, sa_kmajor=True,
-                                sb_kmajor=True)
+                                sb_kmajor=True, mx=layer._native_scaling)
         else:
             dw = ops.gemm(qg.qt, xt, qg.st, xt_scale, out_dtype=saved.weight_grad_dtype)
         if layer.rotation_size:
@@ -472,14 +453,8 @@ class Linear(nn.Module):
         return torch.exp2(scale.float() - 127) if scale.dtype == torch.uint8 else scale
 
     def _encode_weight(self, master, group, limit, *, transposed=False):
-        q, s = ops.group_quantize(master, self.fp8_dtype, group, limit=limit, transposed=transposed)
-        if self._native_scaling:
-            s = _pow2_scales(s)
-            value = master.detach().float().t() if transposed else master.detach().float()
-            expanded = s.repeat_interleave(group[0], 0).repeat_interleave(group[1], 1)[:value.shape[0], :value.shape[1]]
-            limit_value = ops.reference.fp8_limit(self.fp8_dtype, limit)
-            q = (value / expanded).clamp(-limit_value, limit_value).to(self.fp8_dtype)
-        return q, s
+        return ops.group_quantize(master, self.fp8_dtype, group, limit=limit, transposed=transposed,
+                                  pow2=self._native_scaling)
 
     @property
     def in_place_operands(self):

@@ -317,14 +317,15 @@ def _log2(v):
     return v.bit_length() - 1
 
 
-def group_quantize(x, dtype, group, *, limit=None, transposed=False, out=None, scale_out=None, kmajor=False):
+def group_quantize(x, dtype, group, *, limit=None, transposed=False, out=None, scale_out=None, kmajor=False,
+                   pow2=False):
     """Encode ``x`` (or ``x.T`` when ``transposed``) with one fp32 scale per ``group`` block.
 
     Scales come back as ``[ceil(R/gr), ceil(C/gc)]`` or, with ``kmajor``, as its transpose
     (one contiguous row of scales per K-block: the layout the GEMM promotion loop reads).
     """
     if not x.is_cuda:
-        q, s = reference.group_quantize(x, dtype, group, limit=limit, transposed=transposed, out=out)
+        q, s = reference.group_quantize(x, dtype, group, limit=limit, transposed=transposed, out=out, pow2=pow2)
         if kmajor:
             s = s.t().contiguous()
         if scale_out is not None:
@@ -339,18 +340,20 @@ def group_quantize(x, dtype, group, *, limit=None, transposed=False, out=None, s
     s_row, s_col = (1, nr) if kmajor else (nc, 1)
     gr, gc = group
     if transposed:
-        _ops().group_encode(x, _FMT[dtype], _limit(dtype, limit), None, None, 1, 32, 0, 0, q, s, gr, gc, s_row, s_col)
+        _ops().group_encode(x, _FMT[dtype], _limit(dtype, limit), None, None, 1, 32, 0, 0, q, s, gr, gc, s_row, s_col,
+                            bool(pow2))
     else:
-        _ops().group_encode(x, _FMT[dtype], _limit(dtype, limit), q, s, gr, gc, s_row, s_col, None, None, 1, 32, 0, 0)
+        _ops().group_encode(x, _FMT[dtype], _limit(dtype, limit), q, s, gr, gc, s_row, s_col, None, None, 1, 32, 0, 0,
+                            bool(pow2))
     _count()
     return q, s
 
 
-def group_quantize_pair(x, dtype, group, group_t, *, limit=None, kmajor=False):
+def group_quantize_pair(x, dtype, group, group_t, *, limit=None, kmajor=False, pow2=False):
     """Rowwise and transposed encodings from one read of ``x``: returns (q, s, qt, st)."""
     if not x.is_cuda or max(*group, *group_t) > 128:
-        q, s = group_quantize(x, dtype, group, limit=limit, kmajor=kmajor)
-        qt, st = group_quantize(x, dtype, group_t, limit=limit, transposed=True, kmajor=kmajor)
+        q, s = group_quantize(x, dtype, group, limit=limit, kmajor=kmajor, pow2=pow2)
+        qt, st = group_quantize(x, dtype, group_t, limit=limit, transposed=True, kmajor=kmajor, pow2=pow2)
         return q, s, qt, st
     x = x.detach().contiguous()
     rows, cols = x.shape
@@ -364,7 +367,7 @@ def group_quantize_pair(x, dtype, group, group_t, *, limit=None, kmajor=False):
     st_row, st_col = (1, tnr) if kmajor else (tnc, 1)
     # the 1x128 fast path only exists for the single-output call; the pair always uses the tile kernel
     _ops().group_encode(x, _FMT[dtype], _limit(dtype, limit), q, s, group[0], group[1], s_row, s_col, qt, st,
-                        group_t[0], group_t[1], st_row, st_col)
+                        group_t[0], group_t[1], st_row, st_col, bool(pow2))
     _count()
     return q, s, qt, st
 
@@ -393,14 +396,50 @@ def _group_layout(a, b_rows, k, ga, gb, sa_kmajor, sb_kmajor):
     return (1, sa_row, sa_k, sb_row, sb_k, _log2(gb[0]), _log2(gk // 128))
 
 
-def group_gemm(a, b, sa, sb, ga, gb, *, out_dtype, bias=None, sa_kmajor=False, sb_kmajor=False, out=None):
-    """Group-scaled FP8 GEMM: sum over K-groups of (A_g . B_g^T) * sa[row, g] * sb[col-block, g]."""
+def mx_pack_scales(scales, rows, k, *, group_rows=1, kmajor=False):
+    """UE8M0 scale bytes of an MXFP8 operand [rows, k] in the tiled layout the block-scaled tensor-core GEMM reads.
+
+    ``scales``: fp32 powers of two or uint8 exponents, one per (``group_rows`` rows, 32 K elements), stored
+    [rows / group_rows, k / 32] or, with ``kmajor``, [k / 32, rows / group_rows]."""
+    scales = scales.contiguous()
+    row_groups, k_groups = (rows + group_rows - 1) // group_rows, (k + 31) // 32
+    row_stride, group_stride = (1, row_groups) if kmajor else (k_groups, 1)
+    return _ops().mx_pack_scales(scales, row_stride, group_stride, int(rows), int(k), _log2(group_rows))
+
+
+def mx_gemm(a, b, sfa, sfb, *, out_dtype, bias=None, out=None):
+    """MXFP8 GEMM on the hardware block-scaled path: ``sfa`` / ``sfb`` come from :func:`mx_pack_scales`."""
+    if out is None:
+        out = torch.empty((a.shape[0], b.shape[0]), device=a.device, dtype=out_dtype)
+    _ops().mx_gemm(a.view(torch.uint8) if a.dtype != torch.uint8 else a, _FMT.get(a.dtype, 0),
+                   b.view(torch.uint8) if b.dtype != torch.uint8 else b, _FMT.get(b.dtype, 0), sfa, sfb, out, bias,
+                   status_word(a.device))
+    _count()
+    return out
+
+
+def _mx_eligible(a, b, ga, gb):
+    return (tuple(ga) == (1, 32) and gb[1] == 32 and gb[0] & (gb[0] - 1) == 0 and a.shape[1] % 16 == 0
+            and a.dtype in FP8_DTYPES and b.dtype in FP8_DTYPES and a.is_contiguous() and b.is_contiguous())
+
+
+def group_gemm(a, b, sa, sb, ga, gb, *, out_dtype, bias=None, sa_kmajor=False, sb_kmajor=False, out=None, mx=False):
+    """Group-scaled FP8 GEMM: sum over K-groups of (A_g . B_g^T) * sa[row, g] * sb[col-block, g].
+
+    ``mx=True`` states that every scale is a power of two with groups of 32 along K (the MXFP8 recipe); the
+    product then runs on the hardware block-scaled tensor-core path (``tcgen05.mma.kind::mxf8f6f4.block_scale``)."""
     if not a.is_cuda:
         result = reference.group_gemm(a, b, sa.t() if sa_kmajor else sa, sb.t() if sb_kmajor else sb, ga, gb,
                                       out_dtype=out_dtype, bias=bias)
         return result if out is None else out.copy_(result)
     if out is None:
         out = torch.empty((a.shape[0], b.shape[0]), device=a.device, dtype=out_dtype)
+    if mx and _mx_eligible(a, b, ga, gb) and out.dtype in _DT and out.stride(-1) == 1:
+        rows_a, rows_b, k = a.shape[0], b.shape[0], a.shape[1]
+        sfa = mx_pack_scales(sa, rows_a, k, kmajor=sa_kmajor)
+        sfb = mx_pack_scales(sb, rows_b, k, group_rows=gb[0], kmajor=sb_kmajor)
+        _count(2)
+        return mx_gemm(a, b, sfa, sfb, out_dtype=out.dtype, bias=bias, out=out)
     layout = _group_layout(a, b.shape[0], a.shape[1], ga, gb, sa_kmajor, sb_kmajor)
     if layout is None:
         # Group shapes the tcgen05 promotion loop does not cover (K-groups below 128 or multi-row

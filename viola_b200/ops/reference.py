@@ -80,7 +80,14 @@ def scale_shape(shape, group):
     return tuple((n + g - 1) // g for n, g in zip(shape, group))
 
 
-def group_quantize(x, dtype, group, *, limit=None, transposed=False, out=None, scale_out=None):
+def ceil_pow2(scale):
+    """Smallest power of two >= scale, exactly (mantissa / exponent split, no logarithm): the MXFP8 scale rule."""
+    mantissa, exponent = torch.frexp(scale.float())            # scale = mantissa * 2^exponent, mantissa in [0.5, 1)
+    rounded = torch.ldexp(torch.ones_like(mantissa), torch.where(mantissa > 0.5, exponent, exponent - 1))
+    return torch.where(torch.isfinite(scale), rounded, scale.float())
+
+
+def group_quantize(x, dtype, group, *, limit=None, transposed=False, out=None, scale_out=None, pow2=False):
     limit = fp8_limit(dtype, limit)
     value = x.detach().float()
     value = value.t() if transposed else value
@@ -90,6 +97,8 @@ def group_quantize(x, dtype, group, *, limit=None, transposed=False, out=None, s
     blocks = F.pad(value, (0, nc * gc - shape[1], 0, nr * gr - shape[0])).reshape(nr, gr, nc, gc)
     magnitude = torch.where(torch.isnan(blocks), torch.full_like(blocks, float("inf")), blocks.abs())
     scales = magnitude.amax((1, 3)).clamp_min(1e-30) / limit
+    if pow2:
+        scales = ceil_pow2(scales)
     codes = blocks / scales[:, None, :, None]
     codes = torch.where(torch.isnan(codes), codes, codes.clamp(-limit, limit))
     codes = codes.reshape(nr * gr, nc * gc)[:shape[0], :shape[1]].to(dtype)
@@ -449,3 +458,14 @@ def gate_residual_backward(dout, gate, y, tokens):
     dy = (dout.float() * g).to(torch.bfloat16)
     dgate = (dout.float() * y.float()).view(rows // tokens, tokens, cols).sum(dim=1)
     return dy, dgate
+
+
+def mx_gemm(a, b, sa, sb, *, out_dtype, bias=None):
+    """Oracle of the hardware block-scaled GEMM: ``sa`` [M, K/32], ``sb`` [N, K/32] hold UE8M0 exponent bytes."""
+    def decode(codes, exponents):
+        scale = torch.exp2(exponents.float() - 127.0).repeat_interleave(32, 1)[:, :codes.shape[1]]
+        return codes.float() * scale
+    acc = decode(a, sa) @ decode(b, sb).t()
+    if bias is not None:
+        acc = acc + bias.float()
+    return acc.to(out_dtype)

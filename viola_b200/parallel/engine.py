@@ -130,7 +130,8 @@ class violaEngine:  # noqa: N801 - public name kept identical to the reference
                           f"({self.transport_reason})", RuntimeWarning, stacklevel=2)
             return None
         return PeerTransport(self, fp8_format=communication["fp8_format"], tile_size=communication["fp8_tile_size"],
-                             fp8=communication["dtype"] == "fp8", overlap=communication.get("overlap", False))
+                             fp8=communication["dtype"] == "fp8", overlap=communication.get("overlap", False),
+                             prefetch=communication.get("prefetch", True))
 
     def prepare_dataloader(self, loader):
         return prepare_dataloader(loader, rank=self.rank, world_size=self.world_size)

@@ -70,6 +70,7 @@ class ShardedUnit:
     stale: bool = False            # the shards changed since ``full`` was gathered
     pending_gradients: int = 0
     gatherer: object = None        # optional callable(unit) that fills ``full`` from peer memory
+    prefetch_event: object = None  # a gather of this unit is in flight on the prefetch stream
 
     # ------------------------------------------------------------------ views
     def local_view(self, entry):
@@ -90,9 +91,32 @@ class ShardedUnit:
     def _full_bytes(self):
         return self.full.numel()
 
+    def _join_prefetch(self):
+        """Order the current stream after a gather that was started ahead of time on the prefetch stream."""
+        if self.prefetch_event is not None:
+            torch.cuda.current_stream(self.full.device).wait_event(self.prefetch_event)
+            self.prefetch_event = None
+
+    @torch.no_grad()
+    def prefetch(self, stream):
+        """Start this unit's gather on ``stream`` (a side stream) so that it overlaps the compute in front of the
+        unit's use; the storage is allocated on the current stream, which later also frees it."""
+        if self.gatherer is None or self.resident or self.prefetch_event is not None or (self.unsharded and not self.stale):
+            return
+        storage = self.full.untyped_storage()
+        if storage.size() == 0:
+            storage.resize_(self._full_bytes())
+        stream.wait_stream(torch.cuda.current_stream(self.full.device))
+        with torch.cuda.stream(stream):
+            self.gatherer(self)
+            self.prefetch_event = torch.cuda.Event()
+            self.prefetch_event.record(stream)
+        self.unsharded, self.stale = True, False
+
     @torch.no_grad()
     def unshard(self):
         if self.unsharded and not self.stale:
+            self._join_prefetch()
             return
         storage = self.full.untyped_storage()
         if storage.size() == 0:
@@ -114,6 +138,7 @@ class ShardedUnit:
     def reshard(self):
         if not self.unsharded or self.resident:
             return
+        self._join_prefetch()          # never free storage a gather may still be writing
         self.full.untyped_storage().resize_(0)
         self.unsharded = False
 
@@ -156,6 +181,7 @@ class ParameterSharder:
         self.model, self.group, self.rank, self.world = model, group, rank, world
         self.in_backward = False
         self.resident = False
+        self.prefetch_stream = None    # set by the peer transport: gathers of the next unit run there
         self.units = {}
         self.by_parameter = {}
         self.handles = []
@@ -207,6 +233,8 @@ class ParameterSharder:
 
         def before_forward(module, args):
             unit.unshard()
+            if not self.in_backward:
+                self._prefetch_neighbour(unit, +1)
 
         def after_forward(module, args, output):
             keep = self.in_backward or (is_root and torch.is_grad_enabled())
@@ -215,10 +243,34 @@ class ParameterSharder:
 
         def before_backward(module, grad_output):
             unit.unshard()
+            self._prefetch_neighbour(unit, -1)
 
         self.handles.append(unit.module.register_forward_pre_hook(before_forward))
         self.handles.append(unit.module.register_forward_hook(after_forward))
         self.handles.append(unit.module.register_full_backward_pre_hook(before_backward))
+
+    def enable_prefetch(self, stream):
+        """Gather the unit that comes next (forward) or before (backward) on ``stream`` while the current unit
+        computes.  Only with a one-sided gatherer: collectives on a side stream would have to be entered in the
+        same order by all ranks."""
+        self.prefetch_stream = stream
+        self._sequence = [unit for name, unit in self.units.items() if name != ""]
+        self._position = {id(unit): index for index, unit in enumerate(self._sequence)}
+
+    def _prefetch_neighbour(self, unit, direction):
+        if self.prefetch_stream is None or self.resident:
+            return
+        index = self._position.get(id(unit))
+        if index is None:
+            return
+        index += direction
+        if 0 <= index < len(self._sequence):
+            self._sequence[index].prefetch(self.prefetch_stream)
+
+    def join_prefetches(self):
+        """Make the current stream wait for every gather still in flight (end of a microbatch / graph capture)."""
+        for unit in self.units.values():
+            unit._join_prefetch()
 
     def begin_backward(self):
         self.in_backward = True
@@ -235,6 +287,7 @@ class ParameterSharder:
         self.in_backward = False
         for unit in self.units.values():
             unit.reshard()
+        self.join_prefetches()
 
     def set_resident(self, resident=True):
         """Resident mode keeps every unit's gathered parameters allocated: forward and backward of every

@@ -75,12 +75,13 @@ class PeerTransport:
     calls ``attach_gradients`` / ``attach_parameters`` once the bucket and shard layouts are known."""
 
     def __init__(self, engine, *, fp8_format="e4m3", tile_size=256, fp8=True, overlap=True, max_blocks=32,
-                 wait_clocks=_DEFAULT_WAIT_CLOCKS):
+                 wait_clocks=_DEFAULT_WAIT_CLOCKS, prefetch=True):
         if engine.world_size > 16:
             raise RuntimeError("peer transport supports up to 16 ranks on one node")
         self.group, self.rank, self.world, self.device = engine.group, engine.rank, engine.world_size, engine.device
         self.fmt, self.tile, self.fp8 = _FMT[fp8_format], tile_size, fp8
         self.overlap = overlap
+        self.prefetch = prefetch           # gather the next sharding unit on a side stream while this one computes
         # Overlapped communication shares the GPU with compute, so its kernels stay narrow; without overlap they
         # run alone after backward and take the whole GPU (a 25 MB bucket then costs microseconds, not hundreds).
         self.max_blocks, self.wait_clocks = (max_blocks if overlap else 296), wait_clocks
@@ -276,6 +277,9 @@ class PeerTransport:
             unit.panel_flags = torch.zeros(len(unit.entries) * self.world, device=device, dtype=torch.int32)
             unit.gather_generation = 0
             unit.gatherer = self.gather_unit
+        if self.prefetch:
+            self.gather_stream = torch.cuda.Stream(device=device)
+            self.sharder.enable_prefetch(self.gather_stream)
         base = self.offsets["headers"]
         self.header_offset = {}
         for position, record in enumerate(self.header_records):
@@ -294,9 +298,13 @@ class PeerTransport:
     def gather_unit(self, unit):
         """Fill ``unit.full`` with every rank's slabs (local rank first) by loads from peer memory."""
         unit.gather_generation += 1
+        # a gather running beside compute on the prefetch stream stays narrow (NVLink saturates with a few dozen
+        # blocks; more would only take SMs from the GEMMs); a gather the compute stream waits for takes the GPU
+        side = getattr(self, "gather_stream", None)
+        blocks = 48 if side is not None and torch.cuda.current_stream(self.device) == side else 4 * self.max_blocks
         self._ops.gather_pull(unit.gather_entries, self.pointers, self.rank, unit.heap_offset, unit.full,
                               unit.gather_prefix, unit.piece_counts, unit.panel_flags, unit.gather_generation,
-                              unit.gather_pieces, 4 * self.max_blocks)
+                              unit.gather_pieces, blocks)
         ops._count()
 
     def write_fp8_weight(self, record, master, scale, limit):

@@ -171,7 +171,11 @@ def linear_forward(layer, x, weight, bias, *, need_input_grad, need_weight_grad,
                                 weight_scale=w.s, wt=w.qt, wt_scale=w.st, limit=limit, x_dtype=out_dtype,
                                 in_place=in_place, wq=None,
                                 weight_grad_dtype=getattr(weight, "grad_dtype", None) or torch.float32,
-                                bias_grad_dtype=(getattr(bias, "grad_dtype", None) or bias.dtype) if bias is not None else None)
+                                bias_grad_dtype=(getattr(bias, "grad_dtype", None) or bias.dtype) if bias is not None else None,
+                                # an engine may offer a place to write each gradient straight into (its landing
+                                # buffer for the gradient reduction); asked for again at backward time
+                                weight_slot=getattr(weight, "_viola_grad_slot", None),
+                                bias_slot=getattr(bias, "_viola_grad_slot", None) if bias is not None else None)
         if in_place and need_input_grad and layer.weight_dtype != "fp8" and layer.cache_weight_transpose:
             saved.wq = w.q                              # fast mode: keep this call's codes for dgrad
         if save_fp8:
@@ -179,6 +183,17 @@ def linear_forward(layer, x, weight, bias, *, need_input_grad, need_weight_grad,
         elif need_weight_grad:
             saved.x = x.to(_SAVED[layer.saved_input_dtype])
     return y, saved, aux
+
+
+def _gradient_slot(offer, shape, dtype, device):
+    """The engine's landing slot for a gradient about to be computed, when it offers one that fits."""
+    if offer is None:
+        return None
+    slot = offer()
+    if slot is None or tuple(slot.shape) != tuple(shape) or slot.dtype != dtype or slot.device != device \
+            or not slot.is_contiguous():
+        return None
+    return slot
 
 
 def linear_backward(layer, saved, dy, *, need_input_grad, need_weight_grad, need_bias_grad, gated=None, aux=None,
@@ -241,7 +256,9 @@ def linear_backward(layer, saved, dy, *, need_input_grad, need_weight_grad, need
             dw = ops.group_gemm(qg.qt, xt, qg.st, xt_scale, gg, gx, out_dtype=saved.weight_grad_dtype, sa_kmajor=True,
                                 sb_kmajor=True, mx=layer._native_scaling)
         else:
-            dw = ops.gemm(qg.qt, xt, qg.st, xt_scale, out_dtype=saved.weight_grad_dtype)
+            slot = _gradient_slot(getattr(saved, "weight_slot", None), (qg.qt.shape[0], xt.shape[0]),
+                                  saved.weight_grad_dtype, dy.device)
+            dw = ops.gemm(qg.qt, xt, qg.st, xt_scale, out_dtype=saved.weight_grad_dtype, out=slot)
         if layer.rotation_size:
             ops.hadamard64(dw, out=dw)
     if need_bias_grad:
@@ -256,7 +273,11 @@ def _backward_in_place(layer, saved, dy, limit, need_input_grad, need_weight_gra
     fmt, bfmt = layer.fp8_dtype, layer.backward_fp8_dtype
     dx = dw = db = None
     # the bias gradient (column sums of dY) comes out of the pass that encodes dY
-    db_sum = torch.zeros(dy.shape[1], device=dy.device, dtype=torch.float32) if need_bias_grad else None
+    db_sum = None
+    if need_bias_grad:
+        slot = _gradient_slot(getattr(saved, "bias_slot", None), (dy.shape[1],), torch.float32, dy.device) \
+            if saved.bias_grad_dtype == torch.float32 else None
+        db_sum = slot.zero_() if slot is not None else torch.zeros(dy.shape[1], device=dy.device, dtype=torch.float32)
     grad_scale = layer.grad_quantizer.scale_gathered(grad_amax, bfmt, limit) if grad_amax is not None else None
     qg = _quantize_activation(layer_no_rotation(layer), dy, bfmt, None, layer.grad_quantizer, limit, row=True,
                               transposed=False, colsum=db_sum, scale=grad_scale)
@@ -288,7 +309,9 @@ def _backward_in_place(layer, saved, dy, limit, need_input_grad, need_weight_gra
             enc = _quantize_activation(layer, saved.x, fmt, None, layer.input_quantizer, saved.limit, row=True,
                                        transposed=False, scale=saved.input_scale)
             xq, x_scale = enc.q, enc.s
-        dw = ops.gemm(qg.q, xq, qg.s, x_scale, out_dtype=saved.weight_grad_dtype, a_mn=True, b_mn=True)
+        slot = _gradient_slot(getattr(saved, "weight_slot", None), (qg.q.shape[1], xq.shape[1]), saved.weight_grad_dtype,
+                              dy.device)
+        dw = ops.gemm(qg.q, xq, qg.s, x_scale, out_dtype=saved.weight_grad_dtype, a_mn=True, b_mn=True, out=slot)
         if layer.rotation_size:
             ops.hadamard64(dw, out=dw)
     if need_bias_grad:
@@ -388,6 +411,9 @@ class Linear(nn.Module):
             if self._native_scaling and (accum_dtype != "fp32" or accum_block_size or accum_reduce_dtype != "fp32"):
                 raise ValueError("mxfp8 accumulates in fp32")
         self.autotune = autotune
+        if autotune:
+            from .. import tuning
+            tuning.enable()          # first-use tile search for every GEMM signature, cached on disk
         self.accum_dtype, self.accum_block_size, self.accum_reduce_dtype = accum_dtype, accum_block_size, accum_reduce_dtype
         self.quantization_limit = quantization_limit
         self.rotation_size = rotation_size

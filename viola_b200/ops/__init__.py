@@ -18,6 +18,7 @@ from pathlib import Path
 import torch
 
 from . import reference
+from .. import tuning
 from .reference import packet_bytes, packet_views, scale_shape, state_sizes  # noqa: F401
 
 _LIB_PATH = Path(__file__).resolve().parent.parent / "_C.so"
@@ -288,9 +289,22 @@ def _gemm(a, b, out, epilogue, n_logical, *, sa=None, sb=None, layout=_NO_GROUP,
     multiple = 16 if a.element_size() == 1 else 8
     a = _check_mn(a) if a_mn else _pad_k(a, multiple)
     b = _check_mn(b) if b_mn else _pad_k(b, multiple)
-    _ops().gemm(a, b, out, epilogue, n_logical, sa, sb, list(layout), bias, float(alpha), float(beta), resid, out_t,
-                bool(symmetric), int(activation), aux, expert_offsets, tile_map, status_word(a.device), int(force_bn),
-                int(batch), bool(a_mn), bool(b_mn), amax_out)
+    status = status_word(a.device)
+
+    def launch(tile):
+        _ops().gemm(a, b, out, epilogue, n_logical, sa, sb, list(layout), bias, float(alpha), float(beta), resid, out_t,
+                    bool(symmetric), int(activation), aux, expert_offsets, tile_map, status, int(tile), int(batch),
+                    bool(a_mn), bool(b_mn), amax_out)
+
+    if not force_bn and (tuning._enabled or tuning._choices):
+        # the output-tile width of this shape: recorded choice, or (tuning on) measured now on these operands
+        in_place = resid is not None and resid.data_ptr() == out.data_ptr()
+        tunable = (epilogue in (EPI_LINEAR, EPI_AXPBY, EPI_ACT_BWD) and not layout[0] and not symmetric
+                   and expert_offsets is None and not in_place and n_logical > 128)
+        signature = (int(epilogue), tuple(a.shape), tuple(b.shape), str(a.dtype), str(b.dtype), str(out.dtype), bool(a_mn),
+                     bool(b_mn), int(batch), bias is not None, int(activation), out_t is not None)
+        force_bn = tuning.choose(signature, launch, lambda: out, tunable=tunable)
+    launch(force_bn)
     _count(2 if expert_offsets is not None else 1)
     return out
 

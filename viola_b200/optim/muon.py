@@ -3,8 +3,9 @@
 Constructor, per-group options, state layout (``momentum_q`` uint8, ``momentum_scale`` fp32, ``step`` /
 ``exp_avg``, ``exp_avg_sq``), Philox key derivation and the update rule follow the reference
 (viola/optim/muon.py:14-141).  The kernels are this library's: a register-resident momentum kernel
-(optional stochastic rounding), Newton-Schulz on the tcgen05 GEMM (``ns_backend`` is accepted for
-API compatibility; both values run that kernel) and fused master-weight / AdamW updates.
+(optional stochastic rounding), Newton-Schulz on the tcgen05 GEMM (every ``ns_backend`` value runs that
+kernel; naming the kernel backend explicitly, ``"tilelang"`` or ``"tcgen05"``, together with ``ns_autotune``
+switches on the per-shape tile search of :mod:`viola_b200.tuning`) and fused master-weight / AdamW updates.
 """
 
 from __future__ import annotations
@@ -55,6 +56,9 @@ class FP8Muon(MatrixOptimizer):
                         adjust_lr_fn=adjust_lr_fn, betas=betas, eps=eps, adam_state_dtype=_dtype(adam_state_dtype),
                         master_rounding=policy["master_rounding"],
                         master_rounding_seed=policy["master_rounding_seed"])
+        if ns_autotune and ns_backend in ("tilelang", "tcgen05"):
+            from .. import tuning
+            tuning.enable()          # per-shape tile search for the Newton-Schulz GEMMs (cached on disk)
         self.observer = None
         self._workspace = {}
         self._deferred = None

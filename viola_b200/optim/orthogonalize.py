@@ -130,7 +130,17 @@ OUTPUT_DTYPE = {"standard": torch.bfloat16, "gram": torch.float16}
 
 
 def orthogonalize(matrix, *, method="standard", steps=5, autotune=True):
-    """Entry point with the keyword surface of the reference's kernel-backed path."""
+    """Entry point with the keyword surface of the reference's kernel-backed path
+    (viola/optim/_orthogonalize_kernels.py:200-202).  ``autotune``: search the tile width of this shape's GEMMs on
+    first use and remember it on disk (:mod:`viola_b200.tuning`), as the reference's per-shape planner does."""
+    if autotune and matrix.is_cuda:
+        from .. import tuning
+        previous = tuning.enabled()
+        tuning.enable()
+        try:
+            return METHODS[method](matrix, steps=steps)
+        finally:
+            tuning.enable(previous)
     return METHODS[method](matrix, steps=steps)
 
 

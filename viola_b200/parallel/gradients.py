@@ -27,7 +27,7 @@ from .fp8 import FP8Communication
 
 class GradientState:
     def __init__(self, store, *, gradient_dtype, communication_dtype=None, bucket_mb=25, fp8_format="e4m3",
-                 fp8_tile_size=256, shard=False, defer_reduction=False, transport=None, monitor=None):
+                 fp8_tile_size=256, shard=False, defer_reduction=False, transport=None, monitor=None, landing=True):
         self.store = store
         self.monitor = monitor
         self.mailbox = transport          # per-step usage / status exchange, whatever moves the gradients
@@ -81,7 +81,24 @@ class GradientState:
                     self.local[index] = self.accumulator[offset + target:offset + target + self.records[index].numel]
             offset += length
         self.bucket_capacity = max(length for _, _, length in self.buckets)
-        self.buffer = (torch.empty(self.bucket_capacity, device=device, dtype=self.dtype) if self.world > 1 else None)
+        # Landing buffer: one wire-dtype slot per parameter, laid out in bucket order, that this microbatch's
+        # gradients are written into.  Layers of this package write their weight / bias gradient straight into the
+        # slot (``parameter._viola_grad_slot``), so a bucket is ready for the reduction kernels without any
+        # per-parameter copy, and replicated / single-rank accumulation is one add over the whole buffer.
+        self.landing = torch.zeros(total, device=device, dtype=self.dtype) if landing else None
+        self.slots, self.bucket_landing = {}, []
+        if self.landing is not None:
+            start = 0
+            for _, bucket_pieces, length in self.buckets:
+                self.bucket_landing.append(self.landing[start:start + length])
+                for index, position, target, size in bucket_pieces:
+                    if position == 0:
+                        record = self.records[index]
+                        self.slots[index] = self.landing[start + target:start + target + record.numel].view(record.shape)
+                start += length
+        self.claimed = [False] * len(self.records)
+        self.buffer = (torch.empty(self.bucket_capacity, device=device, dtype=self.dtype)
+                       if self.world > 1 and self.landing is None else None)
         self.transport = transport if (transport is not None and self.fp8_requested and self.world > 1
                                        and gradient_dtype == torch.float32) else None
         if self.transport is not None:
@@ -107,10 +124,21 @@ class GradientState:
             return
         self._bound.add(id(parameter))
         self.hooks.append(parameter.register_post_accumulate_grad_hook(partial(self._ready, index)))
+        if index in self.slots and self.dtype == self.gradient_dtype:
+            parameter._viola_grad_slot = partial(self._claim, index)
+
+    def _claim(self, index):
+        """The landing slot of parameter ``index`` for the layer that is about to produce its gradient, once per
+        microbatch (a second producer of a tied parameter gets None and autograd adds the two)."""
+        if not self.in_backward or self.claimed[index]:
+            return None
+        self.claimed[index] = True
+        return self.slots[index]
 
     def begin_backward(self):
         self.in_backward = True
         self.seen = [False] * len(self.records)
+        self.claimed = [False] * len(self.records)
         self.remaining = self.piece_counts.copy()
         self.next_bucket = 0
         if self.transport is not None and self.shard:
@@ -121,14 +149,20 @@ class GradientState:
     @torch.no_grad()
     def _ready(self, index, parameter):
         self.seen[index] = self.used[index] = True
-        gradient = parameter.grad.contiguous().view(-1)
+        gradient = parameter.grad
         parameter.grad = None
-        if self.shard:
-            self.pending[index] = gradient
+        if self.landing is not None:
+            slot = self.slots[index]
+            if gradient.data_ptr() != slot.data_ptr():        # produced elsewhere (torch layers, tied weights)
+                slot.copy_(gradient.view(slot.shape))
+            if self.shard and not self.defer_reduction:
+                self._drain()
+        elif self.shard:
+            self.pending[index] = gradient.contiguous().view(-1)
             if not self.defer_reduction:
                 self._drain()
         else:
-            self.local[index].add_(gradient)
+            self.local[index].add_(gradient.contiguous().view(-1))
         if self.store.sharder is not None:
             self.store.sharder.gradient_arrived(parameter)
 
@@ -138,6 +172,10 @@ class GradientState:
             owner, pieces, length = self.buckets[self.next_bucket]
             if not final and any(not self.seen[i] for i, _, _, _ in pieces):
                 break
+            if self.landing is not None:
+                self._reduce_landed(self.next_bucket, owner, pieces, length)
+                self.next_bucket += 1
+                continue
             if self.transport is not None:
                 staging_index, staging = self.transport.next_staging()
                 buffer = staging[:length]
@@ -165,9 +203,35 @@ class GradientState:
                         self.local[index][target:target + size].add_(buffer[source:source + size])
             self.next_bucket += 1
 
+    def _reduce_landed(self, bucket_index, owner, pieces, length):
+        """Reduce one bucket straight from the landing buffer (no staging copy, no per-piece work)."""
+        buffer = self.bucket_landing[bucket_index]
+        for index, position, target, size in pieces:
+            if not self.seen[index]:
+                buffer[target:target + size].zero_()          # unused on this rank: contributes zeros
+        if self.transport is not None:
+            self.transport.reduce_to_owner(bucket_index, None, length, buffer=buffer)
+            return
+        if self.fp8 is not None:
+            self.fp8.reduce(buffer, owner)
+        else:
+            dist.reduce(buffer, dst=self.store.global_ranks[owner], group=self.group)
+        if self.rank == owner:
+            self.bucket_slices[bucket_index].add_(buffer)
+
+    def _accumulate_landed(self):
+        """Replicated / single-rank accumulation: one add of the whole landing buffer."""
+        if not all(self.seen):
+            for index, seen in enumerate(self.seen):
+                if not seen and index in self.slots:
+                    self.slots[index].zero_()
+        self.accumulator.add_(self.landing)
+
     def finish_backward(self):
         if self.shard:
             self._drain(final=True)
+        elif self.landing is not None:
+            self._accumulate_landed()
         if self.store.sharder is not None:
             self.store.sharder.finish_backward()
         if self.transport is not None:

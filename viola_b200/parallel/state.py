@@ -56,7 +56,8 @@ class DistributedState:
         self.gradients = GradientState(self.parameters, gradient_dtype=gradient_dtype, communication_dtype=wire["dtype"],
                                        bucket_mb=wire["bucket_mb"], fp8_format=wire["fp8_format"],
                                        fp8_tile_size=wire["fp8_tile_size"], shard=self.sharding["gradients"],
-                                       defer_reduction=after_backward, transport=transport, monitor=self.monitor)
+                                       defer_reduction=after_backward, transport=transport, monitor=self.monitor,
+                                       landing=wire.get("gradient_slots", True))
         for position, record in enumerate(self.parameters.records):
             self.gradients.bind(position, record.parameter)
         if transport is not None:

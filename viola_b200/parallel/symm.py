@@ -161,11 +161,9 @@ class PeerTransport:
             owned_counts[owner] += 1
         self.request("grad_receive", max(per_owner) if per_owner else 0)
         self._max_owned = max(owned_counts) if owned_counts else 0
-        # staging buffers rotate only when reduction overlaps backward; after-backward reduction needs one
-        count = 4 if self.overlap else 1
-        self.staging = [torch.empty(capacity, device=self.device, dtype=torch.float32) for _ in range(count)]
-        self.staging_events = [None] * count
-        self.staging_cursor = 0
+        # staging buffers are only for callers without a landing buffer; they are allocated on first use
+        self._staging_capacity = capacity
+        self.staging, self.staging_events, self.staging_cursor = [], [], 0
 
     def finalize_gradients(self):
         self.reduce_flag_offset = self.flags("reduce", max(1, self._max_owned) * self.world)
@@ -173,6 +171,10 @@ class PeerTransport:
 
     def next_staging(self):
         """A staging buffer whose previous communication has finished (stream-ordered, no host wait)."""
+        if not self.staging:
+            count = 4 if self.overlap else 1
+            self.staging = [torch.empty(self._staging_capacity, device=self.device, dtype=torch.float32) for _ in range(count)]
+            self.staging_events = [None] * count
         index = self.staging_cursor
         self.staging_cursor = (index + 1) % len(self.staging)
         event = self.staging_events[index]
@@ -192,10 +194,13 @@ class PeerTransport:
         """Drop cross-stream events recorded outside a CUDA-graph capture (call after a full device sync)."""
         self.staging_events = [None] * len(self.staging_events)
 
-    def reduce_to_owner(self, bucket_index, staging_index, length):
+    def reduce_to_owner(self, bucket_index, staging_index, length, buffer=None):
+        """Push (non-owners) or accumulate (owner) one bucket; ``buffer`` overrides the rotating staging buffers
+        (the gradient landing buffer is read in place)."""
         owner = self.buckets[bucket_index][0]
         generation = self.micro_counter
-        buffer = self.staging[staging_index][:length]
+        if buffer is None:
+            buffer = self.staging[staging_index][:length]
         stream = self._enter()
         region = self.offsets["grad_receive"] + self.bucket_region[bucket_index]
         slot = self.bucket_slot[bucket_index]
@@ -213,9 +218,10 @@ class PeerTransport:
                 self._ops.reduce_push_fp8(buffer, self.tile, self.fmt, destination, destination + scales_offset,
                                           self.peer_pointer(owner, flag_base + 4 * self.rank), self.local_pointer(ack),
                                           generation, self.counters[1:2], self.wait_clocks, self.max_blocks, self.status)
-            event = torch.cuda.Event()
-            event.record(stream)
-        self.staging_events[staging_index] = event
+            if staging_index is not None:
+                event = torch.cuda.Event()
+                event.record(stream)
+                self.staging_events[staging_index] = event
         ops._count()
 
     # ------------------------------------------------------------------ path 2: all-reduce with requantisation

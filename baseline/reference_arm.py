@@ -46,11 +46,11 @@ def run(args, unavailable, shim=None):
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     accumulation, global_batch = 2, args.global_batch
-    named_config = True
+    named_config = global_batch == 256 and getattr(args, "model", "xl_2") == "xl_2"
     if getattr(args, "ref_microbatch", 0):
         # context runs only: same global batch, smaller microbatches, more accumulation steps
         accumulation = global_batch // (world * args.ref_microbatch)
-        named_config = accumulation == 2
+        named_config = named_config and accumulation == 2
     config = dict(num_processes=world, mixed_precision="bf16", gradient_accumulation_steps=accumulation,
                   sharding=dict(parameters=True, gradients=True, optimizer=True, ema=True),
                   precision=dict(master_weight_dtype="fp32", gradient_dtype="fp32"),

@@ -47,7 +47,7 @@ def main():
     torch.manual_seed(0)
     m, k, n = 8192, 4096, 4096
     x = torch.randn(m, k, device=device, dtype=torch.bfloat16, requires_grad=True)
-    for name, options in (("grouped128", GROUPED), ("current", dict(scaling="current"))):
+    for name, options in (("grouped128", GROUPED), ("current", dict(scaling="current")), ("mxfp8", dict(scaling="mxfp8"))):
         for mode in ("fast", "memory"):
             layer = Linear(k, n, bias=False, mode=mode, **options).to(device)
             fwd = measure(lambda: layer(x))

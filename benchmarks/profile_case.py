@@ -26,7 +26,8 @@ def main():
     parser.add_argument("--case", required=True,
                         choices=("gemm_fp8", "gemm_group", "gemm_ns", "gemm_ns_apply", "gemm_act_bwd", "gemm_wgrad",
                                  "gemm_expert", "quantize", "quantize_rows", "group_quantize", "momentum", "gated",
-                                 "ln_quantize", "gelu_quantize", "ln_backward", "gate_backward"))
+                                 "ln_quantize", "gelu_quantize", "ln_backward", "gate_backward", "gemm_mx", "writeback",
+                                 "reduce_push", "reduce_accumulate", "gather_pull"))
     parser.add_argument("--launches", type=int, default=4)
     args = parser.parse_args()
     device = torch.device("cuda")
@@ -52,6 +53,74 @@ def main():
             qx, _ = ops.quantize(x, sx)
             qw, _ = ops.quantize(w, sw)
             run = lambda: ops.gated_gemm_forward(qx, qw, sx, sw, activation="silu", out_dtype=torch.bfloat16)
+    elif args.case == "gemm_mx":
+        # hardware block-scaled MXFP8 product, UE8M0 scale per 32 K elements on both operands
+        a = torch.randn(m, k, device=device).to(E4M3)
+        b = torch.randn(n, k, device=device).to(E4M3)
+        sa = torch.randint(120, 132, (m, k // 32), device=device, dtype=torch.uint8)
+        sb = torch.randint(120, 132, (n, k // 32), device=device, dtype=torch.uint8)
+        sfa, sfb = ops.mx_pack_scales(sa, m, k), ops.mx_pack_scales(sb, n, k)
+        out = torch.empty(m, n, device=device, dtype=torch.bfloat16)
+        run = lambda: ops.mx_gemm(a, b, sfa, sfb, out_dtype=torch.bfloat16, out=out)
+    elif args.case == "writeback":
+        # an owner's write-back of 60 FP8 layers (about 320 MB of fp32 masters) with the EMA folded in; one
+        # process, so every "peer" store lands in local memory (the NVLink leg is not exercised)
+        shapes = [(1152, 3456), (1152, 1152), (1152, 4608), (4608, 1152), (6912, 1152)] * 12
+        masters = [torch.randn(s, device=device) * 0.02 for s in shapes]
+        averages = [t.clone() for t in masters]
+        codes = [torch.zeros(t.numel(), device=device, dtype=torch.uint8) for t in masters]
+        headers = torch.zeros(len(shapes), 32, device=device)
+        rows = [dict(master=t, ema=e, n=t.numel(), slab_elems=t.numel(), dst_offset=c.data_ptr(),
+                     header_offset=h.data_ptr(), base_index=0, limit=448.0, history_len=16, mode=0, out_dtype=None)
+                for t, e, c, h in zip(masters, averages, codes, headers)]
+        table = ops.WritebackTable(rows, device)
+        calls = iter(range(1 << 30))
+        run = lambda: ops.multi_writeback(table, heaps=[0], rank=0, calls=next(calls), decay=0.9999, with_ema=True)
+    elif args.case in ("reduce_push", "reduce_accumulate"):
+        # one 256 MB fp32 gradient bucket through the FP8 wire codec (e4m3, tile 256); destination / source slots
+        # are local buffers, flags are pre-set, so a single process can run the kernels of either side
+        count, tile = 64 << 20, 256
+        tiles = count // tile
+        bucket = torch.randn(count, device=device) * 1e-3
+        slot_bytes = tiles * tile + tiles * 4
+        slot = torch.zeros(2 * slot_bytes, device=device, dtype=torch.uint8)          # one receive slot per "rank"
+        flags = torch.full((4,), 1 << 30, device=device, dtype=torch.int32)
+        generation = torch.ones(1, device=device, dtype=torch.int32)
+        counter = torch.zeros(1, device=device, dtype=torch.int32)
+        status = ops.status_word(device)
+        accum = torch.zeros(count, device=device)
+        op = torch.ops.viola_b200
+        if args.case == "reduce_push":
+            run = lambda: op.reduce_push_fp8(bucket, tile, 0, slot.data_ptr(), slot.data_ptr() + tiles * tile,
+                                             flags.data_ptr(), flags.data_ptr() + 4, generation, counter, 2_000_000, 296,
+                                             status)
+        else:
+            heap = torch.zeros(1 << 16, device=device, dtype=torch.uint8)
+            run = lambda: op.reduce_accumulate_fp8(bucket, tile, 0, slot.data_ptr(), slot_bytes, tiles * tile,
+                                                   flags.data_ptr(), [heap.data_ptr(), heap.data_ptr()], 0, 64, generation,
+                                                   accum, counter, 2_000_000, 296, status)
+    elif args.case == "gather_pull":
+        # the pull of one sharding unit (24 MB of FP8 codes in five parameters) with both "ranks" in local memory
+        world, sizes = 2, [1152 * 3456, 1152 * 1152, 1152 * 4608, 4608 * 1152, 6912 * 1152]
+        shard_bytes = [size // world for size in sizes]
+        region = torch.randint(0, 255, (sum(shard_bytes),), device=device, dtype=torch.uint8)
+        full = torch.zeros(sum(sizes), device=device, dtype=torch.uint8)
+        entries, prefix, total, shard_at, full_at = [], [0], 0, 0, 0
+        for nbytes in shard_bytes:
+            entries += [shard_at, nbytes, full_at]
+            shard_at += nbytes
+            full_at += world * nbytes
+        for nbytes in shard_bytes:
+            for _ in range(world):
+                total += (nbytes + 65535) // 65536
+                prefix.append(total)
+        entries_t = torch.tensor(entries, device=device, dtype=torch.int64)
+        prefix_t = torch.tensor(prefix, device=device, dtype=torch.int64)
+        counts = torch.zeros(len(shard_bytes) * world, device=device, dtype=torch.int32)
+        panel = torch.zeros(len(shard_bytes) * world, device=device, dtype=torch.int32)
+        calls = iter(range(1, 1 << 30))
+        run = lambda: torch.ops.viola_b200.gather_pull(entries_t, [region.data_ptr()] * world, 0, 0, full, prefix_t,
+                                                       counts, panel, next(calls), total, 1184)
     elif args.case == "gemm_ns":
         x = (torch.randn(28, 1152, 4608, device=device) / 68).bfloat16()
         run = lambda: ops.ns_gemm(x, x, symmetric=True)

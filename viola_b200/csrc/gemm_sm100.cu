@@ -556,41 +556,61 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if constexpr (GROUP) {
 #pragma unroll
         for (int j = 0; j < BN; ++j) accr[j] = 0.f;
-        for (int kb = 0; kb < args.num_k_blocks; ++kb) {
+        // Scales are fetched one K-block ahead (global loads whose latency would otherwise sit between the
+        // accumulator wait and the first FMA of every K-block), and the TMEM load of chunk c + 1 is in flight
+        // while chunk c is promoted.
+        const bool per_col = args.sb_shift < 5;      // a B scale block spans fewer than 32 rows: one value per column
+        const int limit_rows = C::kGatedFwd ? 2 * args.N : args.N;
+        auto sb_column = [&](int j) -> long long {   // row of B (scale row before the shift) behind tile column j, or -1
+          int brow = C::kGatedFwd ? (j < BN / 2 ? n0 + j : args.b_gate_up_offset + n0 + (j - BN / 2)) : n0 + j;
+          const bool in = C::kGatedFwd ? (brow - (j < BN / 2 ? 0 : args.b_gate_up_offset) < args.N) : (brow < args.N);
+          return in ? (long long)(brow + expert * args.expert_rows) : -1LL;
+        };
+        auto sb_chunk = [&](int c) -> long long {    // same for a whole 32-column chunk (clamped at the edge)
+          int brow = C::kGatedFwd ? (c < NCHUNK / 2 ? n0 + c * 32 : args.b_gate_up_offset + n0 + (c - NCHUNK / 2) * 32)
+                                  : n0 + c * 32;
+          return (long long)(min(brow, limit_rows - 1) + expert * args.expert_rows);
+        };
+        float next_sa = 0.f, next_sb[NCHUNK];
+        auto fetch_scales = [&](int kb) {
           const int ks = kb >> args.k_shift;
-          // B scales for this K-block: scalar per 32-column chunk when a scale block spans
-          // >= 32 B rows, otherwise one value per column staged through shared memory.
-          const bool per_col = args.sb_shift < 5;
+          next_sa = row_ok ? args.sa[grow * args.sa_row + (long long)ks * args.sa_k] : 0.f;
+#pragma unroll
+          for (int c = 0; c < NCHUNK; ++c) {
+            const long long brow = per_col ? sb_column(c * 32 + lane) : sb_chunk(c);
+            next_sb[c] = brow >= 0 ? args.sb[(brow >> args.sb_shift) * args.sb_row + (long long)ks * args.sb_k] : 0.f;
+          }
+        };
+        fetch_scales(0);
+        for (int kb = 0; kb < args.num_k_blocks; ++kb) {
+          const float sa_v = next_sa;
+          float sb_v[NCHUNK];
+#pragma unroll
+          for (int c = 0; c < NCHUNK; ++c) sb_v[c] = next_sb[c];
           float* sbs = sb_stage + ((warp - 2) * 2 + (kb & 1)) * BN;  // private to this warp: no CTA barrier
           if (per_col) {
-            for (int j = lane; j < BN; j += 32) {
-              int brow = C::kGatedFwd ? (j < BN / 2 ? n0 + j : args.b_gate_up_offset + n0 + (j - BN / 2)) : n0 + j;
-              const bool in = C::kGatedFwd ? (brow - (j < BN / 2 ? 0 : args.b_gate_up_offset) < args.N) : (brow < args.N);
-              brow += expert * args.expert_rows;
-              sbs[j] = in ? args.sb[(long long)(brow >> args.sb_shift) * args.sb_row + (long long)ks * args.sb_k] : 0.f;
-            }
+#pragma unroll
+            for (int c = 0; c < NCHUNK; ++c) sbs[c * 32 + lane] = sb_v[c];
             __syncwarp();
           }
-          const float sa_v = row_ok ? args.sa[grow * args.sa_row + (long long)ks * args.sa_k] : 0.f;
           ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full[acc], acc_phase, abort_flag, args.status, kTimeoutTmemFull));
           if (!ok) break;
           tc_fence_after_sync();
+          uint32_t r[2][32];
+          tmem_ld_32x32(tmem_base + lane_addr + acc * BN, r[0]);
+          if (kb + 1 < args.num_k_blocks) fetch_scales(kb + 1);       // in flight under the promotion below
 #pragma unroll
           for (int c = 0; c < NCHUNK; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32(tmem_base + lane_addr + acc * BN + c * 32, r);
             tmem_ld_wait();
+            if (c + 1 < NCHUNK) tmem_ld_32x32(tmem_base + lane_addr + acc * BN + (c + 1) * 32, r[(c + 1) & 1]);
             if (per_col) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) accr[c * 32 + j] = fmaf(__uint_as_float(r[j]), sa_v * sbs[c * 32 + j], accr[c * 32 + j]);
+              for (int j = 0; j < 32; ++j)
+                accr[c * 32 + j] = fmaf(__uint_as_float(r[c & 1][j]), sa_v * sbs[c * 32 + j], accr[c * 32 + j]);
             } else {
-              int brow = C::kGatedFwd ? (c < NCHUNK / 2 ? n0 + c * 32 : args.b_gate_up_offset + n0 + (c - NCHUNK / 2) * 32)
-                                      : n0 + c * 32;
-              const int limit_rows = C::kGatedFwd ? 2 * args.N : args.N;
-              brow = min(brow, limit_rows - 1) + expert * args.expert_rows;
-              const float s = sa_v * args.sb[(long long)(brow >> args.sb_shift) * args.sb_row + (long long)ks * args.sb_k];
+              const float s = sa_v * sb_v[c];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) accr[c * 32 + j] = fmaf(__uint_as_float(r[j]), s, accr[c * 32 + j]);
+              for (int j = 0; j < 32; ++j) accr[c * 32 + j] = fmaf(__uint_as_float(r[c & 1][j]), s, accr[c * 32 + j]);
             }
           }
           tc_fence_before_sync();

@@ -133,7 +133,9 @@ class GradientState:
         if not self.in_backward or self.claimed[index]:
             return None
         self.claimed[index] = True
-        return self.slots[index]
+        # a fresh view: autograd adopts a gradient tensor as ``.grad`` without copying only when nothing else
+        # holds a reference to that tensor object
+        return self.slots[index].view(self.slots[index].shape)
 
     def begin_backward(self):
         self.in_backward = True

@@ -31,6 +31,7 @@ def main():
     parser.add_argument("--launches", type=int, default=4)
     args = parser.parse_args()
     device = torch.device("cuda")
+    ops.load()
     torch.manual_seed(0)
     m, n, k = 32768, 3456, 1152
     if args.case in ("gemm_fp8", "gemm_group", "gated"):

@@ -84,7 +84,9 @@ class PeerTransport:
         self.prefetch = prefetch           # gather the next sharding unit on a side stream while this one computes
         # Overlapped communication shares the GPU with compute, so its kernels stay narrow; without overlap they
         # run alone after backward and take the whole GPU (a 25 MB bucket then costs microseconds, not hundreds).
-        self.max_blocks, self.wait_clocks = (max_blocks if overlap else 296), wait_clocks
+        # eight 256-thread CTAs per SM fill the warp slots of a memory-bound kernel (296 CTAs reached a third of
+        # the DRAM rate: every warp waits on its own loads)
+        self.max_blocks, self.wait_clocks = (max_blocks if overlap else 1184), wait_clocks
         self.stream = torch.cuda.Stream(device=self.device) if overlap else None
         self.status = ops.status_word(self.device)
         self.counters = torch.zeros(64, device=self.device, dtype=torch.int32)
@@ -307,7 +309,7 @@ class PeerTransport:
         # a gather running beside compute on the prefetch stream stays narrow (NVLink saturates with a few dozen
         # blocks; more would only take SMs from the GEMMs); a gather the compute stream waits for takes the GPU
         side = getattr(self, "gather_stream", None)
-        blocks = 48 if side is not None and torch.cuda.current_stream(self.device) == side else 4 * self.max_blocks
+        blocks = 48 if side is not None and torch.cuda.current_stream(self.device) == side else 1184
         self._ops.gather_pull(unit.gather_entries, self.pointers, self.rank, unit.heap_offset, unit.full,
                               unit.gather_prefix, unit.piece_counts, unit.panel_flags, unit.gather_generation,
                               unit.gather_pieces, blocks)
@@ -320,7 +322,7 @@ class PeerTransport:
         rows = entry.rows
         cols = entry.row_bytes            # FP8: one byte per element
         self._ops.quantize_push(master.view(rows, cols), scale, float(limit), _FMT_OF[record.dtype], None, 0.0,
-                                self.pointers, self.rank, offset, entry.shard_rows, 8 * self.max_blocks)
+                                self.pointers, self.rank, offset, entry.shard_rows, 2368)
         header_offset, header_bytes = self.header_offset[record.index]
         header = self.heap.view(header_offset, _align(header_bytes, 16))
         self._ops.byte_push(header, self.pointers, self.rank, header_offset, 0, 1)
@@ -338,7 +340,7 @@ class PeerTransport:
             staged[:flat.numel()].copy_(flat)
             flat = staged
         self._ops.byte_push(flat, self.pointers, self.rank, unit.heap_offset + entry.shard_offset, entry.shard_bytes,
-                            8 * self.max_blocks)
+                            2368)
         ops._count()
         return True
 

@@ -28,16 +28,14 @@ class _ExpertLinearFunction(torch.autograd.Function):
         grouped = layer.scaling == "grouped"
         experts, n, k = weight.shape
         x2 = x.contiguous()
+        qw, sw = layer.weight_codes()                   # cached until the weight changes
         if grouped:
             qx, sx = ops.group_quantize(x2, E4M3, (1, 128), kmajor=True)
-            qw, sw = ops.group_quantize(weight.reshape(experts * n, k), E4M3, (128, 128))
-            y = ops.expert_gemm(qx, qw.view(experts, n, k), offsets, sx, sw, out_dtype=x.dtype,
-                                group=((1, 128), (128, 128)), sa_kmajor=True)
+            y = ops.expert_gemm(qx, qw, offsets, sx, sw, out_dtype=x.dtype, group=((1, 128), (128, 128)), sa_kmajor=True)
         else:
-            sx, sw = ops.tensor_scale(x2), ops.tensor_scale(weight)
+            sx = ops.tensor_scale(x2)
             qx, _ = ops.quantize(x2, sx)
-            qw, _ = ops.quantize(weight.reshape(experts * n, k), sw)
-            y = ops.expert_gemm(qx, qw.view(experts, n, k), offsets, sx, sw, out_dtype=x.dtype)
+            y = ops.expert_gemm(qx, qw, offsets, sx, sw, out_dtype=x.dtype)
         ctx.save_for_backward(x2, weight, offsets)
         ctx.layer = layer
         ctx.weight_grad_dtype = layer.weight.grad_dtype or torch.float32
@@ -52,18 +50,17 @@ class _ExpertLinearFunction(torch.autograd.Function):
         dy = dy.contiguous()
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            # dX[t] = dY[t] @ W[e]: an expert GEMM against the per-expert transposed weights [E, K, N]
-            wt = weight.transpose(1, 2).contiguous()
+            # dX[t] = dY[t] @ W[e]: an expert GEMM against the per-expert transposed codes [E, K, N] (a byte
+            # transpose of the cached codes; the scales of a transposed 128 x 128 block are the same numbers)
+            qwt, swt = layer.weight_codes(transposed=True)
             if grouped:
                 qg, sg = ops.group_quantize(dy, E5M2, (1, 128), kmajor=True)
-                qwt, swt = ops.group_quantize(wt.reshape(experts * k, n), E4M3, (128, 128))
-                dx = ops.expert_gemm(qg, qwt.view(experts, k, n), offsets, sg, swt, out_dtype=x.dtype,
-                                     group=((1, 128), (128, 128)), sa_kmajor=True)
+                dx = ops.expert_gemm(qg, qwt, offsets, sg, swt, out_dtype=x.dtype, group=((1, 128), (128, 128)),
+                                     sa_kmajor=True)
             else:
-                sg, swt = ops.tensor_scale(dy, fp8_dtype=E5M2), ops.tensor_scale(wt)
+                sg = ops.tensor_scale(dy, fp8_dtype=E5M2)
                 qg, _ = ops.quantize(dy, sg, fp8_dtype=E5M2)
-                qwt, _ = ops.quantize(wt.reshape(experts * k, n), swt)
-                dx = ops.expert_gemm(qg, qwt.view(experts, k, n), offsets, sg, swt, out_dtype=x.dtype)
+                dx = ops.expert_gemm(qg, qwt, offsets, sg, swt, out_dtype=x.dtype)
         if ctx.needs_input_grad[1]:
             # dW[e] = dY[rows e]^T @ X[rows e]: K = the expert's token count, one GEMM per expert
             dw = torch.zeros(weight.shape, device=weight.device, dtype=ctx.weight_grad_dtype)
@@ -103,6 +100,7 @@ class GroupedLinear(nn.Module):
         dtype = dtype or torch.get_default_dtype()
         self.weight = nn.Parameter(torch.empty((num_experts, out_features, in_features), device=device, dtype=dtype))
         self.weight.grad_dtype = settings()["gradient_dtype"] or torch.float32
+        self._codes, self._codes_key = {}, None
         self.reset_parameters()
 
     @torch.no_grad()
@@ -110,10 +108,37 @@ class GroupedLinear(nn.Module):
         for expert in self.weight:
             nn.init.kaiming_uniform_(expert, a=math.sqrt(5))
 
+    @torch.no_grad()
+    def weight_codes(self, transposed=False):
+        """FP8 codes and scales of the expert weights ([E, N, K], or [E, K, N] when ``transposed``), quantised once
+        per weight version: every forward and backward until the next in-place update reuses them."""
+        weight = self.weight
+        key = (weight._version, weight.data_ptr(), weight.dtype, weight.device)
+        if key != self._codes_key:
+            self._codes, self._codes_key = {}, key
+        experts, n, k = weight.shape
+        if "rowwise" not in self._codes:
+            flat = weight.detach().reshape(experts * n, k)
+            if self.scaling == "grouped":
+                q, s = ops.group_quantize(flat, E4M3, (128, 128))
+            else:
+                s = ops.tensor_scale(flat)
+                q, _ = ops.quantize(flat, s)
+            self._codes["rowwise"] = (q.view(experts, n, k), s)
+        if not transposed:
+            return self._codes["rowwise"]
+        if "transposed" not in self._codes:
+            q, s = self._codes["rowwise"]
+            qt = q.view(torch.uint8).transpose(1, 2).contiguous().view(q.dtype)
+            if self.scaling == "grouped":
+                s = s.view(experts, n // 128, k // 128).transpose(1, 2).contiguous().view(experts * (k // 128), n // 128)
+            self._codes["transposed"] = (qt, s)
+        return self._codes["transposed"]
+
     def forward(self, x, offsets):
         if x.is_cuda and torch.is_autocast_enabled("cuda"):
             x = x.to(torch.get_autocast_dtype("cuda"))
-        return _ExpertLinearFunction.apply(x, self.weight.to(x.dtype), offsets.to(torch.int32), self)
+        return _ExpertLinearFunction.apply(x, self.weight, offsets.to(torch.int32), self)
 
     def extra_repr(self):
         return (f"num_experts={self.num_experts}, in_features={self.in_features}, "

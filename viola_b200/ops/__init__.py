@@ -586,7 +586,9 @@ def expert_gemm(a, w, offsets, sa, sw, *, out_dtype, group=None, sa_kmajor=False
                                                out_dtype=out_dtype)
             else:
                 sa_e = (sa.t() if sa_kmajor else sa)[lo:hi]
-                result[lo:hi] = reference.group_gemm(a[lo:hi], w[e], sa_e, sw[e], group[0], group[1],
+                sw_all = sw.t() if sw_kmajor else sw                  # [E * N / block, K / block]
+                sw_e = sw_all.reshape(experts, -1, sw_all.shape[-1])[e]
+                result[lo:hi] = reference.group_gemm(a[lo:hi], w[e], sa_e, sw_e, group[0], group[1],
                                                      out_dtype=out_dtype)
         return result if out is None else out.copy_(result)
     if out is None:

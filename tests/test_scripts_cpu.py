@@ -12,7 +12,9 @@ ROOT = Path(__file__).resolve().parent.parent
 
 
 def run(*command, timeout=600):
-    environment = dict(os.environ, PYTHONPATH=str(ROOT), CUDA_VISIBLE_DEVICES="")
+    environment = {key: value for key, value in os.environ.items()
+                   if key not in ("MASTER_ADDR", "MASTER_PORT", "RANK", "WORLD_SIZE", "LOCAL_RANK", "VIOLA_CONFIG")}
+    environment.update(PYTHONPATH=str(ROOT), CUDA_VISIBLE_DEVICES="")
     done = subprocess.run([sys.executable, *map(str, command)], cwd=ROOT, env=environment, capture_output=True, text=True,
                           timeout=timeout)
     assert done.returncode == 0, done.stdout[-2000:] + done.stderr[-4000:]

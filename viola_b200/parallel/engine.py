@@ -41,9 +41,13 @@ class violaEngine:  # noqa: N801 - public name kept identical to the reference
         else:
             self.device = torch.device(device_type)
         if not dist.is_initialized():
-            if "RANK" not in os.environ:       # single process without a launcher
+            if "RANK" not in os.environ:       # single process without a launcher: any free local port will do
                 os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-                os.environ.setdefault("MASTER_PORT", "29533")
+                if "MASTER_PORT" not in os.environ:
+                    import socket
+                    with socket.socket() as probe:
+                        probe.bind(("127.0.0.1", 0))
+                        os.environ["MASTER_PORT"] = str(probe.getsockname()[1])
                 os.environ.setdefault("RANK", "0")
                 os.environ.setdefault("WORLD_SIZE", "1")
             dist.init_process_group("nccl" if self.device.type == "cuda" else "gloo")

@@ -467,3 +467,71 @@ def test_mxfp8_linear_runs_on_the_block_scaled_path_and_matches_cpu():
     assert rel_l2(y.detach().cpu(), yc.detach()) < 1e-2
     assert rel_l2(x.grad.cpu(), xc.grad) < 2e-2
     assert rel_l2(layer.weight.grad.cpu(), clone.weight.grad) < 2e-2
+
+
+# ------------------------------------------------------------------------------------------------ memory-safety substitutes
+def _guarded(shape, dtype, pad=4096):
+    """A tensor of ``shape`` carved out of a larger buffer whose bytes before and after it are a known pattern."""
+    count = int(np.prod(shape))
+    itemsize = torch.empty((), dtype=dtype).element_size()
+    raw = torch.full((2 * pad + count * itemsize,), 0xA5, device="cuda", dtype=torch.uint8)
+    view = raw[pad:pad + count * itemsize].view(dtype).view(shape)
+
+    def intact():
+        return bool((raw[:pad] == 0xA5).all() and (raw[pad + count * itemsize:] == 0xA5).all())
+
+    return view, intact
+
+
+@pytest.mark.parametrize("shape", [(200, 136, 160), (384, 520, 1152), (130, 264, 96)])
+def test_gemm_outputs_stay_inside_their_buffers_and_repeat_bit_for_bit(shape):
+    """No sanitizer on this pool: outputs are carved out of canary-padded buffers (ragged shapes, so edge tiles are
+    exercised), and every kernel is run twice and must reproduce its result exactly."""
+    m, n, k = shape
+    torch.manual_seed(m * n + k)
+    a = torch.randn(m, k, device="cuda").to(torch.float8_e4m3fn)
+    b = torch.randn(n, k, device="cuda").to(torch.float8_e4m3fn)
+    one = torch.ones(1, device="cuda")
+    for dtype in (torch.bfloat16, torch.float32):
+        out, intact = _guarded((m, n), dtype)
+        ops.gemm(a, b, one, one, out_dtype=dtype, out=out)
+        first = out.clone()
+        ops.gemm(a, b, one, one, out_dtype=dtype, out=out)
+        torch.cuda.synchronize()
+        assert intact() and torch.equal(first, out)
+        assert rel_l2(out, a.float() @ b.float().t()) < 1e-2
+    # hardware block-scaled path
+    sa = torch.randint(120, 132, (m, (k + 31) // 32), device="cuda", dtype=torch.uint8)
+    sb = torch.randint(120, 132, (n, (k + 31) // 32), device="cuda", dtype=torch.uint8)
+    out, intact = _guarded((m, n), torch.float32)
+    sfa, sfb = ops.mx_pack_scales(sa, m, k), ops.mx_pack_scales(sb, n, k)
+    ops.mx_gemm(a, b, sfa, sfb, out_dtype=torch.float32, out=out)
+    first = out.clone()
+    ops.mx_gemm(a, b, sfa, sfb, out_dtype=torch.float32, out=out)
+    torch.cuda.synchronize()
+    assert intact() and torch.equal(first, out)
+    ops.check_status()
+
+
+def test_quantiser_outputs_stay_inside_their_buffers_and_repeat_bit_for_bit():
+    rows, cols = 333, 416
+    x = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
+    scale = ops.tensor_scale(x)
+    q, q_ok = _guarded((rows, cols), torch.float8_e4m3fn)
+    qt, qt_ok = _guarded((cols, rows), torch.float8_e4m3fn)
+    ops.quantize(x, scale, transpose=True, out=q, out_t=qt)
+    first, first_t = q.clone().view(torch.uint8), qt.clone().view(torch.uint8)
+    ops.quantize(x, scale, transpose=True, out=q, out_t=qt)
+    torch.cuda.synchronize()
+    assert q_ok() and qt_ok()
+    assert torch.equal(first, q.view(torch.uint8)) and torch.equal(first_t, qt.view(torch.uint8))
+    assert torch.equal(qt.view(torch.uint8), q.view(torch.uint8).t())
+    for group, transposed in (((1, 128), False), ((1, 32), True), ((128, 128), False)):
+        shape = (cols, rows) if transposed else (rows, cols)
+        g, g_ok = _guarded(shape, torch.float8_e4m3fn)
+        _, s1 = ops.group_quantize(x, torch.float8_e4m3fn, group, transposed=transposed, out=g)
+        keep = g.clone().view(torch.uint8)
+        _, s2 = ops.group_quantize(x, torch.float8_e4m3fn, group, transposed=transposed, out=g)
+        torch.cuda.synchronize()
+        assert g_ok() and torch.equal(keep, g.view(torch.uint8)) and torch.equal(s1, s2)
+    ops.check_status()

@@ -240,6 +240,41 @@ def test_gated_gemm(activation, grouped):
     assert rel_l2(ops.gated_backward(aux, d, activation), expected) < 1e-2
 
 
+@pytest.mark.parametrize("hidden", [1000, 1004, 96])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("save", [True, False])
+def test_gated_gemm_ragged_widths(hidden, dtype, save):
+    """Widths that end inside a 32-column chunk (1000), that cannot use 16-byte rows (1004: per-thread stores) and
+    below one tile (96), rows that end inside a tile, both 16-bit types, with and without the saved halves: nothing
+    may land outside the valid region and the values must match the unfused pair of kernels."""
+    torch.manual_seed(11)
+    m, k, out_features = 333, 256, 384
+    x = torch.randn(m, k, device=dev(), dtype=dtype)
+    w = torch.randn(2 * hidden, k, device=dev(), dtype=dtype) * 0.05
+    sx, sw = ops.tensor_scale(x), ops.tensor_scale(w)
+    qx, _ = ops.quantize(x, sx)
+    qw, _ = ops.quantize(w, sw)
+    z = ops.gemm(qx, qw, sx, sw, out_dtype=dtype)
+    h, aux = ops.gated_gemm_forward(qx, qw, sx, sw, activation="silu", out_dtype=dtype, save=save)
+    assert (aux is None) == (not save)
+    if save:
+        assert rel_l2(aux, z) < 1e-3
+    expected = ref.gated_forward(z, "silu")
+    assert rel_l2(h, expected) < 5e-3
+    assert (h.float() - expected.float()).abs().max() < 0.05 * expected.float().abs().max()
+    dy = torch.randn(m, out_features, device=dev(), dtype=dtype)
+    wdown_t = torch.randn(hidden, out_features, device=dev(), dtype=dtype) * 0.05
+    sg, st = ops.tensor_scale(dy, fp8_dtype=E5M2), ops.tensor_scale(wdown_t)
+    qg, _ = ops.quantize(dy, sg, fp8_dtype=E5M2)
+    qt, _ = ops.quantize(wdown_t, st)
+    d = ops.gemm(qg, qt, sg, st, out_dtype=dtype)
+    dz = ops.gated_gemm_backward(qg, qt, sg, st, z, activation="silu", out_dtype=dtype)
+    want = ref.gated_backward(z, d, "silu")
+    assert rel_l2(dz, want) < 1e-2
+    assert (dz.float() - want.float()).abs().max() < 0.05 * want.float().abs().max()
+    ops.check_status()
+
+
 @pytest.mark.parametrize("grouped", [False, True])
 def test_expert_gemm(grouped):
     torch.manual_seed(6)

@@ -33,6 +33,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <mutex>
+#include <type_traits>
 #include "api.h"
 #include "common/ptx.cuh"
 
@@ -268,6 +269,32 @@ __device__ __forceinline__ float act_grad(float g, int act) {
   return 0.5f * (1.f + t) + 0.5f * g * (1.f - t * t) * k0 * (1.f + 3.f * k1 * g * g);
 }
 
+// Gate activation and its slope for the staged gated epilogues, specialised on the activation.  SiLU and the
+// tanh form of GELU are both g * sigmoid(z) (z = g, or z = 2 k0 (g + k1 g^3), since 0.5 (1 + tanh(z / 2)) =
+// sigmoid(z)), so one exp2 and one reciprocal approximation serve the value and the slope.
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+template <int ACT>
+__device__ __forceinline__ void gate_terms(float g, float& act, float& slope) {
+  if constexpr (ACT == VB_ACT_RELU) {
+    act = fmaxf(g, 0.f);
+    slope = g > 0.f ? 1.f : 0.f;
+  } else {
+    float z = g, dz = 1.f;
+    if constexpr (ACT != VB_ACT_SILU) {
+      const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+      z = 2.f * k0 * (g + k1 * g * g * g);
+      dz = 2.f * k0 * (1.f + 3.f * k1 * g * g);
+    }
+    const float s = rcp_approx(1.f + __expf(-z));
+    act = g * s;
+    slope = s * (1.f + g * (1.f - s) * dz);
+  }
+}
+
 // tile id -> (m_tile, n_tile).  Plain: groups of 8 M-tiles sweep N (L2 reuse of B across the
 // wave, of A inside a group).  Symmetric: row-major walk over the upper triangle.
 __device__ __forceinline__ void tile_coords(const GemmArgs& a, int t, int& mt, int& nt) {
@@ -300,11 +327,20 @@ struct Config {
   // rows of the slab in place with the result and TMA-stores them.  Plain loads issued after the accumulator
   // wait would expose a memory round trip per chunk, and per-thread row stores write half sectors.
   static constexpr bool kEpiSlab = (EPI == VB_EPI_AXPBY || EPI == VB_EPI_ACT_BWD) && !GROUP;
-  static constexpr int kEpiSlabs = 4;
-  static constexpr int kCtaThreads = kEpiSlab ? kThreads + 32 : kThreads;   // a seventh warp feeds the slab ring
+  // The per-tensor gated epilogues use the same slabs.  Forward: every output chunk leaves as three slabs (the
+  // activation product h and, when the caller keeps them, the rounded gate and up halves), written by TMA from a
+  // four-slab ring.  Backward: the loader warp brings the saved gate and up slabs of a chunk in, the epilogue
+  // rewrites them in place with dGate and dUp and TMA-stores both; eight slabs keep four chunks in flight, paid
+  // for with one main-loop stage.
+  static constexpr bool kGatedBwd = EPI == VB_EPI_GATED_BWD;
+  static constexpr bool kGatedSlab = (kGatedFwd || kGatedBwd) && !GROUP;
+  static constexpr bool kSlabRing = kEpiSlab || kGatedSlab;
+  static constexpr bool kSlabLoader = kEpiSlab || (kGatedBwd && !GROUP);
+  static constexpr int kEpiSlabs = (kGatedBwd && !GROUP) ? 8 : 4;
+  static constexpr int kCtaThreads = kSlabLoader ? kThreads + 32 : kThreads;   // a seventh warp feeds the slab ring
   static constexpr int kEpiSlabBytes = BM * 64;
-  static constexpr int kEpiBytes = kEpiSlab ? kEpiSlabs * kEpiSlabBytes : 0;
-  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? ((GROUP && kTmaStore) ? 5 : 6) : 8);
+  static constexpr int kEpiBytes = kSlabRing ? kEpiSlabs * kEpiSlabBytes : 0;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? (((GROUP && kTmaStore) || (kGatedBwd && !GROUP)) ? 5 : 6) : 8);
   static constexpr int kAcc = GROUP ? (512 / BN > 4 ? 4 : 512 / BN) : 2;
   static constexpr int kTmemCols = kAcc * BN;
   static constexpr int kBarrierBytes = 1024;
@@ -481,25 +517,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // ------------------------------ slab loader --------------------------------
     // Feeds the epilogue's operand slabs (AXPBY residual, ACT_BWD slope) on its own, so a full slab ring never
     // holds back the main-loop producer; it runs up to kEpiSlabs chunks ahead of the epilogue.
-    if constexpr (C::kEpiSlab) {
+    if constexpr (C::kSlabLoader) {
       if (args.epi_stage) {
         int eslot = 0;
         uint32_t ephase = 0;
         bool ok = true;
+        constexpr int kHalves = C::kGatedBwd ? 2 : 1;     // gated backward: the gate slab, then the up slab
         for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
           int mt, nt;
           const int bi = t / args.tiles_per_batch;
           tile_coords(args, t - bi * args.tiles_per_batch, mt, nt);
-          for (int c = 0; c < BN / 32 && nt * BN + c * 32 < args.N; ++c) {
-            ok = __all_sync(0xffffffffu, mbar_wait(&epi_empty[eslot], ephase ^ 1, abort_flag, args.status, kTimeoutEmpty));
-            if (!ok) break;
-            if (lane == 0) {
-              mbar_expect_tx(&epi_full[eslot], C::kEpiSlabBytes);
-              tma_load_2d(epi_stage + eslot * C::kEpiSlabBytes, &tmC, &epi_full[eslot], nt * BN + c * 32,
-                          bi * args.M + mt * BM);
+          for (int c = 0; c < BN / 32 && nt * BN + c * 32 < args.N && ok; ++c) {
+            for (int half = 0; half < kHalves; ++half) {
+              ok = __all_sync(0xffffffffu, mbar_wait(&epi_empty[eslot], ephase ^ 1, abort_flag, args.status, kTimeoutEmpty));
+              if (!ok) break;
+              if (lane == 0) {
+                mbar_expect_tx(&epi_full[eslot], C::kEpiSlabBytes);
+                if constexpr (C::kGatedBwd)
+                  tma_load_3d(epi_stage + eslot * C::kEpiSlabBytes, &tmC, &epi_full[eslot], nt * BN + c * 32, half,
+                              mt * BM);
+                else
+                  tma_load_2d(epi_stage + eslot * C::kEpiSlabBytes, &tmC, &epi_full[eslot], nt * BN + c * 32,
+                              bi * args.M + mt * BM);
+              }
+              __syncwarp();
+              if (++eslot == C::kEpiSlabs) { eslot = 0; ephase ^= 1; }
             }
-            __syncwarp();
-            if (++eslot == C::kEpiSlabs) { eslot = 0; ephase ^= 1; }
           }
         }
       }
@@ -627,6 +670,149 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
       const float alpha_pt = GROUP ? 1.f
                                    : (args.sa != nullptr ? args.sa[0] : 1.f) * (args.sb != nullptr ? args.sb[0] : 1.f);
+      // ---- staged gated epilogues (per-tensor scales, 16-bit outputs): rolled over the chunks, specialised on
+      // the 16-bit type and the activation, every result row leaves through a shared-memory slab and a TMA store
+      bool staged_done = false;
+      if constexpr (C::kGatedSlab) {
+        if (args.epi_store) {
+          staged_done = true;
+          const int warp_row = mt * BM + quad * 32;
+          const bool rows_in = warp_row < args.M;
+          if constexpr (C::kGatedFwd) {
+            auto emit = [&](const uint32_t (&w)[16], int half, int col0) {
+              uint8_t* slab = epi_stage + eslot * C::kEpiSlabBytes;
+              if (lane == 0) tma_store_wait_read<C::kEpiSlabs - 1>();   // the store that last read this slab
+              __syncwarp();
+#pragma unroll
+              for (int p = 0; p < 4; ++p)
+                *slab_piece(slab, row_in_tile, p) = make_uint4(w[4 * p], w[4 * p + 1], w[4 * p + 2], w[4 * p + 3]);
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                if (rows_in) {
+                  if (half < 0) tma_store_2d(&tmC, slab + quad * 32 * 64, col0, warp_row);
+                  else tma_store_3d(&tmD, slab + quad * 32 * 64, col0, half, warp_row);
+                }
+                tma_store_commit();
+              }
+              if (++eslot == C::kEpiSlabs) eslot = 0;
+            };
+            auto fwd_tile = [&](auto dt_tag, auto act_tag) {
+              constexpr int DT = decltype(dt_tag)::value;
+              constexpr int ACT = decltype(act_tag)::value;
+#pragma unroll 1
+              for (int c = 0; c < NOUT; ++c) {
+                const int col0 = n0 + c * 32;
+                if (col0 >= args.N) break;
+                uint32_t rg[32], ru[32];
+                tmem_ld_32x32(tmem_base + lane_addr + acc * BN + c * 32, rg);
+                tmem_ld_32x32(tmem_base + lane_addr + acc * BN + BN / 2 + c * 32, ru);
+                float bg = 0.f, bu = 0.f;
+#pragma unroll
+                for (int i = 0; i < NOUT; ++i)
+                  if (i == c) { bg = bias_reg[i]; bu = bias_reg2[i]; }
+                tmem_ld_wait();
+                uint32_t pg[16], pu[16], ph[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  float g0 = __uint_as_float(rg[2 * j]) * alpha_pt, g1 = __uint_as_float(rg[2 * j + 1]) * alpha_pt;
+                  float u0 = __uint_as_float(ru[2 * j]) * alpha_pt, u1 = __uint_as_float(ru[2 * j + 1]) * alpha_pt;
+                  if (args.bias != nullptr) {
+                    g0 += __shfl_sync(0xffffffffu, bg, 2 * j);
+                    g1 += __shfl_sync(0xffffffffu, bg, 2 * j + 1);
+                    u0 += __shfl_sync(0xffffffffu, bu, 2 * j);
+                    u1 += __shfl_sync(0xffffffffu, bu, 2 * j + 1);
+                  }
+                  pg[j] = pack_round2<DT>(g0, g1);
+                  pu[j] = pack_round2<DT>(u0, u1);
+                  const float2 gf = unpack2<DT>(pg[j]), uf = unpack2<DT>(pu[j]);
+                  float a0, a1, unused;
+                  gate_terms<ACT>(gf.x, a0, unused);
+                  gate_terms<ACT>(gf.y, a1, unused);
+                  ph[j] = pack_round2<DT>(a0 * uf.x, a1 * uf.y);
+                }
+                emit(ph, -1, col0);
+                if (args.aux != nullptr) {
+                  emit(pg, 0, col0);
+                  emit(pu, 1, col0);
+                }
+              }
+            };
+            auto with_act = [&](auto dt_tag) {
+              if (args.activation == VB_ACT_SILU) fwd_tile(dt_tag, std::integral_constant<int, VB_ACT_SILU>{});
+              else if (args.activation == VB_ACT_RELU) fwd_tile(dt_tag, std::integral_constant<int, VB_ACT_RELU>{});
+              else fwd_tile(dt_tag, std::integral_constant<int, VB_ACT_GELU>{});
+            };
+            if (args.out_dtype == 1) with_act(std::integral_constant<int, 1>{});
+            else with_act(std::integral_constant<int, 2>{});
+          } else {
+            auto bwd_tile = [&](auto dt_tag, auto act_tag) {
+              constexpr int DT = decltype(dt_tag)::value;
+              constexpr int ACT = decltype(act_tag)::value;
+#pragma unroll 1
+              for (int c = 0; c < NCHUNK; ++c) {
+                const int col0 = n0 + c * 32;
+                if (col0 >= args.N) break;
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + lane_addr + acc * BN + c * 32, r);
+                uint8_t* slab_g = epi_stage + eslot * C::kEpiSlabBytes;     // saved gate, becomes dGate
+                uint8_t* slab_u = slab_g + C::kEpiSlabBytes;                // saved up, becomes dUp
+                const bool got = mbar_wait(&epi_full[eslot], ephase, abort_flag, args.status, kTimeoutFull) &&
+                                 mbar_wait(&epi_full[eslot + 1], ephase, abort_flag, args.status, kTimeoutFull);
+                ok = __all_sync(0xffffffffu, got);
+                tmem_ld_wait();
+                if (!ok) break;
+#pragma unroll
+                for (int p = 0; p < 4; ++p) {
+                  uint4* gp = slab_piece(slab_g, row_in_tile, p);
+                  uint4* up = slab_piece(slab_u, row_in_tile, p);
+                  const uint4 gin = *gp, uin = *up;
+                  const uint32_t gw[4] = {gin.x, gin.y, gin.z, gin.w}, uw[4] = {uin.x, uin.y, uin.z, uin.w};
+                  uint32_t og[4], ou[4];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 d = unpack2<DT>(pack_round2<DT>(__uint_as_float(r[8 * p + 2 * e]) * alpha_pt,
+                                                                 __uint_as_float(r[8 * p + 2 * e + 1]) * alpha_pt));
+                    const float2 g = unpack2<DT>(gw[e]), u = unpack2<DT>(uw[e]);
+                    float a0, s0, a1, s1;
+                    gate_terms<ACT>(g.x, a0, s0);
+                    gate_terms<ACT>(g.y, a1, s1);
+                    og[e] = pack_round2<DT>(d.x * u.x * s0, d.y * u.y * s1);
+                    ou[e] = pack_round2<DT>(d.x * a0, d.y * a1);
+                  }
+                  *gp = make_uint4(og[0], og[1], og[2], og[3]);
+                  *up = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                  if (rows_in) {
+                    tma_store_3d(&tmD, slab_g + quad * 32 * 64, col0, 0, warp_row);
+                    tma_store_3d(&tmD, slab_u + quad * 32 * 64, col0, 1, warp_row);
+                  }
+                  tma_store_commit();
+                  if (prev_slot >= 0) {          // the previous chunk's stores have read their slabs by now
+                    tma_store_wait_read<1>();
+                    mbar_arrive(&epi_empty[prev_slot]);
+                    mbar_arrive(&epi_empty[prev_slot + 1]);
+                  }
+                }
+                prev_slot = eslot;
+                eslot += 2;
+                if (eslot == C::kEpiSlabs) { eslot = 0; ephase ^= 1; }
+              }
+            };
+            auto with_act = [&](auto dt_tag) {
+              if (args.activation == VB_ACT_SILU) bwd_tile(dt_tag, std::integral_constant<int, VB_ACT_SILU>{});
+              else if (args.activation == VB_ACT_RELU) bwd_tile(dt_tag, std::integral_constant<int, VB_ACT_RELU>{});
+              else bwd_tile(dt_tag, std::integral_constant<int, VB_ACT_GELU>{});
+            };
+            if (args.out_dtype == 1) with_act(std::integral_constant<int, 1>{});
+            else with_act(std::integral_constant<int, 2>{});
+          }
+        }
+      }
+      if (!staged_done) {
 #pragma unroll(C::kEpiSlab ? 1 : NOUT)
       for (int c = 0; c < NOUT; ++c) {
         float v[32];
@@ -854,6 +1040,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         finish_slab();
       }
+      }
       if constexpr (!GROUP) {
         tc_fence_before_sync();
         __syncwarp();
@@ -861,7 +1048,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1; }
       }
     }
-    if constexpr (C::kEpiSlab) {
+    if constexpr (C::kSlabRing) {
       if (lane == 0) tma_store_wait_all();   // stores read this CTA's shared memory until they finish
     }
     if constexpr (EPI == VB_EPI_ACT_BWD) {
@@ -985,6 +1172,24 @@ static int make_slab_map(CUtensorMap* map, const void* base, int dtype, long lon
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+// Tensor map of a 16-bit [rows, 2 * cols] matrix holding two [rows, cols] halves side by side (the gate | up
+// layout of the gated MLP), as a 3-D tensor (column, half, row): a slab is 32 columns x 1 half x box_rows rows, and
+// columns past `cols` are clipped (stores) or zero (loads) instead of running into the other half.
+static int make_half_map(CUtensorMap* map, const void* base, int dtype, long long rows, long long cols, long long ld_elems,
+                         int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return (int)cudaErrorNotSupported;
+  CUtensorMapDataType dt = dtype == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, 2, (cuuint64_t)rows};
+  cuuint64_t strides[2] = {(cuuint64_t)(cols * 2), (cuuint64_t)(ld_elems * 2)};
+  cuuint32_t box[3] = {32, 1, (cuuint32_t)box_rows};
+  cuuint32_t estr[3] = {1, 1, 1};
+  if ((strides[0] & 15) != 0 || (strides[1] & 15) != 0 || ld_elems < 2 * cols) return (int)cudaErrorInvalidValue;
+  CUresult r = fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
 // Output tensor map for the TMA-store epilogue: box = 128 bytes of columns x 32 rows, 128B swizzle.
 static int make_out_map(CUtensorMap* map, void* base, int out_dtype, long long rows, long long cols, long long ld_elems) {
   EncodeTiledFn fn = get_encode_fn();
@@ -1083,6 +1288,21 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream) {
         (a.batch == 1 || (d.M % BM == 0 && d.out_batch_stride == (long long)d.M * d.ldo)) &&
         make_slab_map(&tmD, d.out, d.out_dtype, (long long)d.M * a.batch, d.N, d.ldo, 32) == 0)
       a.epi_store = 1;
+  }
+  if constexpr (C::kGatedSlab) {
+    auto usable = [](const void* p, long long ld) { return p != nullptr && (reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld * 2) % 16 == 0; };
+    const bool shape_ok = !expert && a.batch == 1 && d.out_dtype != 0 && d.N % 8 == 0 && !d.no_tma_store;
+    if constexpr (C::kGatedFwd) {
+      if (shape_ok && usable(d.out, d.ldo) && (d.aux == nullptr || usable(d.aux, d.ldaux)) &&
+          make_slab_map(&tmC, d.out, d.out_dtype, d.M, d.N, d.ldo, 32) == 0 &&
+          (d.aux == nullptr || make_half_map(&tmD, d.aux, d.out_dtype, d.M, d.N, d.ldaux, 32) == 0))
+        a.epi_store = 1;
+    } else {
+      if (shape_ok && usable(d.aux, d.ldaux) && usable(d.out, d.ldo) &&
+          make_half_map(&tmC, d.aux, d.out_dtype, d.M, d.N, d.ldaux, BM) == 0 &&
+          make_half_map(&tmD, d.out, d.out_dtype, d.M, d.N, d.ldo, 32) == 0)
+        a.epi_stage = a.epi_store = 1;
+    }
   }
   if (expert) {
     expert_tile_map_kernel<<<1, 32, 0, stream>>>(d.expert_offsets, d.num_experts, a.num_m_tiles, d.tile_map);

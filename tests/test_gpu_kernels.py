@@ -548,6 +548,39 @@ def test_gemm_outputs_stay_inside_their_buffers_and_repeat_bit_for_bit(shape):
     ops.check_status()
 
 
+@pytest.mark.parametrize("shape", [(1152, 1152, 4096), (200, 520, 2064), (1152, 4608, 8192)])
+@pytest.mark.parametrize("layout", ["k-major", "mn-major"])
+def test_split_k_matches_the_unsplit_product_and_repeats(shape, layout):
+    """fp32 results computed by several work units per tile (TMA reduce-add in a fixed order) against the same
+    product from one unit per tile, with and without a bias, into a guarded buffer, twice."""
+    m, n, k = shape
+    torch.manual_seed(k + n)
+    a = torch.randn(m, k, device="cuda").to(torch.float8_e4m3fn)
+    b = torch.randn(n, k, device="cuda").to(torch.float8_e5m2)
+    sa, sb = torch.full((1,), 0.5, device="cuda"), torch.full((1,), 0.25, device="cuda")
+    bias = torch.randn(n, device="cuda")
+    mn = layout == "mn-major"
+    if mn and (m % 16 or n % 16):
+        pytest.skip("MN-major operands need 16-byte rows")
+    left, right = (a.t().contiguous(), b.t().contiguous()) if mn else (a, b)
+    expected = (a.float() @ b.float().t()) * 0.125
+    for use_bias in (False, True):
+        base = ops.gemm(left, right, sa, sb, out_dtype=torch.float32, bias=bias if use_bias else None, a_mn=mn, b_mn=mn,
+                        force_split=1)
+        for split in (2, 3, 5, 0):
+            out, intact = _guarded((m, n), torch.float32)
+            ops.gemm(left, right, sa, sb, out_dtype=torch.float32, bias=bias if use_bias else None, a_mn=mn, b_mn=mn,
+                     out=out, force_split=split)
+            first = out.clone()
+            ops.gemm(left, right, sa, sb, out_dtype=torch.float32, bias=bias if use_bias else None, a_mn=mn, b_mn=mn,
+                     out=out, force_split=split)
+            torch.cuda.synchronize()
+            assert intact() and torch.equal(first, out)
+            assert rel_l2(out, base) < 1e-5
+        assert rel_l2(base, expected + (bias if use_bias else 0.0)) < 1e-5
+    ops.check_status()
+
+
 def test_quantiser_outputs_stay_inside_their_buffers_and_repeat_bit_for_bit():
     rows, cols = 333, 416
     x = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)

@@ -172,7 +172,8 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t epilogue, int64_
     TORCH_CHECK(b.size(0) == (int64_t)d.N * d.num_experts);
   }
   d.status = (int*)ptr(status);
-  d.force_bn = (int)force_bn;
+  d.force_bn = (int)(force_bn & 0xffff);          // low half: tile width; high half: split-K units per tile
+  d.force_split = (int)(force_bn >> 16);
   check(vb_gemm(&d, stream()), "gemm");
 }
 

@@ -27,6 +27,7 @@ enum StatusCode : int {
   kTimeoutPeerFlag = 5,   // waited on a flag another GPU writes
   kTimeoutPanel = 6,      // waited on a gathered weight panel
   kBadArgument = 7,
+  kTimeoutSplit = 8,      // a split-K unit waited for the unit before it on the same tile
 };
 
 __device__ __forceinline__ void report(int* status, int code, int detail) {
@@ -138,6 +139,13 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
 // bulk async-groups.  The x coordinate times the element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+// TMA reduce: the shared-memory tile is ADDED to global memory (element type of the tensor map; fp32 here)
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
                    reinterpret_cast<uint64_t>(map)),
                "r"(smem_u32(smem_src)), "r"(x), "r"(y)
                : "memory");
@@ -284,6 +292,38 @@ __device__ __forceinline__ int ld_relaxed_sys(const int* ptr) {
   int v;
   asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
   return v;
+}
+// Flags between CTAs of one launch (split-K hand-over): gpu scope is enough.
+__device__ __forceinline__ void st_release_gpu(int* ptr, int value) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(ptr), "r"(value) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_gpu(const int* ptr) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+// orders this thread's generic-proxy accesses with its async-proxy (TMA) accesses to global memory
+__device__ __forceinline__ void fence_proxy_async_global() {
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+}
+// Bounded wait until *flag == expected, written by another CTA of the same (fully resident) launch.
+__device__ __forceinline__ bool wait_flag_eq_gpu(const int* flag, int expected, volatile int* abort_flag, int* status,
+                                                 int code) {
+  const long long start = clock64();
+  uint32_t polls = 0;
+  while (true) {
+    const int seen = ld_acquire_gpu(flag);
+    if (seen == expected) return true;
+    if ((++polls & 31u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - start > kWaitBudgetClocks) {
+        *abort_flag = 1;
+        report(status, code, seen);
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
 }
 // Bounded wait until *flag >= expected (flags only ever grow: generation counters).
 __device__ __forceinline__ bool wait_flag_ge(const int* flag, int expected, int* status, int code) {

@@ -32,6 +32,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <atomic>
 #include <mutex>
 #include <type_traits>
 #include "api.h"
@@ -76,6 +77,11 @@ struct GemmArgs {
   int epi_stage;        // AXPBY residual / ACT_BWD slope arrives through the TMA slab ring
   int epi_store;        // AXPBY / ACT_BWD result leaves through the slab ring (TMA store)
   int a_mn, b_mn;       // operand stored MN-major: A as [K, M] / B as [K, N] (row-major, MN contiguous)
+  // split-K (LINEAR epilogue, fp32 output through TMA): every output tile is computed by `split_k` work units, each
+  // over `kb_per_split` K-blocks; unit 0 stores its partial tile, unit s adds its own with a TMA reduce once unit
+  // s - 1 has finished (split_flags[tile * 4 + warp quadrant] counts finished units; the last one clears it)
+  int split_k, kb_per_split;
+  int* split_flags;
   int* status;
 };
 
@@ -413,8 +419,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
+    for (int u = blockIdx.x; u < args.num_tiles * args.split_k && ok; u += gridDim.x) {
       int mt, nt;
+      const int split = u / args.num_tiles, t = u - split * args.num_tiles;
+      const int kb_begin = split * args.kb_per_split, kb_end = min(kb_begin + args.kb_per_split, args.num_k_blocks);
       const int bi = t / args.tiles_per_batch;
       tile_coords(args, t - bi * args.tiles_per_batch, mt, nt);
       int a_row = bi * args.M + mt * BM, b_row = (int)(bi * args.b_rows_per_batch) + nt * C::kBBoxRows;
@@ -424,7 +432,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         a_row = row0;
         b_row += args.tile_map[3 * mt + 2] * args.expert_rows;
       }
-      for (int kb = 0; kb < args.num_k_blocks; ++kb) {
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
         ok = __all_sync(0xffffffffu, mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, args.status, kTimeoutEmpty));
         if (!ok) break;
         if (lane == 0) {
@@ -462,7 +470,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     int stage = 0, acc = 0;
     uint32_t phase = 0, acc_phase = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
+    for (int u = blockIdx.x; u < args.num_tiles * args.split_k && ok; u += gridDim.x) {
+      const int split = u / args.num_tiles, t = u - split * args.num_tiles;
+      const int kb_begin = split * args.kb_per_split, kb_end = min(kb_begin + args.kb_per_split, args.num_k_blocks);
       if (args.tile_map != nullptr) {
         int mt, nt;
         tile_coords(args, t, mt, nt);
@@ -473,7 +483,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (!ok) break;
         tc_fence_after_sync();
       }
-      for (int kb = 0; kb < args.num_k_blocks; ++kb) {
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
         if constexpr (GROUP) {
           ok = __all_sync(0xffffffffu, mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, args.status, kTimeoutTmemEmpty));
           if (!ok) break;
@@ -491,7 +501,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const uint32_t d_tmem = tmem_base + acc * BN;
 #pragma unroll
           for (int k = 0; k < C::kMmasPerStage; ++k) {
-            const uint32_t accumulate = GROUP ? (k > 0) : (kb > 0 || k > 0);
+            const uint32_t accumulate = GROUP ? (k > 0) : (kb > kb_begin || k > 0);
             const uint64_t koff_a = (uint64_t)((k * (args.a_mn ? kMnStep : (uint32_t)C::kUmmaKBytes)) >> 4);
             const uint64_t koff_b = (uint64_t)((k * (args.b_mn ? kMnStep : (uint32_t)C::kUmmaKBytes)) >> 4);
             if constexpr (KIND == VB_KIND_F8) mma_f8_ss(d_tmem, adesc + koff_a, bdesc + koff_b, args.idesc, accumulate);
@@ -560,8 +570,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     uint32_t ephase = 0;
     constexpr int NCHUNK = BN / 32;
     constexpr int NOUT = C::kGatedFwd ? NCHUNK / 2 : NCHUNK;  // output chunks per tile
-    for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
+    for (int u = blockIdx.x; u < args.num_tiles * args.split_k && ok; u += gridDim.x) {
       int mt, nt;
+      const int split = u / args.num_tiles, t = u - split * args.num_tiles;
       const int bi = t / args.tiles_per_batch;
       tile_coords(args, t - bi * args.tiles_per_batch, mt, nt);
       long long grow = (long long)mt * BM + row_in_tile;
@@ -670,6 +681,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
       const float alpha_pt = GROUP ? 1.f
                                    : (args.sa != nullptr ? args.sa[0] : 1.f) * (args.sb != nullptr ? args.sb[0] : 1.f);
+      if constexpr (EPI == VB_EPI_LINEAR && !GROUP) {
+        if (split > 0) {
+          // split-K: these 32 rows of the tile were last written by unit `split - 1`; its warp of the same
+          // quadrant publishes the count once its stores have landed
+          bool ready = true;
+          if (lane == 0) {
+            ready = wait_flag_eq_gpu(args.split_flags + t * 4 + quad, split, abort_flag, args.status, kTimeoutSplit);
+            fence_proxy_async_global();
+          }
+          ok = __all_sync(0xffffffffu, ready);
+          if (!ok) break;
+        }
+      }
       // ---- staged gated epilogues (per-tensor scales, 16-bit outputs): rolled over the chunks, specialised on
       // the 16-bit type and the activation, every result row leaves through a shared-memory slab and a TMA store
       bool staged_done = false;
@@ -887,7 +911,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
         };
         if constexpr (EPI == VB_EPI_LINEAR) {
-          if (args.bias != nullptr) {
+          if (args.bias != nullptr && split == 0) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, bias_reg[c], j);
           }
@@ -930,7 +954,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               const int slab_col = n0 + slab * chunks_per_slab * 32;
               const int warp_row = mt * BM + quad * 32;
               if (lane == 0 && slab_col < args.N && warp_row < args.M) {
-                tma_store_2d(&tmC, buffer, slab_col, warp_row);
+                if (split == 0) tma_store_2d(&tmC, buffer, slab_col, warp_row);
+                else tma_reduce_add_2d(&tmC, buffer, slab_col, warp_row);
               }
               if (lane == 0) tma_store_commit();
             }
@@ -1046,6 +1071,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[acc]);
         if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1; }
+      }
+      if constexpr (EPI == VB_EPI_LINEAR && !GROUP) {
+        if (args.split_k > 1 && ok) {
+          // hand the rows to the next unit of this tile once every store of this warp has landed; the last
+          // unit leaves the counter at zero for the next launch
+          if (lane == 0) {
+            tma_store_wait_all();
+            fence_proxy_async_global();
+            st_release_gpu(args.split_flags + t * 4 + quad, split + 1 == args.split_k ? 0 : split + 1);
+          }
+          __syncwarp();
+        }
       }
     }
     if constexpr (C::kSlabRing) {
@@ -1217,8 +1254,47 @@ static int sm_count() {
   return count;
 }
 
+// Hand-over counters of split-K launches: four per output tile, eight regions used in rotation so that launches
+// in flight on different streams do not share counters.  Every launch leaves its region at zero.
+constexpr int kSplitMaxTiles = 2048, kSplitRegions = 8;
+__device__ int g_split_flags[kSplitRegions * kSplitMaxTiles * 4];
+
+// Work units per output tile for a [tiles] x [k_blocks] problem on `sms` persistent CTAs: whole waves of equal units,
+// each paying a fixed prologue / epilogue cost of about `overhead` K-blocks; 1 = no split.
+static int choose_split(long long tiles, int k_blocks, int sms, double* cost_out = nullptr) {
+  const double overhead = 6.0;
+  int best = 1;
+  double best_cost = (double)((tiles + sms - 1) / sms) * (k_blocks + overhead);
+  if (tiles > 0 && tiles <= kSplitMaxTiles) {
+    for (int s = 2; s <= 16 && s * 8 <= k_blocks; ++s) {
+      const int per = (k_blocks + s - 1) / s;
+      if ((s - 1) * per >= k_blocks) continue;                  // an empty last unit
+      const long long waves = (tiles * s + sms - 1) / sms;
+      const double cost = (double)waves * (per + overhead) * 1.03;   // a split must win clearly
+      if (cost < best_cost) { best_cost = cost; best = s; }
+    }
+  }
+  if (cost_out != nullptr) *cost_out = best_cost;
+  return best;
+}
+
+static int* split_flag_base() {
+  static int* base[64] = {};
+  static std::mutex lock;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> guard(lock);
+  if (base[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_split_flags) != cudaSuccess) return nullptr;
+    base[dev] = static_cast<int*>(ptr);
+  }
+  return base[dev];
+}
+
 template <int KIND, int BN, bool GROUP, int EPI>
-static int launch(const VbGemmDesc& d, cudaStream_t stream) {
+static int launch(const VbGemmDesc& d, cudaStream_t stream, int split = 1) {
   using C = Config<KIND, BN, GROUP, EPI>;
   GemmArgs a{};
   a.M = d.M; a.N = d.N; a.K = d.K;
@@ -1307,6 +1383,23 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream) {
   if (expert) {
     expert_tile_map_kernel<<<1, 32, 0, stream>>>(d.expert_offsets, d.num_experts, a.num_m_tiles, d.tile_map);
   }
+  a.split_k = 1;
+  a.kb_per_split = a.num_k_blocks;
+  if constexpr (EPI == VB_EPI_LINEAR && !GROUP) {
+    // split-K needs the TMA path (reduce-add stores), an fp32 result and one problem per launch
+    if (split > 1 && a.tma_store && d.out_dtype == 0 && a.batch == 1 && a.num_tiles <= kSplitMaxTiles) {
+      const int per = (a.num_k_blocks + split - 1) / split;
+      if ((split - 1) * per < a.num_k_blocks) {
+        static std::atomic<unsigned> rotation{0};
+        int* flags = split_flag_base();
+        if (flags != nullptr) {
+          a.split_k = split;
+          a.kb_per_split = per;
+          a.split_flags = flags + (rotation.fetch_add(1) % kSplitRegions) * kSplitMaxTiles * 4;
+        }
+      }
+    }
+  }
   auto kernel = gemm_kernel<KIND, BN, GROUP, EPI>;
   static bool configured = false;
   if (!configured) {
@@ -1314,7 +1407,7 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream) {
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int grid = std::min(a.num_tiles, sm_count());
+  const int grid = (int)std::min<long long>((long long)a.num_tiles * a.split_k, sm_count());
   kernel<<<grid, C::kCtaThreads, C::kSmemBytes, stream>>>(tmA, tmB, tmC, tmD, a);
   return (int)cudaGetLastError();
 }
@@ -1343,7 +1436,20 @@ extern "C" int vb_gemm(const VbGemmDesc* desc, cudaStream_t stream) {
       if (d.epilogue == VB_EPI_GATED_FWD) bn = 256;
     }
   }
-#define VB_LAUNCH(KIND, BNV, GROUPV, EPIV) return launch<KIND, BNV, GROUPV, EPIV>(d, stream)
+  // split-K for fp32 results (weight gradients: few output tiles, long K): width and unit count are chosen together
+  int split = d.force_split > 0 ? d.force_split : 1;
+  if (d.force_split == 0 && d.epilogue == VB_EPI_LINEAR && !group && !d.symmetric && d.out_dtype == 0 &&
+      d.expert_offsets == nullptr && d.batch <= 1 && !d.no_tma_store) {
+    const int k_blocks = (int)(((long long)d.K * elem + BK_BYTES - 1) / BK_BYTES);
+    const long long rows = (d.M + 127) / 128;
+    double cost128 = 0.0, cost256 = 0.0;
+    const int split128 = choose_split(rows * ((d.N + 127) / 128), k_blocks, sms, &cost128);
+    const int split256 = choose_split(rows * ((d.N + 255) / 256), k_blocks, sms, &cost256);
+    cost128 *= 0.73;
+    if (d.force_bn == 0 && d.N > 128 && (split128 > 1 || split256 > 1)) bn = cost256 <= cost128 ? 256 : 128;
+    split = bn == 256 ? split256 : split128;
+  }
+#define VB_LAUNCH(KIND, BNV, GROUPV, EPIV) return launch<KIND, BNV, GROUPV, EPIV>(d, stream, split)
   if (d.kind == VB_KIND_F8) {
     switch (d.epilogue) {
       case VB_EPI_LINEAR:

@@ -285,7 +285,7 @@ def _check_mn(t):
 
 def _gemm(a, b, out, epilogue, n_logical, *, sa=None, sb=None, layout=_NO_GROUP, bias=None, alpha=1.0, beta=0.0,
           resid=None, out_t=None, symmetric=False, activation=0, aux=None, expert_offsets=None, tile_map=None,
-          force_bn=0, batch=1, a_mn=False, b_mn=False, amax_out=None):
+          force_bn=0, batch=1, a_mn=False, b_mn=False, amax_out=None, force_split=0):
     multiple = 16 if a.element_size() == 1 else 8
     a = _check_mn(a) if a_mn else _pad_k(a, multiple)
     b = _check_mn(b) if b_mn else _pad_k(b, multiple)
@@ -293,7 +293,8 @@ def _gemm(a, b, out, epilogue, n_logical, *, sa=None, sb=None, layout=_NO_GROUP,
 
     def launch(tile):
         _ops().gemm(a, b, out, epilogue, n_logical, sa, sb, list(layout), bias, float(alpha), float(beta), resid, out_t,
-                    bool(symmetric), int(activation), aux, expert_offsets, tile_map, status, int(tile), int(batch),
+                    bool(symmetric), int(activation), aux, expert_offsets, tile_map, status,
+                    int(tile) | (int(force_split) << 16), int(batch),
                     bool(a_mn), bool(b_mn), amax_out)
 
     if not force_bn and (tuning._enabled or tuning._choices):
@@ -309,11 +310,12 @@ def _gemm(a, b, out, epilogue, n_logical, *, sa=None, sb=None, layout=_NO_GROUP,
     return out
 
 
-def gemm(a, b, sa, sb, *, out_dtype, bias=None, out=None, force_bn=0, a_mn=False, b_mn=False):
+def gemm(a, b, sa, sb, *, out_dtype, bias=None, out=None, force_bn=0, a_mn=False, b_mn=False, force_split=0):
     """(a * sa) @ (b * sb).T (+ bias): FP8 or 16-bit operands with per-tensor fp32 scales.
 
     ``a_mn`` / ``b_mn``: the tensor passed holds the operand transposed (``a`` is [K, M] / ``b`` is [K, N]);
     the tensor core reads it MN-major in place, so no transposed copy is needed.
+    ``force_split``: work units per output tile along K for fp32 results (0 = chosen from the wave count, 1 = none).
     """
     if not a.is_cuda:
         result = reference.gemm(a.t() if a_mn else a, b.t() if b_mn else b, sa, sb, out_dtype=out_dtype, bias=bias)
@@ -322,7 +324,8 @@ def gemm(a, b, sa, sb, *, out_dtype, bias=None, out=None, force_bn=0, a_mn=False
     n = b.shape[1] if b_mn else b.shape[0]
     if out is None:
         out = torch.empty((m, n), device=a.device, dtype=out_dtype)
-    return _gemm(a, b, out, EPI_LINEAR, n, sa=sa, sb=sb, bias=bias, force_bn=force_bn, a_mn=a_mn, b_mn=b_mn)
+    return _gemm(a, b, out, EPI_LINEAR, n, sa=sa, sb=sb, bias=bias, force_bn=force_bn, a_mn=a_mn, b_mn=b_mn,
+                 force_split=force_split)
 
 
 # ------------------------------------------------------------------------------ group scaling

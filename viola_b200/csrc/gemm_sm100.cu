@@ -42,7 +42,8 @@ namespace vb {
 
 constexpr int BM = 128;
 constexpr int BK_BYTES = 128;  // one 128-byte swizzle span along K per stage
-constexpr int kThreads = 192;   // warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 epilogue (+ warp 6: slab loader)
+constexpr int kThreads = 192;   // warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 epilogue (+ warp 6: slab loader);
+                                // the per-tensor LINEAR kernels run eight epilogue warps (warps 2-9) instead
 
 struct GemmArgs {
   int M, N, K;
@@ -79,7 +80,7 @@ struct GemmArgs {
   int a_mn, b_mn;       // operand stored MN-major: A as [K, M] / B as [K, N] (row-major, MN contiguous)
   // split-K (LINEAR epilogue, fp32 output through TMA): every output tile is computed by `split_k` work units, each
   // over `kb_per_split` K-blocks; unit 0 stores its partial tile, unit s adds its own with a TMA reduce once unit
-  // s - 1 has finished (split_flags[tile * 4 + warp quadrant] counts finished units; the last one clears it)
+  // s - 1 has finished (split_flags[tile * 8 + epilogue warp] counts finished units; the last one clears it)
   int split_k, kb_per_split;
   int* split_flags;
   int* status;
@@ -326,7 +327,11 @@ struct Config {
   static constexpr int kBBytes = BN * BK_BYTES;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr bool kTmaStore = EPI == VB_EPI_LINEAR;   // epilogue staged in smem and written by TMA
-  static constexpr int kStoreBytes = kTmaStore ? 4 * 2 * 4096 : 0;   // 4 warps x 2 buffers x (32 rows x 128 B)
+  // With K of about a thousand a 128 x 256 tile's MMAs take about as long as four warps need to drain it (one
+  // warp per scheduler, so every TMEM load and shared-memory store latency is exposed): the per-tensor LINEAR
+  // kernels use eight epilogue warps, two per TMEM lane quadrant, each draining half of the tile's columns.
+  static constexpr int kEpiWarps = (EPI == VB_EPI_LINEAR && !GROUP) ? 8 : 4;
+  static constexpr int kStoreBytes = kTmaStore ? kEpiWarps * 4096 : 0;   // per warp: 2 x (32 rows x 64 B) or 32 rows x 128 B
   // AXPBY and ACT_BWD epilogues (16-bit output, optional 16-bit [M, N] operand: the residual / the activation
   // slope) run through a ring of 128-row x 32-column slabs in shared memory, one per output chunk: the
   // producer warp TMA-loads the operand slab while the tile's MMAs run, each epilogue warp rewrites its 32
@@ -343,10 +348,10 @@ struct Config {
   static constexpr bool kSlabRing = kEpiSlab || kGatedSlab;
   static constexpr bool kSlabLoader = kEpiSlab || (kGatedBwd && !GROUP);
   static constexpr int kEpiSlabs = (kGatedBwd && !GROUP) ? 8 : 4;
-  static constexpr int kCtaThreads = kSlabLoader ? kThreads + 32 : kThreads;   // a seventh warp feeds the slab ring
+  static constexpr int kCtaThreads = kSlabLoader ? kThreads + 32 : 64 + 32 * kEpiWarps;   // a seventh warp feeds the slab ring
   static constexpr int kEpiSlabBytes = BM * 64;
   static constexpr int kEpiBytes = kSlabRing ? kEpiSlabs * kEpiSlabBytes : 0;
-  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? (((GROUP && kTmaStore) || (kGatedBwd && !GROUP)) ? 5 : 6) : 8);
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? ((kGatedBwd && !GROUP) ? 5 : 6) : 8);
   static constexpr int kAcc = GROUP ? (512 / BN > 4 ? 4 : 512 / BN) : 2;
   static constexpr int kTmemCols = kAcc * BN;
   static constexpr int kBarrierBytes = 1024;
@@ -394,7 +399,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
     for (int i = 0; i < C::kAcc; ++i) {
       mbar_init(&tmem_full[i], 1);
-      mbar_init(&tmem_empty[i], 4);
+      mbar_init(&tmem_empty[i], C::kEpiWarps);
     }
     for (int i = 0; i < C::kEpiSlabs; ++i) {
       mbar_init(&epi_full[i], 1);
@@ -523,7 +528,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1; }
       }
     }
-  } else if (warp == 6) {
+  } else if (C::kSlabLoader && warp == 6) {
     // ------------------------------ slab loader --------------------------------
     // Feeds the epilogue's operand slabs (AXPBY residual, ACT_BWD slope) on its own, so a full slab ring never
     // holds back the main-loop producer; it runs up to kEpiSlabs chunks ahead of the epilogue.
@@ -560,6 +565,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else {
     // ------------------------------ epilogue ----------------------------------
     const int quad = warp & 3;            // TMEM lane quadrant this warp may read
+    const int epi = warp - 2;             // 0 .. kEpiWarps - 1
+    const int half = epi >> 2;            // which part of the tile's columns this warp drains (0 with four warps)
     const int row_in_tile = quad * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -569,7 +576,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     int eslot = 0, prev_slot = -1;        // epilogue slab ring: position, phase, slot awaiting release
     uint32_t ephase = 0;
     constexpr int NCHUNK = BN / 32;
-    constexpr int NOUT = C::kGatedFwd ? NCHUNK / 2 : NCHUNK;  // output chunks per tile
+    constexpr int NOUT = (C::kGatedFwd ? NCHUNK / 2 : NCHUNK) / (C::kEpiWarps / 4);  // output chunks per tile and warp
+    const int chunk0 = half * NOUT;       // first chunk of this warp
     for (int u = blockIdx.x; u < args.num_tiles * args.split_k && ok; u += gridDim.x) {
       int mt, nt;
       const int split = u / args.num_tiles, t = u - split * args.num_tiles;
@@ -599,7 +607,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if constexpr (kHasBias) {
 #pragma unroll
         for (int c = 0; c < NOUT; ++c) {
-          const int col = n0 + c * 32 + lane;
+          const int col = n0 + (chunk0 + c) * 32 + lane;
           const bool in = args.bias != nullptr && col < args.N;
           bias_reg[c] = in ? load_elem(args.bias, col, args.bias_dtype) : 0.f;
           if constexpr (C::kGatedFwd) bias_reg2[c] = in ? load_elem(args.bias, args.N + col, args.bias_dtype) : 0.f;
@@ -687,7 +695,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           // quadrant publishes the count once its stores have landed
           bool ready = true;
           if (lane == 0) {
-            ready = wait_flag_eq_gpu(args.split_flags + t * 4 + quad, split, abort_flag, args.status, kTimeoutSplit);
+            ready = wait_flag_eq_gpu(args.split_flags + t * 8 + epi, split, abort_flag, args.status, kTimeoutSplit);
             fence_proxy_async_global();
           }
           ok = __all_sync(0xffffffffu, ready);
@@ -850,7 +858,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
         } else {
           uint32_t r[32];
-          tmem_ld_32x32(tmem_base + lane_addr + acc * BN + c * 32, r);
+          tmem_ld_32x32(tmem_base + lane_addr + acc * BN + (chunk0 + c) * 32, r);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha_pt;
@@ -861,7 +869,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int j = 0; j < 32; ++j) v2[j] = __uint_as_float(r[j]) * alpha_pt;
           }
         }
-        const int col0 = n0 + c * 32;
+        const int col0 = n0 + (chunk0 + c) * 32;
         const bool staged = C::kTmaStore && args.tma_store != 0;
         if (col0 >= args.N && !staged) continue;  // warp-uniform; the producer skips these chunks too
         // slab ring: this chunk's slot holds the operand (once epi_full fires) and then the result
@@ -918,26 +926,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (!staged) {
             if (row_ok) store_row32(out_base, args.ldo, args.out_dtype, grow, col0, args.N, v);
           } else {
-            // Each warp owns 32 rows x 128 bytes per slab, double buffered.  A lane writes its row's
-            // 16-byte pieces at the 128B-swizzled position; one lane then issues the TMA store, which
-            // clips rows >= M and columns >= N by itself.
-            const int elem = args.out_dtype == 0 ? 4 : 2;
-            const int chunks_per_slab = 128 / (32 * elem);          // 1 (fp32) or 2 (16-bit)
-            const int in_slab = c % chunks_per_slab;
-            const int slab = c / chunks_per_slab;
-            uint8_t* buffer = store_stage + ((warp - 2) * 2 + (slab & 1)) * 4096;
-            if (in_slab == 0) {
-              if (lane == 0) tma_store_wait_read<1>();               // the store that last used this buffer
+            // Each warp owns a 4 KB staging region: two 32-row x 64-byte buffers (16-bit results, 64B swizzle,
+            // alternating per chunk) or one 32-row x 128-byte buffer (fp32, 128B swizzle).  A lane writes its row's
+            // 16-byte pieces at the swizzled position; one lane then issues the TMA store (or, for the later units
+            // of a split-K tile, the TMA reduce-add), which clips rows >= M and columns >= N by itself.
+            uint8_t* region = store_stage + epi * 4096;
+            uint8_t* buffer = region;
+            if (args.out_dtype == 0) {
+              if (lane == 0) tma_store_wait_read<0>();               // the store that last used this buffer
               __syncwarp();
-            }
-            uint8_t* row_ptr = buffer + lane * 128;
-            const int piece0 = in_slab * (32 * elem / 16);
-            if (elem == 4) {
+              uint8_t* row_ptr = buffer + lane * 128;
 #pragma unroll
               for (int p = 0; p < 8; ++p)
-                *reinterpret_cast<float4*>(row_ptr + (((piece0 + p) ^ (lane & 7)) << 4)) =
+                *reinterpret_cast<float4*>(row_ptr + ((p ^ (lane & 7)) << 4)) =
                     make_float4(v[4 * p], v[4 * p + 1], v[4 * p + 2], v[4 * p + 3]);
             } else {
+              buffer = region + (c & 1) * 2048;
+              if (lane == 0) tma_store_wait_read<1>();               // the store of two chunks ago
+              __syncwarp();
+              uint8_t* row_ptr = buffer + lane * 64;
 #pragma unroll
               for (int p = 0; p < 4; ++p) {
                 uint4 t;
@@ -945,19 +952,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 t.y = pack2(v[8 * p + 2], v[8 * p + 3], args.out_dtype);
                 t.z = pack2(v[8 * p + 4], v[8 * p + 5], args.out_dtype);
                 t.w = pack2(v[8 * p + 6], v[8 * p + 7], args.out_dtype);
-                *reinterpret_cast<uint4*>(row_ptr + (((piece0 + p) ^ (lane & 7)) << 4)) = t;
+                *reinterpret_cast<uint4*>(row_ptr + ((p ^ ((lane >> 1) & 3)) << 4)) = t;
               }
             }
-            if (in_slab == chunks_per_slab - 1 || c == NOUT - 1) {
-              fence_proxy_async_smem();
-              __syncwarp();
-              const int slab_col = n0 + slab * chunks_per_slab * 32;
-              const int warp_row = mt * BM + quad * 32;
-              if (lane == 0 && slab_col < args.N && warp_row < args.M) {
-                if (split == 0) tma_store_2d(&tmC, buffer, slab_col, warp_row);
-                else tma_reduce_add_2d(&tmC, buffer, slab_col, warp_row);
+            fence_proxy_async_smem();
+            __syncwarp();
+            const int warp_row = mt * BM + quad * 32;
+            if (lane == 0) {
+              if (col0 < args.N && warp_row < args.M) {
+                if (split == 0) tma_store_2d(&tmC, buffer, col0, warp_row);
+                else tma_reduce_add_2d(&tmC, buffer, col0, warp_row);
               }
-              if (lane == 0) tma_store_commit();
+              tma_store_commit();
             }
           }
         } else if constexpr (EPI == VB_EPI_AXPBY) {
@@ -1079,7 +1085,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (lane == 0) {
             tma_store_wait_all();
             fence_proxy_async_global();
-            st_release_gpu(args.split_flags + t * 4 + quad, split + 1 == args.split_k ? 0 : split + 1);
+            st_release_gpu(args.split_flags + t * 8 + epi, split + 1 == args.split_k ? 0 : split + 1);
           }
           __syncwarp();
         }
@@ -1254,10 +1260,10 @@ static int sm_count() {
   return count;
 }
 
-// Hand-over counters of split-K launches: four per output tile, eight regions used in rotation so that launches
+// Hand-over counters of split-K launches: one per output tile and epilogue warp, eight regions used in rotation so that launches
 // in flight on different streams do not share counters.  Every launch leaves its region at zero.
 constexpr int kSplitMaxTiles = 2048, kSplitRegions = 8;
-__device__ int g_split_flags[kSplitRegions * kSplitMaxTiles * 4];
+__device__ int g_split_flags[kSplitRegions * kSplitMaxTiles * 8];
 
 // Work units per output tile for a [tiles] x [k_blocks] problem on `sms` persistent CTAs: whole waves of equal units,
 // each paying a fixed prologue / epilogue cost of about `overhead` K-blocks; 1 = no split.
@@ -1346,8 +1352,10 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream, int split = 1) {
   a.tma_store = 0;
   if (C::kTmaStore && !expert && a.batch == 1 && !d.no_tma_store) {
     const int elem = d.out_dtype == 0 ? 4 : 2;
+    // fp32: 32 columns = 128-byte rows (128B swizzle); 16-bit: 32 columns = 64-byte rows (64B swizzle)
     if ((reinterpret_cast<uintptr_t>(d.out) & 15) == 0 && (d.ldo * elem) % 16 == 0 &&
-        make_out_map(&tmC, d.out, d.out_dtype, d.M, d.N, d.ldo) == 0)
+        (d.out_dtype == 0 ? make_out_map(&tmC, d.out, d.out_dtype, d.M, d.N, d.ldo)
+                          : make_slab_map(&tmC, d.out, d.out_dtype, d.M, d.N, d.ldo, 32)) == 0)
       a.tma_store = 1;
   }
   CUtensorMap tmD = tmA;
@@ -1395,7 +1403,7 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream, int split = 1) {
         if (flags != nullptr) {
           a.split_k = split;
           a.kb_per_split = per;
-          a.split_flags = flags + (rotation.fetch_add(1) % kSplitRegions) * kSplitMaxTiles * 4;
+          a.split_flags = flags + (rotation.fetch_add(1) % kSplitRegions) * kSplitMaxTiles * 8;
         }
       }
     }

@@ -581,6 +581,35 @@ def test_split_k_matches_the_unsplit_product_and_repeats(shape, layout):
     ops.check_status()
 
 
+@pytest.mark.parametrize("shape", [(512, 512, 256), (1000, 712, 1152), (130, 264, 96), (4096, 3456, 1152)])
+@pytest.mark.parametrize("layout", ["k-major", "b-mn", "mn-major"])
+def test_cta_pair_gemm_matches_the_single_cta_kernel(shape, layout):
+    """256 x 256 tiles computed by CTA pairs (tcgen05 cta_group::2, each CTA loading half of B) against the
+    single-CTA kernel on the same operands: identical accumulation order per output element, so bit-identical."""
+    m, n, k = shape
+    torch.manual_seed(m + n + k)
+    a = torch.randn(m, k, device="cuda").to(torch.float8_e4m3fn)
+    b = torch.randn(n, k, device="cuda").to(torch.float8_e5m2)
+    sa, sb = torch.full((1,), 0.5, device="cuda"), torch.full((1,), 0.25, device="cuda")
+    bias = torch.randn(n, device="cuda").bfloat16()
+    a_mn, b_mn = layout == "mn-major", layout in ("b-mn", "mn-major")
+    if (a_mn and m % 16) or (b_mn and n % 16):
+        pytest.skip("MN-major operands need 16-byte rows")
+    left = a.t().contiguous() if a_mn else a
+    right = b.t().contiguous() if b_mn else b
+    for dtype in (torch.bfloat16, torch.float32):
+        for use_bias in (False, True):
+            kwargs = dict(out_dtype=dtype, bias=bias if use_bias else None, a_mn=a_mn, b_mn=b_mn)
+            base = ops.gemm(left, right, sa, sb, force_bn=256, force_split=1, **kwargs)
+            out, intact = _guarded((m, n), dtype)
+            ops.gemm(left, right, sa, sb, force_bn=512, out=out, **kwargs)
+            torch.cuda.synchronize()
+            ops.check_status()
+            assert intact()
+            assert torch.equal(out, base)
+    assert rel_l2(base, (a.float() @ b.float().t()) * 0.125 + bias.float()) < 1e-2
+
+
 def test_quantiser_outputs_stay_inside_their_buffers_and_repeat_bit_for_bit():
     rows, cols = 333, 416
     x = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)

@@ -166,14 +166,15 @@ int vb_row_block_count(int rows, int tokens);
 int vb_ln_modulate_backward(const void* dh, const void* x, int x_dtype, const float* mean, const float* rstd,
                             const void* mod_scale, long long mod_stride, int rows, int cols, int tokens,
                             const void* grad_in /* optional, x's dtype: added to dx */, void* dx,
-                            float* dshift, float* dscale, float* workspace, long long workspace_floats,
-                            unsigned int* tickets, int ticket_count, cudaStream_t stream);
+                            void* dshift, void* dscale, int sums_bf16 /* 0: fp32 sums, 1: bf16 sums */,
+                            float* workspace, long long workspace_floats, unsigned int* tickets, int ticket_count,
+                            cudaStream_t stream);
 // out = x + gate[row / tokens] * y (x, out: x_dtype; y, gate: bf16) and the branch side of its backward:
-// dy = dout * gate (bf16), dgate = per-sample column sums of dout * y (fp32)
+// dy = dout * gate (bf16), dgate = per-sample column sums of dout * y (fp32, or bf16 with sums_bf16)
 int vb_gate_residual(const void* x, int x_dtype, const void* gate, long long gate_stride, const void* y, int rows,
                      int cols, int tokens, void* out, cudaStream_t stream);
 int vb_gate_residual_backward(const void* dout, int dout_dtype, const void* gate, long long gate_stride, const void* y,
-                              int rows, int cols, int tokens, void* dy, float* dgate, float* workspace,
+                              int rows, int cols, int tokens, void* dy, void* dgate, int sums_bf16, float* workspace,
                               long long workspace_floats, unsigned int* tickets, int ticket_count, cudaStream_t stream);
 
 // ---- Hadamard-64 rotation --------------------------------------------------------

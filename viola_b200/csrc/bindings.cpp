@@ -525,13 +525,14 @@ void ln_modulate_backward(const Tensor& dh, const Tensor& x, const Tensor& mean,
   TORCH_CHECK(dh.scalar_type() == at::kBFloat16 && dx.scalar_type() == x.scalar_type());
   if (grad_in.has_value() && grad_in->defined())
     TORCH_CHECK(grad_in->is_contiguous() && grad_in->scalar_type() == x.scalar_type() && grad_in->sizes() == x.sizes());
-  TORCH_CHECK(dshift.scalar_type() == at::kFloat && dscale.scalar_type() == at::kFloat);
+  TORCH_CHECK((dshift.scalar_type() == at::kFloat || dshift.scalar_type() == at::kBFloat16) &&
+              dscale.scalar_type() == dshift.scalar_type() && dshift.is_contiguous() && dscale.is_contiguous());
   const int64_t stride = mod_rows(scale, "scale", x.size(1));
   c10::cuda::CUDAGuard guard(x.device());
   check(vb_ln_modulate_backward(dh.data_ptr(), x.data_ptr(), stream_dtype(x, "x"), mean.data_ptr<float>(),
                                 rstd.data_ptr<float>(), scale.data_ptr(), stride, (int)x.size(0), (int)x.size(1),
-                                (int)tokens, ptr(grad_in), dx.data_ptr(), dshift.data_ptr<float>(), dscale.data_ptr<float>(),
-                                workspace.data_ptr<float>(), workspace.numel(), (unsigned int*)tickets.data_ptr(),
+                                (int)tokens, ptr(grad_in), dx.data_ptr(), dshift.data_ptr(), dscale.data_ptr(),
+                                dshift.scalar_type() == at::kBFloat16 ? 1 : 0, workspace.data_ptr<float>(), workspace.numel(), (unsigned int*)tickets.data_ptr(),
                                 (int)tickets.numel(), stream()),
         "ln_modulate_backward");
 }
@@ -558,12 +559,14 @@ void gate_residual_backward(const Tensor& dout, const Tensor& gate, const Tensor
   cuda_contig(dy, "dy");
   cuda_contig(dgate, "dgate");
   TORCH_CHECK(dout.dim() == 2 && y.sizes() == dout.sizes() && dy.sizes() == dout.sizes());
-  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && dy.scalar_type() == at::kBFloat16 && dgate.scalar_type() == at::kFloat);
+  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && dy.scalar_type() == at::kBFloat16 &&
+              (dgate.scalar_type() == at::kFloat || dgate.scalar_type() == at::kBFloat16));
   const int64_t stride = mod_rows(gate, "gate", dout.size(1));
   c10::cuda::CUDAGuard guard(dout.device());
   check(vb_gate_residual_backward(dout.data_ptr(), stream_dtype(dout, "dout"), gate.data_ptr(), stride, y.data_ptr(),
                                   (int)dout.size(0), (int)dout.size(1), (int)tokens, dy.data_ptr(),
-                                  dgate.data_ptr<float>(), workspace.data_ptr<float>(), workspace.numel(),
+                                  dgate.data_ptr(), dgate.scalar_type() == at::kBFloat16 ? 1 : 0,
+                                  workspace.data_ptr<float>(), workspace.numel(),
                                   (unsigned int*)tickets.data_ptr(), (int)tickets.numel(), stream()),
         "gate_residual_backward");
 }

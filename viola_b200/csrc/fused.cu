@@ -458,8 +458,8 @@ ln_modulate_backward_kernel(const __nv_bfloat16* __restrict__ dh, const T* __res
                             const float* __restrict__ mean, const float* __restrict__ rstd,
                             const __nv_bfloat16* __restrict__ mod_scale, long long mod_stride, int rows, int cols,
                             int tokens, int rows_per_block, const T* __restrict__ grad_in, T* __restrict__ dx,
-                            float* __restrict__ dshift, float* __restrict__ dscale, float* __restrict__ workspace,
-                            unsigned int* __restrict__ tickets) {
+                            void* __restrict__ dshift, void* __restrict__ dscale, int sums_bf16,
+                            float* __restrict__ workspace, unsigned int* __restrict__ tickets) {
   extern __shared__ float partial[];            // [8 warps][2][cols]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int chunks = cols >> 3;
@@ -524,7 +524,12 @@ ln_modulate_backward_kernel(const __nv_bfloat16* __restrict__ dh, const T* __res
   ordered_sample_sums(
       partial, 2 * cols, sample, blocks_per_sample, workspace, tickets,
       [=](int i) { const int which = i >= cols, c = i - which * cols; return which * cols + (c & 7) * chunks + (c >> 3); },
-      [=](int i, float total) { (i >= cols ? dscale + mod - cols : dshift + mod)[i] = total; });
+      [=](int i, float total) {
+        void* base = i >= cols ? dscale : dshift;
+        const long long at = mod + (i >= cols ? i - cols : i);
+        if (sums_bf16) reinterpret_cast<__nv_bfloat16*>(base)[at] = __float2bfloat16_rn(total);
+        else reinterpret_cast<float*>(base)[at] = total;
+      });
 }
 
 // out = x + gate[b] * y: x / out in T (the residual stream), y and gate in bf16; 8 elements per thread.
@@ -553,8 +558,8 @@ template <typename T, int VPL>
 __global__ void __launch_bounds__(256)
 gate_residual_backward_kernel(const T* __restrict__ dout, const __nv_bfloat16* __restrict__ gate, long long gate_stride,
                               const __nv_bfloat16* __restrict__ y, int rows, int cols, int tokens, int rows_per_block,
-                              __nv_bfloat16* __restrict__ dy, float* __restrict__ dgate, float* __restrict__ workspace,
-                              unsigned int* __restrict__ tickets) {
+                              __nv_bfloat16* __restrict__ dy, void* __restrict__ dgate, int sums_bf16,
+                              float* __restrict__ workspace, unsigned int* __restrict__ tickets) {
   extern __shared__ float partial[];            // [8 warps][cols], element e of chunk c at e * chunks + c
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int chunks = cols >> 3;
@@ -598,10 +603,14 @@ gate_residual_backward_kernel(const T* __restrict__ dout, const __nv_bfloat16* _
     }
   }
   __syncthreads();
-  float* out_row = dgate + (long long)sample * cols;
+  const long long out_row = (long long)sample * cols;
   ordered_sample_sums(
       partial, cols, sample, blocks_per_sample, workspace, tickets,
-      [=](int c) { return (c & 7) * chunks + (c >> 3); }, [=](int c, float total) { out_row[c] = total; });
+      [=](int c) { return (c & 7) * chunks + (c >> 3); },
+      [=](int c, float total) {
+        if (sums_bf16) reinterpret_cast<__nv_bfloat16*>(dgate)[out_row + c] = __float2bfloat16_rn(total);
+        else reinterpret_cast<float*>(dgate)[out_row + c] = total;
+      });
 }
 
 }  // namespace vb
@@ -708,7 +717,7 @@ extern "C" int vb_fused_quantize(const void* x, int x_dtype, int rows, int cols,
 
 extern "C" int vb_ln_modulate_backward(const void* dh, const void* x, int x_dtype, const float* mean, const float* rstd,
                                        const void* mod_scale, long long mod_stride, int rows, int cols, int tokens,
-                                       const void* grad_in, void* dx, float* dshift, float* dscale, float* workspace,
+                                       const void* grad_in, void* dx, void* dshift, void* dscale, int sums_bf16, float* workspace,
                                        long long workspace_floats, unsigned int* tickets, int ticket_count,
                                        cudaStream_t stream) {
   if (rows <= 0 || cols <= 0 || tokens <= 0 || rows % tokens != 0 || cols % 8 != 0 || mod_stride % 8 != 0 ||
@@ -725,11 +734,11 @@ extern "C" int vb_ln_modulate_backward(const void* dh, const void* x, int x_dtyp
     VB_VPL_SWITCH(cols, (allow_smem(ln_modulate_backward_kernel<__nv_bfloat16, VPL>), ln_modulate_backward_kernel<__nv_bfloat16, VPL><<<grid, 256, smem, stream>>>(
                             (const __nv_bfloat16*)dh, (const __nv_bfloat16*)x, mean, rstd, sc, mod_stride, rows, cols,
                             tokens, rows_per_block, (const __nv_bfloat16*)grad_in, (__nv_bfloat16*)dx, dshift, dscale,
-                            workspace, tickets)));
+                            sums_bf16, workspace, tickets)));
   } else {
     VB_VPL_SWITCH(cols, (allow_smem(ln_modulate_backward_kernel<float, VPL>), ln_modulate_backward_kernel<float, VPL><<<grid, 256, smem, stream>>>(
                             (const __nv_bfloat16*)dh, (const float*)x, mean, rstd, sc, mod_stride, rows, cols, tokens,
-                            rows_per_block, (const float*)grad_in, (float*)dx, dshift, dscale, workspace, tickets)));
+                            rows_per_block, (const float*)grad_in, (float*)dx, dshift, dscale, sums_bf16, workspace, tickets)));
   }
   return (int)cudaGetLastError();
 }
@@ -760,7 +769,7 @@ extern "C" int vb_gate_residual(const void* x, int x_dtype, const void* gate, lo
 }
 
 extern "C" int vb_gate_residual_backward(const void* dout, int dout_dtype, const void* gate, long long gate_stride,
-                                         const void* y, int rows, int cols, int tokens, void* dy, float* dgate,
+                                         const void* y, int rows, int cols, int tokens, void* dy, void* dgate, int sums_bf16,
                                          float* workspace, long long workspace_floats, unsigned int* tickets,
                                          int ticket_count, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0 || tokens <= 0 || rows % tokens != 0 || cols % 8 != 0 || gate_stride % 8 != 0 ||
@@ -776,11 +785,11 @@ extern "C" int vb_gate_residual_backward(const void* dout, int dout_dtype, const
   if (dout_dtype == kBF16) {
     VB_VPL_SWITCH(cols, (allow_smem(gate_residual_backward_kernel<__nv_bfloat16, VPL>), gate_residual_backward_kernel<__nv_bfloat16, VPL><<<grid, 256, smem, stream>>>(
                             (const __nv_bfloat16*)dout, g, gate_stride, (const __nv_bfloat16*)y, rows, cols, tokens,
-                            rows_per_block, (__nv_bfloat16*)dy, dgate, workspace, tickets)));
+                            rows_per_block, (__nv_bfloat16*)dy, dgate, sums_bf16, workspace, tickets)));
   } else {
     VB_VPL_SWITCH(cols, (allow_smem(gate_residual_backward_kernel<float, VPL>), gate_residual_backward_kernel<float, VPL><<<grid, 256, smem, stream>>>(
                             (const float*)dout, g, gate_stride, (const __nv_bfloat16*)y, rows, cols, tokens, rows_per_block,
-                            (__nv_bfloat16*)dy, dgate, workspace, tickets)));
+                            (__nv_bfloat16*)dy, dgate, sums_bf16, workspace, tickets)));
   }
   return (int)cudaGetLastError();
 }

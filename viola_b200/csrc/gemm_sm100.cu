@@ -319,12 +319,18 @@ __device__ __forceinline__ void tile_coords(const GemmArgs& a, int t, int& mt, i
   nt = in / gm;
 }
 
-template <int KIND, int BN, bool GROUP, int EPI>
+// PAIR: two CTAs of a cluster work on one 256 x BN output tile with tcgen05 cta_group::2.  Each CTA loads its own 128
+// rows of A and HALF of the B tile (BN / 2 rows), the leader (cluster rank 0) issues 256-row MMAs that read both
+// CTAs' shared memory and write both CTAs' tensor memory, and each CTA's epilogue drains its own 128 rows.  A stage
+// is 32 KB instead of 48 KB per CTA, so six stages fit where four did, and a third less operand traffic reaches
+// every SM: what a short-K tile needs to keep the tensor pipe fed across the L2 round trip.
+template <int KIND, int BN, bool GROUP, int EPI, bool PAIR = false>
 struct Config {
+  static_assert(!PAIR || (BN == 256 && !GROUP && EPI == VB_EPI_LINEAR), "CTA pairs: per-tensor LINEAR, 256 columns");
   static constexpr bool kGatedFwd = EPI == VB_EPI_GATED_FWD;
-  static constexpr int kBBoxRows = kGatedFwd ? BN / 2 : BN;
+  static constexpr int kBBoxRows = (kGatedFwd || PAIR) ? BN / 2 : BN;
   static constexpr int kABytes = BM * BK_BYTES;
-  static constexpr int kBBytes = BN * BK_BYTES;
+  static constexpr int kBBytes = (PAIR ? BN / 2 : BN) * BK_BYTES;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr bool kTmaStore = EPI == VB_EPI_LINEAR;   // epilogue staged in smem and written by TMA
   // With K of about a thousand a 128 x 256 tile's MMAs take about as long as four warps need to drain it (one
@@ -351,7 +357,7 @@ struct Config {
   static constexpr int kCtaThreads = kSlabLoader ? kThreads + 32 : 64 + 32 * kEpiWarps;   // a seventh warp feeds the slab ring
   static constexpr int kEpiSlabBytes = BM * 64;
   static constexpr int kEpiBytes = kSlabRing ? kEpiSlabs * kEpiSlabBytes : 0;
-  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? ((kGatedBwd && !GROUP) ? 5 : 6) : 8);
+  static constexpr int kStages = PAIR ? 6 : (BN == 256) ? 4 : (BN == 128 ? ((kGatedBwd && !GROUP) ? 5 : 6) : 8);
   static constexpr int kAcc = GROUP ? (512 / BN > 4 ? 4 : 512 / BN) : 2;
   static constexpr int kTmemCols = kAcc * BN;
   static constexpr int kBarrierBytes = 1024;
@@ -366,11 +372,11 @@ struct Config {
   static_assert(kSmemBytes > 116 * 1024, "one CTA per SM so TMEM allocation never contends");
 };
 
-template <int KIND, int BN, bool GROUP, int EPI>
-__global__ void __launch_bounds__((Config<KIND, BN, GROUP, EPI>::kCtaThreads), 1)
+template <int KIND, int BN, bool GROUP, int EPI, bool PAIR = false>
+__global__ void __launch_bounds__((Config<KIND, BN, GROUP, EPI, PAIR>::kCtaThreads), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD, const GemmArgs args) {
-  using C = Config<KIND, BN, GROUP, EPI>;
+  using C = Config<KIND, BN, GROUP, EPI, PAIR>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem;
@@ -391,6 +397,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // CTA pairs: the persistent loop runs over clusters; `rank` selects this CTA's half of the pair tile
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const int cta_first = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int cta_stride = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::kStages; ++i) {
@@ -399,7 +409,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
     for (int i = 0; i < C::kAcc; ++i) {
       mbar_init(&tmem_full[i], 1);
-      mbar_init(&tmem_empty[i], C::kEpiWarps);
+      mbar_init(&tmem_empty[i], PAIR ? 2 * C::kEpiWarps : C::kEpiWarps);   // pairs: both CTAs' warps, on the leader
     }
     for (int i = 0; i < C::kEpiSlabs; ++i) {
       mbar_init(&epi_full[i], 1);
@@ -411,11 +421,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     tma_prefetch_desc(&tmB);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, C::kTmemCols);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(tmem_slot, C::kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, C::kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // the peer's barriers exist before anything arrives on them
+  else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -424,13 +440,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int u = blockIdx.x; u < args.num_tiles * args.split_k && ok; u += gridDim.x) {
+    for (int u = cta_first; u < args.num_tiles * args.split_k && ok; u += cta_stride) {
       int mt, nt;
       const int split = u / args.num_tiles, t = u - split * args.num_tiles;
       const int kb_begin = split * args.kb_per_split, kb_end = min(kb_begin + args.kb_per_split, args.num_k_blocks);
       const int bi = t / args.tiles_per_batch;
       tile_coords(args, t - bi * args.tiles_per_batch, mt, nt);
-      int a_row = bi * args.M + mt * BM, b_row = (int)(bi * args.b_rows_per_batch) + nt * C::kBBoxRows;
+      if constexpr (PAIR) mt = mt * 2 + (int)rank;          // this CTA's 128 rows of the 256-row pair tile
+      const int b_col0 = nt * BN + (PAIR ? (int)rank * (BN / 2) : 0);   // first B row (output column) this CTA loads
+      int a_row = bi * args.M + mt * BM;
+      int b_row = (int)(bi * args.b_rows_per_batch) + (PAIR ? b_col0 : nt * C::kBBoxRows);
       if (args.tile_map != nullptr) {
         const int row0 = args.tile_map[3 * mt];
         if (row0 < 0) continue;
@@ -443,24 +462,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (lane == 0) {
           uint8_t* sa_ptr = stage_base + stage * C::kStageBytes;
           uint8_t* sb_ptr = sa_ptr + C::kABytes;
-          mbar_expect_tx(&full_bar[stage], C::kStageBytes);
           constexpr int kBlockElems = 128 / C::kElemBytes;      // MN elements per 128-byte block
           constexpr int kBlockBytes = C::kBK * 128;             // one MN block: kBK K-rows x 128 bytes
+          // pairs: both CTAs' copies count on the LEADER's barrier, which expects the bytes of both
+          const uint32_t full_addr = PAIR ? mapa_shared(smem_u32(&full_bar[stage]), 0) : 0u;
+          auto load = [&](uint8_t* dst, const CUtensorMap* map, int x, int y) {
+            if constexpr (PAIR) tma_load_2d_pair(dst, map, full_addr, x, y);
+            else tma_load_2d(dst, map, &full_bar[stage], x, y);
+          };
+          if (!PAIR || rank == 0) mbar_expect_tx(&full_bar[stage], (PAIR ? 2 : 1) * C::kStageBytes);
           if (!args.a_mn) {
-            tma_load_2d(sa_ptr, &tmA, &full_bar[stage], kb * C::kBK, a_row);
+            load(sa_ptr, &tmA, kb * C::kBK, a_row);
           } else {
 #pragma unroll
             for (int blk = 0; blk < BM / kBlockElems; ++blk)
-              tma_load_2d(sa_ptr + blk * kBlockBytes, &tmA, &full_bar[stage], mt * BM + blk * kBlockElems,
-                          bi * args.K + kb * C::kBK);
+              load(sa_ptr + blk * kBlockBytes, &tmA, mt * BM + blk * kBlockElems, bi * args.K + kb * C::kBK);
           }
           if (!args.b_mn) {
-            tma_load_2d(sb_ptr, &tmB, &full_bar[stage], kb * C::kBK, b_row);
+            load(sb_ptr, &tmB, kb * C::kBK, b_row);
           } else {
 #pragma unroll
-            for (int blk = 0; blk < BN / kBlockElems; ++blk)
-              tma_load_2d(sb_ptr + blk * kBlockBytes, &tmB, &full_bar[stage], nt * BN + blk * kBlockElems,
-                          bi * args.K + kb * C::kBK);
+            for (int blk = 0; blk < (PAIR ? BN / 2 : BN) / kBlockElems; ++blk)
+              load(sb_ptr + blk * kBlockBytes, &tmB, b_col0 + blk * kBlockElems, bi * args.K + kb * C::kBK);
           }
           if constexpr (C::kGatedFwd)
             tma_load_2d(sb_ptr + C::kBBoxRows * BK_BYTES, &tmB, &full_bar[stage], kb * C::kBK,
@@ -475,7 +498,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     int stage = 0, acc = 0;
     uint32_t phase = 0, acc_phase = 0;
     bool ok = true;
-    for (int u = blockIdx.x; u < args.num_tiles * args.split_k && ok; u += gridDim.x) {
+    // pairs: only the leader issues; its MMAs and commits act on both CTAs
+    for (int u = cta_first; u < args.num_tiles * args.split_k && ok && rank == 0; u += cta_stride) {
       const int split = u / args.num_tiles, t = u - split * args.num_tiles;
       const int kb_begin = split * args.kb_per_split, kb_end = min(kb_begin + args.kb_per_split, args.num_k_blocks);
       if (args.tile_map != nullptr) {
@@ -509,10 +533,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             const uint32_t accumulate = GROUP ? (k > 0) : (kb > kb_begin || k > 0);
             const uint64_t koff_a = (uint64_t)((k * (args.a_mn ? kMnStep : (uint32_t)C::kUmmaKBytes)) >> 4);
             const uint64_t koff_b = (uint64_t)((k * (args.b_mn ? kMnStep : (uint32_t)C::kUmmaKBytes)) >> 4);
-            if constexpr (KIND == VB_KIND_F8) mma_f8_ss(d_tmem, adesc + koff_a, bdesc + koff_b, args.idesc, accumulate);
-            else mma_f16_ss(d_tmem, adesc + koff_a, bdesc + koff_b, args.idesc, accumulate);
+            if constexpr (PAIR) {
+              if constexpr (KIND == VB_KIND_F8) mma_f8_ss_pair(d_tmem, adesc + koff_a, bdesc + koff_b, args.idesc, accumulate);
+              else mma_f16_ss_pair(d_tmem, adesc + koff_a, bdesc + koff_b, args.idesc, accumulate);
+            } else {
+              if constexpr (KIND == VB_KIND_F8) mma_f8_ss(d_tmem, adesc + koff_a, bdesc + koff_b, args.idesc, accumulate);
+              else mma_f16_ss(d_tmem, adesc + koff_a, bdesc + koff_b, args.idesc, accumulate);
+            }
           }
-          tc_commit(&empty_bar[stage]);
+          if constexpr (PAIR) {                 // the stage is free in both CTAs once these MMAs retire
+            tc_commit_pair(smem_u32(&empty_bar[stage]));
+            tc_commit_pair(mapa_shared(smem_u32(&empty_bar[stage]), 1));
+          } else {
+            tc_commit(&empty_bar[stage]);
+          }
           if constexpr (GROUP) tc_commit(&tmem_full[acc]);
         }
         __syncwarp();
@@ -523,7 +557,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
       if (!ok) break;
       if constexpr (!GROUP) {
-        if (lane == 0) tc_commit(&tmem_full[acc]);
+        if (lane == 0) {
+          if constexpr (PAIR) {
+            tc_commit_pair(smem_u32(&tmem_full[acc]));
+            tc_commit_pair(mapa_shared(smem_u32(&tmem_full[acc]), 1));
+          } else {
+            tc_commit(&tmem_full[acc]);
+          }
+        }
         __syncwarp();
         if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1; }
       }
@@ -578,11 +619,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     constexpr int NCHUNK = BN / 32;
     constexpr int NOUT = (C::kGatedFwd ? NCHUNK / 2 : NCHUNK) / (C::kEpiWarps / 4);  // output chunks per tile and warp
     const int chunk0 = half * NOUT;       // first chunk of this warp
-    for (int u = blockIdx.x; u < args.num_tiles * args.split_k && ok; u += gridDim.x) {
+    for (int u = cta_first; u < args.num_tiles * args.split_k && ok; u += cta_stride) {
       int mt, nt;
       const int split = u / args.num_tiles, t = u - split * args.num_tiles;
       const int bi = t / args.tiles_per_batch;
       tile_coords(args, t - bi * args.tiles_per_batch, mt, nt);
+      if constexpr (PAIR) mt = mt * 2 + (int)rank;
       long long grow = (long long)mt * BM + row_in_tile;
       long long row_end = args.M;
       void* const out_base = advance(args.out, bi * args.out_bs, args.out_dtype);
@@ -1075,7 +1117,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if constexpr (!GROUP) {
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty[acc]), 0));   // on the leader
+          else mbar_arrive(&tmem_empty[acc]);
+        }
         if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1; }
       }
       if constexpr (EPI == VB_EPI_LINEAR && !GROUP) {
@@ -1114,10 +1159,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     while (clock64() - start < 2000000LL) { __nanosleep(256); }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  // pairs: neither CTA may leave while the other can still read its shared memory or arrive on its barriers
+  if constexpr (PAIR) cluster_sync_all();
+  else __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, C::kTmemCols);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, C::kTmemCols);
+    else tmem_dealloc(tmem_base, C::kTmemCols);
   }
 }
 
@@ -1299,13 +1347,15 @@ static int* split_flag_base() {
   return base[dev];
 }
 
-template <int KIND, int BN, bool GROUP, int EPI>
+template <int KIND, int BN, bool GROUP, int EPI, bool PAIR = false>
 static int launch(const VbGemmDesc& d, cudaStream_t stream, int split = 1) {
-  using C = Config<KIND, BN, GROUP, EPI>;
+  using C = Config<KIND, BN, GROUP, EPI, PAIR>;
   GemmArgs a{};
   a.M = d.M; a.N = d.N; a.K = d.K;
   const bool expert = d.expert_offsets != nullptr;
-  a.num_m_tiles = expert ? (d.M + BM - 1) / BM + d.num_experts : (d.M + BM - 1) / BM;
+  constexpr int kTileRows = PAIR ? 2 * BM : BM;       // rows of one scheduled tile (a CTA pair covers 256)
+  if (PAIR && (expert || d.batch > 1 || d.symmetric)) return (int)cudaErrorInvalidValue;
+  a.num_m_tiles = expert ? (d.M + BM - 1) / BM + d.num_experts : (d.M + kTileRows - 1) / kTileRows;
   constexpr int n_per_tile = C::kGatedFwd ? BN / 2 : BN;
   a.num_n_tiles = (d.N + n_per_tile - 1) / n_per_tile;
   a.num_k_blocks = (d.K + C::kBK - 1) / C::kBK;
@@ -1324,7 +1374,7 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream, int split = 1) {
   a.b_mn = d.b_mn_major ? 1 : 0;
   if ((a.a_mn || a.b_mn) && (expert || C::kGatedFwd)) return (int)cudaErrorInvalidValue;
   if ((a.a_mn || a.b_mn) && d.batch > 1 && d.K % C::kBK != 0) return (int)cudaErrorInvalidValue;
-  a.idesc = make_idesc(d.a_fmt, d.b_fmt, BM, BN, a.a_mn, a.b_mn);
+  a.idesc = make_idesc(d.a_fmt, d.b_fmt, kTileRows, BN, a.a_mn, a.b_mn);
   a.b_gate_up_offset = d.N;
   a.sa = d.sa; a.sb = d.sb;
   a.sa_row = d.sa_row; a.sa_k = d.sa_k; a.sb_row = d.sb_row; a.sb_k = d.sb_k;
@@ -1395,7 +1445,7 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream, int split = 1) {
   a.kb_per_split = a.num_k_blocks;
   if constexpr (EPI == VB_EPI_LINEAR && !GROUP) {
     // split-K needs the TMA path (reduce-add stores), an fp32 result and one problem per launch
-    if (split > 1 && a.tma_store && d.out_dtype == 0 && a.batch == 1 && a.num_tiles <= kSplitMaxTiles) {
+    if (!PAIR && split > 1 && a.tma_store && d.out_dtype == 0 && a.batch == 1 && a.num_tiles <= kSplitMaxTiles) {
       const int per = (a.num_k_blocks + split - 1) / split;
       if ((split - 1) * per < a.num_k_blocks) {
         static std::atomic<unsigned> rotation{0};
@@ -1408,12 +1458,30 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream, int split = 1) {
       }
     }
   }
-  auto kernel = gemm_kernel<KIND, BN, GROUP, EPI>;
+  auto kernel = gemm_kernel<KIND, BN, GROUP, EPI, PAIR>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return (int)e;
     configured = true;
+  }
+  if constexpr (PAIR) {
+    if (!a.tma_store) return (int)cudaErrorInvalidValue;      // the pair kernel has no other way out
+    // one cluster of two CTAs per scheduled tile, at most one cluster per pair of SMs
+    const int clusters = (int)std::min<long long>(a.num_tiles, sm_count() / 2);
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(2 * clusters);
+    config.blockDim = dim3(C::kCtaThreads);
+    config.dynamicSmemBytes = C::kSmemBytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = 2;
+    attribute.val.clusterDim.y = 1;
+    attribute.val.clusterDim.z = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&config, kernel, tmA, tmB, tmC, tmD, a);
   }
   const int grid = (int)std::min<long long>((long long)a.num_tiles * a.split_k, sm_count());
   kernel<<<grid, C::kCtaThreads, C::kSmemBytes, stream>>>(tmA, tmB, tmC, tmD, a);
@@ -1457,7 +1525,20 @@ extern "C" int vb_gemm(const VbGemmDesc* desc, cudaStream_t stream) {
     if (d.force_bn == 0 && d.N > 128 && (split128 > 1 || split256 > 1)) bn = cost256 <= cost128 ? 256 : 128;
     split = bn == 256 ? split256 : split128;
   }
+  // CTA pairs (256 x 256 tiles): per-tensor LINEAR results leaving through TMA, enough tiles to fill the clusters
+  // (measured equal to the single-CTA 128 x 256 kernel on DiT and 8192-cubed shapes, whose main loops are already
+  // power-bound: chosen only on request, i.e. by the tile tuner when it wins on a shape)
+  bool pair = d.force_bn == 512;
+  const int out_elem = d.out_dtype == 0 ? 4 : 2;
+  if (d.epilogue != VB_EPI_LINEAR || group || d.symmetric || d.expert_offsets != nullptr || d.batch > 1 || d.no_tma_store ||
+      (reinterpret_cast<uintptr_t>(d.out) & 15) != 0 || (d.ldo * out_elem) % 16 != 0 || split != 1)
+    pair = false;
+  if (d.force_bn == 512 && !pair) bn = 256;
 #define VB_LAUNCH(KIND, BNV, GROUPV, EPIV) return launch<KIND, BNV, GROUPV, EPIV>(d, stream, split)
+  if (pair) {
+    if (d.kind == VB_KIND_F8) return launch<VB_KIND_F8, 256, false, VB_EPI_LINEAR, true>(d, stream, 1);
+    return launch<VB_KIND_F16, 256, false, VB_EPI_LINEAR, true>(d, stream, 1);
+  }
   if (d.kind == VB_KIND_F8) {
     switch (d.epilogue) {
       case VB_EPI_LINEAR:

@@ -46,8 +46,9 @@ class Block(nn.Module):
         self.fc2 = Linear(mlp_ratio * width, width, **options)
         self.ada = Linear(width, 6 * width, **options)
 
-    def forward(self, x, c):
-        s1, a1, g1, s2, a2, g2 = self.ada(F.silu(c)).chunk(6, dim=-1)
+    def forward(self, x, c, activated=None):
+        """``activated`` = SiLU(c) when the caller computed it once for all blocks (it is the same for each)."""
+        s1, a1, g1, s2, a2, g2 = self.ada(F.silu(c) if activated is None else activated).chunk(6, dim=-1)
         b, n, d = x.shape
         # LayerNorm + modulate are folded into the FP8 quantiser of qkv / fc1, GELU into that of fc2 (forward)
         # and into the fc2 dgrad epilogue (backward)
@@ -121,8 +122,11 @@ class DiT(nn.Module):
         # the residual stream stays in the input's dtype (fp32 under autocast, as in experiments/dit.py:72-75):
         # the fused block kernels read and write it as stored
         x = self.input(x).flatten(2).transpose(1, 2) + self.position.to(x.dtype)
+        activated = F.silu(c)            # every block's modulation reads SiLU(c): one kernel instead of one per block
+        if x.is_cuda and torch.is_autocast_enabled("cuda"):
+            activated = activated.to(torch.get_autocast_dtype("cuda"))
         for block in self.blocks:
-            x = block(x, c)
+            x = block(x, c, activated)
         shift, scale = self.final_ada(c).chunk(2, -1)
         x = self.output(modulate(self.norm(x), shift, scale))
         b, n, _ = x.shape

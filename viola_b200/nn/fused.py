@@ -43,6 +43,11 @@ def _stream_grad(dstream, x2):
     return dstream.reshape(x2.shape).to(x2.dtype).contiguous()
 
 
+def _common(dtypes):
+    """bf16 when every consumer of the per-sample sums wants bf16 (the kernel then rounds them itself), else fp32."""
+    return torch.bfloat16 if all(d == torch.bfloat16 for d in dtypes) else torch.float32
+
+
 def _needs(ctx, positions):
     return [ctx.needs_input_grad[p] for p in positions]
 
@@ -79,7 +84,8 @@ class _NormModulateLinear(torch.autograd.Function):
         dy2 = dy.reshape(-1, layer.out_features).contiguous()
         dh, dw, db = linear_backward(layer, ctx.saved, dy2, need_input_grad=True, need_weight_grad=ctx.needs_input_grad[3],
                                      need_bias_grad=ctx.need_b)
-        dx, dshift, dscale = ops.ln_modulate_backward(dh, x2, mean, rstd, scale, ctx.shape[1], _stream_grad(dstream, x2))
+        dx, dshift, dscale = ops.ln_modulate_backward(dh, x2, mean, rstd, scale, ctx.shape[1], _stream_grad(dstream, x2),
+                                                      sums_dtype=_common(ctx.mod_dtypes))
         return (dx.view(ctx.shape), dshift.to(ctx.mod_dtypes[0]), dscale.to(ctx.mod_dtypes[1]), dw, db, None, None)
 
 
@@ -167,7 +173,8 @@ class _NormModulateMLP(torch.autograd.Function):
         dh, dw1, db1 = linear_backward(fc1, saved1, dz, need_input_grad=True, need_weight_grad=need[3],
                                        need_bias_grad=ctx.need_bias[0], grad_amax=amax)
         del dz
-        dx, dshift, dscale = ops.ln_modulate_backward(dh, x2, mean, rstd, scale, ctx.shape[1], _stream_grad(dstream, x2))
+        dx, dshift, dscale = ops.ln_modulate_backward(dh, x2, mean, rstd, scale, ctx.shape[1], _stream_grad(dstream, x2),
+                                                      sums_dtype=_common(ctx.mod_dtypes))
         return (dx.view(ctx.shape), dshift.to(ctx.mod_dtypes[0]), dscale.to(ctx.mod_dtypes[1]), dw1, db1, dw2, db2,
                 None, None, None, None)
 
@@ -245,7 +252,8 @@ class _GatedResidual(torch.autograd.Function):
     def backward(ctx, dout):
         gate, y2 = ctx.saved_tensors
         batch, tokens, width = ctx.shape
-        dy, dgate = ops.gate_residual_backward(dout.reshape(-1, width).contiguous(), gate, y2, tokens)
+        dy, dgate = ops.gate_residual_backward(dout.reshape(-1, width).contiguous(), gate, y2, tokens,
+                                               sums_dtype=gate.dtype)
         return dout, dgate.to(gate.dtype), dy.view(ctx.shape)
 
 

@@ -277,7 +277,10 @@ def _backward_in_place(layer, saved, dy, limit, need_input_grad, need_weight_gra
     if need_bias_grad:
         slot = _gradient_slot(getattr(saved, "bias_slot", None), (dy.shape[1],), torch.float32, dy.device) \
             if saved.bias_grad_dtype == torch.float32 else None
-        db_sum = slot.zero_() if slot is not None else torch.zeros(dy.shape[1], device=dy.device, dtype=torch.float32)
+        if slot is None:
+            db_sum = torch.zeros(dy.shape[1], device=dy.device, dtype=torch.float32)
+        else:                             # the engine clears all one-dimensional slots in one launch per microbatch
+            db_sum = slot if getattr(slot, "_viola_zeroed", False) else slot.zero_()
     grad_scale = layer.grad_quantizer.scale_gathered(grad_amax, bfmt, limit) if grad_amax is not None else None
     qg = _quantize_activation(layer_no_rotation(layer), dy, bfmt, None, layer.grad_quantizer, limit, row=True,
                               transposed=False, colsum=db_sum, scale=grad_scale)

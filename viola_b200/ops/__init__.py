@@ -304,7 +304,9 @@ def _gemm(a, b, out, epilogue, n_logical, *, sa=None, sb=None, layout=_NO_GROUP,
                    and expert_offsets is None and not in_place and n_logical > 128)
         signature = (int(epilogue), tuple(a.shape), tuple(b.shape), str(a.dtype), str(b.dtype), str(out.dtype), bool(a_mn),
                      bool(b_mn), int(batch), bias is not None, int(activation), out_t is not None)
-        force_bn = tuning.choose(signature, launch, lambda: out, tunable=tunable)
+        pairs = epilogue == EPI_LINEAR and batch == 1 and out.shape[0] >= 256 and n_logical >= 256
+        force_bn = tuning.choose(signature, launch, lambda: out, tunable=tunable,
+                                 candidates=(128, 256, 512) if pairs else (128, 256))
     launch(force_bn)
     _count(2 if expert_offsets is not None else 1)
     return out
@@ -806,12 +808,14 @@ def activation_quantize(z, activation, *, history=None, index=0, delayed=False, 
     return (q, qt, qscale, slope_out) if slope else (q, qt, qscale)
 
 
-def ln_modulate_backward(dh, x, mean, rstd, scale, tokens, grad_in=None):
-    """Gradients of LN + modulate: returns (dx [rows, cols] in x's dtype, dshift, dscale [samples, cols] fp32).
-    ``grad_in`` (x's shape and dtype) is added to dx: the gradient that reaches x along the residual path."""
+def ln_modulate_backward(dh, x, mean, rstd, scale, tokens, grad_in=None, sums_dtype=torch.float32):
+    """Gradients of LN + modulate: returns (dx [rows, cols] in x's dtype, dshift, dscale [samples, cols]).
+    ``grad_in`` (x's shape and dtype) is added to dx: the gradient that reaches x along the residual path.
+    ``sums_dtype``: fp32, or bf16 to get the per-sample sums (accumulated in fp32) rounded by the kernel."""
     rows, cols = x.shape
     dx = torch.empty_like(x)
-    dshift = torch.empty((rows // tokens, cols), device=x.device, dtype=torch.float32)
+    sums_dtype = sums_dtype if sums_dtype == torch.bfloat16 else torch.float32
+    dshift = torch.empty((rows // tokens, cols), device=x.device, dtype=sums_dtype)
     dscale = torch.empty_like(dshift)
     workspace, tickets = _sample_sum_workspace(x.device, rows, tokens, 2 * cols)
     _ops().ln_modulate_backward(dh, x, mean, rstd, scale, int(tokens), grad_in, dx, dshift, dscale, workspace, tickets)
@@ -829,13 +833,16 @@ def gate_residual(x, gate, y, tokens):
     return out
 
 
-def gate_residual_backward(dout, gate, y, tokens):
-    """Branch gradients of the gated residual: (dy bf16 [rows, cols], dgate fp32 [samples, cols])."""
+def gate_residual_backward(dout, gate, y, tokens, sums_dtype=torch.float32):
+    """Branch gradients of the gated residual: (dy bf16 [rows, cols], dgate [samples, cols] in ``sums_dtype``:
+    fp32, or bf16 rounded by the kernel from its fp32 sums)."""
     if not dout.is_cuda:
-        return reference.gate_residual_backward(dout, gate, y, tokens)
+        dy, dgate = reference.gate_residual_backward(dout, gate, y, tokens)
+        return dy, dgate.to(sums_dtype)
     rows, cols = dout.shape
     dy = torch.empty((rows, cols), device=dout.device, dtype=torch.bfloat16)
-    dgate = torch.empty((rows // tokens, cols), device=dout.device, dtype=torch.float32)
+    sums_dtype = sums_dtype if sums_dtype == torch.bfloat16 else torch.float32
+    dgate = torch.empty((rows // tokens, cols), device=dout.device, dtype=sums_dtype)
     workspace, tickets = _sample_sum_workspace(dout.device, rows, tokens, cols)
     _ops().gate_residual_backward(dout, gate, y, int(tokens), dy, dgate, workspace, tickets)
     _count()

@@ -97,6 +97,10 @@ class GradientState:
                         self.slots[index] = self.landing[start + target:start + target + record.numel].view(record.shape)
                 start += length
         self.claimed = [False] * len(self.records)
+        # one-dimensional slots (biases) are accumulated into by atomic column sums: cleared together, one launch per
+        # microbatch, instead of one fill per layer
+        self.vector_slots = [i for i, slot in self.slots.items() if slot.dim() == 1]
+        self.vectors_cleared = False
         self.buffer = (torch.empty(self.bucket_capacity, device=device, dtype=self.dtype)
                        if self.world > 1 and self.landing is None else None)
         self.transport = transport if (transport is not None and self.fp8_requested and self.world > 1
@@ -135,12 +139,19 @@ class GradientState:
         self.claimed[index] = True
         # a fresh view: autograd adopts a gradient tensor as ``.grad`` without copying only when nothing else
         # holds a reference to that tensor object
-        return self.slots[index].view(self.slots[index].shape)
+        slot = self.slots[index].view(self.slots[index].shape)
+        if self.vectors_cleared and slot.dim() == 1:
+            slot._viola_zeroed = True
+        return slot
 
     def begin_backward(self):
         self.in_backward = True
         self.seen = [False] * len(self.records)
         self.claimed = [False] * len(self.records)
+        self.vectors_cleared = False
+        if self.vector_slots and self.landing is not None:
+            torch._foreach_zero_([self.slots[i] for i in self.vector_slots])
+            self.vectors_cleared = True
         self.remaining = self.piece_counts.copy()
         self.next_bucket = 0
         if self.transport is not None and self.shard:

@@ -165,12 +165,14 @@ def search(signature, run, output, *, candidates=CANDIDATES, measure=measure_cud
     return chosen
 
 
-def choose(signature, run, output, *, tunable=True):
-    """Tile width for a GEMM call: the recorded choice, or a search when tuning is on and timing is possible."""
+def choose(signature, run, output, *, tunable=True, candidates=CANDIDATES):
+    """Tile width for a GEMM call: the recorded choice, or a search when tuning is on and timing is possible.
+    ``candidates``: 128 and 256 (columns of a single-CTA tile) and, where the kernel has it, 512 = a 256 x 256 tile
+    computed by a CTA pair."""
     found = recall(signature)
     if found is not None:
         return found
     if not (_enabled and tunable) or not torch.cuda.is_available() or torch.cuda.is_current_stream_capturing():
         return 0
     with _lock:
-        return search(signature, run, output)
+        return search(signature, run, output, candidates=candidates)

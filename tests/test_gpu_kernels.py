@@ -504,6 +504,40 @@ def test_mxfp8_linear_runs_on_the_block_scaled_path_and_matches_cpu():
     assert rel_l2(layer.weight.grad.cpu(), clone.weight.grad) < 2e-2
 
 
+@pytest.mark.parametrize("head_dim", [72, 64, 128, 40])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_attention_forward_matches_the_fp32_softmax(head_dim, dtype):
+    """The 256-token attention kernel against softmax(Q K^T / sqrt(D)) V in fp32, including the log-sum-exp rows that
+    the backward consumes; scores are scaled up so the softmax is far from uniform."""
+    torch.manual_seed(head_dim)
+    batch, heads = 3, 5
+    qkv = (torch.randn(batch, 256, 3, heads, head_dim, device=dev()) * 1.5).to(dtype)
+    out, lse = ops.attention_forward(qkv)
+    want, want_lse = ref.attention_forward(qkv, head_dim ** -0.5)
+    ops.check_status()
+    assert out.shape == (batch, 256, heads, head_dim) and lse.shape == (batch, heads, 256)
+    assert rel_l2(out, want) < (8e-3 if dtype == torch.bfloat16 else 2e-3)
+    assert (lse - want_lse).abs().max() < 2e-3
+    again, _ = ops.attention_forward(qkv)
+    assert torch.equal(out, again)
+
+
+def test_packed_attention_gradients_match_the_library_path():
+    from viola_b200.nn import attention
+    torch.manual_seed(3)
+    qkv = torch.randn(2, 256, 3, 4, 72, device=dev(), dtype=torch.bfloat16, requires_grad=True)
+    weight = torch.randn(2, 256, 4 * 72, device=dev(), dtype=torch.bfloat16)
+    (attention.packed_attention(qkv) * weight).sum().backward()
+    native = qkv.grad.clone()
+    qkv.grad = None
+    attention._state["native"] = False
+    try:
+        (attention.packed_attention(qkv) * weight).sum().backward()
+    finally:
+        attention._state["native"] = True
+    assert rel_l2(native, qkv.grad) < 1e-2
+
+
 # ------------------------------------------------------------------------------------------------ memory-safety substitutes
 def _guarded(shape, dtype, pad=4096):
     """A tensor of ``shape`` carved out of a larger buffer whose bytes before and after it are a known pattern."""

@@ -21,7 +21,7 @@ CSRC = ROOT / "csrc"
 OBJ = ROOT / "build"
 TARGET = ROOT / "_C.so"
 
-CUDA_SOURCES = ["quant.cu", "gemm_sm100.cu", "mxfp8_gemm_sm100.cu", "optim.cu", "codec.cu", "comm.cu", "fused.cu", "multi.cu", "noalloc.cu"]
+CUDA_SOURCES = ["quant.cu", "gemm_sm100.cu", "mxfp8_gemm_sm100.cu", "attention_sm100.cu", "optim.cu", "codec.cu", "comm.cu", "fused.cu", "multi.cu", "noalloc.cu"]
 CPP_SOURCES = ["bindings.cpp"]
 
 NVCC_FLAGS = [

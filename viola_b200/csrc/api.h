@@ -177,6 +177,12 @@ int vb_gate_residual_backward(const void* dout, int dout_dtype, const void* gate
                               int rows, int cols, int tokens, void* dy, void* dgate, int sums_bf16, float* workspace,
                               long long workspace_floats, unsigned int* tickets, int ticket_count, cudaStream_t stream);
 
+// ---- attention forward for 256-token sequences (tcgen05; one CTA per sample and head) ------------
+// qkv: [batch, 256, 3, heads, head_dim] contiguous (dtype 1 = bf16, 2 = fp16), head_dim a multiple of 8 in [16, 128];
+// out: [batch, 256, heads, head_dim]; lse: [batch, heads, 256] fp32 = log(sum(exp(score * scale))) per query (optional)
+int vb_attention_forward(const void* qkv, int dtype, int batch, int tokens, int heads, int head_dim, float scale,
+                         void* out, float* lse, int* status, cudaStream_t stream);
+
 // ---- Hadamard-64 rotation --------------------------------------------------------
 int vb_hadamard64(const void* x, int dtype, int rows, int cols, void* out, cudaStream_t stream);
 

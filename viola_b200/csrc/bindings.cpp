@@ -177,6 +177,18 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t epilogue, int64_
   check(vb_gemm(&d, stream()), "gemm");
 }
 
+void attention_forward(const Tensor& qkv, Tensor out, Tensor lse, double scale, const OptTensor& status) {
+  TORCH_CHECK(qkv.is_cuda() && qkv.dim() == 5 && qkv.size(2) == 3 && qkv.is_contiguous(), "qkv must be [B, T, 3, H, D]");
+  TORCH_CHECK(qkv.scalar_type() == at::kBFloat16 || qkv.scalar_type() == at::kHalf);
+  TORCH_CHECK(out.is_contiguous() && out.scalar_type() == qkv.scalar_type() && out.numel() == qkv.numel() / 3);
+  TORCH_CHECK(lse.is_contiguous() && lse.scalar_type() == at::kFloat && lse.numel() == qkv.size(0) * qkv.size(1) * qkv.size(3));
+  c10::cuda::CUDAGuard guard(qkv.device());
+  check(vb_attention_forward(qkv.data_ptr(), qkv.scalar_type() == at::kBFloat16 ? 1 : 2, (int)qkv.size(0), (int)qkv.size(1),
+                             (int)qkv.size(3), (int)qkv.size(4), (float)scale, out.data_ptr(), lse.data_ptr<float>(),
+                             (int*)ptr(status), stream()),
+        "attention_forward");
+}
+
 void momentum_1d(const Tensor& grad, const Tensor& old_q, const Tensor& old_scale, Tensor new_q, Tensor new_scale,
                  Tensor update, int64_t tile, double beta, double inv_loss_scale, bool nesterov, bool stochastic,
                  int64_t step, int64_t key) {
@@ -633,6 +645,7 @@ TORCH_LIBRARY(viola_b200, m) {
   m.def("multi_writeback", &multi_writeback);
   m.def("mx_pack_scales", &mx_pack_scales);
   m.def("mx_gemm", &mx_gemm);
+  m.def("attention_forward", &attention_forward);
   m.def("signal", &signal);
   m.def("wait_flags", &wait_flags);
   m.def("gather_pull", &gather_pull);

@@ -336,7 +336,9 @@ struct Config {
   // With K of about a thousand a 128 x 256 tile's MMAs take about as long as four warps need to drain it (one
   // warp per scheduler, so every TMEM load and shared-memory store latency is exposed): the per-tensor LINEAR
   // kernels use eight epilogue warps, two per TMEM lane quadrant, each draining half of the tile's columns.
-  static constexpr int kEpiWarps = (EPI == VB_EPI_LINEAR && !GROUP) ? 8 : 4;
+  // Group-scaled LINEAR: the promotion of every K-block (one FMA per accumulator element) is the epilogue warps'
+  // whole job, so halving the columns per warp halves the time a K-block's accumulator stays occupied.
+  static constexpr int kEpiWarps = EPI == VB_EPI_LINEAR ? 8 : 4;
   static constexpr int kStoreBytes = kTmaStore ? kEpiWarps * 4096 : 0;   // per warp: 2 x (32 rows x 64 B) or 32 rows x 128 B
   // AXPBY and ACT_BWD epilogues (16-bit output, optional 16-bit [M, N] operand: the residual / the activation
   // slope) run through a ring of 128-row x 32-column slabs in shared memory, one per output chunk: the
@@ -357,11 +359,12 @@ struct Config {
   static constexpr int kCtaThreads = kSlabLoader ? kThreads + 32 : 64 + 32 * kEpiWarps;   // a seventh warp feeds the slab ring
   static constexpr int kEpiSlabBytes = BM * 64;
   static constexpr int kEpiBytes = kSlabRing ? kEpiSlabs * kEpiSlabBytes : 0;
-  static constexpr int kStages = PAIR ? 6 : (BN == 256) ? 4 : (BN == 128 ? ((kGatedBwd && !GROUP) ? 5 : 6) : 8);
+  static constexpr int kStages =
+      PAIR ? 6 : (BN == 256) ? 4 : (BN == 128 ? (((kGatedBwd && !GROUP) || (GROUP && kTmaStore)) ? 5 : 6) : 8);
   static constexpr int kAcc = GROUP ? (512 / BN > 4 ? 4 : 512 / BN) : 2;
   static constexpr int kTmemCols = kAcc * BN;
   static constexpr int kBarrierBytes = 1024;
-  static constexpr int kSbStage = GROUP ? 4 * 2 * BN * (int)sizeof(float) : 0;  // per-warp staged B scales
+  static constexpr int kSbStage = GROUP ? 4 * 2 * BN * (int)sizeof(float) : 0;  // per-warp staged B scales (two buffers)
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kSbStage + kStoreBytes + kEpiBytes + 1024;
   static_assert(kSmemBytes <= 232448, "dynamic shared memory limit of sm_100");
   static constexpr int kElemBytes = KIND == VB_KIND_F8 ? 1 : 2;
@@ -656,10 +659,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
       }
 
-      float accr[GROUP ? BN : 1];
+      constexpr int NW = NCHUNK / (C::kEpiWarps / 4);   // accumulator chunks this warp promotes (from chunk0 on)
+      float accr[GROUP ? NW * 32 : 1];
       if constexpr (GROUP) {
 #pragma unroll
-        for (int j = 0; j < BN; ++j) accr[j] = 0.f;
+        for (int j = 0; j < NW * 32; ++j) accr[j] = 0.f;
         // Scales are fetched one K-block ahead (global loads whose latency would otherwise sit between the
         // accumulator wait and the first FMA of every K-block), and the TMEM load of chunk c + 1 is in flight
         // while chunk c is promoted.
@@ -675,38 +679,38 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                   : n0 + c * 32;
           return (long long)(min(brow, limit_rows - 1) + expert * args.expert_rows);
         };
-        float next_sa = 0.f, next_sb[NCHUNK];
+        float next_sa = 0.f, next_sb[NW];
         auto fetch_scales = [&](int kb) {
           const int ks = kb >> args.k_shift;
           next_sa = row_ok ? args.sa[grow * args.sa_row + (long long)ks * args.sa_k] : 0.f;
 #pragma unroll
-          for (int c = 0; c < NCHUNK; ++c) {
-            const long long brow = per_col ? sb_column(c * 32 + lane) : sb_chunk(c);
+          for (int c = 0; c < NW; ++c) {
+            const long long brow = per_col ? sb_column((chunk0 + c) * 32 + lane) : sb_chunk(chunk0 + c);
             next_sb[c] = brow >= 0 ? args.sb[(brow >> args.sb_shift) * args.sb_row + (long long)ks * args.sb_k] : 0.f;
           }
         };
         fetch_scales(0);
         for (int kb = 0; kb < args.num_k_blocks; ++kb) {
           const float sa_v = next_sa;
-          float sb_v[NCHUNK];
+          float sb_v[NW];
 #pragma unroll
-          for (int c = 0; c < NCHUNK; ++c) sb_v[c] = next_sb[c];
-          float* sbs = sb_stage + ((warp - 2) * 2 + (kb & 1)) * BN;  // private to this warp: no CTA barrier
+          for (int c = 0; c < NW; ++c) sb_v[c] = next_sb[c];
+          float* sbs = sb_stage + (epi * 2 + (kb & 1)) * (NW * 32);  // private to this warp: no CTA barrier
           if (per_col) {
 #pragma unroll
-            for (int c = 0; c < NCHUNK; ++c) sbs[c * 32 + lane] = sb_v[c];
+            for (int c = 0; c < NW; ++c) sbs[c * 32 + lane] = sb_v[c];
             __syncwarp();
           }
           ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full[acc], acc_phase, abort_flag, args.status, kTimeoutTmemFull));
           if (!ok) break;
           tc_fence_after_sync();
           uint32_t r[2][32];
-          tmem_ld_32x32(tmem_base + lane_addr + acc * BN, r[0]);
+          tmem_ld_32x32(tmem_base + lane_addr + acc * BN + chunk0 * 32, r[0]);
           if (kb + 1 < args.num_k_blocks) fetch_scales(kb + 1);       // in flight under the promotion below
 #pragma unroll
-          for (int c = 0; c < NCHUNK; ++c) {
+          for (int c = 0; c < NW; ++c) {
             tmem_ld_wait();
-            if (c + 1 < NCHUNK) tmem_ld_32x32(tmem_base + lane_addr + acc * BN + (c + 1) * 32, r[(c + 1) & 1]);
+            if (c + 1 < NW) tmem_ld_32x32(tmem_base + lane_addr + acc * BN + (chunk0 + c + 1) * 32, r[(c + 1) & 1]);
             if (per_col) {
 #pragma unroll
               for (int j = 0; j < 32; ++j)

@@ -437,6 +437,29 @@ def mx_gemm(a, b, sfa, sfb, *, out_dtype, bias=None, out=None):
     return out
 
 
+def attention_eligible(qkv):
+    """Can :func:`attention_forward` take this packed projection ([B, 256, 3, H, D], 16-bit, D % 8 == 0, D <= 128)?"""
+    return (qkv.is_cuda and qkv.dim() == 5 and qkv.shape[1] == 256 and qkv.shape[2] == 3
+            and qkv.dtype in (torch.bfloat16, torch.float16) and qkv.shape[4] % 8 == 0 and 16 <= qkv.shape[4] <= 128
+            and qkv.is_contiguous())
+
+
+def attention_forward(qkv, scale=None):
+    """softmax(Q K^T * scale) V for a packed ``qkv`` [B, 256, 3, H, D]: returns (out [B, 256, H, D], lse [B, H, 256] fp32).
+
+    One tcgen05 kernel, one CTA per (sample, head): both 128 x 256 score tiles stay in tensor memory, the
+    probabilities go back to the tensor core through shared memory.  ``lse`` = log(sum(exp(score * scale)))."""
+    scale = qkv.shape[-1] ** -0.5 if scale is None else float(scale)
+    if not qkv.is_cuda:
+        return reference.attention_forward(qkv, scale)
+    batch, tokens, _, heads, head_dim = qkv.shape
+    out = torch.empty((batch, tokens, heads, head_dim), device=qkv.device, dtype=qkv.dtype)
+    lse = torch.empty((batch, heads, tokens), device=qkv.device, dtype=torch.float32)
+    _ops().attention_forward(qkv, out, lse, scale, status_word(qkv.device))
+    _count()
+    return out, lse
+
+
 def _mx_eligible(a, b, ga, gb):
     return (tuple(ga) == (1, 32) and gb[1] == 32 and gb[0] & (gb[0] - 1) == 0 and a.shape[1] % 16 == 0
             and a.dtype in FP8_DTYPES and b.dtype in FP8_DTYPES and a.is_contiguous() and b.is_contiguous())

@@ -460,6 +460,15 @@ def gate_residual_backward(dout, gate, y, tokens):
     return dy, dgate
 
 
+def attention_forward(qkv, scale):
+    """Oracle of the attention kernel: fp32 softmax(Q K^T * scale) V on a packed [B, T, 3, H, D] projection."""
+    q, k, v = (t.float().transpose(1, 2) for t in qkv.unbind(2))            # [B, H, T, D]
+    scores = torch.matmul(q, k.transpose(-1, -2)) * scale
+    lse = torch.logsumexp(scores, dim=-1)
+    out = torch.matmul(torch.softmax(scores, dim=-1), v).transpose(1, 2)    # [B, T, H, D]
+    return out.to(qkv.dtype).contiguous(), lse
+
+
 def mx_gemm(a, b, sa, sb, *, out_dtype, bias=None):
     """Oracle of the hardware block-scaled GEMM: ``sa`` [M, K/32], ``sb`` [N, K/32] hold UE8M0 exponent bytes."""
     def decode(codes, exponents):

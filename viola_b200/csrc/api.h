@@ -213,6 +213,16 @@ int vb_reduce_accumulate_fp8(const float* bucket, long long n, int tile, int fmt
                              const VbPeerTable* peers, long long ack_offset, const int* generation, float* accum,
                              unsigned int* counter, long long wait_clocks, int max_blocks, int* status,
                              cudaStream_t stream);
+// Path 1 over a device table of 64-byte rows {src, n, codes, scales, accum, slot_stride, scales_offset, reserved}
+// (prefix: int64[buckets + 1] prefix sums of tiles): one launch pushes all buckets owned elsewhere and raises
+// flag[rank] at every peer; one launch accumulates all owned buckets after every peer's flag and acknowledges.
+int vb_reduce_push_many(const void* table, const long long* prefix, int buckets, long long total_tiles, int tile, int fmt,
+                        const VbPeerTable* peers, long long flag_offset, const int* ack_flags, const int* generation,
+                        unsigned int* counter, long long wait_clocks, int max_blocks, int* status, cudaStream_t stream);
+int vb_reduce_accumulate_many(const void* table, const long long* prefix, int buckets, long long total_tiles, int tile,
+                              int fmt, const VbPeerTable* peers, const int* flags, long long ack_offset,
+                              const int* generation, unsigned int* counter, long long wait_clocks, int max_blocks,
+                              int* status, cudaStream_t stream);
 // Path 2: in-place FP8 all-reduce with a second quantisation of the partial sums.
 int vb_allreduce_requant_fp8(float* value, long long n, int tile, int fmt, const VbPeerTable* peers,
                              long long a2a_offset, long long gather_offset, long long slot,

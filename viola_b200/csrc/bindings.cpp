@@ -401,6 +401,30 @@ void reduce_accumulate_fp8(const Tensor& bucket, int64_t tile, int64_t fmt, int6
         "reduce_accumulate_fp8");
 }
 
+void reduce_many(const Tensor& table, const Tensor& prefix, int64_t total_tiles, int64_t tile, int64_t fmt, at::IntArrayRef heaps,
+                 int64_t rank, bool accumulate, int64_t flags, int64_t flag_offset, const Tensor& generation, Tensor counter,
+                 int64_t wait_clocks, int64_t max_blocks, Tensor status) {
+  // push: ``flags`` = local acknowledgement flags, ``flag_offset`` = heap offset of the data flags at the owners;
+  // accumulate: ``flags`` = local data flags, ``flag_offset`` = heap offset of the acknowledgement flags at the sources
+  TORCH_CHECK(table.is_cuda() && table.is_contiguous() && prefix.is_cuda() && prefix.scalar_type() == at::kLong);
+  const int64_t buckets = prefix.numel() - 1;
+  TORCH_CHECK(buckets >= 0 && table.numel() * table.element_size() >= buckets * 64);
+  c10::cuda::CUDAGuard guard(table.device());
+  VbPeerTable peers = peer_table(heaps, rank);
+  if (accumulate)
+    check(vb_reduce_accumulate_many(table.data_ptr(), (const long long*)prefix.data_ptr(), (int)buckets, total_tiles, (int)tile,
+                                    (int)fmt, &peers, reinterpret_cast<const int*>(flags), flag_offset,
+                                    (const int*)generation.data_ptr(), (unsigned int*)counter.data_ptr(), wait_clocks,
+                                    (int)max_blocks, (int*)status.data_ptr(), stream()),
+          "reduce_accumulate_many");
+  else
+    check(vb_reduce_push_many(table.data_ptr(), (const long long*)prefix.data_ptr(), (int)buckets, total_tiles, (int)tile,
+                              (int)fmt, &peers, flag_offset, reinterpret_cast<const int*>(flags),
+                              (const int*)generation.data_ptr(), (unsigned int*)counter.data_ptr(), wait_clocks,
+                              (int)max_blocks, (int*)status.data_ptr(), stream()),
+          "reduce_push_many");
+}
+
 void allreduce_requant_fp8(Tensor value, int64_t tile, int64_t fmt, at::IntArrayRef heaps, int64_t rank, int64_t a2a_offset,
                            int64_t gather_offset, int64_t slot, int64_t a2a_flag_offset, int64_t gather_flag_offset,
                            int64_t generation, Tensor counters, int64_t wait_clocks, int64_t max_blocks, Tensor status) {
@@ -646,6 +670,7 @@ TORCH_LIBRARY(viola_b200, m) {
   m.def("mx_pack_scales", &mx_pack_scales);
   m.def("mx_gemm", &mx_gemm);
   m.def("attention_forward", &attention_forward);
+  m.def("reduce_many", &reduce_many);
   m.def("signal", &signal);
   m.def("wait_flags", &wait_flags);
   m.def("gather_pull", &gather_pull);

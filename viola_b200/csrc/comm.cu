@@ -185,6 +185,85 @@ reduce_accumulate_kernel(const float* __restrict__ bucket, long long n, int fmt,
     st_release_sys(reinterpret_cast<int*>(peers.heap[threadIdx.x] + ack_offset), generation);
 }
 
+// Path 1 over a table of buckets: one launch pushes every bucket this rank does not own, one launch accumulates
+// every bucket it owns.  Used when gradients are reduced once per optimizer step from a rank-local sum: the
+// rendezvous cost (flag round trips, fences, launches) is then paid twice per step instead of twice per bucket.
+struct ReduceDesc {            // 64 bytes per bucket
+  const float* src;            // this rank's fp32 values of the bucket
+  long long n;                 // elements
+  uint8_t* codes;              // push: this rank's slot in the owner's heap; accumulate: slot of source rank 0 (local)
+  float* scales;               // push: scales of that slot; accumulate: unused
+  float* accum;                // accumulate: the owner's fp32 accumulator slice
+  long long slot_stride;       // accumulate: bytes between the slots of consecutive source ranks
+  long long scales_offset;     // accumulate: byte offset of the scales inside a slot
+  long long reserved;
+};
+
+// bucket of global tile t: largest b with prefix[b] <= t (prefix[0] = 0, prefix[buckets] = total tiles)
+__device__ __forceinline__ int bucket_of_tile(const long long* __restrict__ prefix, int buckets, long long t) {
+  int lo = 0, hi = buckets - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (prefix[mid] <= t) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+template <int TILE>
+__global__ void __launch_bounds__(256)
+reduce_push_many_kernel(const ReduceDesc* __restrict__ table, const long long* __restrict__ prefix, int buckets, int fmt,
+                        Peers peers, long long flag_offset, const int* ack_flags, const int* generation_ptr,
+                        unsigned int* counter, long long budget, int* status) {
+  const int generation = *generation_ptr;
+  // every owner must have consumed the previous generation of its slots before they are overwritten
+  const bool ready = generation <= 1 || block_wait_flags(ack_flags, peers.world, peers.rank, generation - 1, budget, status);
+  const long long tiles = prefix[buckets];
+  const int lane = threadIdx.x & 31;
+  if (ready)
+    for (long long t = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); t < tiles; t += (long long)gridDim.x * 8) {
+      const int b = bucket_of_tile(prefix, buckets, t);
+      const ReduceDesc d = table[b];
+      const long long local = t - prefix[b];
+      pack_tile<TILE>(d.src, local * TILE, d.n, fmt, d.codes + local * TILE, d.scales + local, lane);
+    }
+  if (last_block_done(counter, ready) && threadIdx.x < peers.world && (int)threadIdx.x != peers.rank)
+    st_release_sys(reinterpret_cast<int*>(peers.heap[threadIdx.x] + flag_offset) + peers.rank, generation);
+}
+
+template <int TILE>
+__global__ void __launch_bounds__(256)
+reduce_accumulate_many_kernel(const ReduceDesc* __restrict__ table, const long long* __restrict__ prefix, int buckets,
+                              int fmt, Peers peers, const int* flags, long long ack_offset, const int* generation_ptr,
+                              unsigned int* counter, long long budget, int* status) {
+  const int generation = *generation_ptr;
+  const bool ready = block_wait_flags(flags, peers.world, peers.rank, generation, budget, status);
+  const long long tiles = prefix[buckets];
+  const int lane = threadIdx.x & 31;
+  for (long long t = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); ready && t < tiles; t += (long long)gridDim.x * 8) {
+    const int b = bucket_of_tile(prefix, buckets, t);
+    const ReduceDesc d = table[b];
+    const long long local = t - prefix[b];
+    float own[TILE / 32], result[TILE / 32];
+    load_tile<TILE>(d.src, local * TILE, d.n, lane, own);
+    fake_quantize_tile<TILE>(own, fmt);
+#pragma unroll
+    for (int e = 0; e < TILE / 32; ++e) result[e] = 0.f;
+    for (int r = 0; r < peers.world; ++r) {   // ascending source rank, fp32
+      if (r == peers.rank) {
+#pragma unroll
+        for (int e = 0; e < TILE / 32; ++e) result[e] += own[e];
+      } else {
+        const uint8_t* slot = d.codes + (long long)r * d.slot_stride;
+        const float scale = reinterpret_cast<const float*>(slot + d.scales_offset)[local];
+        accumulate_tile<TILE>(slot + local * TILE, scale, fmt, lane, result);
+      }
+    }
+    store_tile<TILE>(d.accum, local * TILE, d.n, lane, result, true);
+  }
+  if (last_block_done(counter, ready) && threadIdx.x < peers.world && (int)threadIdx.x != peers.rank)
+    st_release_sys(reinterpret_cast<int*>(peers.heap[threadIdx.x] + ack_offset) + peers.rank, generation);
+}
+
 // ------------------------------------------------------------------------------------------
 // path 2
 // ------------------------------------------------------------------------------------------
@@ -606,6 +685,32 @@ extern "C" int vb_reduce_accumulate_fp8(const float* bucket, long long n, int ti
   VB_TILE_SWITCH(tile, (reduce_accumulate_kernel<T><<<grid, 256, 0, stream>>>(bucket, n, fmt, (const uint8_t*)recv, slot_stride,
                                                                              scales_offset, flags, make_peers(peers), ack_offset,
                                                                              generation, accum, counter, wait_clocks, status)));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vb_reduce_push_many(const void* table, const long long* prefix, int buckets, long long total_tiles, int tile,
+                                   int fmt, const VbPeerTable* peers, long long flag_offset, const int* ack_flags,
+                                   const int* generation, unsigned int* counter, long long wait_clocks, int max_blocks,
+                                   int* status, cudaStream_t stream) {
+  if (buckets < 0 || total_tiles < 0) return 0;      // an empty table still raises this rank's flag at every peer
+  const int grid = blocks_for(total_tiles, max_blocks);
+  wait_generation_kernel<<<1, 32, 0, stream>>>(ack_flags, peers->world, peers->rank, generation, -1, wait_clocks, status);
+  VB_TILE_SWITCH(tile, (reduce_push_many_kernel<T><<<grid, 256, 0, stream>>>(
+                           reinterpret_cast<const ReduceDesc*>(table), prefix, buckets, fmt, make_peers(peers), flag_offset,
+                           ack_flags, generation, counter, wait_clocks, status)));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vb_reduce_accumulate_many(const void* table, const long long* prefix, int buckets, long long total_tiles,
+                                         int tile, int fmt, const VbPeerTable* peers, const int* flags, long long ack_offset,
+                                         const int* generation, unsigned int* counter, long long wait_clocks, int max_blocks,
+                                         int* status, cudaStream_t stream) {
+  if (buckets < 0 || total_tiles < 0) return 0;      // an empty table still waits and acknowledges
+  const int grid = blocks_for(total_tiles, max_blocks);
+  wait_generation_kernel<<<1, 32, 0, stream>>>(flags, peers->world, peers->rank, generation, 0, wait_clocks, status);
+  VB_TILE_SWITCH(tile, (reduce_accumulate_many_kernel<T><<<grid, 256, 0, stream>>>(
+                           reinterpret_cast<const ReduceDesc*>(table), prefix, buckets, fmt, make_peers(peers), flags,
+                           ack_offset, generation, counter, wait_clocks, status)));
   return (int)cudaGetLastError();
 }
 

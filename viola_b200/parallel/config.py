@@ -9,6 +9,10 @@ blocks}``, ``precision{master_weight_dtype, gradient_dtype, master_rounding, mas
 ``"p2p"`` or ``"nccl"`` — and ``communication.overlap``: true runs the gradient reduction on a side stream bucket by
 bucket while backward is still producing gradients; false (default) runs it once backward is done, with kernels
 that take the whole GPU (measured faster at 2-8 GPUs: the narrow overlapped kernels cost more than they hide).
+``communication.reduce_once`` (default true): with sharded gradients every microbatch adds its gradients into a
+rank-local fp32 sum and the owners receive that sum once per optimizer step; false sends every microbatch's
+gradients to the owners as the reference does (viola/distributed/gradients.py:86-125), which saves one
+gradient-sized buffer per rank and costs one reduction per accumulation step.
 ``sharding.resident`` (``"auto"`` / true / false) keeps the gathered copy of sharded parameters allocated between
 uses when it is small next to the device memory.
 """
@@ -52,7 +56,7 @@ def read_config(config=None):
                       "master_rounding": policy["master_rounding"],
                       "master_rounding_seed": policy["master_rounding_seed"]},
         "communication": {"dtype": None, "bucket_mb": 25, "fp8_format": "e4m3", "fp8_tile_size": 256,
-                          "backend": "auto", "overlap": False},
+                          "backend": "auto", "overlap": False, "reduce_once": True},
         "ema": {"decay": 0, "dtype": "fp32"},
     }
     for key, value in supplied.items():

@@ -27,7 +27,8 @@ from .fp8 import FP8Communication
 
 class GradientState:
     def __init__(self, store, *, gradient_dtype, communication_dtype=None, bucket_mb=25, fp8_format="e4m3",
-                 fp8_tile_size=256, shard=False, defer_reduction=False, transport=None, monitor=None, landing=True):
+                 fp8_tile_size=256, shard=False, defer_reduction=False, transport=None, monitor=None, landing=True,
+                 reduce_once=True):
         self.store = store
         self.monitor = monitor
         self.mailbox = transport          # per-step usage / status exchange, whatever moves the gradients
@@ -96,6 +97,19 @@ class GradientState:
                         record = self.records[index]
                         self.slots[index] = self.landing[start + target:start + target + record.numel].view(record.shape)
                 start += length
+        # Sharded gradients, reduced once per optimizer step: every microbatch adds its landing buffer into a
+        # rank-local fp32 sum (one launch), and the step sends that sum to the owners.  The reduction moves the same
+        # bytes whatever the microbatch size, so doing it per microbatch costs the same again for every accumulation
+        # step; the price is one more buffer of the gradients' size on every rank.
+        self.once = bool(reduce_once) and self.shard and self.landing is not None
+        self.local_sum = torch.zeros_like(self.landing) if self.once else None
+        self.bucket_sum = []
+        self.pending_local = False
+        if self.once:
+            start = 0
+            for _, _, length in self.buckets:
+                self.bucket_sum.append(self.local_sum[start:start + length])
+                start += length
         self.claimed = [False] * len(self.records)
         # one-dimensional slots (biases) are accumulated into by atomic column sums: cleared together, one launch per
         # microbatch, instead of one fill per layer
@@ -154,7 +168,7 @@ class GradientState:
             self.vectors_cleared = True
         self.remaining = self.piece_counts.copy()
         self.next_bucket = 0
-        if self.transport is not None and self.shard:
+        if self.transport is not None and self.shard and not self.once:
             self.transport.begin_microbatch()
         if self.store.sharder is not None:
             self.store.sharder.begin_backward()
@@ -168,7 +182,7 @@ class GradientState:
             slot = self.slots[index]
             if gradient.data_ptr() != slot.data_ptr():        # produced elsewhere (torch layers, tied weights)
                 slot.copy_(gradient.view(slot.shape))
-            if self.shard and not self.defer_reduction:
+            if self.shard and not self.defer_reduction and not self.once:
                 self._drain()
         elif self.shard:
             self.pending[index] = gradient.contiguous().view(-1)
@@ -240,8 +254,41 @@ class GradientState:
                     self.slots[index].zero_()
         self.accumulator.add_(self.landing)
 
+    def _sum_landed(self):
+        """Add this microbatch's gradients to the rank-local sum that the step will reduce."""
+        if not all(self.seen):
+            for index, seen in enumerate(self.seen):
+                if not seen and index in self.slots:
+                    self.slots[index].zero_()             # unused on this rank in this microbatch: contributes zeros
+        self.local_sum.add_(self.landing)
+        self.pending_local = True
+
+    def _reduce_summed(self):
+        """Send the rank-local sums of all buckets to their owners (once per optimizer step)."""
+        if self.transport is not None:
+            # one-sided kernels over a table of buckets: one launch pushes everything owned elsewhere, one launch
+            # accumulates everything owned here (two rendezvous per step instead of two per bucket)
+            self.transport.begin_microbatch()
+            self.transport.reduce_all(self.bucket_sum)
+            self.transport.synchronize()
+            self.local_sum.zero_()
+            self.pending_local = False
+            return
+        for bucket_index, (owner, _, length) in enumerate(self.buckets):
+            buffer = self.bucket_sum[bucket_index]
+            if self.fp8 is not None:
+                self.fp8.reduce(buffer, owner)
+            else:
+                dist.reduce(buffer, dst=self.store.global_ranks[owner], group=self.group)
+            if self.rank == owner:
+                self.bucket_slices[bucket_index].add_(buffer)
+        self.local_sum.zero_()
+        self.pending_local = False
+
     def finish_backward(self):
-        if self.shard:
+        if self.once:
+            self._sum_landed()
+        elif self.shard:
             self._drain(final=True)
         elif self.landing is not None:
             self._accumulate_landed()
@@ -285,6 +332,8 @@ class GradientState:
     @torch.no_grad()
     def reduce(self, divisor):
         """Agree on which parameters were used anywhere, finish replicated reductions, normalise."""
+        if self.once and self.pending_local:
+            self._reduce_summed()
         active = self._agree_on_usage()
         if self.world > 1 and not self.shard:
             for bucket in self.bucket_slices:          # bucket-ordered accumulator: reduce in place, no staging
@@ -315,8 +364,13 @@ class GradientState:
         """A replayed graph runs no Python hooks: restore the bookkeeping those hooks would have done."""
         for index in marks:
             self.used[index] = True
+        if self.once:
+            self.pending_local = True
 
     @torch.no_grad()
     def zero_grad(self):
         self.accumulator.zero_()
+        if self.once and self.pending_local:
+            self.local_sum.zero_()
+            self.pending_local = False
         self.used = [False] * len(self.records)

@@ -57,7 +57,9 @@ class DistributedState:
                                        bucket_mb=wire["bucket_mb"], fp8_format=wire["fp8_format"],
                                        fp8_tile_size=wire["fp8_tile_size"], shard=self.sharding["gradients"],
                                        defer_reduction=after_backward, transport=transport, monitor=self.monitor,
-                                       landing=wire.get("gradient_slots", True))
+                                       landing=wire.get("gradient_slots", True),
+                                       reduce_once=wire.get("reduce_once", True)
+                                       and not (transport is not None and transport.overlap))
         for position, record in enumerate(self.parameters.records):
             self.gradients.bind(position, record.parameter)
         if transport is not None:

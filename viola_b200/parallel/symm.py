@@ -170,6 +170,9 @@ class PeerTransport:
     def finalize_gradients(self):
         self.reduce_flag_offset = self.flags("reduce", max(1, self._max_owned) * self.world)
         self.ack_flag_offset = self.flags("ack", max(1, len(self.buckets)))
+        self.many_flag_offset = self.flags("reduce_all", self.world)
+        self.many_ack_offset = self.flags("ack_all", self.world)
+        self._many = None
 
     def next_staging(self):
         """A staging buffer whose previous communication has finished (stream-ordered, no host wait)."""
@@ -225,6 +228,44 @@ class PeerTransport:
                 event.record(stream)
                 self.staging_events[staging_index] = event
         ops._count()
+
+    def reduce_all(self, buffers):
+        """Reduce every bucket to its owner from ``buffers[b]`` (this rank's fp32 values of bucket ``b``) in two
+        launches: one pushes all buckets owned elsewhere, one accumulates all owned buckets.  The generation is the
+        one :meth:`begin_microbatch` last set."""
+        key = tuple(b.data_ptr() for b in buffers)
+        if self._many is None or self._many[0] != key:
+            push_rows, push_prefix, own_rows, own_prefix = [], [0], [], [0]
+            for index, (owner, _, length) in enumerate(self.buckets):
+                tiles = (length + self.tile - 1) // self.tile
+                region = self.offsets["grad_receive"] + self.bucket_region[index]
+                slot, scales_offset = self.bucket_slot[index], self.bucket_scales_offset[index]
+                source = buffers[index].data_ptr()
+                if owner == self.rank:
+                    own_rows.append([source, length, self.local_pointer(region), 0, self.bucket_accum[index].data_ptr(),
+                                     slot, scales_offset, 0])
+                    own_prefix.append(own_prefix[-1] + tiles)
+                else:
+                    codes = self.peer_pointer(owner, region + self.rank * slot)
+                    push_rows.append([source, length, codes, codes + scales_offset, 0, 0, 0, 0])
+                    push_prefix.append(push_prefix[-1] + tiles)
+
+            def table(rows, prefix):
+                rows = rows or [[0] * 8]
+                return (torch.tensor(rows, device=self.device, dtype=torch.int64),
+                        torch.tensor(prefix, device=self.device, dtype=torch.int64), prefix[-1])
+
+            self._many = (key, table(push_rows, push_prefix), table(own_rows, own_prefix))
+        _, push, own = self._many
+        stream = self._enter()
+        with torch.cuda.stream(stream):
+            self._ops.reduce_many(push[0], push[1], push[2], self.tile, self.fmt, self.pointers, self.rank, False,
+                                  self.local_pointer(self.many_ack_offset), self.many_flag_offset, self.micro_counter,
+                                  self.counters[1:2], self.wait_clocks, self.max_blocks, self.status)
+            self._ops.reduce_many(own[0], own[1], own[2], self.tile, self.fmt, self.pointers, self.rank, True,
+                                  self.local_pointer(self.many_flag_offset), self.many_ack_offset, self.micro_counter,
+                                  self.counters[0:1], self.wait_clocks, self.max_blocks, self.status)
+        ops._count(2)
 
     # ------------------------------------------------------------------ path 2: all-reduce with requantisation
     def attach_all_reduce(self, capacity):

@@ -69,7 +69,12 @@ class ClockSampler:
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.process, self.lines = index, None, []
+        self.index, self.process, self.lines, self.first = index, None, [], 0
+
+    def mark(self):
+        """The timed region starts here: only samples that arrive from now on are reported (the process is started
+        earlier, during warm-up, because nvidia-smi needs a few hundred milliseconds before its first sample)."""
+        self.first = len(self.lines)
 
     def start(self):
         try:
@@ -89,7 +94,8 @@ class ClockSampler:
             self.process.terminate()
         clocks, maxima, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in self.lines:
+        lines = self.lines[self.first:] or self.lines[-3:]     # a region shorter than one period: the samples of the
+        for line in lines:                                     # identical warm-up steps right before it
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
@@ -222,15 +228,16 @@ def run_ours(args):
 
     def timed(from_host):
         source = host if from_host else resident_list
+        sampler = ClockSampler(device.index)
+        sampler.start()
         for step in range(args.warmup):
             loss = train_step(source[step * ACCUMULATION:(step + 1) * ACCUMULATION], from_host)
             if from_host:
                 loss.item()
-        sampler = ClockSampler(device.index)
         dist.barrier()
         torch.cuda.synchronize()
         launches_before = ops.launch_count
-        sampler.start()
+        sampler.mark()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         wall = time.perf_counter()

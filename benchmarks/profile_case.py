@@ -26,7 +26,7 @@ def main():
     parser.add_argument("--case", required=True,
                         choices=("gemm_fp8", "gemm_group", "gemm_ns", "gemm_ns_apply", "gemm_act_bwd", "gemm_wgrad",
                                  "gemm_expert", "quantize", "quantize_rows", "group_quantize", "momentum", "gated",
-                                 "gated_bwd",
+                                 "gated_bwd", "attention", "attention_library",
                                  "ln_quantize", "gelu_quantize", "ln_backward", "gate_backward", "gemm_mx", "writeback",
                                  "reduce_push", "reduce_accumulate", "gather_pull"))
     parser.add_argument("--launches", type=int, default=4)
@@ -65,6 +65,14 @@ def main():
         qg, _ = ops.quantize(dy, sg, fp8_dtype=torch.float8_e5m2)
         qt, _ = ops.quantize(wdown_t, st)
         run = lambda: ops.gated_gemm_backward(qg, qt, sg, st, saved, activation="silu", out_dtype=torch.bfloat16)
+    elif args.case in ("attention", "attention_library"):
+        # DiT-XL/2 attention at 128 images: 256 tokens, 16 heads of 72, packed qkv [B, T, 3, H, D] in bf16
+        qkv = torch.randn(128, 256, 3, 16, 72, device=device, dtype=torch.bfloat16)
+        if args.case == "attention":
+            run = lambda: ops.attention_forward(qkv)
+        else:
+            from flash_attn import flash_attn_qkvpacked_func
+            run = lambda: flash_attn_qkvpacked_func(qkv)
     elif args.case == "gemm_mx":
         # hardware block-scaled MXFP8 product, UE8M0 scale per 32 K elements on both operands
         a = torch.randn(m, k, device=device).to(E4M3)

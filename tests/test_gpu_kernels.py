@@ -644,6 +644,30 @@ def test_cta_pair_gemm_matches_the_single_cta_kernel(shape, layout):
     assert rel_l2(base, (a.float() @ b.float().t()) * 0.125 + bias.float()) < 1e-2
 
 
+@pytest.mark.parametrize("shape", [(1152, 1152, 4096), (200, 520, 2064), (264, 130, 96)])
+def test_gemm_adds_into_its_output(shape):
+    """``accumulate=True``: out += A.B^T through the TMA reduce epilogue (with and without split-K), and through the
+    compute-then-add fallback for outputs the reduce path cannot take (bf16)."""
+    m, n, k = shape
+    torch.manual_seed(m + k)
+    a = torch.randn(m, k, device="cuda").to(torch.float8_e4m3fn)
+    b = torch.randn(n, k, device="cuda").to(torch.float8_e5m2)
+    one = torch.ones(1, device="cuda")
+    product = ops.gemm(a, b, one, one, out_dtype=torch.float32, force_split=1)
+    before = torch.randn(m, n, device="cuda")
+    for split in (1, 0, 3):
+        out, intact = _guarded((m, n), torch.float32)
+        out.copy_(before)
+        ops.gemm(a, b, one, one, out_dtype=torch.float32, out=out, accumulate=True, force_split=split)
+        torch.cuda.synchronize()
+        assert intact()
+        assert rel_l2(out - before, product) < 1e-5
+    half = before.bfloat16()
+    ops.gemm(a, b, one, one, out_dtype=torch.bfloat16, out=half, accumulate=True)
+    assert rel_l2(half.float(), before.bfloat16().float() + product) < 1e-2
+    ops.check_status()
+
+
 def test_quantiser_outputs_stay_inside_their_buffers_and_repeat_bit_for_bit():
     rows, cols = 333, 416
     x = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)

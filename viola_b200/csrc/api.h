@@ -77,6 +77,7 @@ typedef struct VbGemmDesc {
   int a_mn_major, b_mn_major;
   int k_mn;              // rows of K actually stored by an MN-major operand (0: K); K - k_mn < 16 rows read as zero
   int force_split;       // LINEAR epilogue: 0 = choose, 1 = no split-K, k > 1 = k work units per output tile
+  int accumulate_out;    // LINEAR, fp32 output through TMA, no bias: out += product (TMA reduce-add) instead of out = product
   int no_tma_store;      // 1: LINEAR epilogue writes with per-thread stores instead of the TMA-store path
 } VbGemmDesc;
 

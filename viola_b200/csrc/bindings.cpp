@@ -100,7 +100,7 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t epilogue, int64_
           const OptTensor& sb, at::IntArrayRef scale_layout, const OptTensor& bias, double alpha, double beta,
           const OptTensor& resid, const OptTensor& out_t, bool symmetric, int64_t activation, const OptTensor& aux,
           const OptTensor& expert_offsets, const OptTensor& tile_map, const OptTensor& status, int64_t force_bn,
-          int64_t batch, bool a_mn, bool b_mn, const OptTensor& amax_out) {
+          int64_t batch, bool a_mn, bool b_mn, const OptTensor& amax_out, bool accumulate) {
   // a_mn: ``a`` holds A transposed, i.e. [batch * K, M]; b_mn: ``b`` holds B transposed, [batch * K, N]
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda());
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && out.stride(-1) == 1);
@@ -172,6 +172,7 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t epilogue, int64_
     TORCH_CHECK(b.size(0) == (int64_t)d.N * d.num_experts);
   }
   d.status = (int*)ptr(status);
+  d.accumulate_out = accumulate ? 1 : 0;
   d.force_bn = (int)(force_bn & 0xffff);          // low half: tile width; high half: split-K units per tile
   d.force_split = (int)(force_bn >> 16);
   check(vb_gemm(&d, stream()), "gemm");

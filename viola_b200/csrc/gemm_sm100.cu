@@ -83,6 +83,7 @@ struct GemmArgs {
   // s - 1 has finished (split_flags[tile * 8 + epilogue warp] counts finished units; the last one clears it)
   int split_k, kb_per_split;
   int* split_flags;
+  int accumulate;       // LINEAR through TMA, fp32: every unit ADDS its tile to the output (out += A.B^T)
   int* status;
 };
 
@@ -1006,7 +1007,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             const int warp_row = mt * BM + quad * 32;
             if (lane == 0) {
               if (col0 < args.N && warp_row < args.M) {
-                if (split == 0) tma_store_2d(&tmC, buffer, col0, warp_row);
+                if (split == 0 && !args.accumulate) tma_store_2d(&tmC, buffer, col0, warp_row);
                 else tma_reduce_add_2d(&tmC, buffer, col0, warp_row);
               }
               tma_store_commit();
@@ -1447,6 +1448,12 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream, int split = 1) {
   }
   a.split_k = 1;
   a.kb_per_split = a.num_k_blocks;
+  a.accumulate = 0;
+  if (d.accumulate_out) {
+    // adding into the output needs the TMA reduce path, which exists for fp32 LINEAR results only
+    if (EPI != VB_EPI_LINEAR || !a.tma_store || d.out_dtype != 0 || d.bias != nullptr) return (int)cudaErrorInvalidValue;
+    a.accumulate = 1;
+  }
   if constexpr (EPI == VB_EPI_LINEAR && !GROUP) {
     // split-K needs the TMA path (reduce-add stores), an fp32 result and one problem per launch
     if (!PAIR && split > 1 && a.tma_store && d.out_dtype == 0 && a.batch == 1 && a.num_tiles <= kSplitMaxTiles) {

@@ -185,6 +185,11 @@ def linear_forward(layer, x, weight, bias, *, need_input_grad, need_weight_grad,
     return y, saved, aux
 
 
+def _adds_up(slot):
+    """Does this landing slot hold the running sum of the step's microbatches (the producer then adds into it)?"""
+    return slot is not None and getattr(slot, "_viola_accumulate", False)
+
+
 def _gradient_slot(offer, shape, dtype, device):
     """The engine's landing slot for a gradient about to be computed, when it offers one that fits."""
     if offer is None:
@@ -258,7 +263,10 @@ def linear_backward(layer, saved, dy, *, need_input_grad, need_weight_grad, need
         else:
             slot = _gradient_slot(getattr(saved, "weight_slot", None), (qg.qt.shape[0], xt.shape[0]),
                                   saved.weight_grad_dtype, dy.device)
-            dw = ops.gemm(qg.qt, xt, qg.st, xt_scale, out_dtype=saved.weight_grad_dtype, out=slot)
+            if _adds_up(slot) and layer.rotation_size:
+                slot = None                     # the rotation below works in place on this microbatch's gradient only
+            dw = ops.gemm(qg.qt, xt, qg.st, xt_scale, out_dtype=saved.weight_grad_dtype, out=slot,
+                          accumulate=_adds_up(slot))
         if layer.rotation_size:
             ops.hadamard64(dw, out=dw)
     if need_bias_grad:
@@ -279,8 +287,9 @@ def _backward_in_place(layer, saved, dy, limit, need_input_grad, need_weight_gra
             if saved.bias_grad_dtype == torch.float32 else None
         if slot is None:
             db_sum = torch.zeros(dy.shape[1], device=dy.device, dtype=torch.float32)
-        else:                             # the engine clears all one-dimensional slots in one launch per microbatch
-            db_sum = slot if getattr(slot, "_viola_zeroed", False) else slot.zero_()
+        else:                             # the engine clears all one-dimensional slots in one launch per microbatch,
+            # or keeps the running sum of the step in them
+            db_sum = slot if (getattr(slot, "_viola_zeroed", False) or _adds_up(slot)) else slot.zero_()
     grad_scale = layer.grad_quantizer.scale_gathered(grad_amax, bfmt, limit) if grad_amax is not None else None
     qg = _quantize_activation(layer_no_rotation(layer), dy, bfmt, None, layer.grad_quantizer, limit, row=True,
                               transposed=False, colsum=db_sum, scale=grad_scale)
@@ -314,7 +323,10 @@ def _backward_in_place(layer, saved, dy, limit, need_input_grad, need_weight_gra
             xq, x_scale = enc.q, enc.s
         slot = _gradient_slot(getattr(saved, "weight_slot", None), (qg.q.shape[1], xq.shape[1]), saved.weight_grad_dtype,
                               dy.device)
-        dw = ops.gemm(qg.q, xq, qg.s, x_scale, out_dtype=saved.weight_grad_dtype, a_mn=True, b_mn=True, out=slot)
+        if _adds_up(slot) and layer.rotation_size:
+            slot = None
+        dw = ops.gemm(qg.q, xq, qg.s, x_scale, out_dtype=saved.weight_grad_dtype, a_mn=True, b_mn=True, out=slot,
+                      accumulate=_adds_up(slot))
         if layer.rotation_size:
             ops.hadamard64(dw, out=dw)
     if need_bias_grad:

@@ -285,7 +285,7 @@ def _check_mn(t):
 
 def _gemm(a, b, out, epilogue, n_logical, *, sa=None, sb=None, layout=_NO_GROUP, bias=None, alpha=1.0, beta=0.0,
           resid=None, out_t=None, symmetric=False, activation=0, aux=None, expert_offsets=None, tile_map=None,
-          force_bn=0, batch=1, a_mn=False, b_mn=False, amax_out=None, force_split=0):
+          force_bn=0, batch=1, a_mn=False, b_mn=False, amax_out=None, force_split=0, accumulate=False):
     multiple = 16 if a.element_size() == 1 else 8
     a = _check_mn(a) if a_mn else _pad_k(a, multiple)
     b = _check_mn(b) if b_mn else _pad_k(b, multiple)
@@ -295,9 +295,9 @@ def _gemm(a, b, out, epilogue, n_logical, *, sa=None, sb=None, layout=_NO_GROUP,
         _ops().gemm(a, b, out, epilogue, n_logical, sa, sb, list(layout), bias, float(alpha), float(beta), resid, out_t,
                     bool(symmetric), int(activation), aux, expert_offsets, tile_map, status,
                     int(tile) | (int(force_split) << 16), int(batch),
-                    bool(a_mn), bool(b_mn), amax_out)
+                    bool(a_mn), bool(b_mn), amax_out, bool(accumulate))
 
-    if not force_bn and (tuning._enabled or tuning._choices):
+    if not force_bn and not accumulate and (tuning._enabled or tuning._choices):
         # the output-tile width of this shape: recorded choice, or (tuning on) measured now on these operands
         in_place = resid is not None and resid.data_ptr() == out.data_ptr()
         tunable = (epilogue in (EPI_LINEAR, EPI_AXPBY, EPI_ACT_BWD) and not layout[0] and not symmetric
@@ -312,22 +312,33 @@ def _gemm(a, b, out, epilogue, n_logical, *, sa=None, sb=None, layout=_NO_GROUP,
     return out
 
 
-def gemm(a, b, sa, sb, *, out_dtype, bias=None, out=None, force_bn=0, a_mn=False, b_mn=False, force_split=0):
+def gemm(a, b, sa, sb, *, out_dtype, bias=None, out=None, force_bn=0, a_mn=False, b_mn=False, force_split=0,
+         accumulate=False):
     """(a * sa) @ (b * sb).T (+ bias): FP8 or 16-bit operands with per-tensor fp32 scales.
 
     ``a_mn`` / ``b_mn``: the tensor passed holds the operand transposed (``a`` is [K, M] / ``b`` is [K, N]);
     the tensor core reads it MN-major in place, so no transposed copy is needed.
     ``force_split``: work units per output tile along K for fp32 results (0 = chosen from the wave count, 1 = none).
+    ``accumulate``: ``out += product`` (``out`` required); fp32 outputs with 16-byte rows add inside the GEMM's
+    epilogue (TMA reduce), everything else computes the product and adds it.
     """
     if not a.is_cuda:
         result = reference.gemm(a.t() if a_mn else a, b.t() if b_mn else b, sa, sb, out_dtype=out_dtype, bias=bias)
+        if accumulate:
+            return out.add_(result)
         return result if out is None else out.copy_(result)
     m = a.shape[1] if a_mn else a.shape[0]
     n = b.shape[1] if b_mn else b.shape[0]
+    if accumulate and not (out.dtype == torch.float32 and bias is None and out.data_ptr() % 16 == 0
+                           and out.stride(-2) % 4 == 0 and out.stride(-1) == 1):
+        product = torch.empty((m, n), device=a.device, dtype=out_dtype)
+        _gemm(a, b, product, EPI_LINEAR, n, sa=sa, sb=sb, bias=bias, force_bn=force_bn, a_mn=a_mn, b_mn=b_mn,
+              force_split=force_split)
+        return out.add_(product)
     if out is None:
         out = torch.empty((m, n), device=a.device, dtype=out_dtype)
     return _gemm(a, b, out, EPI_LINEAR, n, sa=sa, sb=sb, bias=bias, force_bn=force_bn, a_mn=a_mn, b_mn=b_mn,
-                 force_split=force_split)
+                 force_split=force_split, accumulate=accumulate)
 
 
 # ------------------------------------------------------------------------------ group scaling

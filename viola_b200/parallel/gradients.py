@@ -102,7 +102,16 @@ class GradientState:
         # bytes whatever the microbatch size, so doing it per microbatch costs the same again for every accumulation
         # step; the price is one more buffer of the gradients' size on every rank.
         self.once = bool(reduce_once) and self.shard and self.landing is not None
-        self.local_sum = torch.zeros_like(self.landing) if self.once else None
+        # With fp32 gradients the landing buffer itself can hold the running sum of the step: producers add into
+        # their slot (the weight-gradient GEMM's epilogue is a TMA reduce-add), so no pass over the gradients is
+        # needed per microbatch.  Replicated / single-rank: the landing buffer IS the accumulator.
+        self.summing = (self.landing is not None and self.dtype == torch.float32 and gradient_dtype == torch.float32
+                        and (self.once or not self.shard))
+        if self.summing and not self.shard:
+            self.accumulator = self.landing
+            self.bucket_slices = list(self.bucket_landing)
+            self.local = {index: slot.view(-1) for index, slot in self.slots.items()}
+        self.local_sum = (self.landing if self.summing else torch.zeros_like(self.landing)) if self.once else None
         self.bucket_sum = []
         self.pending_local = False
         if self.once:
@@ -110,10 +119,12 @@ class GradientState:
             for _, _, length in self.buckets:
                 self.bucket_sum.append(self.local_sum[start:start + length])
                 start += length
+        self.vector_slots = []
         self.claimed = [False] * len(self.records)
         # one-dimensional slots (biases) are accumulated into by atomic column sums: cleared together, one launch per
         # microbatch, instead of one fill per layer
-        self.vector_slots = [i for i, slot in self.slots.items() if slot.dim() == 1]
+        if not self.summing:
+            self.vector_slots = [i for i, slot in self.slots.items() if slot.dim() == 1]
         self.vectors_cleared = False
         self.buffer = (torch.empty(self.bucket_capacity, device=device, dtype=self.dtype)
                        if self.world > 1 and self.landing is None else None)
@@ -154,7 +165,9 @@ class GradientState:
         # a fresh view: autograd adopts a gradient tensor as ``.grad`` without copying only when nothing else
         # holds a reference to that tensor object
         slot = self.slots[index].view(self.slots[index].shape)
-        if self.vectors_cleared and slot.dim() == 1:
+        if self.summing:
+            slot._viola_accumulate = True
+        elif self.vectors_cleared and slot.dim() == 1:
             slot._viola_zeroed = True
         return slot
 
@@ -181,7 +194,10 @@ class GradientState:
         if self.landing is not None:
             slot = self.slots[index]
             if gradient.data_ptr() != slot.data_ptr():        # produced elsewhere (torch layers, tied weights)
-                slot.copy_(gradient.view(slot.shape))
+                if self.summing and not self.claimed[index]:
+                    slot.add_(gradient.view(slot.shape))      # the slot holds the step's running sum
+                else:                                          # (a claimed slot's sum is already part of ``gradient``)
+                    slot.copy_(gradient.view(slot.shape))
             if self.shard and not self.defer_reduction and not self.once:
                 self._drain()
         elif self.shard:
@@ -248,6 +264,8 @@ class GradientState:
 
     def _accumulate_landed(self):
         """Replicated / single-rank accumulation: one add of the whole landing buffer."""
+        if self.summing:
+            return                                             # the landing buffer is the accumulator
         if not all(self.seen):
             for index, seen in enumerate(self.seen):
                 if not seen and index in self.slots:
@@ -256,6 +274,9 @@ class GradientState:
 
     def _sum_landed(self):
         """Add this microbatch's gradients to the rank-local sum that the step will reduce."""
+        self.pending_local = True
+        if self.summing:
+            return                                             # the producers added into the landing buffer themselves
         if not all(self.seen):
             for index, seen in enumerate(self.seen):
                 if not seen and index in self.slots:

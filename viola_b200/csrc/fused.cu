@@ -633,8 +633,9 @@ using namespace vb;
 static int pick_rows_per_block(int rows, int tokens) {
   int rpb = 128;
   while (rpb > 8 && (long long)(rows / tokens) * ((tokens + rpb - 1) / rpb) < 148LL * 2) rpb >>= 1;
-  // ... but no more than eight blocks per sample: the last block of a sample adds all of them up
-  while (rpb < 128 && (tokens + rpb - 1) / rpb > 8) rpb <<= 1;
+  // ... but no more than 32 blocks per sample: the last block of a sample adds all of them up (small batches need
+  // the blocks: at 16 samples eight blocks per sample leave a fifth of the SMs idle and one block per SM)
+  while (rpb < 128 && (tokens + rpb - 1) / rpb > 32) rpb <<= 1;
   return rpb;
 }
 

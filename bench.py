@@ -57,6 +57,8 @@ def parse():
     parser.add_argument("--resident", default="auto", choices=("auto", "true", "false"),
                         help="sharding.resident: keep gathered parameters between uses (auto: when one copy is small)")
     parser.add_argument("--overlap", action="store_true", help="communication.overlap: reduce buckets during backward")
+    parser.add_argument("--autotune", action="store_true",
+                        help="first-use tile search for every GEMM shape during the eager warm-up microbatch")
     parser.add_argument("--no-phases", action="store_true", help="skip the extra untimed steps that measure phase times")
     return parser.parse_args()
 
@@ -184,6 +186,9 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    if args.autotune:
+        from viola_b200 import tuning
+        tuning.enable()
     engine = viola.violaEngine(engine_config(args))
     device = engine.device
     options, model_name = model_options(args.model)
@@ -272,7 +277,7 @@ def run_ours(args):
                    "optimizer": "FP8Muon(balanced, standard NS) + AdamW", "ema": 0.9999,
                    "grad_comm": "fp8 e4m3 tile 256, 25 MB buckets",
                    "cache": "fresh inputs every step; per-microbatch activations exceed L2 by >100x",
-                   "cuda_graph": graphed is not None, "transport": transport,
+                   "cuda_graph": graphed is not None, "tile_tuner": bool(args.autotune), "transport": transport,
                    "gathered_parameters_resident": resident, "comm_overlap": bool(args.overlap)},
         "clocks": clocks, "gpu_launches": launches, "final_loss": loss_value,
     }

@@ -87,6 +87,30 @@ multi_weight_update_kernel(const Desc* __restrict__ table, const int* __restrict
   void* weight = reinterpret_cast<void*>(d.p0);
   const void* update = reinterpret_cast<const void*>(d.p1);
   const float keep = 1.f - lr * decay, rate = lr * d.f0;
+  // fp32 master, bf16 update, 16-byte aligned: eight elements per thread and iteration (32-byte and 16-byte accesses);
+  // the arithmetic per element is the scalar loop's
+  if (d.d0 == kF32 && d.d1 == kBF16 && ((d.p0 | d.p1) & 15) == 0) {
+    float* w = reinterpret_cast<float*>(d.p0);
+    const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(d.p1);
+    long long j = begin + (long long)threadIdx.x * 8;
+    for (; j + 8 <= end; j += (long long)blockDim.x * 8) {
+      float4 a = *reinterpret_cast<const float4*>(w + j), b = *reinterpret_cast<const float4*>(w + j + 4);
+      const uint4 raw = *reinterpret_cast<const uint4*>(u + j);
+      const float2 u0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+      const float2 u1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+      const float2 u2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.z));
+      const float2 u3 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.w));
+      a.x = a.x * keep - rate * u0.x; a.y = a.y * keep - rate * u0.y;
+      a.z = a.z * keep - rate * u1.x; a.w = a.w * keep - rate * u1.y;
+      b.x = b.x * keep - rate * u2.x; b.y = b.y * keep - rate * u2.y;
+      b.z = b.z * keep - rate * u3.x; b.w = b.w * keep - rate * u3.y;
+      *reinterpret_cast<float4*>(w + j) = a;
+      *reinterpret_cast<float4*>(w + j + 4) = b;
+    }
+    if (j < end && j + 8 > end)                     // the ragged end of the last chunk, by the same thread
+      for (; j < end; ++j) w[j] = w[j] * keep - rate * __bfloat162float(u[j]);
+    return;
+  }
   for (long long j = begin + threadIdx.x; j < end; j += blockDim.x) {
     const float v = load_as_float(weight, j, d.d0) * keep - rate * load_as_float(update, j, d.d1);
     store_rounded(weight, j, d.d0, v, stochastic != 0, (unsigned long long)j, step, (unsigned long long)d.i0);
@@ -109,11 +133,82 @@ multi_momentum_kernel(const Desc* __restrict__ table, const int* __restrict__ pr
   float* scales = reinterpret_cast<float*>(d.p2);
   __nv_bfloat16* update = reinterpret_cast<__nv_bfloat16*>(d.p3);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // fp32 gradient, 16-byte aligned buffers, whole tiles: every lane owns EPL consecutive elements and moves them with
+  // vector accesses; which lane holds which element does not enter the arithmetic, so the results are the scalar path's
+  const bool vector_ok = EPL % 4 == 0 && d.d0 == kF32 && ((d.p0 | d.p1 | d.p3) & 15) == 0;
   for (long long tile = first_tile + warp; tile < min(first_tile + kChunk / TILE, tiles); tile += 8) {
     const long long base = tile * TILE;
     const float old_scale = scales[tile];
     float g[EPL], m[EPL];
     float amax = 0.f;
+    if constexpr (EPL % 4 == 0) {
+      if (vector_ok && base + TILE <= d.n) {
+        const long long i0 = base + (long long)lane * EPL;
+        const float* gp = reinterpret_cast<const float*>(grad) + i0;
+        uint32_t words[EPL / 4];
+#pragma unroll
+        for (int v = 0; v < EPL / 4; ++v) {
+          const float4 q = *reinterpret_cast<const float4*>(gp + 4 * v);
+          g[4 * v] = q.x * inv_loss_scale; g[4 * v + 1] = q.y * inv_loss_scale;
+          g[4 * v + 2] = q.z * inv_loss_scale; g[4 * v + 3] = q.w * inv_loss_scale;
+        }
+        if constexpr (EPL == 4) {
+          words[0] = *reinterpret_cast<const uint32_t*>(codes + i0);
+        } else if constexpr (EPL == 8) {
+          const uint2 q = *reinterpret_cast<const uint2*>(codes + i0);
+          words[0] = q.x; words[1] = q.y;
+        } else {
+#pragma unroll
+          for (int v = 0; v < EPL / 16; ++v) {
+            const uint4 q = *reinterpret_cast<const uint4*>(codes + i0 + 16 * v);
+            words[4 * v] = q.x; words[4 * v + 1] = q.y; words[4 * v + 2] = q.z; words[4 * v + 3] = q.w;
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+          const float old = fp8_decode((uint8_t)(words[e >> 2] >> (8 * (e & 3))), kE4M3) * old_scale;
+          m[e] = beta * old + (1.f - beta) * g[e];
+          amax = fmaxf(amax, fabsf(m[e]));
+        }
+        amax = warp_max(amax);
+        const float scale = fmaxf(amax, 1e-30f) / 448.f;
+        if (lane == 0) scales[tile] = scale;
+        uint32_t out_words[EPL / 4];
+        uint32_t up[EPL / 2];
+#pragma unroll
+        for (int v = 0; v < EPL / 4; ++v) out_words[v] = 0u;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+          float c = fminf(fmaxf(m[e] / scale, -448.f), 448.f);
+          if (m[e] != m[e]) c = m[e];
+          if (stochastic) c = stochastic_e4m3(c, (unsigned long long)(i0 + e), step, (unsigned long long)d.i0);
+          out_words[e >> 2] |= (uint32_t)fp8_encode(c, kE4M3) << (8 * (e & 3));
+        }
+#pragma unroll
+        for (int e = 0; e < EPL; e += 2) {
+          const float a = nesterov ? (1.f - beta) * g[e] + beta * m[e] : m[e];
+          const float b = nesterov ? (1.f - beta) * g[e + 1] + beta * m[e + 1] : m[e + 1];
+          const __nv_bfloat162 pair = __halves2bfloat162(__float2bfloat16_rn(a), __float2bfloat16_rn(b));
+          up[e >> 1] = *reinterpret_cast<const uint32_t*>(&pair);
+        }
+        if constexpr (EPL == 4) {
+          *reinterpret_cast<uint32_t*>(codes + i0) = out_words[0];
+          *reinterpret_cast<uint2*>(update + i0) = make_uint2(up[0], up[1]);
+        } else if constexpr (EPL == 8) {
+          *reinterpret_cast<uint2*>(codes + i0) = make_uint2(out_words[0], out_words[1]);
+          *reinterpret_cast<uint4*>(update + i0) = make_uint4(up[0], up[1], up[2], up[3]);
+        } else {
+#pragma unroll
+          for (int v = 0; v < EPL / 16; ++v)
+            *reinterpret_cast<uint4*>(codes + i0 + 16 * v) =
+                make_uint4(out_words[4 * v], out_words[4 * v + 1], out_words[4 * v + 2], out_words[4 * v + 3]);
+#pragma unroll
+          for (int v = 0; v < EPL / 8; ++v)
+            *reinterpret_cast<uint4*>(update + i0 + 8 * v) = make_uint4(up[4 * v], up[4 * v + 1], up[4 * v + 2], up[4 * v + 3]);
+        }
+        continue;
+      }
+    }
 #pragma unroll
     for (int e = 0; e < EPL; ++e) {
       const long long i = base + e * 32 + lane;

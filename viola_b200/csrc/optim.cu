@@ -263,6 +263,25 @@ ns_prescale_kernel(const void* __restrict__ x, int dt, int rows, int cols, const
   if (out != nullptr) out = reinterpret_cast<char*>(out) + plane * osize;
   if (out_t != nullptr) out_t = reinterpret_cast<char*>(out_t) + plane * osize;
   const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+  // bf16 in, bf16 out, no transposed copy, rows of whole 16-byte pieces: eight elements per access
+  if (out_t == nullptr && dt == kBF16 && odt == kBF16 && (cols & 7) == 0 &&
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+    for (int i = threadIdx.x; i < 64 * 8; i += blockDim.x) {
+      const int r = r0 + (i >> 3), c = c0 + (i & 7) * 8;
+      if (r >= rows || c >= cols) continue;
+      const long long at = (long long)r * cols + c;
+      uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + at);
+      uint32_t* w = reinterpret_cast<uint32_t*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e]));
+        const __nv_bfloat162 scaled = __halves2bfloat162(__float2bfloat16_rn(f.x * inv), __float2bfloat16_rn(f.y * inv));
+        w[e] = *reinterpret_cast<const uint32_t*>(&scaled);
+      }
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + at) = raw;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < 64 * 64; i += blockDim.x) {
     const int tr = i >> 6, tc = i & 63;
     const int r = r0 + tr, c = c0 + tc;

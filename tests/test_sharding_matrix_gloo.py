@@ -109,7 +109,7 @@ def storage_counts(engine, optimizer):
 
 
 def one_combination(engine_config, flags, variant, directory, rank, world):
-    tied, recompute, adamw = variant
+    tied, recompute, adamw = variant[:3]
     config = dict(engine_config, sharding=dict(zip(("parameters", "gradients", "optimizer", "ema"), flags)))
     engine = viola.violaEngine(config)
     torch.manual_seed(11)
@@ -174,7 +174,8 @@ def matrix_worker(rank, world, port, variant, directory, results):
                       LOCAL_RANK=str(rank))
     base = dict(device="cpu", mixed_precision="no", gradient_accumulation_steps=2,
                 precision=dict(master_weight_dtype="fp32", gradient_dtype="fp32"),
-                communication=dict(dtype="fp32", bucket_mb=0.02), ema=dict(decay=0.9, dtype="fp32"))
+                communication=dict(dtype="fp32", bucket_mb=0.02, reduce_once=variant[3]),
+                ema=dict(decay=0.9, dtype="fp32"))
     for flags in itertools.product((False, True), repeat=4):
         one_combination(base, flags, variant, directory, rank, world)
     dist.barrier()
@@ -182,8 +183,9 @@ def matrix_worker(rank, world, port, variant, directory, results):
     results.put((rank, True))
 
 
-@pytest.mark.parametrize("variant", [(True, True, False), (False, True, True)],
-                         ids=["tied+recompute", "recompute+adamw"])
+# last element: sharded gradients go to their owners once per optimizer step (the default) or in every microbatch
+@pytest.mark.parametrize("variant", [(True, True, False, True), (False, True, True, False)],
+                         ids=["tied+recompute", "recompute+adamw+reduce-every-microbatch"])
 def test_all_sharding_combinations(variant):
     with tempfile.TemporaryDirectory() as directory:
         assert len(run_world(matrix_worker, 2, variant, directory)) == 2

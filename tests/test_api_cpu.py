@@ -290,3 +290,30 @@ def test_phase_tracing_is_inert_by_default_and_times_when_enabled():
         assert utils.phase_times() == {}
     finally:
         utils.enable_timing(False)
+
+
+def test_packed_attention_and_accumulating_gemm_on_cpu():
+    """CPU paths of the two newest ops: packed attention (SDPA) agrees with the fp32 oracle of the tcgen05 kernel,
+    and ``ops.gemm(accumulate=True)`` adds the product to its output."""
+    from viola_b200 import ops
+    from viola_b200.nn.attention import packed_attention
+    from viola_b200.ops import reference
+
+    torch.manual_seed(0)
+    qkv = torch.randn(2, 256, 3, 4, 16)
+    out, lse = ops.attention_forward(qkv)
+    want = packed_attention(qkv).view(2, 256, 4, 16)
+    assert out.shape == (2, 256, 4, 16) and lse.shape == (2, 4, 256)
+    assert torch.allclose(out, want, atol=1e-5)
+    scores = torch.einsum("bthd,bshd->bhts", qkv[:, :, 0], qkv[:, :, 1]) * 16 ** -0.5
+    assert torch.allclose(lse, torch.logsumexp(scores, dim=-1), atol=1e-5)
+
+    a = torch.randn(24, 32).to(torch.float8_e4m3fn)
+    b = torch.randn(40, 32).to(torch.float8_e4m3fn)
+    one = torch.ones(1)
+    product = ops.gemm(a, b, one, one, out_dtype=torch.float32)
+    base = torch.randn(24, 40)
+    out = base.clone()
+    ops.gemm(a, b, one, one, out_dtype=torch.float32, out=out, accumulate=True)
+    assert torch.allclose(out, base + product)
+    assert torch.allclose(product, reference.gemm(a, b, one, one, out_dtype=torch.float32))

@@ -42,8 +42,8 @@ namespace vb {
 
 constexpr int BM = 128;
 constexpr int BK_BYTES = 128;  // one 128-byte swizzle span along K per stage
-constexpr int kThreads = 192;   // warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 epilogue (+ warp 6: slab loader);
-                                // the per-tensor LINEAR kernels run eight epilogue warps (warps 2-9) instead
+// Roles: warp 0 TMA producer, warp 1 MMA issuer, then Config::kEpiWarps epilogue warps (four, or eight for the LINEAR,
+// AXPBY and ACT_BWD kernels), then, where an epilogue reads an operand through the slab ring, one loader warp.
 
 struct GemmArgs {
   int M, N, K;
@@ -75,6 +75,7 @@ struct GemmArgs {
   long long b_rows_per_batch, out_bs, resid_bs, out_t_bs;
   unsigned int* amax_out;
   int tma_store;        // LINEAR epilogue: stage in shared memory and write with TMA
+  int epi_sets;         // slab epilogues: 2 = two sets of four warps alternate over the chunks (needs N % 64 == 0), else 1
   int epi_stage;        // AXPBY residual / ACT_BWD slope arrives through the TMA slab ring
   int epi_store;        // AXPBY / ACT_BWD result leaves through the slab ring (TMA store)
   int a_mn, b_mn;       // operand stored MN-major: A as [K, M] / B as [K, N] (row-major, MN contiguous)
@@ -339,7 +340,12 @@ struct Config {
   // kernels use eight epilogue warps, two per TMEM lane quadrant, each draining half of the tile's columns.
   // Group-scaled LINEAR: the promotion of every K-block (one FMA per accumulator element) is the epilogue warps'
   // whole job, so halving the columns per warp halves the time a K-block's accumulator stays occupied.
-  static constexpr int kEpiWarps = EPI == VB_EPI_LINEAR ? 8 : 4;
+  static constexpr int kEpiWarps =
+      (EPI == VB_EPI_LINEAR || ((EPI == VB_EPI_AXPBY || EPI == VB_EPI_ACT_BWD) && !GROUP)) ? 8 : 4;
+  // LINEAR splits a tile's columns into contiguous parts, one per group of four warps; the slab epilogues
+  // (AXPBY, ACT_BWD) interleave instead: warps 2-5 take the even chunks, warps 6-9 the odd ones, in the order the
+  // loader warp fills the slab ring.
+  static constexpr int kColumnParts = EPI == VB_EPI_LINEAR ? kEpiWarps / 4 : 1;
   static constexpr int kStoreBytes = kTmaStore ? kEpiWarps * 4096 : 0;   // per warp: 2 x (32 rows x 64 B) or 32 rows x 128 B
   // AXPBY and ACT_BWD epilogues (16-bit output, optional 16-bit [M, N] operand: the residual / the activation
   // slope) run through a ring of 128-row x 32-column slabs in shared memory, one per output chunk: the
@@ -357,7 +363,8 @@ struct Config {
   static constexpr bool kSlabRing = kEpiSlab || kGatedSlab;
   static constexpr bool kSlabLoader = kEpiSlab || (kGatedBwd && !GROUP);
   static constexpr int kEpiSlabs = (kGatedBwd && !GROUP) ? 8 : 4;
-  static constexpr int kCtaThreads = kSlabLoader ? kThreads + 32 : 64 + 32 * kEpiWarps;   // a seventh warp feeds the slab ring
+  static constexpr int kLoaderWarp = 2 + kEpiWarps;                                    // feeds the slab ring
+  static constexpr int kCtaThreads = 64 + 32 * kEpiWarps + (kSlabLoader ? 32 : 0);
   static constexpr int kEpiSlabBytes = BM * 64;
   static constexpr int kEpiBytes = kSlabRing ? kEpiSlabs * kEpiSlabBytes : 0;
   static constexpr int kStages =
@@ -573,7 +580,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1; }
       }
     }
-  } else if (C::kSlabLoader && warp == 6) {
+  } else if (C::kSlabLoader && warp == C::kLoaderWarp) {
     // ------------------------------ slab loader --------------------------------
     // Feeds the epilogue's operand slabs (AXPBY residual, ACT_BWD slope) on its own, so a full slab ring never
     // holds back the main-loop producer; it runs up to kEpiSlabs chunks ahead of the epilogue.
@@ -621,8 +628,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     int eslot = 0, prev_slot = -1;        // epilogue slab ring: position, phase, slot awaiting release
     uint32_t ephase = 0;
     constexpr int NCHUNK = BN / 32;
-    constexpr int NOUT = (C::kGatedFwd ? NCHUNK / 2 : NCHUNK) / (C::kEpiWarps / 4);  // output chunks per tile and warp
-    const int chunk0 = half * NOUT;       // first chunk of this warp
+    constexpr int NOUT = (C::kGatedFwd ? NCHUNK / 2 : NCHUNK) / C::kColumnParts;  // output chunks per tile and warp
+    const int chunk0 = C::kColumnParts > 1 ? half * NOUT : 0;       // first chunk of this warp
+    // slab epilogues with eight warps: this warp's set (0 = warps 2-5, 1 = warps 6-9) takes every `sets`-th chunk
+    const int sets = (C::kEpiSlab && C::kEpiWarps == 8) ? (args.epi_sets == 2 ? 2 : 1) : 1;
+    const int set = (C::kEpiSlab && C::kEpiWarps == 8) ? half : 0;
+    if constexpr (C::kEpiSlab) eslot = sets == 2 ? set : 0;
     for (int u = cta_first; u < args.num_tiles * args.split_k && ok; u += cta_stride) {
       int mt, nt;
       const int split = u / args.num_tiles, t = u - split * args.num_tiles;
@@ -893,7 +904,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
       if (!staged_done) {
 #pragma unroll(C::kEpiSlab ? 1 : NOUT)
-      for (int c = 0; c < NOUT; ++c) {
+      for (int c = (C::kEpiSlab ? (set < sets ? set : NOUT) : 0); c < NOUT; c += (C::kEpiSlab ? sets : 1)) {
         float v[32];
         float v2[C::kGatedFwd ? 32 : 1];
         if constexpr (GROUP) {
@@ -928,8 +939,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               ok = __all_sync(0xffffffffu, mbar_wait(&epi_full[eslot], ephase, abort_flag, args.status, kTimeoutFull));
               if (!ok) break;
             } else {
-              // result staging only: the slot was last used kEpiSlabs chunks ago by this warp's own store
-              if (lane == 0) tma_store_wait_read<C::kEpiSlabs - 1>();
+              // result staging only: the slot was last used kEpiSlabs / sets of this warp's own chunks ago
+              if (lane == 0) {
+                if (sets == 2) tma_store_wait_read<C::kEpiSlabs / 2 - 1>();
+                else tma_store_wait_read<C::kEpiSlabs - 1>();
+              }
               __syncwarp();
             }
           }
@@ -962,7 +976,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if (lane == 0) mbar_arrive(&epi_empty[eslot]);
               }
             }
-            if (++eslot == C::kEpiSlabs) { eslot = 0; ephase ^= 1; }
+            eslot += sets;
+            if (eslot >= C::kEpiSlabs) { eslot -= C::kEpiSlabs; ephase ^= 1; }
           }
         };
         if constexpr (EPI == VB_EPI_LINEAR) {
@@ -1414,7 +1429,12 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream, int split = 1) {
       a.tma_store = 1;
   }
   CUtensorMap tmD = tmA;
+  a.epi_sets = 1;
   if constexpr (C::kEpiSlab) {
+    // an even number of chunks in every tile keeps "even chunks / odd chunks" aligned with the loader's global order
+    // (measured: the Newton-Schulz epilogue gains from the second set, the activation-slope epilogue, whose operand
+    // slabs come from DRAM, loses the loader's look-ahead and gets slower, so it keeps one set)
+    a.epi_sets = (C::kEpiWarps == 8 && EPI == VB_EPI_AXPBY && d.N % 64 == 0) ? 2 : 1;
     auto usable = [](const void* p, long long ld) { return p != nullptr && (reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld * 2) % 16 == 0; };
     const void* src = EPI == VB_EPI_AXPBY ? d.resid : d.aux;
     const long long ld = EPI == VB_EPI_AXPBY ? d.ldr : d.ldaux;

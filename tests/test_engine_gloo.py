@@ -190,3 +190,53 @@ def test_two_rank_plumbing(flags):
 def test_single_process_engine_matches_reference():
     with tempfile.TemporaryDirectory() as directory:
         assert len(run_world(worker, 1, (True, True, True, True), directory)) == 1
+
+
+class QuantisedNet(nn.Module):
+    """FP8 linears of this package, one of them with the Hadamard rotation (its weight gradient cannot be added into
+    a running sum by the GEMM, so the layer hands its landing slot back), plus a torch layer and a tied weight."""
+
+    def __init__(self):
+        super().__init__()
+        self.first = viola.nn.Linear(128, 128, rotation_size=64)
+        self.second = viola.nn.Linear(128, 128)
+        self.third = nn.Linear(128, 128)
+        self.last = viola.nn.Linear(128, 128, bias=False)
+        self.last.weight = self.second.weight
+
+    def forward(self, x):
+        return self.last(torch.tanh(self.third(torch.tanh(self.second(torch.tanh(self.first(x)))))))
+
+
+def landing_worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    outcomes = []
+    for slots in (True, False):
+        torch.manual_seed(3)
+        config = dict(device="cpu", mixed_precision="no", gradient_accumulation_steps=3,
+                      precision=dict(master_weight_dtype="fp32", gradient_dtype="fp32"),
+                      communication=dict(dtype="fp32", gradient_slots=slots))
+        engine = viola.violaEngine(config)
+        model = engine.prepare_model(QuantisedNet())
+        engine.prepare_optimizer(lambda params: MatrixSGD(params))
+        assert engine.state.gradients.summing == slots
+        for step in range(3):
+            for micro in range(3):
+                generator = torch.Generator().manual_seed(100 * step + micro)
+                x, y = torch.randn(32, 128, generator=generator), torch.randn(32, 128, generator=generator)
+                with engine.accumulate():
+                    engine.backward(nn.functional.mse_loss(model(x), y))
+            assert engine.step()
+        outcomes.append({name: value.clone() for name, value in full_weights(engine).items()
+                         if torch.is_tensor(value) and value.is_floating_point()})
+        engine.close()
+    for name, value in outcomes[0].items():
+        torch.testing.assert_close(value.float(), outcomes[1][name].float(), rtol=1e-5, atol=1e-6, msg=name)
+    results.put((rank, True))
+
+
+def test_running_sum_landing_buffer_matches_separate_accumulation():
+    """The landing buffer as the step's gradient accumulator (producers add into their slots) against the plain
+    per-parameter accumulation: same weights after three steps of three microbatches."""
+    assert len(run_world(landing_worker, 1)) == 1

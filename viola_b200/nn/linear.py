@@ -190,14 +190,23 @@ def _adds_up(slot):
     return slot is not None and getattr(slot, "_viola_accumulate", False)
 
 
+def _hand_back(slot):
+    """Tell the engine that this landing slot will not be written by the producer after all."""
+    release = getattr(slot, "_viola_release", None)
+    if release is not None:
+        release()
+    return None
+
+
 def _gradient_slot(offer, shape, dtype, device):
     """The engine's landing slot for a gradient about to be computed, when it offers one that fits."""
     if offer is None:
         return None
     slot = offer()
-    if slot is None or tuple(slot.shape) != tuple(shape) or slot.dtype != dtype or slot.device != device \
-            or not slot.is_contiguous():
+    if slot is None:
         return None
+    if tuple(slot.shape) != tuple(shape) or slot.dtype != dtype or slot.device != device or not slot.is_contiguous():
+        return _hand_back(slot)
     return slot
 
 
@@ -264,7 +273,7 @@ def linear_backward(layer, saved, dy, *, need_input_grad, need_weight_grad, need
             slot = _gradient_slot(getattr(saved, "weight_slot", None), (qg.qt.shape[0], xt.shape[0]),
                                   saved.weight_grad_dtype, dy.device)
             if _adds_up(slot) and layer.rotation_size:
-                slot = None                     # the rotation below works in place on this microbatch's gradient only
+                slot = _hand_back(slot)         # the rotation below works in place on this microbatch's gradient only
             dw = ops.gemm(qg.qt, xt, qg.st, xt_scale, out_dtype=saved.weight_grad_dtype, out=slot,
                           accumulate=_adds_up(slot))
         if layer.rotation_size:
@@ -324,7 +333,7 @@ def _backward_in_place(layer, saved, dy, limit, need_input_grad, need_weight_gra
         slot = _gradient_slot(getattr(saved, "weight_slot", None), (qg.q.shape[1], xq.shape[1]), saved.weight_grad_dtype,
                               dy.device)
         if _adds_up(slot) and layer.rotation_size:
-            slot = None
+            slot = _hand_back(slot)
         dw = ops.gemm(qg.q, xq, qg.s, x_scale, out_dtype=saved.weight_grad_dtype, a_mn=True, b_mn=True, out=slot,
                       accumulate=_adds_up(slot))
         if layer.rotation_size:

@@ -167,9 +167,14 @@ class GradientState:
         slot = self.slots[index].view(self.slots[index].shape)
         if self.summing:
             slot._viola_accumulate = True
+            # a producer that cannot add into the running sum hands the slot back and returns its own tensor
+            slot._viola_release = partial(self._unclaim, index)
         elif self.vectors_cleared and slot.dim() == 1:
             slot._viola_zeroed = True
         return slot
+
+    def _unclaim(self, index):
+        self.claimed[index] = False
 
     def begin_backward(self):
         self.in_backward = True

@@ -362,13 +362,14 @@ struct Config {
   static constexpr bool kGatedSlab = (kGatedFwd || kGatedBwd) && !GROUP;
   static constexpr bool kSlabRing = kEpiSlab || kGatedSlab;
   static constexpr bool kSlabLoader = kEpiSlab || (kGatedBwd && !GROUP);
-  static constexpr int kEpiSlabs = (kGatedBwd && !GROUP) ? 8 : 4;
+  static constexpr int kEpiSlabs = ((kGatedBwd || EPI == VB_EPI_ACT_BWD) && !GROUP) ? 8 : 4;
   static constexpr int kLoaderWarp = 2 + kEpiWarps;                                    // feeds the slab ring
   static constexpr int kCtaThreads = 64 + 32 * kEpiWarps + (kSlabLoader ? 32 : 0);
   static constexpr int kEpiSlabBytes = BM * 64;
   static constexpr int kEpiBytes = kSlabRing ? kEpiSlabs * kEpiSlabBytes : 0;
   static constexpr int kStages =
-      PAIR ? 6 : (BN == 256) ? 4 : (BN == 128 ? (((kGatedBwd && !GROUP) || (GROUP && kTmaStore)) ? 5 : 6) : 8);
+      PAIR ? 6 : (BN == 256) ? ((EPI == VB_EPI_ACT_BWD && !GROUP) ? 3 : 4)
+                             : (BN == 128 ? ((((kGatedBwd || EPI == VB_EPI_ACT_BWD) && !GROUP) || (GROUP && kTmaStore)) ? 5 : 6) : 8);
   static constexpr int kAcc = GROUP ? (512 / BN > 4 ? 4 : 512 / BN) : 2;
   static constexpr int kTmemCols = kAcc * BN;
   static constexpr int kBarrierBytes = 1024;
@@ -1432,9 +1433,9 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream, int split = 1) {
   a.epi_sets = 1;
   if constexpr (C::kEpiSlab) {
     // an even number of chunks in every tile keeps "even chunks / odd chunks" aligned with the loader's global order
-    // (measured: the Newton-Schulz epilogue gains from the second set, the activation-slope epilogue, whose operand
-    // slabs come from DRAM, loses the loader's look-ahead and gets slower, so it keeps one set)
-    a.epi_sets = (C::kEpiWarps == 8 && EPI == VB_EPI_AXPBY && d.N % 64 == 0) ? 2 : 1;
+    // (the activation-slope epilogue, whose operand slabs come from DRAM, needs the deeper ring of eight slabs for
+    // this: with four slabs shared by two sets it lost the loader's look-ahead and got slower)
+    a.epi_sets = (C::kEpiWarps == 8 && d.N % 64 == 0) ? 2 : 1;
     auto usable = [](const void* p, long long ld) { return p != nullptr && (reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld * 2) % 16 == 0; };
     const void* src = EPI == VB_EPI_AXPBY ? d.resid : d.aux;
     const long long ld = EPI == VB_EPI_AXPBY ? d.ldr : d.ldaux;

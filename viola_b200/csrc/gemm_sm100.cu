@@ -341,7 +341,7 @@ struct Config {
   // Group-scaled LINEAR: the promotion of every K-block (one FMA per accumulator element) is the epilogue warps'
   // whole job, so halving the columns per warp halves the time a K-block's accumulator stays occupied.
   static constexpr int kEpiWarps =
-      (EPI == VB_EPI_LINEAR || ((EPI == VB_EPI_AXPBY || EPI == VB_EPI_ACT_BWD) && !GROUP)) ? 8 : 4;
+      (EPI == VB_EPI_LINEAR || !GROUP) ? 8 : 4;     // every per-tensor kernel; of the group-scaled ones, LINEAR
   // LINEAR splits a tile's columns into contiguous parts, one per group of four warps; the slab epilogues
   // (AXPBY, ACT_BWD) interleave instead: warps 2-5 take the even chunks, warps 6-9 the odd ones, in the order the
   // loader warp fills the slab ring.
@@ -632,9 +632,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     constexpr int NOUT = (C::kGatedFwd ? NCHUNK / 2 : NCHUNK) / C::kColumnParts;  // output chunks per tile and warp
     const int chunk0 = C::kColumnParts > 1 ? half * NOUT : 0;       // first chunk of this warp
     // slab epilogues with eight warps: this warp's set (0 = warps 2-5, 1 = warps 6-9) takes every `sets`-th chunk
-    const int sets = (C::kEpiSlab && C::kEpiWarps == 8) ? (args.epi_sets == 2 ? 2 : 1) : 1;
-    const int set = (C::kEpiSlab && C::kEpiWarps == 8) ? half : 0;
+    constexpr bool kTwoSets = (C::kEpiSlab || C::kGatedSlab) && C::kEpiWarps == 8;
+    const int sets = kTwoSets ? (args.epi_sets == 2 ? 2 : 1) : 1;
+    const int set = kTwoSets ? half : 0;
     if constexpr (C::kEpiSlab) eslot = sets == 2 ? set : 0;
+    // gated backward: a chunk owns two consecutive slabs (gate, up), so a set starts two slabs further on
+    if constexpr (C::kGatedSlab && C::kGatedBwd) eslot = sets == 2 ? 2 * set : 0;
     for (int u = cta_first; u < args.num_tiles * args.split_k && ok; u += cta_stride) {
       int mt, nt;
       const int split = u / args.num_tiles, t = u - split * args.num_tiles;
@@ -770,9 +773,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const int warp_row = mt * BM + quad * 32;
           const bool rows_in = warp_row < args.M;
           if constexpr (C::kGatedFwd) {
+            // two sets: each set stages through its own two slabs (ring of two), one set: ring of four
+            const int ring = sets == 2 ? C::kEpiSlabs / 2 : C::kEpiSlabs;
             auto emit = [&](const uint32_t (&w)[16], int half, int col0) {
-              uint8_t* slab = epi_stage + eslot * C::kEpiSlabBytes;
-              if (lane == 0) tma_store_wait_read<C::kEpiSlabs - 1>();   // the store that last read this slab
+              uint8_t* slab = epi_stage + ((sets == 2 ? set * ring : 0) + eslot) * C::kEpiSlabBytes;
+              if (lane == 0) {                                          // the store that last read this slab
+                if (sets == 2) tma_store_wait_read<C::kEpiSlabs / 2 - 1>();
+                else tma_store_wait_read<C::kEpiSlabs - 1>();
+              }
               __syncwarp();
 #pragma unroll
               for (int p = 0; p < 4; ++p)
@@ -786,13 +794,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 }
                 tma_store_commit();
               }
-              if (++eslot == C::kEpiSlabs) eslot = 0;
+              if (++eslot == ring) eslot = 0;
             };
             auto fwd_tile = [&](auto dt_tag, auto act_tag) {
               constexpr int DT = decltype(dt_tag)::value;
               constexpr int ACT = decltype(act_tag)::value;
 #pragma unroll 1
-              for (int c = 0; c < NOUT; ++c) {
+              for (int c = (set < sets ? set : NOUT); c < NOUT; c += sets) {
                 const int col0 = n0 + c * 32;
                 if (col0 >= args.N) break;
                 uint32_t rg[32], ru[32];
@@ -841,7 +849,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               constexpr int DT = decltype(dt_tag)::value;
               constexpr int ACT = decltype(act_tag)::value;
 #pragma unroll 1
-              for (int c = 0; c < NCHUNK; ++c) {
+              for (int c = (set < sets ? set : NCHUNK); c < NCHUNK; c += sets) {
                 const int col0 = n0 + c * 32;
                 if (col0 >= args.N) break;
                 uint32_t r[32];
@@ -889,8 +897,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                   }
                 }
                 prev_slot = eslot;
-                eslot += 2;
-                if (eslot == C::kEpiSlabs) { eslot = 0; ephase ^= 1; }
+                eslot += 2 * sets;
+                if (eslot >= C::kEpiSlabs) { eslot -= C::kEpiSlabs; ephase ^= 1; }
               }
             };
             auto with_act = [&](auto dt_tag) {
@@ -905,7 +913,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
       if (!staged_done) {
 #pragma unroll(C::kEpiSlab ? 1 : NOUT)
-      for (int c = (C::kEpiSlab ? (set < sets ? set : NOUT) : 0); c < NOUT; c += (C::kEpiSlab ? sets : 1)) {
+      for (int c = (kTwoSets ? (set < sets ? set : NOUT) : 0); c < NOUT; c += (kTwoSets ? sets : 1)) {
         float v[32];
         float v2[C::kGatedFwd ? 32 : 1];
         if constexpr (GROUP) {
@@ -1450,6 +1458,10 @@ static int launch(const VbGemmDesc& d, cudaStream_t stream, int split = 1) {
       a.epi_store = 1;
   }
   if constexpr (C::kGatedSlab) {
+    // forward: two sets, each staging through its own two slabs (186 -> 164 us at 32768 x 2*1728 x 1152).  Backward:
+    // one active set; with two, each chunk's pair of operand slabs shares the eight-slab ring's look-ahead and the
+    // kernel got slower (159 -> 189 us), as the activation-slope epilogue did on four slabs.
+    a.epi_sets = (C::kEpiWarps == 8 && C::kGatedFwd) ? 2 : 1;
     auto usable = [](const void* p, long long ld) { return p != nullptr && (reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld * 2) % 16 == 0; };
     const bool shape_ok = !expert && a.batch == 1 && d.out_dtype != 0 && d.N % 8 == 0 && !d.no_tma_store;
     if constexpr (C::kGatedFwd) {

@@ -52,6 +52,9 @@ def parse():
     parser.add_argument("--ref-microbatch", type=int, default=0,
                         help="reference arm only: images per microbatch (raises the accumulation steps above the "
                              "named config's 2 to keep the global batch); 0 = the named config")
+    parser.add_argument("--ref-timeout", type=float, default=1500.0,
+                        help="reference arm: seconds after which it prints an 'unavailable' line and exits 0 "
+                             "(its TileLang kernels compile during the first pass, eight ranks at once take long)")
     parser.add_argument("--no-e2e", action="store_true")
     parser.add_argument("--no-graph", action="store_true", help="run every microbatch eagerly (no CUDA graph)")
     parser.add_argument("--resident", default="auto", choices=("auto", "true", "false"),
@@ -351,7 +354,21 @@ def run_reference(args):
     except Exception as error:
         return unavailable(f"import viola failed: {type(error).__name__}: {str(error).splitlines()[0][:160]}")
     from baseline.reference_arm import run
-    return run(args, unavailable, REFERENCE_SHIM if shimmed else None)
+
+    def give_up():
+        unavailable(f"the reference did not finish within {args.ref_timeout:.0f} s on {args.gpus} GPU(s): its first pass "
+                    "JIT-compiles the TileLang kernels of this world size's shapes (results are cached under "
+                    "baseline/_ref/tilelang_cache for the next run)")
+        sys.stdout.flush()
+        os._exit(0)
+
+    watchdog = threading.Timer(args.ref_timeout, give_up)
+    watchdog.daemon = True
+    watchdog.start()
+    try:
+        return run(args, unavailable, REFERENCE_SHIM if shimmed else None)
+    finally:
+        watchdog.cancel()
 
 
 if __name__ == "__main__":

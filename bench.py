@@ -52,7 +52,7 @@ def parse():
     parser.add_argument("--ref-microbatch", type=int, default=0,
                         help="reference arm only: images per microbatch (raises the accumulation steps above the "
                              "named config's 2 to keep the global batch); 0 = the named config")
-    parser.add_argument("--ref-timeout", type=float, default=1500.0,
+    parser.add_argument("--ref-timeout", type=float, default=900.0,
                         help="reference arm: seconds after which it prints an 'unavailable' line and exits 0 "
                              "(its TileLang kernels compile during the first pass, eight ranks at once take long)")
     parser.add_argument("--no-e2e", action="store_true")
